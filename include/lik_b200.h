@@ -1,0 +1,219 @@
+/*
+ * lik_b200.h — C ABI of the B200 (sm_100a) MaxSim engine.
+ *
+ * The reference project (hcompai/late-interaction-kernels) is pure Python: its
+ * GPU work is Triton kernels launched from Python launcher functions, so it has
+ * no FFI of its own.  Each entry point below replaces one of those launchers;
+ * the comment above it names the launcher (file:line inside the reference
+ * repository) whose behaviour it reproduces.
+ *
+ * Conventions
+ *   - every pointer is a DEVICE pointer unless the name ends in _host;
+ *   - the caller allocates inputs, outputs and workspaces; the library never
+ *     allocates device memory, never synchronises and keeps no per-call state;
+ *   - launches go to the cudaStream_t passed as lik_stream_t;
+ *   - return value: LIK_OK or a negative lik_status; lik_last_error() gives the
+ *     text for the calling thread;
+ *   - data-dependent problems found on the device (a pair index out of range, a
+ *     query longer than the argmax stride, a bounded wait that gave up) never
+ *     trap: the kernel ORs a LIK_DEV_* bit into *status (if non-NULL), skips the
+ *     offending work and returns.
+ */
+#ifndef LIK_B200_H
+#define LIK_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef void* lik_stream_t; /* cudaStream_t */
+
+enum lik_dtype { LIK_F32 = 0, LIK_F16 = 1, LIK_BF16 = 2, LIK_E4M3 = 3 };
+
+enum lik_status {
+  LIK_OK = 0,
+  LIK_ERR_INVALID = -1,     /* bad argument (NULL pointer, negative size, unknown enum) */
+  LIK_ERR_UNSUPPORTED = -2, /* valid request this build has no kernel for */
+  LIK_ERR_CUDA = -3,        /* a CUDA runtime/driver call failed */
+  LIK_ERR_WORKSPACE = -4    /* workspace too small (see the *_workspace function) */
+};
+
+/* bits OR-ed into the device status word */
+enum lik_dev_status {
+  LIK_DEV_PAIR_RANGE = 1,   /* pair_q / pair_d entry outside [0, n_seq) */
+  LIK_DEV_ARGMAX_STRIDE = 2,/* a query has more tokens than argmax_stride */
+  LIK_DEV_WAIT_TIMEOUT = 4, /* a bounded mbarrier wait expired inside the tensor-core kernel */
+  LIK_DEV_CODE_RANGE = 8,   /* PLAID centroid code outside [0, n_centroids) (read as centroid 0) */
+  LIK_DEV_LEN_RANGE = 16    /* a length exceeds the padded extent (clamped) */
+};
+
+enum lik_normalize { LIK_NORM_NONE = 0, LIK_NORM_Q = 1, LIK_NORM_D = 2, LIK_NORM_BOTH = 3 };
+
+enum lik_pairing {
+  LIK_PAIR_CROSS = 0,   /* every query against every document: scores[i * d.n_seq + j] */
+  LIK_PAIR_GROUPED = 1, /* document j belongs to query j / group: scores[j]            */
+  LIK_PAIR_LIST = 2     /* explicit list: scores[p] = MaxSim(q[pair_q[p]], d[pair_d[p]]) */
+};
+
+/*
+ * One side of a MaxSim problem: token sequences stored as rows of one matrix.
+ *   padded layout (cu == NULL): sequence i occupies rows [i*seq_stride, i*seq_stride + max_len);
+ *       token t of it is valid when t < lens[i] (lens optional) and mask[row] != 0 (mask optional).
+ *   packed layout (cu != NULL): sequence i occupies rows [cu[i], cu[i+1]).
+ * mask and scale are indexed by row number, like data.
+ */
+typedef struct lik_seqs {
+  const void* data;     /* [n_rows, dim] row-major */
+  int64_t row_stride;   /* elements between consecutive rows */
+  int64_t n_rows;       /* rows addressable from data */
+  int32_t n_seq;
+  int32_t max_len;      /* padded: stored length; packed: upper bound used to size per-query buffers */
+  int64_t seq_stride;   /* padded: rows between sequence starts */
+  const int32_t* cu;    /* packed: [n_seq + 1] */
+  const int32_t* lens;  /* padded, optional: [n_seq] */
+  const uint8_t* mask;  /* padded, optional: [n_rows] */
+  const float* scale;   /* optional per-token dequantisation scale: [n_rows] */
+  float scale_scalar;   /* multiplies every token (1.0f when unused) */
+  int32_t reserved;
+} lik_seqs;
+
+/* ------------------------------------------------------------------------- */
+/* Forward.  Replaces _run_forward (forward.py:228-346), _varlen_forward        */
+/* (varlen.py:271-364), _scatter_forward (score_pairs.py:281-341) and the FP8   */
+/* launcher maxsim_inference_fp8 (fp8.py:234-422).                              */
+/*   scores[p] = sum_{valid s} max_{valid t} <q_s, d_t> * scales                */
+/*   argmax (optional) [n_scores, argmax_stride] int32: winning token of the    */
+/*   document for every query token, relative to the document start; -1 when    */
+/*   the document has no valid token, and for positions >= the query length.    */
+/* normalize: bit 0 (LIK_NORM_Q) / bit 1 (LIK_NORM_D): divide the query /       */
+/* document tokens by max(||x||, 1e-12) inside the kernel (fused L2 norm).     */
+/* ------------------------------------------------------------------------- */
+typedef struct lik_fwd_args {
+  lik_seqs q, d;
+  int32_t dtype; /* lik_dtype of q.data and d.data */
+  int32_t dim;
+  int32_t pairing;
+  int32_t group; /* LIK_PAIR_GROUPED: documents per query */
+  const int32_t* pair_q;
+  const int32_t* pair_d;
+  int64_t n_pairs; /* LIK_PAIR_LIST */
+  int32_t normalize;
+  int32_t engine; /* 0 = automatic, 1 = force the portable fp32 kernel, 2 = force the tcgen05 kernel */
+  float* scores;
+  int32_t* argmax;
+  int32_t argmax_stride;
+  int32_t reserved;
+  void* workspace;
+  size_t workspace_bytes;
+  int32_t* status;
+} lik_fwd_args;
+
+size_t lik_maxsim_fwd_workspace(const lik_fwd_args* args);
+int lik_maxsim_fwd(const lik_fwd_args* args, lik_stream_t stream);
+
+/* ------------------------------------------------------------------------- */
+/* Backward.  Replaces maxsim_backward_unified (backward/unified.py:205-289),   */
+/* maxsim_backward_lowmem (backward/lowmem.py:205-322), the varlen backward     */
+/* (varlen.py:389-449) and the pair-list backward (score_pairs.py:356-420).     */
+/*   grad_q[row(i,s)] = sum_p g[p] * d[row(j_p, argmax[p,s])]                   */
+/*   grad_d[row(j,t)] = sum_{p,s : argmax[p,s]=t} g[p] * q[row(i_p,s)]          */
+/* With normalize != 0 the L2-normalise Jacobian (autograd.py:213-225) is       */
+/* applied inside the kernels.  grad_q / grad_d are [n_rows, dim] contiguous.   */
+/* deterministic != 0 (CROSS and GROUPED pairing): destination-owned reduction, */
+/* grads written once in grad_dtype, bitwise reproducible.  deterministic == 0: */
+/* fp32 atomics into the workspace followed by a finalise pass.                 */
+/* ------------------------------------------------------------------------- */
+typedef struct lik_bwd_args {
+  lik_seqs q, d;
+  int32_t dtype;
+  int32_t dim;
+  int32_t pairing;
+  int32_t group;
+  const int32_t* pair_q;
+  const int32_t* pair_d;
+  int64_t n_pairs;
+  int32_t normalize;
+  int32_t deterministic;
+  const float* grad_scores;
+  const int32_t* argmax;
+  int32_t argmax_stride;
+  int32_t grad_dtype; /* lik_dtype of grad_q / grad_d (F32, F16 or BF16) */
+  void* grad_q;       /* may be NULL to skip */
+  void* grad_d;       /* may be NULL to skip */
+  void* workspace;
+  size_t workspace_bytes;
+  int32_t* status;
+} lik_bwd_args;
+
+size_t lik_maxsim_bwd_workspace(const lik_bwd_args* args);
+int lik_maxsim_bwd(const lik_bwd_args* args, lik_stream_t stream);
+
+/* ------------------------------------------------------------------------- */
+/* Top-k.  Replaces the torch.topk / cat / topk merge loop of maxsim_topk        */
+/* (topk.py:41-86) and retrieve (retrieve.py:254-310).                          */
+/* lik_topk_rows: per row of scores [n_rows, n_cols] (row stride ld) keep the k */
+/* best as (score, index + index_offset), sorted best first; ties go to the     */
+/* lower index.  k <= LIK_TOPK_MAX.  If merge != 0 the k entries already in      */
+/* out_scores/out_index take part (running merge across chunks).  Entries with  */
+/* index < 0 are padding.                                                       */
+/* lik_topk_merge: cand_* are [n_lists, n_rows, k]; result is the top k of the  */
+/* union per row (used for per-CTA partial lists and for the all-gathered       */
+/* per-GPU lists of the sharded retrieve).                                      */
+/* ------------------------------------------------------------------------- */
+#define LIK_TOPK_MAX 1024
+int lik_topk_rows(const float* scores, int64_t n_rows, int64_t n_cols, int64_t ld, int32_t k, int32_t largest,
+                  int64_t index_offset, int32_t merge, float* out_scores, int64_t* out_index, lik_stream_t stream);
+int lik_topk_merge(const float* cand_scores, const int64_t* cand_index, int32_t n_lists, int64_t n_rows, int32_t k,
+                   int32_t largest, float* out_scores, int64_t* out_index, lik_stream_t stream);
+
+/* ------------------------------------------------------------------------- */
+/* PLAID.                                                                       */
+/* lik_plaid_decompress: emb = centroids[code] + bucket_weights[bucket(f)],     */
+/* optional L2 norm, written as out_dtype rows [n_tokens, dim] — the            */
+/* decompress stage of _maxsim_residual_kernel (plaid.py:236-284) and           */
+/* _maxsim_residual_varlen_kernel (plaid.py:684-829), run once per token instead*/
+/* of once per (query, document) program.  Bit layout: feature f is in byte     */
+/* f / (8/nbits), bit offset (f % (8/nbits)) * nbits (reference.py:124-139).     */
+/* lik_plaid_approx: replaces plaid_approx_score (plaid.py:82-136).             */
+/* lik_plaid_bwd_dq: replaces _maxsim_residual_bwd_dQ_kernel + the Q Jacobian    */
+/* (plaid.py:310-401, 596-605).                                                 */
+/* ------------------------------------------------------------------------- */
+typedef struct lik_plaid_index {
+  const int32_t* codes;       /* [n_tokens] */
+  const uint8_t* residuals;   /* [n_tokens, packed_dim], packed_dim = ceil(dim*nbits/8) */
+  int64_t n_tokens;
+  const void* centroids;      /* [n_centroids, dim] */
+  int32_t centroid_dtype;     /* LIK_F32 / LIK_F16 / LIK_BF16 */
+  int32_t n_centroids;
+  const float* bucket_weights;/* [1 << nbits] */
+  int32_t nbits;              /* 2, 4 or 8 */
+  int32_t dim;
+} lik_plaid_index;
+
+int lik_plaid_decompress(const lik_plaid_index* index, int64_t token_begin, int64_t token_count, int32_t normalize,
+                         void* out, int32_t out_dtype, int32_t* status, lik_stream_t stream);
+int lik_plaid_approx(const float* qcs, int32_t n_centroids, int32_t lq, const int32_t* codes, int64_t n_docs,
+                     int32_t max_ld, const int64_t* doc_lengths, float* out, lik_stream_t stream);
+/* grad_q [n_q, lq, dim] fp32 from argmax [n_q, n_docs, lq] over a padded index (row of doc j token t = j*max_ld + t) */
+int lik_plaid_bwd_dq(const lik_plaid_index* index, int32_t max_ld, int64_t n_docs, const void* q, int32_t q_dtype,
+                     int32_t n_q, int32_t lq, const float* grad_scores, const int32_t* argmax, int32_t normalize,
+                     float* grad_q, lik_stream_t stream);
+
+/* ------------------------------------------------------------------------- */
+/* Utilities                                                                    */
+/* ------------------------------------------------------------------------- */
+/* out[r] = 1 / max(||x_r||, eps) for every row; the fused-normalise kernels take these. */
+int lik_row_inv_norm(const void* data, int32_t dtype, int64_t n_rows, int32_t dim, int64_t row_stride, float eps,
+                     float* out, lik_stream_t stream);
+const char* lik_last_error(void);
+int lik_version(void);
+/* 1 when the device the calling thread has current is sm_100 (tcgen05 kernels usable) */
+int lik_device_supported(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LIK_B200_H */

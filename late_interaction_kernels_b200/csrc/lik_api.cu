@@ -1,0 +1,122 @@
+// C-ABI entry points of the forward path and the small utilities.
+#include "lik_common.cuh"
+
+namespace lik {
+int launch_row_inv_norm(const void* data, int dtype, long long n_rows, int dim, long long stride, float eps, float* out,
+                        cudaStream_t st);
+int launch_fwd_generic(const lik_fwd_args& a, const float* qn, const float* dn, cudaStream_t st);
+// tcgen05 path (lik_fwd_tc.cu)
+bool fwd_tc_supported(const lik_fwd_args& a);
+size_t fwd_tc_workspace(const lik_fwd_args& a);
+int launch_fwd_tc(const lik_fwd_args& a, const float* qn, const float* dn, void* ws, size_t ws_bytes, cudaStream_t st);
+
+namespace {
+constexpr float kFwdNormEps = 1e-12f;
+
+struct FwdPlan {
+  size_t qn_off, dn_off, tc_off, total;
+  bool use_tc;
+};
+
+int validate_seqs(const lik_seqs& s, const char* name) {
+  LIK_REQUIRE(s.n_seq >= 0 && s.max_len >= 0 && s.n_rows >= 0, "%s: negative size", name);
+  LIK_REQUIRE(s.data != nullptr || s.n_rows == 0, "%s.data is NULL", name);
+  LIK_REQUIRE(s.row_stride > 0 || s.n_rows == 0, "%s.row_stride must be positive", name);
+  if (!s.cu) {
+    LIK_REQUIRE(s.seq_stride >= s.max_len, "%s.seq_stride < max_len", name);
+    LIK_REQUIRE(s.n_seq == 0 || (int64_t)(s.n_seq - 1) * s.seq_stride + s.max_len <= s.n_rows,
+                "%s: padded sequences exceed n_rows", name);
+  }
+  return LIK_OK;
+}
+
+int validate_fwd(const lik_fwd_args& a) {
+  int rc = validate_seqs(a.q, "q");
+  if (rc) return rc;
+  rc = validate_seqs(a.d, "d");
+  if (rc) return rc;
+  LIK_REQUIRE(a.dim > 0, "dim must be positive");
+  LIK_REQUIRE(a.dtype >= LIK_F32 && a.dtype <= LIK_E4M3, "unknown dtype %d", a.dtype);
+  LIK_REQUIRE(a.pairing >= LIK_PAIR_CROSS && a.pairing <= LIK_PAIR_LIST, "unknown pairing %d", a.pairing);
+  if (a.pairing == LIK_PAIR_GROUPED)
+    LIK_REQUIRE(a.group > 0 && (int64_t)a.q.n_seq * a.group == a.d.n_seq, "grouped pairing needs d.n_seq == q.n_seq * group");
+  if (a.pairing == LIK_PAIR_LIST)
+    LIK_REQUIRE(a.n_pairs >= 0 && (a.n_pairs == 0 || (a.pair_q && a.pair_d)), "pair list missing");
+  LIK_REQUIRE(a.scores != nullptr || n_scores_of(a.pairing, a.q.n_seq, a.d.n_seq, a.n_pairs) == 0, "scores is NULL");
+  LIK_REQUIRE(!a.argmax || a.argmax_stride >= 0, "argmax_stride negative");
+  return LIK_OK;
+}
+
+FwdPlan plan_fwd(const lik_fwd_args& a) {
+  FwdPlan pl{};
+  size_t off = 0;
+  auto take = [&](size_t bytes) {
+    size_t o = off;
+    off = align_up(off + bytes, 256);
+    return o;
+  };
+  pl.qn_off = pl.dn_off = pl.tc_off = (size_t)-1;
+  if (a.normalize & LIK_NORM_Q) pl.qn_off = take((size_t)a.q.n_rows * 4);
+  if (a.normalize & LIK_NORM_D) pl.dn_off = take((size_t)a.d.n_rows * 4);
+  pl.use_tc = a.engine != 1 && fwd_tc_supported(a);
+  if (pl.use_tc) pl.tc_off = take(fwd_tc_workspace(a));
+  pl.total = off;
+  return pl;
+}
+}  // namespace
+}  // namespace lik
+
+extern "C" size_t lik_maxsim_fwd_workspace(const lik_fwd_args* a) {
+  if (!a) return 0;
+  return lik::plan_fwd(*a).total;
+}
+
+extern "C" int lik_maxsim_fwd(const lik_fwd_args* a, lik_stream_t stream) {
+  using namespace lik;
+  LIK_REQUIRE(a != nullptr, "args is NULL");
+  int rc = validate_fwd(*a);
+  if (rc) return rc;
+  FwdPlan pl = plan_fwd(*a);
+  if (a->engine == 2 && !pl.use_tc) {
+    set_error("tcgen05 engine requested but this problem is outside what it takes");
+    return LIK_ERR_UNSUPPORTED;
+  }
+  if (pl.total > a->workspace_bytes || (pl.total && !a->workspace)) {
+    set_error("workspace too small: need %zu bytes, got %zu", pl.total, a->workspace_bytes);
+    return LIK_ERR_WORKSPACE;
+  }
+  cudaStream_t st = (cudaStream_t)stream;
+  char* ws = (char*)a->workspace;
+  const float *qn = nullptr, *dn = nullptr;
+  if (a->normalize & LIK_NORM_Q) {
+    float* w = (float*)(ws + pl.qn_off);
+    rc = launch_row_inv_norm(a->q.data, a->dtype, a->q.n_rows, a->dim, a->q.row_stride, kFwdNormEps, w, st);
+    if (rc) return rc;
+    qn = w;
+  }
+  if (a->normalize & LIK_NORM_D) {
+    float* w = (float*)(ws + pl.dn_off);
+    rc = launch_row_inv_norm(a->d.data, a->dtype, a->d.n_rows, a->dim, a->d.row_stride, kFwdNormEps, w, st);
+    if (rc) return rc;
+    dn = w;
+  }
+  if (pl.use_tc) return launch_fwd_tc(*a, qn, dn, ws + pl.tc_off, fwd_tc_workspace(*a), st);
+  return launch_fwd_generic(*a, qn, dn, st);
+}
+
+extern "C" int lik_row_inv_norm(const void* data, int32_t dtype, int64_t n_rows, int32_t dim, int64_t row_stride, float eps,
+                                float* out, lik_stream_t stream) {
+  using namespace lik;
+  LIK_REQUIRE(n_rows >= 0 && dim > 0 && row_stride >= dim, "bad shape");
+  LIK_REQUIRE((data && out) || n_rows == 0, "NULL pointer");
+  return launch_row_inv_norm(data, dtype, n_rows, dim, row_stride, eps, out, (cudaStream_t)stream);
+}
+
+extern "C" const char* lik_last_error(void) { return lik::get_error(); }
+extern "C" int lik_version(void) { return 100; }
+extern "C" int lik_device_supported(void) {
+  int dev = 0, major = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+  if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess) return 0;
+  return major == 10;
+}

@@ -1,0 +1,202 @@
+// Per-query top-k selection and merge.
+//
+// One CTA per query row keeps the current best KP = pow2(k) candidates sorted in
+// shared memory.  New candidates arrive KP at a time (a slice of a score row, or
+// one of several already-selected lists), are bitonic-sorted, combined with the
+// kept list by the "best of top[i] and block[KP-1-i]" step (which leaves the KP
+// best of the union as a bitonic sequence) and re-sorted by a bitonic merge.
+// Order: better score first, ties to the lower document index; padding
+// (index < 0) last.
+#include <climits>
+
+#include "lik_common.cuh"
+
+namespace lik {
+
+struct Cand {
+  float key;  // score for largest=true, -score otherwise
+  long long idx;
+};
+
+__device__ __forceinline__ bool before(const Cand& a, const Cand& b) {
+  return a.key > b.key || (a.key == b.key && a.idx < b.idx);
+}
+
+constexpr long long kPadIdx = LLONG_MAX;
+
+// sort KP entries in shared memory, best first
+__device__ void bitonic_sort(float* key, long long* idx, int KP, int tid, int nthreads) {
+  for (int size = 2; size <= KP; size <<= 1) {
+    for (int stride = size >> 1; stride > 0; stride >>= 1) {
+      __syncthreads();
+      for (int t = tid; t < (KP >> 1); t += nthreads) {
+        int i = 2 * t - (t & (stride - 1));
+        int j = i + stride;
+        bool up = (i & size) == 0;  // this sub-sequence is ordered best first
+        Cand a{key[i], idx[i]}, b{key[j], idx[j]};
+        bool swap = up ? before(b, a) : before(a, b);
+        if (swap) {
+          key[i] = b.key;
+          idx[i] = b.idx;
+          key[j] = a.key;
+          idx[j] = a.idx;
+        }
+      }
+    }
+  }
+  __syncthreads();
+}
+
+// merge a bitonic sequence of KP entries into best-first order
+__device__ void bitonic_merge(float* key, long long* idx, int KP, int tid, int nthreads) {
+  for (int stride = KP >> 1; stride > 0; stride >>= 1) {
+    __syncthreads();
+    for (int t = tid; t < (KP >> 1); t += nthreads) {
+      int i = 2 * t - (t & (stride - 1));
+      int j = i + stride;
+      Cand a{key[i], idx[i]}, b{key[j], idx[j]};
+      if (before(b, a)) {
+        key[i] = b.key;
+        idx[i] = b.idx;
+        key[j] = a.key;
+        idx[j] = a.idx;
+      }
+    }
+  }
+  __syncthreads();
+}
+
+struct TopkParams {
+  // mode 0: slices of a score row; mode 1: lists [n_lists, n_rows, k]
+  int mode;
+  const float* scores;
+  long long n_cols, ld, index_offset;
+  const float* cand_scores;
+  const long long* cand_index;
+  int n_lists;
+  long long n_rows;
+  int k, KP, largest, merge;
+  float* out_scores;
+  long long* out_index;
+};
+
+__global__ void __launch_bounds__(256) topk_kernel(TopkParams P) {
+  extern __shared__ unsigned char raw[];
+  long long* top_i = reinterpret_cast<long long*>(raw);
+  long long* blk_i = top_i + P.KP;
+  float* top_k = reinterpret_cast<float*>(blk_i + P.KP);
+  float* blk_k = top_k + P.KP;
+  const int tid = threadIdx.x, nt = blockDim.x;
+  const long long row = blockIdx.x;
+  const float sgn = P.largest ? 1.f : -1.f;
+
+  for (int t = tid; t < P.KP; t += nt) {
+    float key = -INFINITY;
+    long long id = kPadIdx;
+    if (P.merge && t < P.k) {
+      long long o = P.out_index[row * P.k + t];
+      if (o >= 0) {
+        id = o;
+        key = sgn * P.out_scores[row * P.k + t];
+      }
+    }
+    top_k[t] = key;
+    top_i[t] = id;
+  }
+  __syncthreads();
+  if (P.merge) bitonic_sort(top_k, top_i, P.KP, tid, nt);
+
+  const long long n_blocks = P.mode == 0 ? (P.n_cols + P.KP - 1) / P.KP : P.n_lists;
+  for (long long b = 0; b < n_blocks; ++b) {
+    for (int t = tid; t < P.KP; t += nt) {
+      float key = -INFINITY;
+      long long id = kPadIdx;
+      if (P.mode == 0) {
+        long long c = b * P.KP + t;
+        if (c < P.n_cols) {
+          key = sgn * P.scores[row * P.ld + c];
+          id = c + P.index_offset;
+        }
+      } else if (t < P.k) {
+        long long o = (b * P.n_rows + row) * P.k + t;
+        long long ci = P.cand_index[o];
+        if (ci >= 0) {
+          id = ci;
+          key = sgn * P.cand_scores[o];
+        }
+      }
+      blk_k[t] = key;
+      blk_i[t] = id;
+    }
+    bitonic_sort(blk_k, blk_i, P.KP, tid, nt);
+    for (int t = tid; t < P.KP; t += nt) {
+      Cand a{top_k[t], top_i[t]}, c{blk_k[P.KP - 1 - t], blk_i[P.KP - 1 - t]};
+      if (before(c, a)) {
+        top_k[t] = c.key;
+        top_i[t] = c.idx;
+      }
+    }
+    bitonic_merge(top_k, top_i, P.KP, tid, nt);
+  }
+  for (int t = tid; t < P.k; t += nt) {
+    bool pad = top_i[t] == kPadIdx;
+    P.out_scores[row * P.k + t] = pad ? -sgn * INFINITY : sgn * top_k[t];
+    P.out_index[row * P.k + t] = pad ? -1 : top_i[t];
+  }
+}
+
+static int launch_topk(TopkParams& P, cudaStream_t st) {
+  if (P.n_rows <= 0 || P.k <= 0) return LIK_OK;
+  int KP = 1;
+  while (KP < P.k) KP <<= 1;
+  if (KP < 2) KP = 2;
+  P.KP = KP;
+  size_t smem = (size_t)KP * 2 * (sizeof(long long) + sizeof(float));
+  topk_kernel<<<(unsigned)P.n_rows, 256, smem, st>>>(P);
+  LIK_CUDA_OK(cudaGetLastError());
+  return LIK_OK;
+}
+
+}  // namespace lik
+
+extern "C" int lik_topk_rows(const float* scores, int64_t n_rows, int64_t n_cols, int64_t ld, int32_t k, int32_t largest,
+                             int64_t index_offset, int32_t merge, float* out_scores, int64_t* out_index,
+                             lik_stream_t stream) {
+  using namespace lik;
+  LIK_REQUIRE(k > 0 && k <= LIK_TOPK_MAX, "k=%d outside [1, %d]", k, LIK_TOPK_MAX);
+  LIK_REQUIRE(n_rows >= 0 && n_cols >= 0 && ld >= n_cols, "bad score matrix shape");
+  LIK_REQUIRE(out_scores && out_index && (scores || n_cols == 0), "NULL pointer");
+  TopkParams P{};
+  P.mode = 0;
+  P.scores = scores;
+  P.n_cols = n_cols;
+  P.ld = ld;
+  P.index_offset = index_offset;
+  P.n_rows = n_rows;
+  P.k = k;
+  P.largest = largest;
+  P.merge = merge;
+  P.out_scores = out_scores;
+  P.out_index = (long long*)out_index;
+  return launch_topk(P, (cudaStream_t)stream);
+}
+
+extern "C" int lik_topk_merge(const float* cand_scores, const int64_t* cand_index, int32_t n_lists, int64_t n_rows,
+                              int32_t k, int32_t largest, float* out_scores, int64_t* out_index, lik_stream_t stream) {
+  using namespace lik;
+  LIK_REQUIRE(k > 0 && k <= LIK_TOPK_MAX, "k=%d outside [1, %d]", k, LIK_TOPK_MAX);
+  LIK_REQUIRE(n_lists >= 0 && n_rows >= 0, "negative size");
+  LIK_REQUIRE(out_scores && out_index && ((cand_scores && cand_index) || n_lists == 0), "NULL pointer");
+  TopkParams P{};
+  P.mode = 1;
+  P.cand_scores = cand_scores;
+  P.cand_index = (const long long*)cand_index;
+  P.n_lists = n_lists;
+  P.n_rows = n_rows;
+  P.k = k;
+  P.largest = largest;
+  P.merge = 0;
+  P.out_scores = out_scores;
+  P.out_index = (long long*)out_index;
+  return launch_topk(P, (cudaStream_t)stream);
+}
