@@ -1,10 +1,765 @@
-// tcgen05 forward (placeholder until the kernel lands).
+// Blackwell tensor-core MaxSim forward (sm_100a: TMA + tcgen05.mma + TMEM).
+//
+// GEMM view: rows = query tokens (A operand, K-major, 128 per tile), columns = document tokens (B
+// operand, K-major, up to 256 per tile), K = embedding width.  A CTA is persistent: it keeps one or
+// two 128-row query tiles resident in shared memory and streams document tiles through a TMA ring.
+// Every document tile feeds one MMA group per resident query tile; the fp32 accumulator of query
+// tile m lives in TMEM columns [256 m, 256 m + 256).  A tile never spans two documents, so the
+// epilogue is: per thread (= one query token = one TMEM lane) a running max over the tile's columns,
+// carried across the tiles of a document; at the end of the document the 128 row maxima are summed
+// per query (fixed order) into one score.  Scores for a (query, document) pair have exactly one
+// writer, so the forward is bitwise reproducible.
+//
+// Warp roles (320 threads): warp 0 = TMA producer, warp 1 = MMA issuer + TMEM owner, warps 2-5 =
+// epilogue group 0 (accumulator 0), warps 6-9 = epilogue group 1 (accumulator 1).
+//
+// Every mbarrier wait is bounded: on expiry the CTA raises LIK_DEV_WAIT_TIMEOUT in the status word,
+// sets a shared abort flag, drains its TMA copies, frees TMEM and returns.
+#include <cuda.h>
+
 #include "lik_common.cuh"
+
 namespace lik {
-bool fwd_tc_supported(const lik_fwd_args&) { return false; }
-size_t fwd_tc_workspace(const lik_fwd_args&) { return 0; }
-int launch_fwd_tc(const lik_fwd_args&, const float*, const float*, void*, size_t, cudaStream_t) {
-  set_error("tcgen05 forward not built");
-  return LIK_ERR_UNSUPPORTED;
+
+namespace {
+
+constexpr int TILE_M = 128;
+constexpr int TILE_N = 256;
+constexpr int BOX_ROWS = 64;        // rows per TMA box of the document ring
+constexpr int SLAB_BYTES_ROW = 128; // one swizzle span: 64 two-byte or 128 one-byte elements
+constexpr int MAX_SLABS = 2;
+constexpr int NUM_THREADS = 320;
+constexpr int EPI_THREADS = 128;
+constexpr long long WAIT_LIMIT_NS = 2000000000ll;  // 2 s per wait
+
+// ---------------------------------------------------------------------------------------------
+// PTX wrappers
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
 }
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ long long global_ns() {
+  long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+      "l"(map), "r"(x), "r"(y), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void prefetch_tmap(const CUtensorMap* map) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+template <bool FP8>
+__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  if (FP8) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+  }
+}
+// 32 lanes x 32 consecutive fp32 columns of TMEM -> 32 registers per thread
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
+  uint32_t r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// Shared-memory matrix descriptor: K-major operand, 128-byte swizzle, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((addr & 0x3FFFFu) >> 4);  // start address
+  d |= (uint64_t)1 << 16;                   // leading byte offset (unused for swizzled K-major)
+  d |= (uint64_t)(1024 >> 4) << 32;         // stride byte offset between 8-row groups
+  d |= (uint64_t)1 << 46;                   // descriptor version for sm_100
+  d |= (uint64_t)2 << 61;                   // SWIZZLE_128B
+  return d;
+}
+// Instruction descriptor: fp32 accumulate, both operands K-major, M = 128, N = n.
+__device__ __forceinline__ uint32_t instr_desc(int ab_format, int n) {
+  return (1u << 4) | ((uint32_t)ab_format << 7) | ((uint32_t)ab_format << 10) | ((uint32_t)(n >> 3) << 17) |
+         ((uint32_t)(TILE_M >> 4) << 24);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Kernel parameters
+// ---------------------------------------------------------------------------------------------
+struct TcParams {
+  SeqView q, d;
+  int pairing;       // CROSS or GROUPED
+  int group;         // GROUPED: documents per query
+  int n_q, n_d;
+  int elt_bytes;     // 1 or 2
+  int ab_format;     // instruction-descriptor operand format
+  int n_slabs;       // 128-byte K slabs per row
+  int k_steps;       // MMA K steps (32 bytes each)
+  int stages;        // document ring depth
+  int q_per_tile;    // whole queries per 128-row tile (when q_chunks == 1)
+  int q_chunks;      // 128-row chunks per query (> 1: one query chunk per tile)
+  int n_tiles;       // query tiles
+  int mt;            // query tiles resident per CTA (1 or 2)
+  long long n_units; // work units (tile group, document)
+  float* scores;
+  float* partial;    // [n_tiles, n_d] when q_chunks > 1
+  int* argmax;
+  int argmax_stride;
+  int* status;
+};
+
+struct SharedCtl {
+  unsigned long long q_full, q_empty;
+  unsigned long long d_full[8], d_empty[8];
+  unsigned long long acc_full[2], acc_empty[2];
+  unsigned long long wg_bar[2];
+  uint32_t tmem_base;
+  volatile int abort_flag;
+  int seg_off[2][TILE_M], seg_len[2][TILE_M], seg_q[2][TILE_M];
+  short row_seg[2][TILE_M];
+  int n_seg[2];
+  float emit[2][2][TILE_M];
+  float col_scale[2][TILE_N];
+  float col_bias[2][TILE_N];
+};
+
+// Bounded wait.  Returns false when the CTA is aborting.
+__device__ __forceinline__ bool wait_bar(unsigned long long* bar, uint32_t parity, SharedCtl* ctl, int* status) {
+  const uint32_t b = smem_u32(bar);
+  if (mbar_try_wait(b, parity)) return true;
+  const long long t0 = global_ns();
+  int spins = 0;
+  while (true) {
+    if (mbar_try_wait(b, parity)) return true;
+    if (ctl->abort_flag) return false;
+    if ((++spins & 63) == 0 && global_ns() - t0 > WAIT_LIMIT_NS) {
+      ctl->abort_flag = 1;
+      if (status) atomicOr(status, LIK_DEV_WAIT_TIMEOUT);
+      return false;
+    }
+  }
+}
+
+// Query tiles of tile-group g: tiles [g*mt, min((g+1)*mt, n_tiles)).
+struct TileInfo {
+  int qa, qb;        // queries [qa, qb)
+  int chunk;         // chunk index when q_chunks > 1
+  long long row0;    // first matrix row of the tile
+};
+
+__device__ __forceinline__ TileInfo tile_info(const TcParams& P, int tile) {
+  TileInfo t;
+  if (P.q_chunks == 1) {
+    t.qa = tile * P.q_per_tile;
+    t.qb = min(t.qa + P.q_per_tile, P.n_q);
+    t.chunk = 0;
+  } else {
+    t.qa = tile / P.q_chunks;
+    t.qb = t.qa + 1;
+    t.chunk = tile - t.qa * P.q_chunks;
+  }
+  long long r0;
+  int len;
+  seq_bounds(P.q, t.qa, r0, len, nullptr);
+  t.row0 = r0 + (long long)t.chunk * TILE_M;
+  return t;
+}
+
+// Work unit u -> (tile group, document).  CROSS: group-major over all documents.  GROUPED: one
+// query per tile, unit == document, group == owning query.
+__device__ __forceinline__ void unit_decode(const TcParams& P, long long u, int& grp, int& doc) {
+  if (P.pairing == LIK_PAIR_CROSS) {
+    grp = (int)(u / P.n_d);
+    doc = (int)(u - (long long)grp * P.n_d);
+  } else {
+    doc = (int)u;
+    grp = doc / P.group;
+  }
+}
+
+template <bool FP8, bool ARGMAX, bool AFFINE>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap d_map, const TcParams P) {
+  extern __shared__ unsigned char smem_raw[];
+  // operand tiles need 1024-byte alignment for the 128-byte swizzle
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  const int q_tile_bytes = P.n_slabs * TILE_M * SLAB_BYTES_ROW;
+  const int d_stage_bytes = P.n_slabs * TILE_N * SLAB_BYTES_ROW;
+  unsigned char* q_smem = smem;                              // [2][n_slabs][128 rows][128 B]
+  unsigned char* d_smem = smem + 2 * q_tile_bytes;           // [stages][n_slabs][256 rows][128 B]
+  SharedCtl* ctl = reinterpret_cast<SharedCtl*>(d_smem + (size_t)P.stages * d_stage_bytes);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+  // contiguous range of work units for this CTA
+  const long long u_begin = P.n_units * (long long)blockIdx.x / gridDim.x;
+  const long long u_end = P.n_units * (long long)(blockIdx.x + 1) / gridDim.x;
+
+  if (tid == 0) {
+    mbar_init(smem_u32(&ctl->q_full), 1);
+    mbar_init(smem_u32(&ctl->q_empty), 1);
+    for (int s = 0; s < P.stages; ++s) {
+      mbar_init(smem_u32(&ctl->d_full[s]), 1);
+      mbar_init(smem_u32(&ctl->d_empty[s]), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(smem_u32(&ctl->acc_full[a]), 1);
+      mbar_init(smem_u32(&ctl->acc_empty[a]), EPI_THREADS);
+      mbar_init(smem_u32(&ctl->wg_bar[a]), EPI_THREADS);
+    }
+    ctl->abort_flag = 0;
+    fence_barrier_init();
+    prefetch_tmap(&q_map);
+    prefetch_tmap(&d_map);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(&ctl->tmem_base), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = ctl->tmem_base;
+
+  if (warp == 0) {
+    // =========================== TMA producer ===========================
+    if (lane == 0) {
+      int cur_grp = -1;
+      uint32_t n_qload = 0, n_dload = 0;
+      const int x_per_slab = SLAB_BYTES_ROW / P.elt_bytes;
+      bool ok = true;
+      for (long long u = u_begin; u < u_end && ok; ++u) {
+        int grp, doc;
+        unit_decode(P, u, grp, doc);
+        if (grp != cur_grp) {
+          cur_grp = grp;
+          // wait until the MMAs that read the previous query tiles are done
+          ok = wait_bar(&ctl->q_empty, (n_qload & 1) ^ 1, ctl, P.status);
+          if (!ok) break;
+          const int t0 = grp * P.mt, t1 = min(t0 + P.mt, P.n_tiles);
+          mbar_arrive_expect_tx(smem_u32(&ctl->q_full), (uint32_t)((t1 - t0) * q_tile_bytes));
+          for (int t = t0; t < t1; ++t) {
+            TileInfo ti = tile_info(P, t);
+            for (int sl = 0; sl < P.n_slabs; ++sl)
+              tma_load_2d(smem_u32(q_smem + (t - t0) * q_tile_bytes + sl * TILE_M * SLAB_BYTES_ROW), &q_map, sl * x_per_slab,
+                          (int)ti.row0, smem_u32(&ctl->q_full));
+          }
+          ++n_qload;
+        }
+        long long drow0;
+        int dlen;
+        seq_bounds(P.d, doc, drow0, dlen, nullptr);
+        for (int c0 = 0; c0 < dlen; c0 += TILE_N) {
+          const int ncols = min(TILE_N, dlen - c0);
+          const int boxes = (ncols + BOX_ROWS - 1) / BOX_ROWS;
+          const int st = n_dload % P.stages;
+          ok = wait_bar(&ctl->d_empty[st], ((n_dload / P.stages) & 1) ^ 1, ctl, P.status);
+          if (!ok) break;
+          const uint32_t full = smem_u32(&ctl->d_full[st]);
+          mbar_arrive_expect_tx(full, (uint32_t)(boxes * BOX_ROWS * SLAB_BYTES_ROW * P.n_slabs));
+          for (int sl = 0; sl < P.n_slabs; ++sl)
+            for (int b = 0; b < boxes; ++b)
+              tma_load_2d(smem_u32(d_smem + (size_t)st * d_stage_bytes + sl * TILE_N * SLAB_BYTES_ROW + b * BOX_ROWS * SLAB_BYTES_ROW),
+                          &d_map, sl * x_per_slab, (int)(drow0 + c0) + b * BOX_ROWS, full);
+          ++n_dload;
+        }
+      }
+      if (!ok) {
+        // aborting: let the copies already issued land before the CTA goes away
+        const uint32_t issued = n_dload < (uint32_t)P.stages ? n_dload : (uint32_t)P.stages;
+        for (uint32_t i = 0; i < issued; ++i) {
+          const uint32_t n = n_dload - 1 - i;
+          const uint32_t bar = smem_u32(&ctl->d_full[n % P.stages]);
+          for (int spin = 0; spin < (1 << 20) && !mbar_try_wait(bar, (n / P.stages) & 1); ++spin) {
+          }
+        }
+        if (n_qload) {
+          const uint32_t bar = smem_u32(&ctl->q_full);
+          for (int spin = 0; spin < (1 << 20) && !mbar_try_wait(bar, (n_qload - 1) & 1); ++spin) {
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // =========================== MMA issuer ===========================
+    if (lane == 0) {
+      int cur_grp = -1;
+      uint32_t n_qload = 0, n_dload = 0, n_acc[2] = {0, 0};
+      long long uc = 0;
+      bool ok = true;
+      int mt_valid = 0;
+      for (long long u = u_begin; u < u_end && ok; ++u, ++uc) {
+        int grp, doc;
+        unit_decode(P, u, grp, doc);
+        if (grp != cur_grp) {
+          if (cur_grp >= 0) tc_commit(smem_u32(&ctl->q_empty));  // previous query tiles are free once issued MMAs retire
+          cur_grp = grp;
+          mt_valid = min(P.mt, P.n_tiles - grp * P.mt);
+          ok = wait_bar(&ctl->q_full, n_qload & 1, ctl, P.status);
+          if (!ok) break;
+          ++n_qload;
+          tc_fence_after();
+        }
+        long long drow0;
+        int dlen;
+        seq_bounds(P.d, doc, drow0, dlen, nullptr);
+        for (int c0 = 0; c0 < dlen && ok; c0 += TILE_N) {
+          const int ncols = min(TILE_N, dlen - c0);
+          const int n_mma = (ncols + 15) & ~15;
+          const uint32_t idesc = instr_desc(P.ab_format, n_mma);
+          const int st = n_dload % P.stages;
+          ok = wait_bar(&ctl->d_full[st], (n_dload / P.stages) & 1, ctl, P.status);
+          if (!ok) break;
+          tc_fence_after();
+          for (int m = 0; m < mt_valid; ++m) {
+            const int a = P.mt == 2 ? m : (int)(uc & 1);
+            ok = wait_bar(&ctl->acc_empty[a], (n_acc[a] & 1) ^ 1, ctl, P.status);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t d_tmem = tmem_base + (uint32_t)(a * TILE_N);
+            for (int ks = 0; ks < P.k_steps; ++ks) {
+              const int sl = ks >> 2, kk = ks & 3;
+              const uint32_t a_addr = smem_u32(q_smem + m * q_tile_bytes + sl * TILE_M * SLAB_BYTES_ROW) + kk * 32;
+              const uint32_t b_addr = smem_u32(d_smem + (size_t)st * d_stage_bytes + sl * TILE_N * SLAB_BYTES_ROW) + kk * 32;
+              tc_mma<FP8>(d_tmem, smem_desc_sw128(a_addr), smem_desc_sw128(b_addr), idesc, ks > 0 ? 1u : 0u);
+            }
+            tc_commit(smem_u32(&ctl->acc_full[a]));
+            ++n_acc[a];
+          }
+          tc_commit(smem_u32(&ctl->d_empty[st]));  // ring slot reusable once these MMAs retire
+          ++n_dload;
+        }
+      }
+    }
+  } else {
+    // =========================== epilogue groups ===========================
+    const int wg = (warp - 2) >> 2;          // 0 or 1
+    const int quad = warp & 3;               // TMEM lane quadrant this warp may read
+    const int wq = (warp - 2) & 3;           // warp index inside the group
+    const int row = quad * 32 + lane;        // accumulator row == query token slot in the tile
+    const int et = wq * 32 + lane;           // thread index inside the group (0..127)
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
+    int cur_grp = -1;
+    uint32_t n_acc = 0, n_wg = 0;
+    long long uc = 0;
+    bool ok = true;
+    // per-row state for the resident query tile
+    bool have_tile = false, in_seg = false, row_ok = false;
+    int my_q = 0, my_s = 0;
+    float my_qf = 1.f;
+    int tile_id = 0;
+    for (long long u = u_begin; u < u_end && ok; ++u, ++uc) {
+      int grp, doc;
+      unit_decode(P, u, grp, doc);
+      const int acc = P.mt == 2 ? wg : (int)(uc & 1);
+      if (grp != cur_grp) {
+        cur_grp = grp;
+        // (re)build the segment table of this group's tile `wg` (mt == 2) or tile 0 (mt == 1: both groups)
+        const int m = P.mt == 2 ? wg : 0;
+        tile_id = grp * P.mt + m;
+        have_tile = tile_id < P.n_tiles;
+        // everyone in the group must be done reading the old table
+        mbar_arrive(smem_u32(&ctl->wg_bar[wg]));
+        ok = wait_bar(&ctl->wg_bar[wg], n_wg & 1, ctl, P.status);
+        ++n_wg;
+        if (!ok) break;
+        if (have_tile) {
+          TileInfo ti = tile_info(P, tile_id);
+          const int nseg = ti.qb - ti.qa;
+          ctl->row_seg[wg][et] = -1;
+          if (et == 0) ctl->n_seg[wg] = nseg;
+        }
+        mbar_arrive(smem_u32(&ctl->wg_bar[wg]));
+        ok = wait_bar(&ctl->wg_bar[wg], n_wg & 1, ctl, P.status);
+        ++n_wg;
+        if (!ok) break;
+        if (have_tile) {
+          TileInfo ti = tile_info(P, tile_id);
+          const int nseg = ti.qb - ti.qa;
+          if (et < nseg) {
+            long long r0;
+            int len;
+            seq_bounds(P.q, ti.qa + et, r0, len, P.status);
+            int off, l;
+            if (P.q_chunks == 1) {
+              off = (int)(r0 - ti.row0);
+              l = len;
+              if (off + l > TILE_M) {  // max_len was smaller than a real query: report, stay in bounds
+                l = max(0, TILE_M - off);
+                if (P.status) atomicOr(P.status, LIK_DEV_LEN_RANGE);
+              }
+            } else {
+              off = 0;
+              l = min(TILE_M, max(0, len - ti.chunk * TILE_M));
+              if (len > P.q_chunks * TILE_M && P.status) atomicOr(P.status, LIK_DEV_LEN_RANGE);
+            }
+            ctl->seg_off[wg][et] = off;
+            ctl->seg_len[wg][et] = l;
+            ctl->seg_q[wg][et] = ti.qa + et;
+            for (int i = 0; i < l; ++i) ctl->row_seg[wg][off + i] = (short)et;
+          }
+        }
+        mbar_arrive(smem_u32(&ctl->wg_bar[wg]));
+        ok = wait_bar(&ctl->wg_bar[wg], n_wg & 1, ctl, P.status);
+        ++n_wg;
+        if (!ok) break;
+        in_seg = false;
+        row_ok = false;
+        if (have_tile) {
+          const int sg = ctl->row_seg[wg][row];
+          if (sg >= 0) {
+            in_seg = true;
+            my_q = ctl->seg_q[wg][sg];
+            TileInfo ti = tile_info(P, tile_id);
+            my_s = row - ctl->seg_off[wg][sg] + ti.chunk * TILE_M;
+            const long long qrow = ti.row0 + row;
+            row_ok = row_valid(P.q, qrow);
+            my_qf = row_factor(P.q, qrow);
+          }
+        }
+      }
+      // with two resident tiles each group handles its own tile for every document; with one tile the
+      // groups alternate documents
+      const bool mine = P.mt == 2 ? have_tile : (acc == wg);
+      if (!mine) continue;
+
+      long long drow0;
+      int dlen;
+      seq_bounds(P.d, doc, drow0, dlen, nullptr);
+      float run_m = -INFINITY;
+      int run_i = -1;
+      for (int c0 = 0; c0 < dlen && ok; c0 += TILE_N) {
+        const int ncols = min(TILE_N, dlen - c0);
+        if (AFFINE) {
+          // per-column multiplier and additive mask for this tile (two columns per thread)
+          mbar_arrive(smem_u32(&ctl->wg_bar[wg]));  // previous tile's readers are done
+          ok = wait_bar(&ctl->wg_bar[wg], n_wg & 1, ctl, P.status);
+          ++n_wg;
+          if (!ok) break;
+          for (int c = et; c < ncols; c += EPI_THREADS) {
+            const long long drow = drow0 + c0 + c;
+            ctl->col_scale[wg][c] = row_factor(P.d, drow);
+            ctl->col_bias[wg][c] = row_valid(P.d, drow) ? 0.f : -INFINITY;
+          }
+          mbar_arrive(smem_u32(&ctl->wg_bar[wg]));
+          ok = wait_bar(&ctl->wg_bar[wg], n_wg & 1, ctl, P.status);
+          ++n_wg;
+          if (!ok) break;
+        }
+        ok = wait_bar(&ctl->acc_full[acc], n_acc & 1, ctl, P.status);
+        if (!ok) break;
+        ++n_acc;
+        tc_fence_after();
+        const uint32_t taddr = lane_addr + (uint32_t)(acc * TILE_N);
+        for (int cc = 0; cc < ncols; cc += 32) {
+          float v[32];
+          tmem_ld32(taddr + (uint32_t)cc, v);
+          const int lim = ncols - cc;  // valid columns in this chunk (>= 1)
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            float x = v[i];
+            if (AFFINE) x = fmaf(x, ctl->col_scale[wg][cc + i], ctl->col_bias[wg][cc + i]);
+            if (i < lim) {
+              if (ARGMAX || AFFINE) {
+                if (x > run_m) {
+                  run_m = x;
+                  run_i = c0 + cc + i;
+                }
+              } else {
+                run_m = fmaxf(run_m, x);
+              }
+            }
+          }
+        }
+        tc_fence_before();
+        mbar_arrive(smem_u32(&ctl->acc_empty[acc]));
+      }
+      if (!ok) break;
+      // ---- end of document: one value per row, summed per query in a fixed order ----
+      bool has_winner = (ARGMAX || AFFINE) ? (run_i >= 0) : (run_m != -INFINITY);
+      const float val = (in_seg && row_ok && has_winner) ? run_m * my_qf : 0.f;
+      const long long slot = P.pairing == LIK_PAIR_CROSS ? (long long)my_q * P.n_d + doc : (long long)doc;
+      if (ARGMAX && in_seg && my_s < P.argmax_stride) P.argmax[slot * P.argmax_stride + my_s] = has_winner ? run_i : -1;
+      float* ebuf = ctl->emit[wg][n_wg & 1];
+      ebuf[row] = val;
+      mbar_arrive(smem_u32(&ctl->wg_bar[wg]));
+      ok = wait_bar(&ctl->wg_bar[wg], n_wg & 1, ctl, P.status);
+      ++n_wg;
+      if (!ok) break;
+      const int nseg = ctl->n_seg[wg];
+      for (int sg = wq; sg < nseg; sg += 4) {
+        const int off = ctl->seg_off[wg][sg], len = ctl->seg_len[wg][sg];
+        float sum = 0.f;
+        for (int i = lane; i < len; i += 32) sum += ebuf[off + i];
+        sum = warp_sum(sum);
+        if (lane == 0) {
+          const int qq = ctl->seg_q[wg][sg];
+          if (P.q_chunks == 1) {
+            const long long o = P.pairing == LIK_PAIR_CROSS ? (long long)qq * P.n_d + doc : (long long)doc;
+            P.scores[o] = sum;
+          } else {
+            P.partial[(long long)tile_id * P.n_d + doc] = sum;
+          }
+        }
+      }
+    }
+  }
+
+  // ---- teardown (also reached when aborting: every wait above is bounded) ----
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// scores[q, j] = sum over the chunks of query q, in chunk order
+__global__ void reduce_chunks_kernel(const float* __restrict__ partial, int n_q, int n_d, int q_chunks, float* __restrict__ scores) {
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (long long)n_q * n_d) return;
+  const int q = (int)(idx / n_d), j = (int)(idx - (long long)q * n_d);
+  float s = 0.f;
+  for (int c = 0; c < q_chunks; ++c) s += partial[((long long)q * q_chunks + c) * n_d + j];
+  scores[idx] = s;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+  }
+  return fn;
+}
+
+int make_map(CUtensorMap* map, const lik_seqs& s, int dtype, int dim, int box_rows) {
+  EncodeTiledFn enc = get_encode_fn();
+  if (!enc) {
+    set_error("cuTensorMapEncodeTiled is not available from this driver");
+    return LIK_ERR_CUDA;
+  }
+  const int eb = (int)dtype_size(dtype);
+  CUtensorMapDataType dt = dtype == LIK_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                           : dtype == LIK_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                                              : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+  cuuint64_t gdim[2] = {(cuuint64_t)dim, (cuuint64_t)(s.n_rows > 0 ? s.n_rows : 1)};
+  cuuint64_t gstride[1] = {(cuuint64_t)s.row_stride * eb};
+  cuuint32_t box[2] = {(cuuint32_t)(SLAB_BYTES_ROW / eb), (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(map, dt, 2, const_cast<void*>(s.data), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_error("cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+    return LIK_ERR_CUDA;
+  }
+  return LIK_OK;
+}
+
+struct TcPlan {
+  int q_per_tile, q_chunks, n_tiles, mt, n_slabs, k_steps, stages;
+  long long n_units;
+  size_t smem_bytes;
+};
+
+TcPlan plan_tc(const lik_fwd_args& a) {
+  TcPlan pl{};
+  const int eb = (int)dtype_size(a.dtype);
+  pl.n_slabs = (a.dim * eb + SLAB_BYTES_ROW - 1) / SLAB_BYTES_ROW;
+  pl.k_steps = (a.dim * eb + 31) / 32;
+  const int ml = a.q.max_len > 0 ? a.q.max_len : 1;
+  if (a.pairing == LIK_PAIR_GROUPED) {
+    pl.q_per_tile = 1;
+    pl.q_chunks = 1;
+    pl.n_tiles = a.q.n_seq;
+    pl.mt = 1;
+    pl.n_units = a.d.n_seq;
+  } else {
+    if (ml <= TILE_M) {
+      pl.q_per_tile = TILE_M / ml;
+      pl.q_chunks = 1;
+      pl.n_tiles = (int)ceil_div(a.q.n_seq, pl.q_per_tile);
+    } else {
+      pl.q_per_tile = 1;
+      pl.q_chunks = (int)ceil_div(ml, TILE_M);
+      pl.n_tiles = a.q.n_seq * pl.q_chunks;
+    }
+    pl.mt = pl.n_tiles >= 2 ? 2 : 1;
+    pl.n_units = ceil_div(pl.n_tiles, pl.mt) * (long long)a.d.n_seq;
+  }
+  const size_t q_bytes = 2 * (size_t)pl.n_slabs * TILE_M * SLAB_BYTES_ROW;
+  const size_t stage = (size_t)pl.n_slabs * TILE_N * SLAB_BYTES_ROW;
+  const size_t fixed = q_bytes + sizeof(SharedCtl) + 1024;
+  const size_t budget = 227 * 1024;
+  int st = (int)((budget - fixed) / stage);
+  pl.stages = st > 8 ? 8 : st;
+  pl.smem_bytes = fixed + (size_t)pl.stages * stage;
+  return pl;
+}
+
+}  // namespace
+
+bool fwd_tc_supported(const lik_fwd_args& a) {
+  static int dev_ok = -1;
+  if (dev_ok < 0) dev_ok = lik_device_supported();
+  if (!dev_ok) return false;
+  if (a.dtype != LIK_BF16 && a.dtype != LIK_F16 && a.dtype != LIK_E4M3) return false;
+  if (a.pairing != LIK_PAIR_CROSS && a.pairing != LIK_PAIR_GROUPED) return false;
+  const int eb = (int)dtype_size(a.dtype);
+  if ((a.dim * eb) % 16 != 0 || a.dim * eb > MAX_SLABS * SLAB_BYTES_ROW) return false;
+  if (a.q.n_seq <= 0 || a.d.n_seq <= 0 || a.q.n_rows <= 0 || a.d.n_rows <= 0) return false;
+  if (a.q.max_len <= 0) return false;  // packed queries need their longest length to form tiles
+  if (a.pairing == LIK_PAIR_GROUPED && a.q.max_len > TILE_M) return false;
+  if ((a.q.row_stride * eb) % 16 != 0 || (a.d.row_stride * eb) % 16 != 0) return false;
+  if (((uintptr_t)a.q.data & 15) || ((uintptr_t)a.d.data & 15)) return false;
+  if (a.q.n_rows >= (1ll << 31) || a.d.n_rows >= (1ll << 31)) return false;
+  if (a.argmax && a.argmax_stride < 0) return false;
+  return get_encode_fn() != nullptr;
+}
+
+size_t fwd_tc_workspace(const lik_fwd_args& a) {
+  TcPlan pl = plan_tc(a);
+  return pl.q_chunks > 1 ? (size_t)pl.n_tiles * a.d.n_seq * sizeof(float) : 0;
+}
+
+int launch_fwd_tc(const lik_fwd_args& a, const float* qn, const float* dn, void* ws, size_t ws_bytes, cudaStream_t st) {
+  TcPlan pl = plan_tc(a);
+  if (pl.stages < 1) {
+    set_error("not enough shared memory for the document ring");
+    return LIK_ERR_UNSUPPORTED;
+  }
+  CUtensorMap q_map, d_map;
+  int rc = make_map(&q_map, a.q, a.dtype, a.dim, TILE_M);
+  if (rc) return rc;
+  rc = make_map(&d_map, a.d, a.dtype, a.dim, BOX_ROWS);
+  if (rc) return rc;
+
+  TcParams P{};
+  P.q = make_view(a.q, qn);
+  P.d = make_view(a.d, dn);
+  P.pairing = a.pairing;
+  P.group = a.group;
+  P.n_q = a.q.n_seq;
+  P.n_d = a.d.n_seq;
+  P.elt_bytes = (int)dtype_size(a.dtype);
+  P.ab_format = a.dtype == LIK_BF16 ? 1 : 0;  // kind::f16: F16 = 0, BF16 = 1; kind::f8f6f4: E4M3 = 0
+  P.n_slabs = pl.n_slabs;
+  P.k_steps = pl.k_steps;
+  P.stages = pl.stages;
+  P.q_per_tile = pl.q_per_tile;
+  P.q_chunks = pl.q_chunks;
+  P.n_tiles = pl.n_tiles;
+  P.mt = pl.mt;
+  P.n_units = pl.n_units;
+  P.scores = a.scores;
+  P.partial = pl.q_chunks > 1 ? (float*)ws : nullptr;
+  P.argmax = a.argmax;
+  P.argmax_stride = a.argmax_stride;
+  P.status = a.status;
+  if (pl.q_chunks > 1 && ws_bytes < (size_t)pl.n_tiles * a.d.n_seq * sizeof(float)) {
+    set_error("tcgen05 forward: workspace too small");
+    return LIK_ERR_WORKSPACE;
+  }
+  // positions of the saved argmax that no accumulator row covers (packed queries shorter than the stride)
+  if (a.argmax && (a.q.cu || a.q.lens))
+    LIK_CUDA_OK(cudaMemsetAsync(a.argmax, 0xFF,
+                                (size_t)n_scores_of(a.pairing, a.q.n_seq, a.d.n_seq, 0) * a.argmax_stride * sizeof(int), st));
+
+  const bool fp8 = a.dtype == LIK_E4M3;
+  const bool argmax = a.argmax != nullptr;
+  const bool affine = a.d.mask || a.d.scale || dn;
+  long long grid_ll = pl.n_units < sm_count() ? pl.n_units : sm_count();
+  if (grid_ll < 1) return LIK_OK;
+  dim3 grid((unsigned)grid_ll), block(NUM_THREADS);
+#define LIK_TC_LAUNCH(F, A, X)                                                                                         \
+  do {                                                                                                                 \
+    LIK_CUDA_OK(cudaFuncSetAttribute(fwd_tc_kernel<F, A, X>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem_bytes)); \
+    fwd_tc_kernel<F, A, X><<<grid, block, pl.smem_bytes, st>>>(q_map, d_map, P);                                       \
+  } while (0)
+  if (fp8) {
+    if (argmax && affine) LIK_TC_LAUNCH(true, true, true);
+    else if (argmax) LIK_TC_LAUNCH(true, true, false);
+    else if (affine) LIK_TC_LAUNCH(true, false, true);
+    else LIK_TC_LAUNCH(true, false, false);
+  } else {
+    if (argmax && affine) LIK_TC_LAUNCH(false, true, true);
+    else if (argmax) LIK_TC_LAUNCH(false, true, false);
+    else if (affine) LIK_TC_LAUNCH(false, false, true);
+    else LIK_TC_LAUNCH(false, false, false);
+  }
+#undef LIK_TC_LAUNCH
+  LIK_CUDA_OK(cudaGetLastError());
+  if (pl.q_chunks > 1) {
+    const long long n = (long long)a.q.n_seq * a.d.n_seq;
+    reduce_chunks_kernel<<<(unsigned)ceil_div(n, 256), 256, 0, st>>>(P.partial, a.q.n_seq, a.d.n_seq, pl.q_chunks, a.scores);
+    LIK_CUDA_OK(cudaGetLastError());
+  }
+  return LIK_OK;
+}
+
 }  // namespace lik
