@@ -1,0 +1,300 @@
+"""Benchmark of the MaxSim hot path on B200.
+
+    python bench.py --gpus N --steps K --warmup W            # this engine
+    python bench.py --impl reference ...                       # the reference algorithm on host cores
+
+Workload (BASELINE config 2, "ColBERTv2-shaped in-batch training"): bf16 Q[512,32,128] and
+D[512,300,128] ~N(0,1) L2-normalised, document lengths U[64,300] as a boolean d_mask, full q_mask,
+one step = forward + backward (gradients w.r.t. Q and D) through the autograd path.  Inputs are
+seeded synthetic data.  With N > 1 every rank runs its own replica of the step (MaxSim training does
+not shard; data parallelism is the caller's), so the whole-job figure is N times the per-rank work
+over the slowest rank's time ("weak" scaling).
+
+Metric: TFLOP/s counting only algorithmic work on valid tokens:
+    forward  2 * d * sum_{(i,j)} lq_i * ld_j        backward  4 * d * sum_{(i,j)} lq_i
+One JSON line is printed by rank 0.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "MaxSim fwd+bwd TFLOP/s (bf16)"
+WORKLOAD = "colbert_inbatch_train_bf16: Q[512,32,128] x D[512,300,128], d_len U[64,300], fwd+bwd"
+NQ, ND, LQ, LD, DIM = 512, 512, 32, 300, 128
+
+
+def make_inputs(seed=0):
+    rng = np.random.default_rng(seed)
+    Q = rng.standard_normal((NQ, LQ, DIM), dtype=np.float32)
+    D = rng.standard_normal((ND, LD, DIM), dtype=np.float32)
+    Q /= np.linalg.norm(Q, axis=-1, keepdims=True)
+    D /= np.linalg.norm(D, axis=-1, keepdims=True)
+    lens = rng.integers(64, LD + 1, size=ND)
+    dm = np.arange(LD)[None, :] < lens[:, None]
+    g = rng.standard_normal((NQ, ND), dtype=np.float32)
+    return Q, D, dm, lens, g
+
+
+def flops_of(lens, n_q=NQ, lq=LQ):
+    fwd = 2.0 * DIM * n_q * lq * float(lens.sum())
+    bwd = 4.0 * DIM * n_q * lq * len(lens)
+    return fwd, bwd
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            d = json.load(f)
+        return float(d["bf16_tflops"]), float(d["hbm_gbs"]), "measured"
+    return 1590.0, 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu = gpu_index
+        self.rows = []
+        self._stop = threading.Event()
+        self._t = None
+
+    def _run(self):
+        while not self._stop.is_set():
+            try:
+                out = subprocess.run(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-i", str(self.gpu)],
+                                     capture_output=True, text=True, timeout=5).stdout.strip()
+                if out:
+                    self.rows.append([c.strip() for c in out.split(",")])
+            except Exception:  # noqa: BLE001
+                pass
+            self._stop.wait(0.2)
+
+    def __enter__(self):
+        self._t = threading.Thread(target=self._run, daemon=True)
+        self._t.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        self._t.join(timeout=6)
+
+    def summary(self):
+        sm, mx, reasons = [], 0.0, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            try:
+                sm.append(float(r[1]))
+                mx = max(mx, float(r[2]))
+                for n, v in zip(names, r[5:9]):
+                    if v.lower().startswith("active"):
+                        reasons.add(n)
+            except Exception:  # noqa: BLE001
+                continue
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": mx or None, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def cpu_reference_step(sample_q, Q, D, dm, g):
+    """One forward + backward of the reference algorithm (the CPU oracle, a port of the reference's
+    reference.py) on the first `sample_q` queries against all documents."""
+    from oracle import maxsim_oracle as O
+
+    s = O.maxsim(Q[:sample_q], D, None, dm)
+    gq, gd = O.maxsim_grads(g[:sample_q], Q[:sample_q], D, None, dm)
+    return float(s.sum()) + float(gq.sum()) + float(gd.sum())
+
+
+def run_reference(args, rank):
+    if rank != 0:
+        return
+    Q, D, dm, lens, g = make_inputs()
+    sample_q = 16
+    fwd, bwd = flops_of(lens, n_q=sample_q)
+    for _ in range(max(args.warmup, 0) and 1):
+        cpu_reference_step(sample_q, Q, D, dm, g)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        cpu_reference_step(sample_q, Q, D, dm, g)
+    dt = time.perf_counter() - t0
+    val = (fwd + bwd) * args.steps / dt / 1e12
+    cores = os.cpu_count() or 1
+    line = {
+        "impl": "reference", "metric": METRIC, "value": val, "unit": "TFLOP/s", "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "sample": f"first {sample_q} of {NQ} queries against all {ND} documents per step"},
+        "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": cores, "kind": "port",
+                         "sample": f"{sample_q} queries x {ND} docs fwd+bwd per step, numpy (OpenBLAS, all host threads)"},
+        "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    import late_interaction_kernels_b200 as lik
+    from late_interaction_kernels_b200 import _lib, _ops
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device; there is no CPU path")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    _lib.load()
+
+    Q, D, dm, lens, g = make_inputs()
+    fwd_flops, bwd_flops = flops_of(lens)
+    hQ = torch.from_numpy(Q).to(torch.bfloat16).pin_memory()
+    hD = torch.from_numpy(D).to(torch.bfloat16).pin_memory()
+    hM = torch.from_numpy(dm).pin_memory()
+    hG = torch.from_numpy(g).pin_memory()
+    dQ, dD, dM, dG = hQ.to(dev), hD.to(dev), hM.to(dev), hG.to(dev)
+    Qr, Dr = dQ.clone().requires_grad_(), dD.clone().requires_grad_()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)  # > 126 MB L2
+
+    def step():
+        Qr.grad = None
+        Dr.grad = None
+        s = lik.maxsim(Qr, Dr, d_mask=dM)
+        s.backward(dG)
+        return s
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    with ClockSampler(local_rank) as clocks:
+        barrier()
+        for a, b in ev:
+            flush.zero_()
+            a.record()
+            step()
+            b.record()
+        barrier()
+    total_ms = sum(a.elapsed_time(b) for a, b in ev)
+    lik.check_device_status(dev)
+    t = torch.tensor([total_ms], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    total_ms = float(t.item())
+    value = world * (fwd_flops + bwd_flops) * args.steps / (total_ms * 1e-3) / 1e12
+
+    # ---- end to end: host buffers in, results out, every step ----
+    hS = torch.empty((NQ, ND), dtype=torch.float32).pin_memory()
+    hGQ, hGD = torch.empty_like(hQ).pin_memory(), torch.empty_like(hD).pin_memory()
+
+    def e2e_step():
+        q = hQ.to(dev, non_blocking=True).requires_grad_()
+        d = hD.to(dev, non_blocking=True).requires_grad_()
+        m = hM.to(dev, non_blocking=True)
+        go = hG.to(dev, non_blocking=True)
+        s = lik.maxsim(q, d, d_mask=m)
+        s.backward(go)
+        hS.copy_(s.detach(), non_blocking=True)
+        hGQ.copy_(q.grad, non_blocking=True)
+        hGD.copy_(d.grad, non_blocking=True)
+
+    for _ in range(2):
+        e2e_step()
+    barrier()
+    n_e2e = max(3, min(args.steps, 10))
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(n_e2e):
+        e2e_step()
+    e1.record()
+    barrier()
+    te = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(te, op=dist.ReduceOp.MAX)
+    e2e_val = world * (fwd_flops + bwd_flops) * n_e2e / (float(te.item()) * 1e-3) / 1e12
+    h2d = hQ.numel() * 2 + hD.numel() * 2 + hM.numel() + hG.numel() * 4
+    d2h = hS.numel() * 4 + hGQ.numel() * 2 + hGD.numel() * 2
+
+    # ---- roofline of the dominant kernel (the tcgen05 forward with argmax), timed alone ----
+    qs, ds = _ops.padded_spec(dQ), _ops.padded_spec(dD, dM)
+    for _ in range(3):
+        _ops.forward(qs, ds, save_argmax=True)
+    fev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(10)]
+    for a, b in fev:
+        flush.zero_()
+        a.record()
+        _ops.forward(qs, ds, save_argmax=True)
+        b.record()
+    torch.cuda.synchronize()
+    fwd_ms = float(np.mean([a.elapsed_time(b) for a, b in fev]))
+    peak_tf, _, which = measured_peaks()
+    achieved = fwd_flops / (fwd_ms * 1e-3) / 1e12
+    roofline = {"bound": "tensor", "achieved": achieved, "peak": peak_tf, "unit": "TFLOP/s", "frac": achieved / peak_tf,
+                "traffic": None, "kernel": "fwd_tc_kernel (bf16, argmax, masked)", "kernel_ms": fwd_ms, "peak_source": which}
+
+    line = {
+        "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "parallelism": f"replicas x{world}", "l2": "flushed between steps (256 MB write)",
+                   "fwd_flops_per_step": fwd_flops, "bwd_flops_per_step": bwd_flops},
+        "e2e": {"value": e2e_val, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+        "gpu_launches": 3 * args.steps,
+        "roofline": roofline,
+        "clocks": clocks.summary(),
+    }
+    if rank == 0:
+        if not args.no_cpu_baseline and world == 1:
+            sample_q = 16
+            cf, cb = flops_of(lens, n_q=sample_q)
+            t0 = time.perf_counter()
+            reps = 0
+            while reps < 2 or (time.perf_counter() - t0 < 10 and reps < 50):
+                cpu_reference_step(sample_q, Q, D, dm, g)
+                reps += 1
+            dt = time.perf_counter() - t0
+            line["cpu_baseline"] = {"value": (cf + cb) * reps / dt / 1e12, "unit": "TFLOP/s", "cores": os.cpu_count() or 1,
+                                    "kind": "port", "sample": f"{reps} x ({sample_q} queries x {ND} docs fwd+bwd), numpy oracle, all host threads"}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
