@@ -71,28 +71,38 @@ class ClockSampler:
     def __init__(self, gpu_index):
         self.gpu = gpu_index
         self.rows = []
-        self._stop = threading.Event()
+        self._proc = None
         self._t = None
 
     def _run(self):
-        while not self._stop.is_set():
-            try:
-                out = subprocess.run(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-i", str(self.gpu)],
-                                     capture_output=True, text=True, timeout=5).stdout.strip()
-                if out:
-                    self.rows.append([c.strip() for c in out.split(",")])
-            except Exception:  # noqa: BLE001
-                pass
-            self._stop.wait(0.2)
+        try:
+            for line in self._proc.stdout:
+                if line.strip():
+                    self.rows.append([c.strip() for c in line.split(",")])
+        except Exception:  # noqa: BLE001
+            pass
 
     def __enter__(self):
-        self._t = threading.Thread(target=self._run, daemon=True)
-        self._t.start()
+        try:
+            self._proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100", "-i", str(self.gpu)],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self._t = threading.Thread(target=self._run, daemon=True)
+            self._t.start()
+            time.sleep(0.3)  # let the first sample arrive
+        except Exception:  # noqa: BLE001
+            self._proc = None
         return self
 
     def __exit__(self, *exc):
-        self._stop.set()
-        self._t.join(timeout=6)
+        if self._proc is not None:
+            self._proc.terminate()
+            try:
+                self._proc.wait(timeout=5)
+            except Exception:  # noqa: BLE001
+                self._proc.kill()
+            if self._t is not None:
+                self._t.join(timeout=5)
 
     def summary(self):
         sm, mx, reasons = [], 0.0, set()
@@ -153,6 +163,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--only", default=None, choices=["fwd", "fwd_infer", "bwd", "step"],
+                    help="profiling aid: launch only this part of the step, --steps times, and print its mean time")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -198,6 +210,29 @@ def main():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
+
+    if args.only:
+        from late_interaction_kernels_b200.backward import maxsim_backward_lowmem
+
+        qs, ds = _ops.padded_spec(dQ), _ops.padded_spec(dD, dM)
+        _, am = _ops.forward(qs, ds, save_argmax=True)
+        part = {
+            "fwd": lambda: _ops.forward(qs, ds, save_argmax=True),
+            "fwd_infer": lambda: _ops.forward(qs, ds),
+            "bwd": lambda: maxsim_backward_lowmem(dG, dQ, dD, am),
+            "step": step,
+        }[args.only]
+        for _ in range(args.warmup):
+            part()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(args.steps):
+            part()
+        b.record()
+        torch.cuda.synchronize()
+        print(json.dumps({"only": args.only, "ms": a.elapsed_time(b) / args.steps, "steps": args.steps}), flush=True)
+        return
 
     for _ in range(args.warmup):
         step()

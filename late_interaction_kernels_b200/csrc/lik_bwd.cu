@@ -263,6 +263,357 @@ __global__ void __launch_bounds__(256) bwd_dd_owned_kernel(BwdParams P) {
   }
 }
 
+
+// =================================================================================
+// Fast paths (embedding width a multiple of 4, at most 256): every lane moves 4
+// consecutive elements per 128-column chunk with one vector load.
+// =================================================================================
+template <typename T>
+__device__ __forceinline__ void load4(const T* p, float (&v)[4]);
+template <>
+__device__ __forceinline__ void load4<float>(const float* p, float (&v)[4]) {
+  float4 x = __ldg(reinterpret_cast<const float4*>(p));
+  v[0] = x.x; v[1] = x.y; v[2] = x.z; v[3] = x.w;
+}
+template <>
+__device__ __forceinline__ void load4<__half>(const __half* p, float (&v)[4]) {
+  uint2 x = __ldg(reinterpret_cast<const uint2*>(p));
+  float2 a = __half22float2(*reinterpret_cast<__half2*>(&x.x)), b = __half22float2(*reinterpret_cast<__half2*>(&x.y));
+  v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+}
+template <>
+__device__ __forceinline__ void load4<__nv_bfloat16>(const __nv_bfloat16* p, float (&v)[4]) {
+  uint2 x = __ldg(reinterpret_cast<const uint2*>(p));
+  v[0] = __uint_as_float(x.x << 16); v[1] = __uint_as_float(x.x & 0xffff0000u);
+  v[2] = __uint_as_float(x.y << 16); v[3] = __uint_as_float(x.y & 0xffff0000u);
+}
+template <typename G>
+__device__ __forceinline__ void store4(G* p, const float (&v)[4]);
+template <>
+__device__ __forceinline__ void store4<float>(float* p, const float (&v)[4]) {
+  *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+}
+template <>
+__device__ __forceinline__ void store4<__half>(__half* p, const float (&v)[4]) {
+  __half2 a = __floats2half2_rn(v[0], v[1]), b = __floats2half2_rn(v[2], v[3]);
+  uint2 x;
+  x.x = *reinterpret_cast<unsigned*>(&a);
+  x.y = *reinterpret_cast<unsigned*>(&b);
+  *reinterpret_cast<uint2*>(p) = x;
+}
+template <>
+__device__ __forceinline__ void store4<__nv_bfloat16>(__nv_bfloat16* p, const float (&v)[4]) {
+  __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
+  uint2 x;
+  x.x = *reinterpret_cast<unsigned*>(&a);
+  x.y = *reinterpret_cast<unsigned*>(&b);
+  *reinterpret_cast<uint2*>(p) = x;
+}
+
+// Pull a gradient w.r.t. x_hat = x * inv back to x:  (g - <g, x_hat> x_hat) * inv.   acc is [CH][4] per lane.
+template <typename T, int CH>
+__device__ __forceinline__ void normalize_jacobian_row(float (&acc)[CH][4], const T* src, float inv, int dim, int lane) {
+  float xh[CH][4];
+  float dot = 0.f;
+#pragma unroll
+  for (int c = 0; c < CH; ++c) {
+    const int k = c * 128 + lane * 4;
+    if (k < dim) {
+      load4<T>(src + k, xh[c]);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        xh[c][e] *= inv;
+        dot = fmaf(acc[c][e], xh[c][e], dot);
+      }
+    } else {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) xh[c][e] = 0.f;
+    }
+  }
+  dot = warp_sum(dot);
+#pragma unroll
+  for (int c = 0; c < CH; ++c)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) acc[c][e] = (acc[c][e] - dot * xh[c][e]) * inv;
+}
+
+// ---------------------------------------------------------------------------------
+// grad_q fast: grid = (n_q, ceil(rows / 8)); warp = query token.  The winners and
+// upstream gradients of 32 documents at a time are staged through shared memory
+// (coalesced), then every warp gathers its 32 winning rows with independent loads.
+// ---------------------------------------------------------------------------------
+constexpr int DQ_JC = 32;
+
+template <typename T, typename G, int CH>
+__global__ void __launch_bounds__(256) bwd_dq_fast_kernel(BwdParams P) {
+  __shared__ int s_t[DQ_JC][8];
+  __shared__ float s_g[DQ_JC];
+  __shared__ long long s_row0[DQ_JC];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int i = blockIdx.x;
+  const int s0 = blockIdx.y * 8;
+  const int s = s0 + warp;
+  long long qrow0;
+  int qlen;
+  seq_bounds(P.q, i, qrow0, qlen, nullptr);
+  const int q_rows = P.q.cu ? qlen : P.q.max_len;
+  if (s0 >= q_rows) return;  // whole CTA out of range
+  const long long qrow = qrow0 + s;
+  const bool owns = s < q_rows;
+  const bool active = owns && s < qlen && s < P.argmax_stride && row_valid(P.q, qrow);
+  float acc[CH][4];
+#pragma unroll
+  for (int c = 0; c < CH; ++c)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) acc[c][e] = 0.f;
+  long long p0;
+  int count, j0;
+  query_slots(P.pm, i, p0, count, j0);
+  const T* __restrict__ Dg = (const T*)P.d.data;
+  const int lq = P.argmax_stride;
+  for (int jb = 0; jb < count; jb += DQ_JC) {
+    __syncthreads();
+    {
+      // thread (jj, r): winner of document jb + jj for query token s0 + r
+      const int jj = tid >> 3, r = tid & 7;
+      int t = -1;
+      if (jb + jj < count && s0 + r < lq) t = P.argmax[(p0 + jb + jj) * lq + s0 + r];
+      s_t[jj][r] = t;
+      if (tid < DQ_JC) {
+        const int j = jb + tid;
+        float g = 0.f;
+        long long r0 = 0;
+        if (j < count) {
+          g = P.g[p0 + j];
+          int dl;
+          seq_bounds(P.d, j0 + j, r0, dl, nullptr);
+        }
+        s_g[tid] = g;
+        s_row0[tid] = r0;
+      }
+    }
+    __syncthreads();
+    if (active) {
+#pragma unroll 8
+      for (int jj = 0; jj < DQ_JC; ++jj) {
+        const int t = s_t[jj][warp];
+        if (t < 0) continue;
+        const long long drow = s_row0[jj] + t;
+        float f = s_g[jj];
+        if (P.d.inv_norm || P.d.scale || P.d.scale_scalar != 1.f) f *= row_factor(P.d, drow);
+        const T* src = Dg + drow * P.d.row_stride;
+#pragma unroll
+        for (int c = 0; c < CH; ++c) {
+          const int k = c * 128 + lane * 4;
+          if (k < P.dim) {
+            float v[4];
+            load4<T>(src + k, v);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) acc[c][e] = fmaf(f, v[e], acc[c][e]);
+          }
+        }
+      }
+    }
+  }
+  if (!owns) return;
+  if (active) {
+    if (P.normalize) {
+      normalize_jacobian_row<T, CH>(acc, (const T*)P.q.data + qrow * P.q.row_stride, P.q.inv_norm[qrow], P.dim, lane);
+    } else {
+      const float qf = P.q.scale_scalar * (P.q.scale ? P.q.scale[qrow] : 1.f);
+      if (qf != 1.f) {
+#pragma unroll
+        for (int c = 0; c < CH; ++c)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) acc[c][e] *= qf;
+      }
+    }
+  }
+  G* out = (G*)P.grad_q + qrow * P.dim;
+#pragma unroll
+  for (int c = 0; c < CH; ++c) {
+    const int k = c * 128 + lane * 4;
+    if (k < P.dim) store4<G>(out + k, acc[c]);
+  }
+}
+
+// ---------------------------------------------------------------------------------
+// grad_d fast, destination-owned: one CTA (16 warps) per document.
+//   1. every warp histograms the winners of its contiguous slice of (query, token)
+//      entries per document token;
+//   2. a scan turns the histograms into write offsets (token-major, then warp, so
+//      the order inside a token's list is the entry order);
+//   3. the entries are placed (stable counting sort) into a list in shared memory;
+//   4. warps take document tokens round-robin and reduce each token's list in order,
+//      gathering query rows with vector loads; one store per output row.
+// ---------------------------------------------------------------------------------
+constexpr int DDS_WARPS = 16;
+
+struct DdsSmem {
+  int* ent;       // [n_entries] sorted entry ids
+  int* hist;      // [DDS_WARPS][ld_pad]
+  int* tok_off;   // [ld_pad + 1]
+  float* gcol;    // [n_qrange]
+};
+
+template <typename T, typename G, int CH>
+__global__ void __launch_bounds__(DDS_WARPS * 32) bwd_dd_sorted_kernel(BwdParams P, int ld_pad, int e_cap) {
+  extern __shared__ int dds_raw[];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int j = blockIdx.x;
+  long long drow0;
+  int dlen;
+  seq_bounds(P.d, j, drow0, dlen, nullptr);
+  const int d_rows = P.d.cu ? dlen : P.d.max_len;
+  if (d_rows <= 0) return;
+  if (dlen >= ld_pad) {  // max_len understated the longest document: report instead of overrunning shared memory
+    if (tid == 0 && P.status) atomicOr(P.status, LIK_DEV_LEN_RANGE);
+    return;
+  }
+  int i_begin, i_end;
+  if (P.pm.pairing == LIK_PAIR_CROSS) {
+    i_begin = 0;
+    i_end = P.pm.n_q;
+  } else {
+    i_begin = j / P.pm.group;
+    i_end = i_begin + 1;
+  }
+  const int lq = P.argmax_stride;
+  const int n_ent = (i_end - i_begin) * lq;
+  int* ent = dds_raw;
+  int* hist = ent + e_cap;
+  int* tok_off = hist + DDS_WARPS * ld_pad;
+  float* gcol = reinterpret_cast<float*>(tok_off + ld_pad + 1);
+
+  for (int x = tid; x < DDS_WARPS * ld_pad; x += blockDim.x) hist[x] = 0;
+  for (int x = tid; x < i_end - i_begin; x += blockDim.x) {
+    const long long p = P.pm.pairing == LIK_PAIR_CROSS ? (long long)(i_begin + x) * P.pm.n_d + j : (long long)j;
+    gcol[x] = P.g[p];
+  }
+  __syncthreads();
+
+  // entry e = (i - i_begin) * lq + s ; slice of this warp (multiple of 32 so rounds stay aligned)
+  const int per_warp = ((n_ent + DDS_WARPS - 1) / DDS_WARPS + 31) & ~31;
+  const int e_lo = warp * per_warp, e_hi = min(n_ent, e_lo + per_warp);
+
+  auto winner = [&](int e) -> int {
+    // token this entry points at, or -1 when it contributes nothing
+    const int ii = e / lq, s = e - ii * lq;
+    const int i = i_begin + ii;
+    const long long p = P.pm.pairing == LIK_PAIR_CROSS ? (long long)i * P.pm.n_d + j : (long long)j;
+    const int t = P.argmax[p * lq + s];
+    if (t < 0 || t >= dlen) return -1;
+    long long qrow0;
+    int qlen;
+    seq_bounds(P.q, i, qrow0, qlen, nullptr);
+    if (s >= qlen || !row_valid(P.q, qrow0 + s)) return -1;
+    return t;
+  };
+
+  for (int e = e_lo + lane; e < e_hi; e += 32) {
+    const int t = winner(e);
+    if (t >= 0) atomicAdd(&hist[warp * ld_pad + t], 1);
+  }
+  __syncthreads();
+  // offsets: warp 0 scans the tokens; hist[w][t] becomes the first write position of warp w for token t
+  if (warp == 0) {
+    int running = 0;
+    for (int tb = 0; tb < dlen; tb += 32) {
+      const int t = tb + lane;
+      int tot = 0;
+      if (t < dlen)
+        for (int w = 0; w < DDS_WARPS; ++w) tot += hist[w * ld_pad + t];
+      int incl = tot;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        int v = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += v;
+      }
+      const int excl = running + incl - tot;
+      if (t < dlen) {
+        tok_off[t] = excl;
+        int base = excl;
+        for (int w = 0; w < DDS_WARPS; ++w) {
+          const int c = hist[w * ld_pad + t];
+          hist[w * ld_pad + t] = base;
+          base += c;
+        }
+      }
+      running += __shfl_sync(0xffffffffu, incl, 31);
+    }
+    if (lane == 0) tok_off[dlen] = running;
+  }
+  __syncthreads();
+  // stable placement
+  for (int eb = e_lo; eb < e_hi; eb += 32) {
+    const int e = eb + lane;
+    const int t = e < e_hi ? winner(e) : -1;
+    const unsigned peers = __match_any_sync(0xffffffffu, t);
+    if (t >= 0) {
+      const int rank = __popc(peers & ((1u << lane) - 1u));
+      const int pos = hist[warp * ld_pad + t] + rank;
+      ent[pos] = e;
+    }
+    __syncwarp();
+    if (t >= 0 && (peers & ((1u << lane) - 1u)) == 0) hist[warp * ld_pad + t] += __popc(peers);
+    __syncwarp();
+  }
+  __syncthreads();
+
+  const T* __restrict__ Qg = (const T*)P.q.data;
+  const bool q_factor = P.q.inv_norm || P.q.scale || P.q.scale_scalar != 1.f;
+  for (int t = warp; t < d_rows; t += DDS_WARPS) {
+    float acc[CH][4];
+#pragma unroll
+    for (int c = 0; c < CH; ++c)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) acc[c][e] = 0.f;
+    if (t < dlen) {
+      const int lo = tok_off[t], hi = tok_off[t + 1];
+#pragma unroll 4
+      for (int k = lo; k < hi; ++k) {
+        const int e = ent[k];
+        const int ii = e / lq, s = e - ii * lq;
+        long long qrow0;
+        int qlen;
+        seq_bounds(P.q, i_begin + ii, qrow0, qlen, nullptr);
+        const long long qrow = qrow0 + s;
+        float f = gcol[ii];
+        if (q_factor) f *= row_factor(P.q, qrow);
+        const T* src = Qg + qrow * P.q.row_stride;
+#pragma unroll
+        for (int c = 0; c < CH; ++c) {
+          const int kk = c * 128 + lane * 4;
+          if (kk < P.dim) {
+            float v[4];
+            load4<T>(src + kk, v);
+#pragma unroll
+            for (int x = 0; x < 4; ++x) acc[c][x] = fmaf(f, v[x], acc[c][x]);
+          }
+        }
+      }
+    }
+    const long long drow = drow0 + t;
+    if (P.normalize) {
+      normalize_jacobian_row<T, CH>(acc, (const T*)P.d.data + drow * P.d.row_stride, P.d.inv_norm[drow], P.dim, lane);
+    } else {
+      const float df = P.d.scale_scalar * (P.d.scale ? P.d.scale[drow] : 1.f);
+      if (df != 1.f) {
+#pragma unroll
+        for (int c = 0; c < CH; ++c)
+#pragma unroll
+          for (int x = 0; x < 4; ++x) acc[c][x] *= df;
+      }
+    }
+    G* out = (G*)P.grad_d + drow * P.dim;
+#pragma unroll
+    for (int c = 0; c < CH; ++c) {
+      const int kk = c * 128 + lane * 4;
+      if (kk < P.dim) store4<G>(out + kk, acc[c]);
+    }
+  }
+}
+
 // ---------------------------------------------------------------------------------
 // Atomic scatter: one warp per (score slot, query token).  Adds into fp32 buffers.
 // WITH_DQ also scatters grad_q (pair lists, where a query's slots are not contiguous).
@@ -366,14 +717,42 @@ int run_bwd(const lik_bwd_args& a, BwdParams& P, const BwdPlan& pl, cudaStream_t
       KERNEL<T, G, 32><<<GRID, 256, 0, st>>>(__VA_ARGS__);                       \
   } while (0)
 
+  // vector fast paths: rows 8/16-byte aligned, width a multiple of 4 and at most 256
+  const size_t eb = dtype_size(a.dtype);
+  const bool fast = a.dim % 4 == 0 && a.dim <= 256 && (a.q.row_stride * eb) % (4 * eb) == 0 &&
+                    (a.d.row_stride * eb) % (4 * eb) == 0 && ((uintptr_t)a.q.data % (4 * eb)) == 0 &&
+                    ((uintptr_t)a.d.data % (4 * eb)) == 0 && ((uintptr_t)a.grad_q % 16) == 0 && ((uintptr_t)a.grad_d % 16) == 0;
   if (a.grad_q && !list && a.q.n_seq > 0 && a.q.max_len > 0) {
     dim3 grid((unsigned)a.q.n_seq, (unsigned)ceil_div(a.q.max_len, 8));
-    LIK_BY_CMAX(bwd_dq_kernel, grid, P);
+    if (fast) {
+      if (a.dim <= 128)
+        bwd_dq_fast_kernel<T, G, 1><<<grid, 256, 0, st>>>(P);
+      else
+        bwd_dq_fast_kernel<T, G, 2><<<grid, 256, 0, st>>>(P);
+    } else {
+      LIK_BY_CMAX(bwd_dq_kernel, grid, P);
+    }
     LIK_CUDA_OK(cudaGetLastError());
   }
   if (a.grad_d && !list && a.deterministic && a.d.n_seq > 0 && a.d.max_len > 0) {
-    dim3 grid((unsigned)a.d.n_seq, (unsigned)ceil_div(a.d.max_len, DD_TOK));
-    LIK_BY_CMAX(bwd_dd_owned_kernel, grid, P);
+    // sorted kernel needs the winner list of one document in shared memory
+    const long long n_ent = (long long)(a.pairing == LIK_PAIR_CROSS ? a.q.n_seq : 1) * a.argmax_stride;
+    const int ld_pad = a.d.max_len + 1;
+    const long long n_qrange = a.pairing == LIK_PAIR_CROSS ? a.q.n_seq : 1;
+    const size_t smem = ((size_t)n_ent + (size_t)DDS_WARPS * ld_pad + ld_pad + 1 + n_qrange) * 4;
+    if (fast && smem <= 200 * 1024) {
+      dim3 grid((unsigned)a.d.n_seq);
+      if (a.dim <= 128) {
+        LIK_CUDA_OK(cudaFuncSetAttribute(bwd_dd_sorted_kernel<T, G, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        bwd_dd_sorted_kernel<T, G, 1><<<grid, DDS_WARPS * 32, smem, st>>>(P, ld_pad, (int)n_ent);
+      } else {
+        LIK_CUDA_OK(cudaFuncSetAttribute(bwd_dd_sorted_kernel<T, G, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        bwd_dd_sorted_kernel<T, G, 2><<<grid, DDS_WARPS * 32, smem, st>>>(P, ld_pad, (int)n_ent);
+      }
+    } else {
+      dim3 grid((unsigned)a.d.n_seq, (unsigned)ceil_div(a.d.max_len, DD_TOK));
+      LIK_BY_CMAX(bwd_dd_owned_kernel, grid, P);
+    }
     LIK_CUDA_OK(cudaGetLastError());
   }
 #undef LIK_BY_CMAX

@@ -1,10 +1,10 @@
 // Blackwell tensor-core MaxSim forward (sm_100a: TMA + tcgen05.mma + TMEM).
 //
 // GEMM view: rows = query tokens (A operand, K-major, 128 per tile), columns = document tokens (B
-// operand, K-major, up to 256 per tile), K = embedding width.  A CTA is persistent: it keeps one or
+// operand, K-major, up to 128 per tile), K = embedding width.  A CTA is persistent: it keeps one or
 // two 128-row query tiles resident in shared memory and streams document tiles through a TMA ring.
 // Every document tile feeds one MMA group per resident query tile; the fp32 accumulator of query
-// tile m lives in TMEM columns [256 m, 256 m + 256).  A tile never spans two documents, so the
+// tile m alternates between TMEM columns [256 m, +128) and [256 m + 128, +128).  A tile never spans two documents, so the
 // epilogue is: per thread (= one query token = one TMEM lane) a running max over the tile's columns,
 // carried across the tiles of a document; at the end of the document the 128 row maxima are summed
 // per query (fixed order) into one score.  Scores for a (query, document) pair have exactly one
@@ -24,13 +24,19 @@ namespace lik {
 namespace {
 
 constexpr int TILE_M = 128;
-constexpr int TILE_N = 256;
+#ifndef LIK_TILE_N
+#define LIK_TILE_N 256
+#endif
+constexpr int TILE_N = LIK_TILE_N;     // document tokens per tile
+constexpr int ACC_PER_GROUP = 256 / TILE_N;  // TMEM accumulators each epilogue group alternates between
 constexpr int BOX_ROWS = 64;        // rows per TMA box of the document ring
 constexpr int SLAB_BYTES_ROW = 128; // one swizzle span: 64 two-byte or 128 one-byte elements
 constexpr int MAX_SLABS = 2;
 constexpr int NUM_THREADS = 320;
 constexpr int EPI_THREADS = 128;
-constexpr long long WAIT_LIMIT_NS = 2000000000ll;  // 2 s per wait
+constexpr int EPI_WARPS = 4;         // barrier arrivals are one per warp (elected lane), not one per thread
+constexpr long long WAIT_LIMIT_CYCLES = 4000000000ll;  // about 2 s per wait at 2 GHz
+constexpr int LEN_FLAG_MASKED = 1 << 30;
 
 // ---------------------------------------------------------------------------------------------
 // PTX wrappers
@@ -56,11 +62,6 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "r"(bar), "r"(parity)
       : "memory");
   return ok != 0;
-}
-__device__ __forceinline__ long long global_ns() {
-  long long t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
 }
 __device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
@@ -102,9 +103,10 @@ __device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t a_desc, uint64_
         : "memory");
   }
 }
-// 32 lanes x 32 consecutive fp32 columns of TMEM -> 32 registers per thread
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
-  uint32_t r[32];
+// 32 lanes x 32 consecutive fp32 columns of TMEM -> 32 registers per thread.  The load is
+// asynchronous: the registers may only be read after tmem_ld_wait(), which takes them as in/out
+// operands so that no use can be scheduled ahead of it.
+__device__ __forceinline__ void tmem_ld32_issue(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
       "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
@@ -115,9 +117,75 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
         "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
       : "r"(taddr)
       : "memory");
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait(uint32_t (&r)[32]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;"
+               : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]), "+r"(r[8]),
+                 "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]), "+r"(r[16]),
+                 "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]), "+r"(r[24]),
+                 "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
+               :
+               : "memory");
+}
+__device__ __forceinline__ void as_floats(const uint32_t (&r)[32], float (&v)[32]) {
 #pragma unroll
   for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+// maximum of 32 values as a shallow tree of independent 3-input max operations
+__device__ __forceinline__ float max32(const float (&v)[32]) {
+  float a0 = max3(v[0], v[1], v[2]), a1 = max3(v[3], v[4], v[5]), a2 = max3(v[6], v[7], v[8]);
+  float a3 = max3(v[9], v[10], v[11]), a4 = max3(v[12], v[13], v[14]), a5 = max3(v[15], v[16], v[17]);
+  float a6 = max3(v[18], v[19], v[20]), a7 = max3(v[21], v[22], v[23]), a8 = max3(v[24], v[25], v[26]);
+  float a9 = max3(v[27], v[28], v[29]);
+  float b0 = max3(a0, a1, a2), b1 = max3(a3, a4, a5), b2 = max3(a6, a7, a8), b3 = max3(a9, v[30], v[31]);
+  return fmaxf(max3(b0, b1, b2), b3);
+}
+
+// Fold one 32-column chunk of a score tile into the running (max, argmax) of a row.
+//   COLS: apply the per-column multiplier / additive mask staged in shared memory.
+//   lim:  number of valid columns in the chunk (1..32).
+template <bool ARGMAX, bool COLS>
+__device__ __forceinline__ void fold_chunk(float (&v)[32], int lim, int col0, const float* scale, const float* bias,
+                                           float& run_m, int& run_i) {
+  if (COLS) {
+#pragma unroll
+    for (int i = 0; i < 32; i += 4) {
+      const float4 sc = *reinterpret_cast<const float4*>(scale + i);
+      const float4 bi = *reinterpret_cast<const float4*>(bias + i);
+      v[i + 0] = fmaf(v[i + 0], sc.x, bi.x);
+      v[i + 1] = fmaf(v[i + 1], sc.y, bi.y);
+      v[i + 2] = fmaf(v[i + 2], sc.z, bi.z);
+      v[i + 3] = fmaf(v[i + 3], sc.w, bi.w);
+    }
+  }
+  if (lim < 32) {
+#pragma unroll
+    for (int i = 0; i < 32; ++i)
+      if (i >= lim) v[i] = -INFINITY;
+  }
+  const float cmax = max32(v);
+  if (ARGMAX) {
+    if (cmax > run_m) {  // strict: an equal value in a later chunk never displaces an earlier winner
+      unsigned m0 = 0, m1 = 0, m2 = 0, m3 = 0;
+#pragma unroll
+      for (int i = 0; i < 32; i += 4) {
+        if (v[i + 0] == cmax) m0 |= 1u << (i + 0);
+        if (v[i + 1] == cmax) m1 |= 1u << (i + 1);
+        if (v[i + 2] == cmax) m2 |= 1u << (i + 2);
+        if (v[i + 3] == cmax) m3 |= 1u << (i + 3);
+      }
+      run_i = col0 + __ffs((int)(m0 | m1 | m2 | m3)) - 1;  // lowest matching column
+      run_m = cmax;
+    }
+  } else {
+    run_m = fmaxf(run_m, cmax);
+  }
 }
 
 // Shared-memory matrix descriptor: K-major operand, 128-byte swizzle, 8-row groups 1024 bytes apart.
@@ -159,33 +227,50 @@ struct TcParams {
   int* argmax;
   int argmax_stride;
   int* status;
+  int d_len_flagged;  // d.lens carries LEN_FLAG_MASKED on documents whose mask is not a plain prefix
 };
 
 struct SharedCtl {
   unsigned long long q_full, q_empty;
   unsigned long long d_full[8], d_empty[8];
-  unsigned long long acc_full[2], acc_empty[2];
+  unsigned long long acc_full[4], acc_empty[4];
   unsigned long long wg_bar[2];
   uint32_t tmem_base;
   volatile int abort_flag;
   int seg_off[2][TILE_M], seg_len[2][TILE_M], seg_q[2][TILE_M];
   short row_seg[2][TILE_M];
   int n_seg[2];
+  int warp_aligned[2];  // every query of the tile sits inside one warp's 32 rows, starting at its first row
   float emit[2][2][TILE_M];
-  float col_scale[2][TILE_N];
-  float col_bias[2][TILE_N];
+  alignas(16) float col_scale[2][TILE_N];  // read as float4
+  alignas(16) float col_bias[2][TILE_N];
 };
+
+#ifdef LIK_TC_PROFILE
+}  // namespace
+__device__ unsigned long long g_prof[16];
+namespace {
+#define PROF_T0(var) long long var = clock64()
+#define PROF_ADD(slot, var) prof[slot] += clock64() - var
+#define PROF_DECL() unsigned long long prof[16] = {0}
+#define PROF_FLUSH(cond) if (cond) { for (int i_ = 0; i_ < 16; ++i_) if (prof[i_]) atomicAdd(&g_prof[i_], prof[i_]); }
+#else
+#define PROF_T0(var)
+#define PROF_ADD(slot, var)
+#define PROF_DECL()
+#define PROF_FLUSH(cond)
+#endif
 
 // Bounded wait.  Returns false when the CTA is aborting.
 __device__ __forceinline__ bool wait_bar(unsigned long long* bar, uint32_t parity, SharedCtl* ctl, int* status) {
   const uint32_t b = smem_u32(bar);
   if (mbar_try_wait(b, parity)) return true;
-  const long long t0 = global_ns();
+  const long long t0 = clock64();
   int spins = 0;
   while (true) {
     if (mbar_try_wait(b, parity)) return true;
     if (ctl->abort_flag) return false;
-    if ((++spins & 63) == 0 && global_ns() - t0 > WAIT_LIMIT_NS) {
+    if ((++spins & 63) == 0 && clock64() - t0 > WAIT_LIMIT_CYCLES) {
       ctl->abort_flag = 1;
       if (status) atomicOr(status, LIK_DEV_WAIT_TIMEOUT);
       return false;
@@ -230,7 +315,37 @@ __device__ __forceinline__ void unit_decode(const TcParams& P, long long u, int&
   }
 }
 
-template <bool FP8, bool ARGMAX, bool AFFINE>
+
+// First row and column count of document `doc`; `masked` tells whether its mask has holes.
+// Lengths come from the caller-validated views, clamped to the padded extent.
+__device__ __forceinline__ void doc_bounds(const TcParams& P, int doc, long long& row0, int& len, bool& masked) {
+  masked = false;
+  if (P.d.cu) {
+    const int a = P.d.cu[doc], b = P.d.cu[doc + 1];
+    row0 = a;
+    len = b > a ? b - a : 0;
+    if ((long long)a + len > P.d.n_rows) len = P.d.n_rows > a ? (int)(P.d.n_rows - a) : 0;
+  } else {
+    row0 = (long long)doc * P.d.seq_stride;
+    len = P.d.max_len;
+    if (P.d.lens) {
+      int l = P.d.lens[doc];
+      if (P.d_len_flagged) {
+        masked = (l & LEN_FLAG_MASKED) != 0;
+        l &= ~LEN_FLAG_MASKED;
+      }
+      len = l < 0 ? 0 : (l > P.d.max_len ? P.d.max_len : l);
+    }
+  }
+}
+
+#ifdef LIK_TC_PROFILE
+__device__ __forceinline__ void prof_tiles(unsigned long long* prof) { prof[11] += 1; }
+#else
+#define prof_tiles(x)
+#endif
+
+template <bool FP8, bool ARGMAX, bool SCALED>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap d_map, const TcParams P) {
   extern __shared__ unsigned char smem_raw[];
@@ -255,11 +370,11 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
       mbar_init(smem_u32(&ctl->d_full[s]), 1);
       mbar_init(smem_u32(&ctl->d_empty[s]), 1);
     }
-    for (int a = 0; a < 2; ++a) {
+    for (int a = 0; a < 4; ++a) {
       mbar_init(smem_u32(&ctl->acc_full[a]), 1);
-      mbar_init(smem_u32(&ctl->acc_empty[a]), EPI_THREADS);
-      mbar_init(smem_u32(&ctl->wg_bar[a]), EPI_THREADS);
+      mbar_init(smem_u32(&ctl->acc_empty[a]), EPI_WARPS);
     }
+    for (int a = 0; a < 2; ++a) mbar_init(smem_u32(&ctl->wg_bar[a]), EPI_WARPS);
     ctl->abort_flag = 0;
     fence_barrier_init();
     prefetch_tmap(&q_map);
@@ -274,6 +389,25 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
   tc_fence_after();
   const uint32_t tmem_base = ctl->tmem_base;
 
+  // Every role walks the same unit sequence.  The bounds of the next document are fetched one
+  // iteration ahead so that the load latency hides behind the current document's work.
+  long long nx_row0 = 0;
+  int nx_len = 0, nx_grp = 0, nx_doc = 0;
+  bool nx_masked = false;
+  if (u_begin < u_end) {
+    unit_decode(P, u_begin, nx_grp, nx_doc);
+    doc_bounds(P, nx_doc, nx_row0, nx_len, nx_masked);
+  }
+#define LIK_NEXT_UNIT()                                            \
+  const int grp = nx_grp, doc = nx_doc, dlen = nx_len;             \
+  const long long drow0 = nx_row0;                                 \
+  const bool dmasked = nx_masked;                                  \
+  (void)dmasked;                                                   \
+  if (u + 1 < u_end) {                                             \
+    unit_decode(P, u + 1, nx_grp, nx_doc);                         \
+    doc_bounds(P, nx_doc, nx_row0, nx_len, nx_masked);             \
+  }
+
   if (warp == 0) {
     // =========================== TMA producer ===========================
     if (lane == 0) {
@@ -281,13 +415,16 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
       uint32_t n_qload = 0, n_dload = 0;
       const int x_per_slab = SLAB_BYTES_ROW / P.elt_bytes;
       bool ok = true;
+      PROF_DECL();
+      PROF_T0(p_all);
       for (long long u = u_begin; u < u_end && ok; ++u) {
-        int grp, doc;
-        unit_decode(P, u, grp, doc);
+        LIK_NEXT_UNIT();
         if (grp != cur_grp) {
           cur_grp = grp;
           // wait until the MMAs that read the previous query tiles are done
+          PROF_T0(p_q);
           ok = wait_bar(&ctl->q_empty, (n_qload & 1) ^ 1, ctl, P.status);
+          PROF_ADD(2, p_q);
           if (!ok) break;
           const int t0 = grp * P.mt, t1 = min(t0 + P.mt, P.n_tiles);
           mbar_arrive_expect_tx(smem_u32(&ctl->q_full), (uint32_t)((t1 - t0) * q_tile_bytes));
@@ -299,14 +436,13 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
           }
           ++n_qload;
         }
-        long long drow0;
-        int dlen;
-        seq_bounds(P.d, doc, drow0, dlen, nullptr);
         for (int c0 = 0; c0 < dlen; c0 += TILE_N) {
           const int ncols = min(TILE_N, dlen - c0);
           const int boxes = (ncols + BOX_ROWS - 1) / BOX_ROWS;
           const int st = n_dload % P.stages;
+          PROF_T0(p_d);
           ok = wait_bar(&ctl->d_empty[st], ((n_dload / P.stages) & 1) ^ 1, ctl, P.status);
+          PROF_ADD(1, p_d);
           if (!ok) break;
           const uint32_t full = smem_u32(&ctl->d_full[st]);
           mbar_arrive_expect_tx(full, (uint32_t)(boxes * BOX_ROWS * SLAB_BYTES_ROW * P.n_slabs));
@@ -317,6 +453,8 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
           ++n_dload;
         }
       }
+      PROF_ADD(0, p_all);
+      PROF_FLUSH(true);
       if (!ok) {
         // aborting: let the copies already issued land before the CTA goes away
         const uint32_t issued = n_dload < (uint32_t)P.stages ? n_dload : (uint32_t)P.stages;
@@ -341,48 +479,68 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
       long long uc = 0;
       bool ok = true;
       int mt_valid = 0;
+      const uint64_t q_desc0 = smem_desc_sw128(smem_u32(q_smem));
+      PROF_DECL();
+      PROF_T0(m_all);
       for (long long u = u_begin; u < u_end && ok; ++u, ++uc) {
-        int grp, doc;
-        unit_decode(P, u, grp, doc);
+        LIK_NEXT_UNIT();
         if (grp != cur_grp) {
           if (cur_grp >= 0) tc_commit(smem_u32(&ctl->q_empty));  // previous query tiles are free once issued MMAs retire
           cur_grp = grp;
           mt_valid = min(P.mt, P.n_tiles - grp * P.mt);
+          PROF_T0(m_q);
           ok = wait_bar(&ctl->q_full, n_qload & 1, ctl, P.status);
+          PROF_ADD(6, m_q);
           if (!ok) break;
           ++n_qload;
           tc_fence_after();
         }
-        long long drow0;
-        int dlen;
-        seq_bounds(P.d, doc, drow0, dlen, nullptr);
         for (int c0 = 0; c0 < dlen && ok; c0 += TILE_N) {
           const int ncols = min(TILE_N, dlen - c0);
           const int n_mma = (ncols + 15) & ~15;
           const uint32_t idesc = instr_desc(P.ab_format, n_mma);
           const int st = n_dload % P.stages;
+          PROF_T0(m_d);
           ok = wait_bar(&ctl->d_full[st], (n_dload / P.stages) & 1, ctl, P.status);
+          PROF_ADD(4, m_d);
           if (!ok) break;
           tc_fence_after();
+          const uint64_t b_desc0 = smem_desc_sw128(smem_u32(d_smem + (size_t)st * d_stage_bytes));
           for (int m = 0; m < mt_valid; ++m) {
-            const int a = P.mt == 2 ? m : (int)(uc & 1);
-            ok = wait_bar(&ctl->acc_empty[a], (n_acc[a] & 1) ^ 1, ctl, P.status);
+            // each epilogue group owns two accumulators and alternates between them, so the MMAs of
+            // the next tile run while the previous tile is still being drained
+            const int g = P.mt == 2 ? m : (int)(uc & 1);
+            const int a = g * ACC_PER_GROUP + (int)(n_acc[g] % ACC_PER_GROUP);
+            PROF_T0(m_a);
+            ok = wait_bar(&ctl->acc_empty[a], ((n_acc[g] / ACC_PER_GROUP) & 1) ^ 1, ctl, P.status);
+            PROF_ADD(5, m_a);
             if (!ok) break;
             tc_fence_after();
             const uint32_t d_tmem = tmem_base + (uint32_t)(a * TILE_N);
-            for (int ks = 0; ks < P.k_steps; ++ks) {
-              const int sl = ks >> 2, kk = ks & 3;
-              const uint32_t a_addr = smem_u32(q_smem + m * q_tile_bytes + sl * TILE_M * SLAB_BYTES_ROW) + kk * 32;
-              const uint32_t b_addr = smem_u32(d_smem + (size_t)st * d_stage_bytes + sl * TILE_N * SLAB_BYTES_ROW) + kk * 32;
-              tc_mma<FP8>(d_tmem, smem_desc_sw128(a_addr), smem_desc_sw128(b_addr), idesc, ks > 0 ? 1u : 0u);
+            // descriptors differ only in the 16-byte-unit start address: add offsets to a base descriptor
+            uint64_t a_desc = q_desc0 + (uint64_t)((m * q_tile_bytes) >> 4);
+            uint64_t b_desc = b_desc0;
+            int left = P.k_steps;
+            uint32_t accum = 0;
+            for (int sl = 0; sl < P.n_slabs; ++sl) {
+              tc_mma<FP8>(d_tmem, a_desc, b_desc, idesc, accum);
+              accum = 1;
+              if (left > 1) tc_mma<FP8>(d_tmem, a_desc + 2, b_desc + 2, idesc, 1u);
+              if (left > 2) tc_mma<FP8>(d_tmem, a_desc + 4, b_desc + 4, idesc, 1u);
+              if (left > 3) tc_mma<FP8>(d_tmem, a_desc + 6, b_desc + 6, idesc, 1u);
+              left -= 4;
+              a_desc += (uint64_t)((TILE_M * SLAB_BYTES_ROW) >> 4);
+              b_desc += (uint64_t)((TILE_N * SLAB_BYTES_ROW) >> 4);
             }
             tc_commit(smem_u32(&ctl->acc_full[a]));
-            ++n_acc[a];
+            ++n_acc[g];
           }
           tc_commit(smem_u32(&ctl->d_empty[st]));  // ring slot reusable once these MMAs retire
           ++n_dload;
         }
       }
+      PROF_ADD(3, m_all);
+      PROF_FLUSH(true);
     }
   } else {
     // =========================== epilogue groups ===========================
@@ -397,13 +555,23 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
     long long uc = 0;
     bool ok = true;
     // per-row state for the resident query tile
-    bool have_tile = false, in_seg = false, row_ok = false;
+    bool have_tile = false, in_seg = false, row_ok = false, aligned = false;
     int my_q = 0, my_s = 0;
     float my_qf = 1.f;
     int tile_id = 0;
+    // one group-wide rendezvous (bounded)
+#define LIK_WG_SYNC()                                             \
+  do {                                                            \
+    __syncwarp();                                                 \
+    if (lane == 0) mbar_arrive(smem_u32(&ctl->wg_bar[wg]));       \
+    ok = wait_bar(&ctl->wg_bar[wg], n_wg & 1, ctl, P.status);     \
+    ++n_wg;                                                       \
+  } while (0)
+
+    PROF_DECL();
+    PROF_T0(e_all);
     for (long long u = u_begin; u < u_end && ok; ++u, ++uc) {
-      int grp, doc;
-      unit_decode(P, u, grp, doc);
+      LIK_NEXT_UNIT();
       const int acc = P.mt == 2 ? wg : (int)(uc & 1);
       if (grp != cur_grp) {
         cur_grp = grp;
@@ -411,59 +579,54 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
         const int m = P.mt == 2 ? wg : 0;
         tile_id = grp * P.mt + m;
         have_tile = tile_id < P.n_tiles;
-        // everyone in the group must be done reading the old table
-        mbar_arrive(smem_u32(&ctl->wg_bar[wg]));
-        ok = wait_bar(&ctl->wg_bar[wg], n_wg & 1, ctl, P.status);
-        ++n_wg;
+        LIK_WG_SYNC();  // everyone in the group is done reading the old table
         if (!ok) break;
+        TileInfo ti{};
+        int nseg = 0;
         if (have_tile) {
-          TileInfo ti = tile_info(P, tile_id);
-          const int nseg = ti.qb - ti.qa;
+          ti = tile_info(P, tile_id);
+          nseg = ti.qb - ti.qa;
           ctl->row_seg[wg][et] = -1;
-          if (et == 0) ctl->n_seg[wg] = nseg;
-        }
-        mbar_arrive(smem_u32(&ctl->wg_bar[wg]));
-        ok = wait_bar(&ctl->wg_bar[wg], n_wg & 1, ctl, P.status);
-        ++n_wg;
-        if (!ok) break;
-        if (have_tile) {
-          TileInfo ti = tile_info(P, tile_id);
-          const int nseg = ti.qb - ti.qa;
-          if (et < nseg) {
-            long long r0;
-            int len;
-            seq_bounds(P.q, ti.qa + et, r0, len, P.status);
-            int off, l;
-            if (P.q_chunks == 1) {
-              off = (int)(r0 - ti.row0);
-              l = len;
-              if (off + l > TILE_M) {  // max_len was smaller than a real query: report, stay in bounds
-                l = max(0, TILE_M - off);
-                if (P.status) atomicOr(P.status, LIK_DEV_LEN_RANGE);
-              }
-            } else {
-              off = 0;
-              l = min(TILE_M, max(0, len - ti.chunk * TILE_M));
-              if (len > P.q_chunks * TILE_M && P.status) atomicOr(P.status, LIK_DEV_LEN_RANGE);
-            }
-            ctl->seg_off[wg][et] = off;
-            ctl->seg_len[wg][et] = l;
-            ctl->seg_q[wg][et] = ti.qa + et;
-            for (int i = 0; i < l; ++i) ctl->row_seg[wg][off + i] = (short)et;
+          if (et == 0) {
+            ctl->n_seg[wg] = nseg;
+            ctl->warp_aligned[wg] = P.q_chunks == 1 ? 1 : 0;
           }
         }
-        mbar_arrive(smem_u32(&ctl->wg_bar[wg]));
-        ok = wait_bar(&ctl->wg_bar[wg], n_wg & 1, ctl, P.status);
-        ++n_wg;
+        LIK_WG_SYNC();
+        if (!ok) break;
+        if (have_tile && et < nseg) {
+          long long r0;
+          int len;
+          seq_bounds(P.q, ti.qa + et, r0, len, P.status);
+          int off, l;
+          if (P.q_chunks == 1) {
+            off = (int)(r0 - ti.row0);
+            l = len;
+            if (off + l > TILE_M) {  // max_len was smaller than a real query: report, stay in bounds
+              l = max(0, TILE_M - off);
+              if (P.status) atomicOr(P.status, LIK_DEV_LEN_RANGE);
+            }
+          } else {
+            off = 0;
+            l = min(TILE_M, max(0, len - ti.chunk * TILE_M));
+            if (len > P.q_chunks * TILE_M && P.status) atomicOr(P.status, LIK_DEV_LEN_RANGE);
+          }
+          if ((off & 31) != 0 || l > 32) ctl->warp_aligned[wg] = 0;
+          ctl->seg_off[wg][et] = off;
+          ctl->seg_len[wg][et] = l;
+          ctl->seg_q[wg][et] = ti.qa + et;
+          for (int i = 0; i < l; ++i) ctl->row_seg[wg][off + i] = (short)et;
+        }
+        LIK_WG_SYNC();
         if (!ok) break;
         in_seg = false;
         row_ok = false;
+        aligned = have_tile && ctl->warp_aligned[wg] != 0;
         if (have_tile) {
           const int sg = ctl->row_seg[wg][row];
           if (sg >= 0) {
             in_seg = true;
             my_q = ctl->seg_q[wg][sg];
-            TileInfo ti = tile_info(P, tile_id);
             my_s = row - ctl->seg_off[wg][sg] + ti.chunk * TILE_M;
             const long long qrow = ti.row0 + row;
             row_ok = row_valid(P.q, qrow);
@@ -476,68 +639,77 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
       const bool mine = P.mt == 2 ? have_tile : (acc == wg);
       if (!mine) continue;
 
-      long long drow0;
-      int dlen;
-      seq_bounds(P.d, doc, drow0, dlen, nullptr);
+      const bool use_cols = SCALED || dmasked;  // per-column multiplier / additive mask needed for this document
       float run_m = -INFINITY;
       int run_i = -1;
       for (int c0 = 0; c0 < dlen && ok; c0 += TILE_N) {
         const int ncols = min(TILE_N, dlen - c0);
-        if (AFFINE) {
-          // per-column multiplier and additive mask for this tile (two columns per thread)
-          mbar_arrive(smem_u32(&ctl->wg_bar[wg]));  // previous tile's readers are done
-          ok = wait_bar(&ctl->wg_bar[wg], n_wg & 1, ctl, P.status);
-          ++n_wg;
+        if (use_cols) {
+          LIK_WG_SYNC();  // the previous tile's readers are done with the column arrays
           if (!ok) break;
-          for (int c = et; c < ncols; c += EPI_THREADS) {
-            const long long drow = drow0 + c0 + c;
-            ctl->col_scale[wg][c] = row_factor(P.d, drow);
-            ctl->col_bias[wg][c] = row_valid(P.d, drow) ? 0.f : -INFINITY;
+          for (int c = et; c < ((ncols + 31) & ~31); c += EPI_THREADS) {
+            float sc = 1.f, bi = -INFINITY;
+            if (c < ncols) {
+              const long long drow = drow0 + c0 + c;
+              sc = row_factor(P.d, drow);
+              bi = row_valid(P.d, drow) ? 0.f : -INFINITY;
+            }
+            ctl->col_scale[wg][c] = sc;
+            ctl->col_bias[wg][c] = bi;
           }
-          mbar_arrive(smem_u32(&ctl->wg_bar[wg]));
-          ok = wait_bar(&ctl->wg_bar[wg], n_wg & 1, ctl, P.status);
-          ++n_wg;
+          LIK_WG_SYNC();
           if (!ok) break;
         }
-        ok = wait_bar(&ctl->acc_full[acc], n_acc & 1, ctl, P.status);
+        const int abuf = wg * ACC_PER_GROUP + (int)(n_acc % ACC_PER_GROUP);
+        PROF_T0(e_w);
+        ok = wait_bar(&ctl->acc_full[abuf], (n_acc / ACC_PER_GROUP) & 1, ctl, P.status);
+        PROF_ADD(8, e_w);
+        prof_tiles(prof);
+        PROF_T0(e_f);
         if (!ok) break;
         ++n_acc;
         tc_fence_after();
-        const uint32_t taddr = lane_addr + (uint32_t)(acc * TILE_N);
+        const uint32_t taddr = lane_addr + (uint32_t)(abuf * TILE_N);
         for (int cc = 0; cc < ncols; cc += 32) {
+          uint32_t r[32];
           float v[32];
-          tmem_ld32(taddr + (uint32_t)cc, v);
-          const int lim = ncols - cc;  // valid columns in this chunk (>= 1)
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            float x = v[i];
-            if (AFFINE) x = fmaf(x, ctl->col_scale[wg][cc + i], ctl->col_bias[wg][cc + i]);
-            if (i < lim) {
-              if (ARGMAX || AFFINE) {
-                if (x > run_m) {
-                  run_m = x;
-                  run_i = c0 + cc + i;
-                }
-              } else {
-                run_m = fmaxf(run_m, x);
-              }
-            }
-          }
+          tmem_ld32_issue(taddr + (uint32_t)cc, r);
+          tmem_ld_wait(r);
+          as_floats(r, v);
+          if (use_cols)  // columns past ncols carry bias -inf, so the whole chunk can be folded
+            fold_chunk<ARGMAX, true>(v, 32, c0 + cc, &ctl->col_scale[wg][cc], &ctl->col_bias[wg][cc], run_m, run_i);
+          else
+            fold_chunk<ARGMAX, false>(v, ncols - cc, c0 + cc, nullptr, nullptr, run_m, run_i);
         }
         tc_fence_before();
-        mbar_arrive(smem_u32(&ctl->acc_empty[acc]));
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&ctl->acc_empty[abuf]));
+        PROF_ADD(9, e_f);
       }
       if (!ok) break;
+      PROF_T0(e_e);
       // ---- end of document: one value per row, summed per query in a fixed order ----
-      bool has_winner = (ARGMAX || AFFINE) ? (run_i >= 0) : (run_m != -INFINITY);
+      const bool has_winner = ARGMAX ? (run_i >= 0) : (run_m != -INFINITY);
       const float val = (in_seg && row_ok && has_winner) ? run_m * my_qf : 0.f;
-      const long long slot = P.pairing == LIK_PAIR_CROSS ? (long long)my_q * P.n_d + doc : (long long)doc;
-      if (ARGMAX && in_seg && my_s < P.argmax_stride) P.argmax[slot * P.argmax_stride + my_s] = has_winner ? run_i : -1;
+      if (ARGMAX && in_seg && my_s < P.argmax_stride) {
+        const long long slot = P.pairing == LIK_PAIR_CROSS ? (long long)my_q * P.n_d + doc : (long long)doc;
+        P.argmax[slot * P.argmax_stride + my_s] = has_winner ? run_i : -1;
+      }
+      if (aligned) {
+        // one query per warp: a shuffle tree (fixed order) replaces the shared-memory pass
+        const float sum = warp_sum(val);
+        const int sg0 = ctl->row_seg[wg][quad * 32];
+        if (lane == 0 && sg0 >= 0) {
+          const int qq = ctl->seg_q[wg][sg0];
+          const long long o = P.pairing == LIK_PAIR_CROSS ? (long long)qq * P.n_d + doc : (long long)doc;
+          P.scores[o] = sum;
+        }
+        PROF_ADD(10, e_e);
+        continue;
+      }
       float* ebuf = ctl->emit[wg][n_wg & 1];
       ebuf[row] = val;
-      mbar_arrive(smem_u32(&ctl->wg_bar[wg]));
-      ok = wait_bar(&ctl->wg_bar[wg], n_wg & 1, ctl, P.status);
-      ++n_wg;
+      LIK_WG_SYNC();
       if (!ok) break;
       const int nseg = ctl->n_seg[wg];
       for (int sg = wq; sg < nseg; sg += 4) {
@@ -555,8 +727,13 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
           }
         }
       }
+      PROF_ADD(10, e_e);
     }
+    PROF_ADD(7, e_all);
+    PROF_FLUSH(warp == 2 && lane == 0);
+#undef LIK_WG_SYNC
   }
+#undef LIK_NEXT_UNIT
 
   // ---- teardown (also reached when aborting: every wait above is bounded) ----
   tc_fence_before();
@@ -565,6 +742,30 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
     tc_fence_after();
     tmem_dealloc(tmem_base, 512);
   }
+}
+
+// Effective length of every padded document under its token mask: 1 + index of the last valid
+// token, tagged with LEN_FLAG_MASKED when the valid tokens are not exactly the prefix [0, length).
+__global__ void mask_lens_kernel(const unsigned char* __restrict__ mask, const int* __restrict__ lens, int n_seq, int max_len,
+                                 long long seq_stride, int* __restrict__ out) {
+  const int lane = threadIdx.x & 31;
+  const int j = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (j >= n_seq) return;
+  int len0 = max_len;
+  if (lens) len0 = min(max(lens[j], 0), max_len);
+  const unsigned char* m = mask + (long long)j * seq_stride;
+  int last = -1, cnt = 0;
+  for (int t = lane; t < len0; t += 32)
+    if (m[t]) {
+      last = t;
+      ++cnt;
+    }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    last = max(last, __shfl_xor_sync(0xffffffffu, last, o));
+    cnt += __shfl_xor_sync(0xffffffffu, cnt, o);
+  }
+  if (lane == 0) out[j] = (last + 1) | (cnt != last + 1 ? LEN_FLAG_MASKED : 0);
 }
 
 // scores[q, j] = sum over the chunks of query q, in chunk order
@@ -682,9 +883,14 @@ bool fwd_tc_supported(const lik_fwd_args& a) {
   return get_encode_fn() != nullptr;
 }
 
+static size_t partial_bytes(const TcPlan& pl, const lik_fwd_args& a) {
+  return pl.q_chunks > 1 ? align_up((size_t)pl.n_tiles * a.d.n_seq * sizeof(float), 256) : 0;
+}
+
 size_t fwd_tc_workspace(const lik_fwd_args& a) {
   TcPlan pl = plan_tc(a);
-  return pl.q_chunks > 1 ? (size_t)pl.n_tiles * a.d.n_seq * sizeof(float) : 0;
+  const size_t lens_bytes = (a.d.mask && !a.d.cu) ? align_up((size_t)a.d.n_seq * sizeof(int), 256) : 0;
+  return partial_bytes(pl, a) + lens_bytes;
 }
 
 int launch_fwd_tc(const lik_fwd_args& a, const float* qn, const float* dn, void* ws, size_t ws_bytes, cudaStream_t st) {
@@ -718,10 +924,19 @@ int launch_fwd_tc(const lik_fwd_args& a, const float* qn, const float* dn, void*
   P.n_units = pl.n_units;
   P.scores = a.scores;
   P.partial = pl.q_chunks > 1 ? (float*)ws : nullptr;
+  P.d_len_flagged = 0;
+  if (a.d.mask && !a.d.cu) {
+    // trim every document to its last valid token; only documents with holes pay for per-column masking
+    int* eff = (int*)((char*)ws + partial_bytes(pl, a));
+    mask_lens_kernel<<<(unsigned)ceil_div(a.d.n_seq, 8), 256, 0, st>>>(a.d.mask, a.d.lens, a.d.n_seq, a.d.max_len, a.d.seq_stride, eff);
+    LIK_CUDA_OK(cudaGetLastError());
+    P.d.lens = eff;
+    P.d_len_flagged = 1;
+  }
   P.argmax = a.argmax;
   P.argmax_stride = a.argmax_stride;
   P.status = a.status;
-  if (pl.q_chunks > 1 && ws_bytes < (size_t)pl.n_tiles * a.d.n_seq * sizeof(float)) {
+  if (ws_bytes < fwd_tc_workspace(a)) {
     set_error("tcgen05 forward: workspace too small");
     return LIK_ERR_WORKSPACE;
   }
@@ -732,7 +947,7 @@ int launch_fwd_tc(const lik_fwd_args& a, const float* qn, const float* dn, void*
 
   const bool fp8 = a.dtype == LIK_E4M3;
   const bool argmax = a.argmax != nullptr;
-  const bool affine = a.d.mask || a.d.scale || dn;
+  const bool affine = a.d.scale || dn;  // a per-column multiplier for every document
   long long grid_ll = pl.n_units < sm_count() ? pl.n_units : sm_count();
   if (grid_ll < 1) return LIK_OK;
   dim3 grid((unsigned)grid_ll), block(NUM_THREADS);
@@ -763,3 +978,14 @@ int launch_fwd_tc(const lik_fwd_args& a, const float* qn, const float* dn, void*
 }
 
 }  // namespace lik
+
+#ifdef LIK_TC_PROFILE
+extern "C" int lik_debug_profile(unsigned long long* out_host, int reset) {
+  cudaMemcpyFromSymbol(out_host, lik::g_prof, sizeof(unsigned long long) * 16);
+  if (reset) {
+    unsigned long long z[16] = {0};
+    cudaMemcpyToSymbol(lik::g_prof, z, sizeof(z));
+  }
+  return 0;
+}
+#endif
