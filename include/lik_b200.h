@@ -114,6 +114,31 @@ typedef struct lik_fwd_args {
 size_t lik_maxsim_fwd_workspace(const lik_fwd_args* args);
 int lik_maxsim_fwd(const lik_fwd_args* args, lik_stream_t stream);
 
+/*
+ * lik_maxsim_fwd_static — the same forward for callers that have no way to hand over device
+ * scratch.  (No counterpart in the reference; added for this library.)
+ *
+ * Some embedders of this ABI run inside a host that owns all device memory — a serving runtime
+ * with a fixed memory plan, a plugin sandbox that forbids cudaMalloc, a process that must not touch
+ * the allocator while a CUDA graph pool is live.  They can pass inputs and outputs they were given,
+ * but they cannot allocate the workspace lik_maxsim_fwd asks for.  This entry point takes the same
+ * argument struct, ignores args->workspace / workspace_bytes and uses a scratch array that is part
+ * of the library's device image instead (LIK_STATIC_SCRATCH_BYTES, resident on every GPU that loads
+ * the library until the process exits).  It allocates nothing and frees nothing.
+ *
+ * Limits and rules:
+ *   - problems whose lik_maxsim_fwd_workspace() exceeds LIK_STATIC_SCRATCH_BYTES are refused with
+ *     LIK_ERR_WORKSPACE (roughly: fused L2 norm over more than 4 M token rows, or very long queries
+ *     against very many documents);
+ *   - the first call on each device looks up the array's device address (cudaGetSymbolAddress);
+ *     make that first call outside any stream capture, with the device current;
+ *   - all calls on a device share the one array.  Its previous contents are never relied on (every
+ *     region is rewritten before it is read, nothing needs zeroing), but two calls whose kernels
+ *     overlap on the GPU — different streams, no ordering — would race on it: serialise them.
+ */
+#define LIK_STATIC_SCRATCH_BYTES (16u << 20)
+int lik_maxsim_fwd_static(const lik_fwd_args* args, lik_stream_t stream);
+
 /* ------------------------------------------------------------------------- */
 /* Backward.  Replaces maxsim_backward_unified (backward/unified.py:205-289),   */
 /* maxsim_backward_lowmem (backward/lowmem.py:205-322), the varlen backward     */

@@ -19,6 +19,7 @@ LIK_F32, LIK_F16, LIK_BF16, LIK_E4M3 = 0, 1, 2, 3
 PAIR_CROSS, PAIR_GROUPED, PAIR_LIST = 0, 1, 2
 NORM_NONE, NORM_Q, NORM_D, NORM_BOTH = 0, 1, 2, 3
 TOPK_MAX = 1024
+STATIC_SCRATCH_BYTES = 16 << 20
 
 DEV_STATUS_TEXT = {
     1: "a pair index is outside [0, n_seq)",
@@ -87,6 +88,8 @@ def _declare(lib):
     lib.lik_maxsim_fwd_workspace.restype = sz
     lib.lik_maxsim_fwd.argtypes = [C.POINTER(FwdArgs), vp]
     lib.lik_maxsim_fwd.restype = i32
+    lib.lik_maxsim_fwd_static.argtypes = [C.POINTER(FwdArgs), vp]
+    lib.lik_maxsim_fwd_static.restype = i32
     lib.lik_maxsim_bwd_workspace.argtypes = [C.POINTER(BwdArgs)]
     lib.lik_maxsim_bwd_workspace.restype = sz
     lib.lik_maxsim_bwd.argtypes = [C.POINTER(BwdArgs), vp]
@@ -110,7 +113,7 @@ def _declare(lib):
 
 
 EXPORTED_SYMBOLS = (
-    "lik_maxsim_fwd_workspace", "lik_maxsim_fwd", "lik_maxsim_bwd_workspace", "lik_maxsim_bwd", "lik_topk_rows",
+    "lik_maxsim_fwd_workspace", "lik_maxsim_fwd", "lik_maxsim_fwd_static", "lik_maxsim_bwd_workspace", "lik_maxsim_bwd", "lik_topk_rows",
     "lik_topk_merge", "lik_plaid_decompress", "lik_plaid_approx", "lik_plaid_bwd_dq", "lik_row_inv_norm",
     "lik_last_error", "lik_version", "lik_device_supported",
 )

@@ -1,4 +1,6 @@
 // C-ABI entry points of the forward path and the small utilities.
+#include <mutex>
+
 #include "lik_common.cuh"
 
 namespace lik {
@@ -102,6 +104,56 @@ extern "C" int lik_maxsim_fwd(const lik_fwd_args* a, lik_stream_t stream) {
   }
   if (pl.use_tc) return launch_fwd_tc(*a, qn, dn, ws + pl.tc_off, fwd_tc_workspace(*a), st);
   return launch_fwd_generic(*a, qn, dn, st);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Forward without a caller workspace: the scratch lives in this library's device image.
+// ---------------------------------------------------------------------------------------------
+static __device__ __align__(256) unsigned char g_static_scratch[LIK_STATIC_SCRATCH_BYTES];
+
+namespace {
+constexpr int kMaxDevices = 64;
+void* g_scratch_ptr[kMaxDevices] = {nullptr};
+std::mutex g_scratch_mutex;
+
+// Device address of g_static_scratch on the current device.  In host code the array's name is only
+// a handle; the address a kernel can use comes from cudaGetSymbolAddress, once per device.
+int static_scratch(void** out) {
+  int dev = 0;
+  LIK_CUDA_OK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) {
+    lik::set_error("device ordinal %d not supported by lik_maxsim_fwd_static", dev);
+    return LIK_ERR_UNSUPPORTED;
+  }
+  std::lock_guard<std::mutex> lock(g_scratch_mutex);
+  if (!g_scratch_ptr[dev]) {
+    void* p = nullptr;
+    LIK_CUDA_OK(cudaGetSymbolAddress(&p, g_static_scratch));
+    g_scratch_ptr[dev] = p;
+  }
+  *out = g_scratch_ptr[dev];
+  return LIK_OK;
+}
+}  // namespace
+
+extern "C" int lik_maxsim_fwd_static(const lik_fwd_args* a, lik_stream_t stream) {
+  using namespace lik;
+  LIK_REQUIRE(a != nullptr, "args is NULL");
+  int rc = validate_fwd(*a);
+  if (rc) return rc;
+  const size_t need = plan_fwd(*a).total;
+  if (need > (size_t)LIK_STATIC_SCRATCH_BYTES) {
+    set_error("lik_maxsim_fwd_static: this problem needs %zu bytes of scratch, the built-in buffer holds %zu; "
+              "use lik_maxsim_fwd with a caller workspace", need, (size_t)LIK_STATIC_SCRATCH_BYTES);
+    return LIK_ERR_WORKSPACE;
+  }
+  void* scratch = nullptr;
+  rc = static_scratch(&scratch);
+  if (rc) return rc;
+  lik_fwd_args b = *a;
+  b.workspace = scratch;
+  b.workspace_bytes = LIK_STATIC_SCRATCH_BYTES;
+  return lik_maxsim_fwd(&b, stream);
 }
 
 extern "C" int lik_row_inv_norm(const void* data, int32_t dtype, int64_t n_rows, int32_t dim, int64_t row_stride, float eps,
