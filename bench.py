@@ -156,6 +156,57 @@ def run_reference(args, rank):
     print(json.dumps(line), flush=True)
 
 
+def retrieve_bench(n_docs, world, rank, dev):
+    """Sharded top-k retrieve (BASELINE config 5 shape): `n_docs` documents of U[32,300] tokens, d=128, bf16
+    normalised, split by document over the ranks; 1024 queries x 32 tokens, top_k=100, chunk=4096.
+    Strong scaling: the corpus is fixed, every rank scores its slice, one all-gather + merge."""
+    import torch
+    import torch.distributed as dist
+
+    from late_interaction_kernels_b200 import sharded
+
+    lo, hi = sharded.shard_bounds(n_docs, world, rank)
+    nd, Ld, d, chunk = hi - lo, 300, 128, 4096
+    D = torch.empty((nd, Ld, d), dtype=torch.bfloat16, device=dev)
+    lens = torch.empty(nd, dtype=torch.int64, device=dev)
+    g = torch.Generator(device=dev)
+    for c0 in range(0, nd, chunk):  # chunk-addressable seeds: any rank can regenerate any chunk
+        c1 = min(nd, c0 + chunk)
+        g.manual_seed(1234 + (lo + c0) // chunk)
+        x = torch.randn((c1 - c0, Ld, d), generator=g, device=dev, dtype=torch.float32)
+        D[c0:c1] = torch.nn.functional.normalize(x, dim=-1).to(torch.bfloat16)
+        lens[c0:c1] = torch.randint(32, Ld + 1, (c1 - c0,), generator=g, device=dev)
+    dm = torch.arange(Ld, device=dev)[None, :] < lens[:, None]
+    g.manual_seed(99)
+    Q = torch.nn.functional.normalize(torch.randn((1024, 32, d), generator=g, device=dev), dim=-1).to(torch.bfloat16)
+    valid_tokens = torch.tensor([float(lens.sum())], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(valid_tokens)
+
+    def run():
+        return sharded.retrieve_sharded(Q, D, 100, d_mask=dm, doc_offset=lo, n_docs_total=n_docs, normalize=False, chunk=chunk)
+
+    run()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    reps = 2
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        s, i = run()
+    e1.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1) / reps], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    flops = 2.0 * d * 1024 * 32 * float(valid_tokens.item())
+    return {"metric": "retrieve queries/s", "value": 1024 / (ms * 1e-3), "unit": "queries/s", "ms_per_batch": ms,
+            "n_docs": n_docs, "queries": 1024, "top_k": 100, "chunk": chunk, "scaling": "strong",
+            "tflops_valid": flops / (ms * 1e-3) / 1e12, "best_index_q0": int(i[0, 0])}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -163,6 +214,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--retrieve-docs", type=int, default=1_000_000,
+                    help="corpus size of the sharded top-k retrieve reported under extra.retrieve (0 = skip)")
     ap.add_argument("--only", default=None, choices=["fwd", "fwd_infer", "bwd", "step"],
                     help="profiling aid: launch only this part of the step, --steps times, and print its mean time")
     args = ap.parse_args()
@@ -310,10 +363,15 @@ def main():
         "config": {"workload": WORKLOAD, "parallelism": f"replicas x{world}", "l2": "flushed between steps (256 MB write)",
                    "fwd_flops_per_step": fwd_flops, "bwd_flops_per_step": bwd_flops},
         "e2e": {"value": e2e_val, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
-        "gpu_launches": 3 * args.steps,
+        # per step: mask_lens + fwd_tc (forward), bwd_dq_fast + bwd_dd_sort + bwd_dd_reduce (backward)
+        "gpu_launches": 5 * args.steps,
         "roofline": roofline,
         "clocks": clocks.summary(),
     }
+    if args.retrieve_docs > 0:
+        del Qr, Dr, flush
+        torch.cuda.empty_cache()
+        line["extra"] = {"retrieve": retrieve_bench(args.retrieve_docs, world, rank, dev)}
     if rank == 0:
         if not args.no_cpu_baseline and world == 1:
             sample_q = 16

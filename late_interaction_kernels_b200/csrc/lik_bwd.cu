@@ -438,34 +438,33 @@ __global__ void __launch_bounds__(256) bwd_dq_fast_kernel(BwdParams P) {
 }
 
 // ---------------------------------------------------------------------------------
-// grad_d fast, destination-owned: one CTA (16 warps) per document.
-//   1. every warp histograms the winners of its contiguous slice of (query, token)
-//      entries per document token;
-//   2. a scan turns the histograms into write offsets (token-major, then warp, so
-//      the order inside a token's list is the entry order);
-//   3. the entries are placed (stable counting sort) into a list in shared memory;
-//   4. warps take document tokens round-robin and reduce each token's list in order,
-//      gathering query rows with vector loads; one store per output row.
+// grad_d fast, destination-owned, in two kernels.
+//
+// bwd_dd_sort_kernel, one CTA (16 warps) per document: a stable counting sort of the document's
+// winners by token.
+//   1. every warp histograms the winners of its contiguous slice of (query, token) entries;
+//   2. a scan turns the histograms into write offsets (token-major, then warp, so the order inside
+//      a token's list is the entry order);
+//   3. the entries are placed into the document's slice of a global list as (query row, weight).
+// bwd_dd_reduce_kernel, one warp per document token: reads its list (coalesced), gathers the query
+// rows with independent vector loads, accumulates in list order and stores the row once.
 // ---------------------------------------------------------------------------------
 constexpr int DDS_WARPS = 16;
 
-struct DdsSmem {
-  int* ent;       // [n_entries] sorted entry ids
-  int* hist;      // [DDS_WARPS][ld_pad]
-  int* tok_off;   // [ld_pad + 1]
-  float* gcol;    // [n_qrange]
+struct DdSortOut {
+  int2* pairs;            // [n_scores * lq] (query row, weight bits), grouped by document then token
+  long long* tok_begin;   // [d.n_rows] first list entry of every document row
+  int* tok_cnt;           // [d.n_rows] list length (zero-initialised by the launcher)
 };
 
-template <typename T, typename G, int CH>
-__global__ void __launch_bounds__(DDS_WARPS * 32) bwd_dd_sorted_kernel(BwdParams P, int ld_pad, int e_cap) {
+__global__ void __launch_bounds__(DDS_WARPS * 32) bwd_dd_sort_kernel(BwdParams P, DdSortOut O, int ld_pad) {
   extern __shared__ int dds_raw[];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int j = blockIdx.x;
   long long drow0;
   int dlen;
   seq_bounds(P.d, j, drow0, dlen, nullptr);
-  const int d_rows = P.d.cu ? dlen : P.d.max_len;
-  if (d_rows <= 0) return;
+  if (dlen <= 0) return;
   if (dlen >= ld_pad) {  // max_len understated the longest document: report instead of overrunning shared memory
     if (tid == 0 && P.status) atomicOr(P.status, LIK_DEV_LEN_RANGE);
     return;
@@ -480,10 +479,10 @@ __global__ void __launch_bounds__(DDS_WARPS * 32) bwd_dd_sorted_kernel(BwdParams
   }
   const int lq = P.argmax_stride;
   const int n_ent = (i_end - i_begin) * lq;
-  int* ent = dds_raw;
-  int* hist = ent + e_cap;
-  int* tok_off = hist + DDS_WARPS * ld_pad;
-  float* gcol = reinterpret_cast<float*>(tok_off + ld_pad + 1);
+  const long long base = (long long)j * n_ent;  // every document has the same number of entries
+  int* hist = dds_raw;                          // [DDS_WARPS][ld_pad]
+  int* tok_off = hist + DDS_WARPS * ld_pad;     // [ld_pad + 1]
+  float* gcol = reinterpret_cast<float*>(tok_off + ld_pad + 1);  // [i_end - i_begin]
 
   for (int x = tid; x < DDS_WARPS * ld_pad; x += blockDim.x) hist[x] = 0;
   for (int x = tid; x < i_end - i_begin; x += blockDim.x) {
@@ -496,23 +495,35 @@ __global__ void __launch_bounds__(DDS_WARPS * 32) bwd_dd_sorted_kernel(BwdParams
   const int per_warp = ((n_ent + DDS_WARPS - 1) / DDS_WARPS + 31) & ~31;
   const int e_lo = warp * per_warp, e_hi = min(n_ent, e_lo + per_warp);
 
-  auto winner = [&](int e) -> int {
-    // token this entry points at, or -1 when it contributes nothing
+  // raw saved winner of entry e (no validation): a plain load that can be issued ahead of its use
+  auto raw_winner = [&](int e) -> int {
+    if (e >= e_hi) return -1;
     const int ii = e / lq, s = e - ii * lq;
-    const int i = i_begin + ii;
-    const long long p = P.pm.pairing == LIK_PAIR_CROSS ? (long long)i * P.pm.n_d + j : (long long)j;
-    const int t = P.argmax[p * lq + s];
+    const long long p = P.pm.pairing == LIK_PAIR_CROSS ? (long long)(i_begin + ii) * P.pm.n_d + j : (long long)j;
+    return __ldg(P.argmax + p * lq + s);
+  };
+  // validate a raw winner: -1 when the entry contributes nothing
+  auto checked = [&](int e, int t, int& qrow_out) -> int {
     if (t < 0 || t >= dlen) return -1;
+    const int ii = e / lq, s = e - ii * lq;
     long long qrow0;
     int qlen;
-    seq_bounds(P.q, i, qrow0, qlen, nullptr);
+    seq_bounds(P.q, i_begin + ii, qrow0, qlen, nullptr);
     if (s >= qlen || !row_valid(P.q, qrow0 + s)) return -1;
+    qrow_out = (int)(qrow0 + s);
     return t;
   };
 
-  for (int e = e_lo + lane; e < e_hi; e += 32) {
-    const int t = winner(e);
-    if (t >= 0) atomicAdd(&hist[warp * ld_pad + t], 1);
+  for (int e = e_lo + lane; e < e_hi; e += 128) {
+    int t4[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) t4[u] = raw_winner(e + 32 * u);
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      int qr;
+      const int t = checked(e + 32 * u, t4[u], qr);
+      if (t >= 0) atomicAdd(&hist[warp * ld_pad + t], 1);
+    }
   }
   __syncthreads();
   // offsets: warp 0 scans the tokens; hist[w][t] becomes the first write position of warp w for token t
@@ -531,86 +542,103 @@ __global__ void __launch_bounds__(DDS_WARPS * 32) bwd_dd_sorted_kernel(BwdParams
       }
       const int excl = running + incl - tot;
       if (t < dlen) {
-        tok_off[t] = excl;
-        int base = excl;
+        O.tok_begin[drow0 + t] = base + excl;
+        O.tok_cnt[drow0 + t] = tot;
+        int b = excl;
         for (int w = 0; w < DDS_WARPS; ++w) {
           const int c = hist[w * ld_pad + t];
-          hist[w * ld_pad + t] = base;
-          base += c;
+          hist[w * ld_pad + t] = b;
+          b += c;
         }
       }
       running += __shfl_sync(0xffffffffu, incl, 31);
     }
-    if (lane == 0) tok_off[dlen] = running;
   }
   __syncthreads();
   // stable placement
+  int t_next = raw_winner(e_lo + lane);
   for (int eb = e_lo; eb < e_hi; eb += 32) {
     const int e = eb + lane;
-    const int t = e < e_hi ? winner(e) : -1;
+    int qrow = 0;
+    const int t_raw = t_next;
+    t_next = raw_winner(e + 32);  // in flight while this round is placed
+    const int t = e < e_hi ? checked(e, t_raw, qrow) : -1;
     const unsigned peers = __match_any_sync(0xffffffffu, t);
     if (t >= 0) {
       const int rank = __popc(peers & ((1u << lane) - 1u));
       const int pos = hist[warp * ld_pad + t] + rank;
-      ent[pos] = e;
+      const float w = gcol[e / lq] * row_factor(P.q, qrow);
+      O.pairs[base + pos] = make_int2(qrow, __float_as_int(w));
     }
     __syncwarp();
     if (t >= 0 && (peers & ((1u << lane) - 1u)) == 0) hist[warp * ld_pad + t] += __popc(peers);
     __syncwarp();
   }
-  __syncthreads();
+}
 
+template <typename T, typename G, int CH>
+__global__ void __launch_bounds__(256) bwd_dd_reduce_kernel(BwdParams P, DdSortOut O) {
+  const int lane = threadIdx.x & 31;
+  const long long drow = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (drow >= P.d.n_rows) return;
+  float acc[CH][4];
+#pragma unroll
+  for (int c = 0; c < CH; ++c)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) acc[c][e] = 0.f;
+  const int cnt = O.tok_cnt[drow];
   const T* __restrict__ Qg = (const T*)P.q.data;
-  const bool q_factor = P.q.inv_norm || P.q.scale || P.q.scale_scalar != 1.f;
-  for (int t = warp; t < d_rows; t += DDS_WARPS) {
-    float acc[CH][4];
+  if (cnt > 0) {
+    const int2* list = O.pairs + O.tok_begin[drow];
+    for (int k0 = 0; k0 < cnt; k0 += 32) {
+      const int n = min(32, cnt - k0);
+      int2 mine = make_int2(0, 0);
+      if (lane < n) mine = list[k0 + lane];
+      // gather in groups of 8 independent row loads, accumulate in list order
+      for (int k = 0; k < n; k += 8) {
+        float v[8][CH][4];
+        float w[8];
 #pragma unroll
-    for (int c = 0; c < CH; ++c)
+        for (int u = 0; u < 8; ++u) {
+          const int row = __shfl_sync(0xffffffffu, mine.x, (k + u) & 31);
+          w[u] = __int_as_float(__shfl_sync(0xffffffffu, mine.y, (k + u) & 31));
+          if (k + u >= n) w[u] = 0.f;  // row 0 is a valid address; its weight is zero
+          const T* src = Qg + (long long)(k + u < n ? row : 0) * P.q.row_stride;
 #pragma unroll
-      for (int e = 0; e < 4; ++e) acc[c][e] = 0.f;
-    if (t < dlen) {
-      const int lo = tok_off[t], hi = tok_off[t + 1];
-#pragma unroll 4
-      for (int k = lo; k < hi; ++k) {
-        const int e = ent[k];
-        const int ii = e / lq, s = e - ii * lq;
-        long long qrow0;
-        int qlen;
-        seq_bounds(P.q, i_begin + ii, qrow0, qlen, nullptr);
-        const long long qrow = qrow0 + s;
-        float f = gcol[ii];
-        if (q_factor) f *= row_factor(P.q, qrow);
-        const T* src = Qg + qrow * P.q.row_stride;
-#pragma unroll
-        for (int c = 0; c < CH; ++c) {
-          const int kk = c * 128 + lane * 4;
-          if (kk < P.dim) {
-            float v[4];
-            load4<T>(src + kk, v);
-#pragma unroll
-            for (int x = 0; x < 4; ++x) acc[c][x] = fmaf(f, v[x], acc[c][x]);
+          for (int c = 0; c < CH; ++c) {
+            const int kk = c * 128 + lane * 4;
+            if (kk < P.dim) load4<T>(src + kk, v[u][c]);
           }
         }
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+#pragma unroll
+          for (int c = 0; c < CH; ++c) {
+            const int kk = c * 128 + lane * 4;
+            if (kk < P.dim) {
+#pragma unroll
+              for (int x = 0; x < 4; ++x) acc[c][x] = fmaf(w[u], v[u][c][x], acc[c][x]);
+            }
+          }
       }
     }
-    const long long drow = drow0 + t;
-    if (P.normalize) {
-      normalize_jacobian_row<T, CH>(acc, (const T*)P.d.data + drow * P.d.row_stride, P.d.inv_norm[drow], P.dim, lane);
-    } else {
-      const float df = P.d.scale_scalar * (P.d.scale ? P.d.scale[drow] : 1.f);
-      if (df != 1.f) {
+  }
+  if (P.normalize) {
+    normalize_jacobian_row<T, CH>(acc, (const T*)P.d.data + drow * P.d.row_stride, P.d.inv_norm[drow], P.dim, lane);
+  } else {
+    const float df = P.d.scale_scalar * (P.d.scale ? P.d.scale[drow] : 1.f);
+    if (df != 1.f) {
 #pragma unroll
-        for (int c = 0; c < CH; ++c)
+      for (int c = 0; c < CH; ++c)
 #pragma unroll
-          for (int x = 0; x < 4; ++x) acc[c][x] *= df;
-      }
+        for (int x = 0; x < 4; ++x) acc[c][x] *= df;
     }
-    G* out = (G*)P.grad_d + drow * P.dim;
+  }
+  G* out = (G*)P.grad_d + drow * P.dim;
 #pragma unroll
-    for (int c = 0; c < CH; ++c) {
-      const int kk = c * 128 + lane * 4;
-      if (kk < P.dim) store4<G>(out + kk, acc[c]);
-    }
+  for (int c = 0; c < CH; ++c) {
+    const int kk = c * 128 + lane * 4;
+    if (kk < P.dim) store4<G>(out + kk, acc[c]);
   }
 }
 
@@ -677,8 +705,19 @@ int launch_row_inv_norm(const void* data, int dtype, long long n_rows, int dim, 
 namespace {
 
 struct BwdPlan {
-  size_t qn_off, dn_off, gq32_off, gd32_off, total;
+  size_t qn_off, dn_off, gq32_off, gd32_off, pairs_off, begin_off, cnt_off, total;
+  bool fast, sorted;
+  int ld_pad;
+  size_t sort_smem;
 };
+
+bool bwd_fast_ok(const lik_bwd_args& a) {
+  // vector fast paths: rows 8/16-byte aligned, width a multiple of 4 and at most 256
+  const size_t eb = dtype_size(a.dtype);
+  return a.dim % 4 == 0 && a.dim <= 256 && (a.q.row_stride * eb) % (4 * eb) == 0 && (a.d.row_stride * eb) % (4 * eb) == 0 &&
+         ((uintptr_t)a.q.data % (4 * eb)) == 0 && ((uintptr_t)a.d.data % (4 * eb)) == 0 && ((uintptr_t)a.grad_q % 16) == 0 &&
+         ((uintptr_t)a.grad_d % 16) == 0;
+}
 
 BwdPlan plan_bwd(const lik_bwd_args& a) {
   BwdPlan pl{};
@@ -688,7 +727,9 @@ BwdPlan plan_bwd(const lik_bwd_args& a) {
     off = align_up(off + bytes, 256);
     return o;
   };
-  pl.qn_off = pl.dn_off = pl.gq32_off = pl.gd32_off = (size_t)-1;
+  pl.qn_off = pl.dn_off = pl.gq32_off = pl.gd32_off = pl.pairs_off = pl.begin_off = pl.cnt_off = (size_t)-1;
+  pl.fast = bwd_fast_ok(a);
+  pl.sorted = false;
   if (a.normalize) {
     pl.qn_off = take((size_t)a.q.n_rows * 4);
     pl.dn_off = take((size_t)a.d.n_rows * 4);
@@ -696,6 +737,19 @@ BwdPlan plan_bwd(const lik_bwd_args& a) {
   const bool list = a.pairing == LIK_PAIR_LIST;
   if (a.grad_q && list) pl.gq32_off = take((size_t)a.q.n_rows * a.dim * 4);
   if (a.grad_d && (list || !a.deterministic)) pl.gd32_off = take((size_t)a.d.n_rows * a.dim * 4);
+  if (a.grad_d && !list && a.deterministic && pl.fast && a.d.n_seq > 0 && a.d.max_len > 0 && a.d.n_rows < (1ll << 31) &&
+      a.q.n_rows < (1ll << 31)) {
+    const long long n_qrange = a.pairing == LIK_PAIR_CROSS ? a.q.n_seq : 1;
+    pl.ld_pad = a.d.max_len + 1;
+    pl.sort_smem = ((size_t)DDS_WARPS * pl.ld_pad + pl.ld_pad + 1 + (size_t)n_qrange) * 4;
+    if (pl.sort_smem <= 200 * 1024) {
+      pl.sorted = true;
+      const long long n_ent = n_scores_of(a.pairing, a.q.n_seq, a.d.n_seq, a.n_pairs) * (long long)a.argmax_stride;
+      pl.pairs_off = take((size_t)n_ent * sizeof(int2));
+      pl.begin_off = take((size_t)a.d.n_rows * sizeof(long long));
+      pl.cnt_off = take((size_t)a.d.n_rows * sizeof(int));
+    }
+  }
   pl.total = off;
   return pl;
 }
@@ -717,11 +771,7 @@ int run_bwd(const lik_bwd_args& a, BwdParams& P, const BwdPlan& pl, cudaStream_t
       KERNEL<T, G, 32><<<GRID, 256, 0, st>>>(__VA_ARGS__);                       \
   } while (0)
 
-  // vector fast paths: rows 8/16-byte aligned, width a multiple of 4 and at most 256
-  const size_t eb = dtype_size(a.dtype);
-  const bool fast = a.dim % 4 == 0 && a.dim <= 256 && (a.q.row_stride * eb) % (4 * eb) == 0 &&
-                    (a.d.row_stride * eb) % (4 * eb) == 0 && ((uintptr_t)a.q.data % (4 * eb)) == 0 &&
-                    ((uintptr_t)a.d.data % (4 * eb)) == 0 && ((uintptr_t)a.grad_q % 16) == 0 && ((uintptr_t)a.grad_d % 16) == 0;
+  const bool fast = pl.fast;
   if (a.grad_q && !list && a.q.n_seq > 0 && a.q.max_len > 0) {
     dim3 grid((unsigned)a.q.n_seq, (unsigned)ceil_div(a.q.max_len, 8));
     if (fast) {
@@ -735,20 +785,20 @@ int run_bwd(const lik_bwd_args& a, BwdParams& P, const BwdPlan& pl, cudaStream_t
     LIK_CUDA_OK(cudaGetLastError());
   }
   if (a.grad_d && !list && a.deterministic && a.d.n_seq > 0 && a.d.max_len > 0) {
-    // sorted kernel needs the winner list of one document in shared memory
-    const long long n_ent = (long long)(a.pairing == LIK_PAIR_CROSS ? a.q.n_seq : 1) * a.argmax_stride;
-    const int ld_pad = a.d.max_len + 1;
-    const long long n_qrange = a.pairing == LIK_PAIR_CROSS ? a.q.n_seq : 1;
-    const size_t smem = ((size_t)n_ent + (size_t)DDS_WARPS * ld_pad + ld_pad + 1 + n_qrange) * 4;
-    if (fast && smem <= 200 * 1024) {
-      dim3 grid((unsigned)a.d.n_seq);
-      if (a.dim <= 128) {
-        LIK_CUDA_OK(cudaFuncSetAttribute(bwd_dd_sorted_kernel<T, G, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        bwd_dd_sorted_kernel<T, G, 1><<<grid, DDS_WARPS * 32, smem, st>>>(P, ld_pad, (int)n_ent);
-      } else {
-        LIK_CUDA_OK(cudaFuncSetAttribute(bwd_dd_sorted_kernel<T, G, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        bwd_dd_sorted_kernel<T, G, 2><<<grid, DDS_WARPS * 32, smem, st>>>(P, ld_pad, (int)n_ent);
-      }
+    if (pl.sorted) {
+      DdSortOut O;
+      O.pairs = (int2*)(ws + pl.pairs_off);
+      O.tok_begin = (long long*)(ws + pl.begin_off);
+      O.tok_cnt = (int*)(ws + pl.cnt_off);
+      LIK_CUDA_OK(cudaMemsetAsync(O.tok_cnt, 0, (size_t)a.d.n_rows * sizeof(int), st));
+      LIK_CUDA_OK(cudaFuncSetAttribute(bwd_dd_sort_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.sort_smem));
+      bwd_dd_sort_kernel<<<(unsigned)a.d.n_seq, DDS_WARPS * 32, pl.sort_smem, st>>>(P, O, pl.ld_pad);
+      LIK_CUDA_OK(cudaGetLastError());
+      const unsigned rgrid = (unsigned)ceil_div(a.d.n_rows, 8);
+      if (a.dim <= 128)
+        bwd_dd_reduce_kernel<T, G, 1><<<rgrid, 256, 0, st>>>(P, O);
+      else
+        bwd_dd_reduce_kernel<T, G, 2><<<rgrid, 256, 0, st>>>(P, O);
     } else {
       dim3 grid((unsigned)a.d.n_seq, (unsigned)ceil_div(a.d.max_len, DD_TOK));
       LIK_BY_CMAX(bwd_dd_owned_kernel, grid, P);

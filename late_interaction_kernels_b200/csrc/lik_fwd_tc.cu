@@ -127,6 +127,16 @@ __device__ __forceinline__ void tmem_ld_wait(uint32_t (&r)[32]) {
                :
                : "memory");
 }
+// 64-column variant: one TMEM round trip per 64 columns.
+__device__ __forceinline__ void tmem_ld64_issue(uint32_t taddr, uint32_t (&r)[64]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x64.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32, %33, %34, %35, %36, %37, %38, %39, %40, %41, %42, %43, %44, %45, %46, %47, %48, %49, %50, %51, %52, %53, %54, %55, %56, %57, %58, %59, %60, %61, %62, %63}, [%64];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31]), "=r"(r[32]), "=r"(r[33]), "=r"(r[34]), "=r"(r[35]), "=r"(r[36]), "=r"(r[37]), "=r"(r[38]), "=r"(r[39]), "=r"(r[40]), "=r"(r[41]), "=r"(r[42]), "=r"(r[43]), "=r"(r[44]), "=r"(r[45]), "=r"(r[46]), "=r"(r[47]), "=r"(r[48]), "=r"(r[49]), "=r"(r[50]), "=r"(r[51]), "=r"(r[52]), "=r"(r[53]), "=r"(r[54]), "=r"(r[55]), "=r"(r[56]), "=r"(r[57]), "=r"(r[58]), "=r"(r[59]), "=r"(r[60]), "=r"(r[61]), "=r"(r[62]), "=r"(r[63])
+               : "r"(taddr)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_ld64_wait(uint32_t (&r)[64]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;" : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]), "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]), "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]), "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31]), "+r"(r[32]), "+r"(r[33]), "+r"(r[34]), "+r"(r[35]), "+r"(r[36]), "+r"(r[37]), "+r"(r[38]), "+r"(r[39]), "+r"(r[40]), "+r"(r[41]), "+r"(r[42]), "+r"(r[43]), "+r"(r[44]), "+r"(r[45]), "+r"(r[46]), "+r"(r[47]), "+r"(r[48]), "+r"(r[49]), "+r"(r[50]), "+r"(r[51]), "+r"(r[52]), "+r"(r[53]), "+r"(r[54]), "+r"(r[55]), "+r"(r[56]), "+r"(r[57]), "+r"(r[58]), "+r"(r[59]), "+r"(r[60]), "+r"(r[61]), "+r"(r[62]), "+r"(r[63]) : : "memory");
+}
 __device__ __forceinline__ void as_floats(const uint32_t (&r)[32], float (&v)[32]) {
 #pragma unroll
   for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
@@ -227,6 +237,7 @@ struct TcParams {
   int* argmax;
   int argmax_stride;
   int* status;
+  const int* tile_q0;  // packed queries: tile m holds queries [tile_q0[m], tile_q0[m+1]); tile_q0[-1] is the tile count
   int d_len_flagged;  // d.lens carries LEN_FLAG_MASKED on documents whose mask is not a plain prefix
 };
 
@@ -287,7 +298,11 @@ struct TileInfo {
 
 __device__ __forceinline__ TileInfo tile_info(const TcParams& P, int tile) {
   TileInfo t;
-  if (P.q_chunks == 1) {
+  if (P.tile_q0) {
+    t.qa = P.tile_q0[tile];
+    t.qb = P.tile_q0[tile + 1];
+    t.chunk = 0;
+  } else if (P.q_chunks == 1) {
     t.qa = tile * P.q_per_tile;
     t.qb = min(t.qa + P.q_per_tile, P.n_q);
     t.chunk = 0;
@@ -360,8 +375,11 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
   // contiguous range of work units for this CTA
-  const long long u_begin = P.n_units * (long long)blockIdx.x / gridDim.x;
-  const long long u_end = P.n_units * (long long)(blockIdx.x + 1) / gridDim.x;
+  // greedy-packed query tiles are counted on the device (the count sits in front of the table)
+  const int n_tiles = P.tile_q0 ? P.tile_q0[-1] : P.n_tiles;
+  const long long n_units = P.tile_q0 ? (long long)((n_tiles + P.mt - 1) / P.mt) * P.n_d : P.n_units;
+  const long long u_begin = n_units * (long long)blockIdx.x / gridDim.x;
+  const long long u_end = n_units * (long long)(blockIdx.x + 1) / gridDim.x;
 
   if (tid == 0) {
     mbar_init(smem_u32(&ctl->q_full), 1);
@@ -426,7 +444,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
           ok = wait_bar(&ctl->q_empty, (n_qload & 1) ^ 1, ctl, P.status);
           PROF_ADD(2, p_q);
           if (!ok) break;
-          const int t0 = grp * P.mt, t1 = min(t0 + P.mt, P.n_tiles);
+          const int t0 = grp * P.mt, t1 = min(t0 + P.mt, n_tiles);
           mbar_arrive_expect_tx(smem_u32(&ctl->q_full), (uint32_t)((t1 - t0) * q_tile_bytes));
           for (int t = t0; t < t1; ++t) {
             TileInfo ti = tile_info(P, t);
@@ -487,7 +505,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
         if (grp != cur_grp) {
           if (cur_grp >= 0) tc_commit(smem_u32(&ctl->q_empty));  // previous query tiles are free once issued MMAs retire
           cur_grp = grp;
-          mt_valid = min(P.mt, P.n_tiles - grp * P.mt);
+          mt_valid = min(P.mt, n_tiles - grp * P.mt);
           PROF_T0(m_q);
           ok = wait_bar(&ctl->q_full, n_qload & 1, ctl, P.status);
           PROF_ADD(6, m_q);
@@ -578,7 +596,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
         // (re)build the segment table of this group's tile `wg` (mt == 2) or tile 0 (mt == 1: both groups)
         const int m = P.mt == 2 ? wg : 0;
         tile_id = grp * P.mt + m;
-        have_tile = tile_id < P.n_tiles;
+        have_tile = tile_id < n_tiles;
         LIK_WG_SYNC();  // everyone in the group is done reading the old table
         if (!ok) break;
         TileInfo ti{};
@@ -670,16 +688,35 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
         ++n_acc;
         tc_fence_after();
         const uint32_t taddr = lane_addr + (uint32_t)(abuf * TILE_N);
-        for (int cc = 0; cc < ncols; cc += 32) {
-          uint32_t r[32];
+        for (int cc = 0; cc < ncols; cc += 64) {
+          // one TMEM round trip per 64 columns (a load that starts past ncols is skipped by the 32-wide tail)
           float v[32];
-          tmem_ld32_issue(taddr + (uint32_t)cc, r);
-          tmem_ld_wait(r);
-          as_floats(r, v);
-          if (use_cols)  // columns past ncols carry bias -inf, so the whole chunk can be folded
-            fold_chunk<ARGMAX, true>(v, 32, c0 + cc, &ctl->col_scale[wg][cc], &ctl->col_bias[wg][cc], run_m, run_i);
-          else
-            fold_chunk<ARGMAX, false>(v, ncols - cc, c0 + cc, nullptr, nullptr, run_m, run_i);
+          if (ncols - cc > 32) {
+            uint32_t r[64];
+            tmem_ld64_issue(taddr + (uint32_t)cc, r);
+            tmem_ld64_wait(r);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+            if (use_cols)  // columns past ncols carry bias -inf, so whole chunks can be folded
+              fold_chunk<ARGMAX, true>(v, 32, c0 + cc, &ctl->col_scale[wg][cc], &ctl->col_bias[wg][cc], run_m, run_i);
+            else
+              fold_chunk<ARGMAX, false>(v, 32, c0 + cc, nullptr, nullptr, run_m, run_i);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[32 + i]);
+            if (use_cols)
+              fold_chunk<ARGMAX, true>(v, 32, c0 + cc + 32, &ctl->col_scale[wg][cc + 32], &ctl->col_bias[wg][cc + 32], run_m, run_i);
+            else
+              fold_chunk<ARGMAX, false>(v, ncols - cc - 32, c0 + cc + 32, nullptr, nullptr, run_m, run_i);
+          } else {
+            uint32_t r[32];
+            tmem_ld32_issue(taddr + (uint32_t)cc, r);
+            tmem_ld_wait(r);
+            as_floats(r, v);
+            if (use_cols)
+              fold_chunk<ARGMAX, true>(v, 32, c0 + cc, &ctl->col_scale[wg][cc], &ctl->col_bias[wg][cc], run_m, run_i);
+            else
+              fold_chunk<ARGMAX, false>(v, ncols - cc, c0 + cc, nullptr, nullptr, run_m, run_i);
+          }
         }
         tc_fence_before();
         __syncwarp();
@@ -768,6 +805,28 @@ __global__ void mask_lens_kernel(const unsigned char* __restrict__ mask, const i
   if (lane == 0) out[j] = (last + 1) | (cnt != last + 1 ? LEN_FLAG_MASKED : 0);
 }
 
+// Greedy packing of ragged queries into 128-row tiles: a tile takes whole consecutive queries until the next
+// one would not fit.  out[0] = tile count, out[1 + m] = first query of tile m (out[1 + count] = n_q).
+__global__ void pack_query_tiles_kernel(const int* __restrict__ cu, int n_q, int* __restrict__ out) {
+  if (threadIdx.x != 0 || blockIdx.x != 0) return;
+  int tiles = 0, rows = 0, count = 0;  // a tile also holds at most TILE_M queries (empty ones take no rows)
+  out[1] = 0;
+  for (int q = 0; q < n_q; ++q) {
+    const int len = max(cu[q + 1] - cu[q], 0);
+    if (count > 0 && (rows + len > TILE_M || count == TILE_M)) {
+      ++tiles;
+      out[1 + tiles] = q;
+      rows = 0;
+      count = 0;
+    }
+    rows += len;
+    ++count;
+  }
+  ++tiles;
+  out[1 + tiles] = n_q;
+  out[0] = tiles;
+}
+
 // scores[q, j] = sum over the chunks of query q, in chunk order
 __global__ void reduce_chunks_kernel(const float* __restrict__ partial, int n_q, int n_d, int q_chunks, float* __restrict__ scores) {
   const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -822,7 +881,10 @@ int make_map(CUtensorMap* map, const lik_seqs& s, int dtype, int dim, int box_ro
   return LIK_OK;
 }
 
+constexpr int PACK_MAX_QUERIES = 8192;  // the packing scan is serial; larger batches use fixed groups
+
 struct TcPlan {
+  bool pack_tiles;  // ragged queries packed greedily into tiles by pack_query_tiles_kernel
   int q_per_tile, q_chunks, n_tiles, mt, n_slabs, k_steps, stages;
   long long n_units;
   size_t smem_bytes;
@@ -851,6 +913,8 @@ TcPlan plan_tc(const lik_fwd_args& a) {
       pl.n_tiles = a.q.n_seq * pl.q_chunks;
     }
     pl.mt = pl.n_tiles >= 2 ? 2 : 1;
+    // packed queries shorter than the fixed slot: let the device pack them tightly (n_tiles becomes an upper bound)
+    pl.pack_tiles = a.q.cu && ml < TILE_M && pl.q_per_tile > 1 && a.q.n_seq > 1 && a.q.n_seq <= PACK_MAX_QUERIES;
     pl.n_units = ceil_div(pl.n_tiles, pl.mt) * (long long)a.d.n_seq;
   }
   const size_t q_bytes = 2 * (size_t)pl.n_slabs * TILE_M * SLAB_BYTES_ROW;
@@ -890,7 +954,8 @@ static size_t partial_bytes(const TcPlan& pl, const lik_fwd_args& a) {
 size_t fwd_tc_workspace(const lik_fwd_args& a) {
   TcPlan pl = plan_tc(a);
   const size_t lens_bytes = (a.d.mask && !a.d.cu) ? align_up((size_t)a.d.n_seq * sizeof(int), 256) : 0;
-  return partial_bytes(pl, a) + lens_bytes;
+  const size_t tiles_bytes = pl.pack_tiles ? align_up((size_t)(a.q.n_seq + 3) * sizeof(int), 256) : 0;
+  return partial_bytes(pl, a) + lens_bytes + tiles_bytes;
 }
 
 int launch_fwd_tc(const lik_fwd_args& a, const float* qn, const float* dn, void* ws, size_t ws_bytes, cudaStream_t st) {
@@ -925,6 +990,14 @@ int launch_fwd_tc(const lik_fwd_args& a, const float* qn, const float* dn, void*
   P.scores = a.scores;
   P.partial = pl.q_chunks > 1 ? (float*)ws : nullptr;
   P.d_len_flagged = 0;
+  P.tile_q0 = nullptr;
+  if (pl.pack_tiles) {
+    const size_t lens_bytes = (a.d.mask && !a.d.cu) ? align_up((size_t)a.d.n_seq * sizeof(int), 256) : 0;
+    int* tbl = (int*)((char*)ws + partial_bytes(pl, a) + lens_bytes);
+    pack_query_tiles_kernel<<<1, 32, 0, st>>>(a.q.cu, a.q.n_seq, tbl);
+    LIK_CUDA_OK(cudaGetLastError());
+    P.tile_q0 = tbl + 1;
+  }
   if (a.d.mask && !a.d.cu) {
     // trim every document to its last valid token; only documents with holes pay for per-column masking
     int* eff = (int*)((char*)ws + partial_bytes(pl, a));

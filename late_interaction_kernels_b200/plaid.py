@@ -223,4 +223,63 @@ def maxsim_residual_varlen(Q, codes_flat, residuals_flat, cu_seqlens_d, centroid
     return out.squeeze(0) if q2 else out
 
 
-__all__ = ["plaid_approx_score", "maxsim_residual", "maxsim_residual_varlen"]
+def retrieve_residual_varlen(Q, codes_flat, residuals_flat, cu_seqlens_d, centroids, bucket_weights, nbits, top_k, *,
+                             normalize=True, chunk=4096, largest=True, doc_lengths_host=None):
+    """Top-``top_k`` documents per query straight from a ragged PLAID index, never materialising
+    ``[Nq, Nd]``: documents are decompressed ``chunk`` at a time into operand rows, scored, and merged
+    into a running ``[Nq, k]`` list (score desc, index asc).  This is the build's fused form of "call
+    ``maxsim_residual_varlen`` then ``torch.topk``" (docs/benchmarks.md:191-206 of the reference).
+
+    ``cu_seqlens_d`` is read on the host once to place chunk boundaries (pass ``doc_lengths_host``, a CPU
+    int64 tensor of per-document lengths, to skip that device->host copy).  Returns
+    ``(scores fp32 [Nq, k], indices int64 [Nq, k])`` with ``k = min(top_k, Nd)``; 2-D ``Q`` squeezes."""
+    if nbits not in (2, 4, 8):
+        raise ValueError(f"nbits must be 2, 4, or 8; got {nbits}")
+    if top_k <= 0:
+        raise ValueError(f"top_k must be positive, got {top_k}")
+    q2 = Q.dim() == 2
+    if q2:
+        Q = Q.unsqueeze(0)
+    _lib.require_cuda(Q, codes_flat, residuals_flat, cu_seqlens_d, centroids, op="retrieve_residual_varlen")
+    Q = Q.contiguous()
+    codes_flat, residuals_flat, centroids, bucket_weights, expected = _prepare_index(
+        Q, codes_flat, residuals_flat, centroids, bucket_weights, nbits
+    )
+    if residuals_flat.shape[-1] != expected:
+        raise ValueError(
+            f"residuals_flat last dim {residuals_flat.shape[-1]} != expected {expected} for d={Q.shape[-1]}, nbits={nbits}"
+        )
+    cu = cu_seqlens_d.contiguous().to(torch.int32)
+    Nd = cu.numel() - 1
+    k = min(top_k, max(Nd, 0))
+    if k > _lib.TOPK_MAX:
+        raise ValueError(f"k={k} exceeds the supported maximum {_lib.TOPK_MAX}")
+    Nq, Lq, d = Q.shape
+    dev = Q.device
+    if Nd <= 0:
+        out = (torch.empty((Nq, 0), dtype=torch.float32, device=dev), torch.empty((Nq, 0), dtype=torch.int64, device=dev))
+        return (out[0].squeeze(0), out[1].squeeze(0)) if q2 else out
+    if doc_lengths_host is not None:
+        cu_host = torch.zeros(Nd + 1, dtype=torch.int64)
+        cu_host[1:] = doc_lengths_host.to(torch.int64).cumsum(0)
+    else:
+        cu_host = cu.cpu().to(torch.int64)
+    ix, keep = _ops.plaid_index(codes_flat, residuals_flat, centroids, bucket_weights, nbits, d)
+    odt = _operand_dtype(Q)
+    q = _ops.padded_spec(Q.to(odt))
+    norm = _lib.NORM_Q if normalize else _lib.NORM_NONE
+    out = None
+    with torch.no_grad():
+        for j0 in range(0, Nd, chunk):
+            j1 = min(Nd, j0 + chunk)
+            t0, t1 = int(cu_host[j0]), int(cu_host[j1])
+            emb = _ops.plaid_decompress(ix, t0, t1 - t0, normalize, odt, dev)
+            max_ld = int((cu_host[j0 + 1 : j1 + 1] - cu_host[j0:j1]).max())
+            dd = _ops.packed_spec(emb, cu[j0 : j1 + 1] - t0, max_ld)
+            s, _ = _ops.forward(q, dd, normalize=norm)
+            out = _ops.topk_rows(s.view(Nq, j1 - j0), k, largest=largest, index_offset=j0, out=out)
+    ts, ti = out
+    return (ts.squeeze(0), ti.squeeze(0)) if q2 else (ts, ti)
+
+
+__all__ = ["plaid_approx_score", "maxsim_residual", "maxsim_residual_varlen", "retrieve_residual_varlen"]

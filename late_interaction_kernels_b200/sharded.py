@@ -109,4 +109,34 @@ def retrieve_sharded(Q, D_local, top_k, q_mask=None, d_mask=None, *, doc_offset:
     return s, i
 
 
-__all__ = ["shard_bounds", "pad_candidates", "gather_candidates", "merge_candidates", "retrieve_sharded"]
+def retrieve_plaid_sharded(Q, codes_local, residuals_local, cu_local, centroids, bucket_weights, nbits, top_k, *,
+                           doc_offset: int, n_docs_total: int, normalize: bool = True, chunk: int = 4096,
+                           largest: bool = True, group=None):
+    """Sharded top-k over a PLAID index: every rank holds the codes / residuals / offsets of its own
+    contiguous document range (``cu_local`` re-based to start at 0) and the replicated centroids and bucket
+    weights; local fused decompress + score + top-k, one all-gather, one merge."""
+    from .plaid import retrieve_residual_varlen
+
+    q2 = Q.dim() == 2
+    if q2:
+        Q = Q.unsqueeze(0)
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    k = min(top_k, n_docs_total)
+    nd_local = cu_local.numel() - 1
+    if nd_local > 0:
+        s, i = retrieve_residual_varlen(Q, codes_local, residuals_local, cu_local, centroids, bucket_weights, nbits,
+                                        min(k, nd_local), normalize=normalize, chunk=chunk, largest=largest)
+        i = i + doc_offset
+    else:
+        s = torch.empty((Q.shape[0], 0), dtype=torch.float32, device=Q.device)
+        i = torch.empty((Q.shape[0], 0), dtype=torch.int64, device=Q.device)
+    s, i = pad_candidates(s, i, k, largest=largest)
+    if world > 1:
+        gs, gi = gather_candidates(s, i, group)
+        s, i = merge_candidates(gs, gi, k, largest=largest)
+    if q2:
+        s, i = s.squeeze(0), i.squeeze(0)
+    return s, i
+
+
+__all__ = ["retrieve_plaid_sharded", "shard_bounds", "pad_candidates", "gather_candidates", "merge_candidates", "retrieve_sharded"]

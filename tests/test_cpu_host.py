@@ -145,3 +145,15 @@ def test_fp8_quantisers_on_cpu_match_reference_golden():
     assert np.array_equal(fp8.dequantize_fp8_per_token(xq, sc).numpy(), g["deq_tok"])
     xq2, sc2 = fp8.quantize_fp8_per_tensor(torch.tensor(X))
     assert np.array_equal(xq2.float().numpy(), g["q_ten"]) and np.array_equal(sc2.numpy(), g["s_ten"])
+
+
+def test_reference_package_name_resolves_to_this_build():
+    import importlib
+
+    import late_interaction_kernels as alias
+    import late_interaction_kernels_b200 as impl
+
+    assert alias.maxsim is impl.maxsim and alias.MaxSimScorer is impl.MaxSimScorer and callable(alias.retrieve)
+    assert importlib.import_module("late_interaction_kernels.plaid").maxsim_residual is impl.plaid.maxsim_residual
+    assert importlib.import_module("late_interaction_kernels.retrieve").retrieve is impl.retrieve
+    from late_interaction_kernels.backward.lowmem import maxsim_backward_lowmem  # noqa: F401

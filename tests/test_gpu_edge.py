@@ -1,0 +1,188 @@
+"""GPU edge cases and size-independent properties (the reference's test_edge_cases / test_robustness,
+plus checks at BASELINE sizes where the CPU oracle is too slow to be the checker)."""
+
+import numpy as np
+import pytest
+import torch
+
+import cases
+from oracle import maxsim_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+
+def dev(x, dtype=None):
+    t = torch.from_numpy(np.ascontiguousarray(x)).cuda()
+    return t.to(dtype) if dtype is not None else t
+
+
+def f32(t):
+    return t.detach().float().cpu().numpy()
+
+
+@pytest.mark.parametrize("d", [8, 16, 33, 37, 63, 96, 111, 250, 513])
+def test_embedding_widths(d):
+    import late_interaction_kernels_b200 as lik
+
+    Q, D, _, dm = cases.dense_case(d, 3, 5, 7, 21, d, d_len=(1, 21), normalized=True)
+    for dtype, tol in ((torch.float32, 1e-5), (torch.bfloat16, 2e-2)):
+        want = O.maxsim(f32(dev(Q, dtype)), f32(dev(D, dtype)), None, dm)
+        got = lik.maxsim(dev(Q, dtype), dev(D, dtype), None, dev(dm))
+        assert O.rel_err(f32(got), want) < tol, (d, dtype)
+
+
+def test_degenerate_lengths_and_many_docs():
+    import late_interaction_kernels_b200 as lik
+
+    rng = np.random.default_rng(0)
+    for Lq, Ld in ((1, 1), (1, 40), (33, 1), (200, 3)):
+        Q = cases.unit(rng.standard_normal((2, Lq, 64))).astype(np.float32)
+        D = cases.unit(rng.standard_normal((3, Ld, 64))).astype(np.float32)
+        got = lik.maxsim(dev(Q, torch.bfloat16), dev(D, torch.bfloat16))
+        assert O.rel_err(f32(got), O.maxsim(f32(dev(Q, torch.bfloat16)), f32(dev(D, torch.bfloat16)))) < 2e-2
+    Q = cases.unit(rng.standard_normal((1, 32, 128))).astype(np.float32)
+    D = cases.unit(rng.standard_normal((1000, 60, 128))).astype(np.float32)
+    got = lik.maxsim(dev(Q, torch.float16), dev(D, torch.float16))
+    assert got.shape == (1, 1000)
+    assert O.rel_err(f32(got), O.maxsim(f32(dev(Q, torch.float16)), f32(dev(D, torch.float16)))) < 5e-3
+    # empty batches
+    assert lik.maxsim(dev(Q), dev(D[:0])).shape == (1, 0)
+    assert lik.maxsim(dev(Q[:0]), dev(D[:4])).shape == (0, 4)
+
+
+def test_long_queries_are_chunked_exactly():
+    import late_interaction_kernels_b200 as lik
+
+    Q, D, qm, dm = cases.dense_case(77, 3, 4, 300, 140, 128, q_len=(130, 300), d_len=(1, 140), normalized=True)
+    Qb, Db = dev(Q, torch.bfloat16), dev(D, torch.bfloat16)
+    want = O.maxsim(f32(Qb), f32(Db), qm, dm)
+    got = lik.maxsim(Qb, Db, dev(qm), dev(dm))
+    assert O.rel_err(f32(got), want) < 2e-2
+    # summing per-128-token pieces of the query reproduces the full score (MaxSim is additive over query tokens)
+    parts = sum(lik.maxsim(Qb[:, a:a + 128], Db, dev(qm[:, a:a + 128]), dev(dm)) for a in range(0, 300, 128))
+    assert torch.allclose(parts, got, rtol=1e-5, atol=1e-4)
+    Qt, Dt = Qb.clone().requires_grad_(), Db.clone().requires_grad_()
+    go = np.random.default_rng(1).standard_normal((3, 4)).astype(np.float32)
+    (lik.maxsim(Qt, Dt, dev(qm), dev(dm)) * dev(go)).sum().backward()
+    wq, wd = O.maxsim_grads(go, f32(Qb), f32(Db), qm, dm)
+    assert O.rel_err(f32(Qt.grad), wq) < 2e-2 and O.rel_err(f32(Dt.grad), wd) < 2e-2
+
+
+def test_tensor_core_engine_agrees_with_portable_engine():
+    from late_interaction_kernels_b200 import _lib, _ops
+
+    rng = np.random.default_rng(5)
+    for (nq, nd, lq, ld, d, dtype) in ((9, 31, 32, 300, 128, torch.bfloat16), (5, 12, 17, 77, 64, torch.float16),
+                                      (3, 6, 128, 513, 96, torch.bfloat16), (2, 8, 150, 64, 128, torch.bfloat16)):
+        Q = dev(cases.unit(rng.standard_normal((nq, lq, d))).astype(np.float32), dtype)
+        D = dev(cases.unit(rng.standard_normal((nd, ld, d))).astype(np.float32), dtype)
+        holes = dev(rng.random((nd, ld)) > 0.3)
+        holes[:, 0] = True
+        holes[1] = False
+        q, dd = _ops.padded_spec(Q), _ops.padded_spec(D, holes)
+        for norm in (_lib.NORM_NONE, _lib.NORM_BOTH):
+            s1, a1 = _ops.forward(q, dd, normalize=norm, save_argmax=True, engine=1)
+            s2, a2 = _ops.forward(q, dd, normalize=norm, save_argmax=True, engine=2)
+            assert torch.allclose(s1, s2, rtol=2e-5, atol=2e-5), (nq, nd, lq, ld, d, norm)
+            assert (a1 == a2).float().mean() > 0.999
+            assert (a2.view(nq, nd, lq)[:, 1] == -1).all()
+
+
+def test_int64_offsets_explicit_maxima_and_status_word():
+    import late_interaction_kernels_b200 as lik
+
+    Q, D, cu_q, cu_d = cases.varlen_case(16, Nq=6, Nd=5, lq=(3, 20), ld=(10, 90), d=64, normalized=True)
+    Qb, Db = dev(Q, torch.bfloat16), dev(D, torch.bfloat16)
+    base = lik.maxsim_varlen(Qb, Db, dev(cu_q.astype(np.int64)), dev(cu_d.astype(np.int64)))
+    assert torch.equal(lik.maxsim_varlen(Qb, Db, dev(cu_q), dev(cu_d), 20, 90), base)
+    assert torch.equal(lik.maxsim_varlen(Qb, Db, dev(cu_q), dev(cu_d), 64, 1000), base), "generous maxima change nothing"
+    lik.check_device_status()
+    # a max_seqlen_q below the longest query cannot store every winner: reported through the status word
+    Qt = Qb.clone().requires_grad_()
+    lik.maxsim_varlen(Qt, Db, dev(cu_q), dev(cu_d), 2, 90)
+    with pytest.raises(RuntimeError, match="max_seqlen_q|padded extent"):
+        lik.check_device_status()
+
+
+def test_full_size_inbatch_properties():
+    """BASELINE config 2 shape: checked through properties instead of the (too slow) oracle."""
+    import late_interaction_kernels_b200 as lik
+
+    g = torch.Generator(device="cuda").manual_seed(0)
+    Q = torch.nn.functional.normalize(torch.randn(512, 32, 128, generator=g, device="cuda"), dim=-1).bfloat16()
+    D = torch.nn.functional.normalize(torch.randn(512, 300, 128, generator=g, device="cuda"), dim=-1).bfloat16()
+    lens = torch.randint(64, 301, (512,), generator=g, device="cuda")
+    dm = torch.arange(300, device="cuda")[None] < lens[:, None]
+    s = lik.maxsim(Q, D, d_mask=dm)
+    # 1. a block of the score matrix equals scoring that block alone (tiling independence), bit for bit
+    assert torch.equal(lik.maxsim(Q[100:228], D[37:300], d_mask=dm[37:300]), s[100:228, 37:300])
+    # 2. permuting documents permutes columns
+    perm = torch.randperm(512, generator=g, device="cuda")
+    assert torch.equal(lik.maxsim(Q, D[perm], d_mask=dm[perm]), s[:, perm])
+    # 3. a sampled corner against the oracle
+    want = O.maxsim(f32(Q[:8]), f32(D[:16]), None, dm[:16].cpu().numpy())
+    assert O.rel_err(f32(s[:8, :16]), want) < 2e-2
+    # 4. backward is linear in the upstream gradient and deterministic
+    Qt, Dt = Q.clone().requires_grad_(), D.clone().requires_grad_()
+    g1 = torch.randn(512, 512, generator=g, device="cuda")
+    out = lik.maxsim(Qt, Dt, d_mask=dm)
+    gq1, gd1 = torch.autograd.grad(out, (Qt, Dt), g1, retain_graph=True)
+    gq1b, gd1b = torch.autograd.grad(out, (Qt, Dt), g1, retain_graph=True)
+    assert torch.equal(gq1, gq1b) and torch.equal(gd1, gd1b)
+    gq2, gd2 = torch.autograd.grad(out, (Qt, Dt), 2 * g1)
+    assert torch.allclose(gq2.float(), 2 * gq1.float(), rtol=2e-2, atol=1e-3)
+    assert torch.allclose(gd2.float(), 2 * gd1.float(), rtol=2e-2, atol=1e-3)
+    assert (gd1[~dm] == 0).all(), "masked document tokens get exactly zero gradient"
+    # 5. sampled gradient rows against the oracle (first 4 queries see every document)
+    wq, _ = O.maxsim_grads(f32(g1[:4]), f32(Q[:4]), f32(D), None, dm.cpu().numpy())
+    assert O.rel_err(f32(gq1[:4]), wq) < 2e-2
+
+
+def test_torch_compile_and_module_in_a_model():
+    import late_interaction_kernels_b200 as lik
+
+    scorer = lik.MaxSimScorer(normalize=True)
+    Q = torch.randn(4, 16, 64, device="cuda", dtype=torch.bfloat16)
+    D = torch.randn(6, 40, 64, device="cuda", dtype=torch.bfloat16)
+    eager = scorer(Q, D)
+
+    @torch.compile(fullgraph=False)
+    def f(q, d):
+        return scorer(q, d) * 2
+
+    assert torch.allclose(f(Q, D), eager * 2)
+    ids_q = torch.randint(1, 5, (4, 16), device="cuda")
+    ids_d = torch.randint(0, 5, (6, 40), device="cuda")
+    s = lik.MaxSimScorer(mask_pad_token=0).forward_with_ids(Q, D, ids_q, ids_d)
+    assert torch.equal(s, lik.maxsim(Q, D, q_mask=ids_q != 0, d_mask=ids_d != 0, normalize=True))
+
+
+def test_plaid_retrieve_matches_score_then_topk():
+    from late_interaction_kernels_b200 import plaid, sharded
+
+    rng = np.random.default_rng(3)
+    Nd, d, nbits, ncent = 300, 64, 2, 128
+    lens = rng.integers(0, 40, size=Nd)
+    lens[5] = 0
+    T = int(lens.sum())
+    codes = rng.integers(0, ncent, size=T).astype(np.int32)
+    res = rng.integers(0, 256, size=(T, d * nbits // 8)).astype(np.uint8)
+    cu = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+    cent = cases.unit(rng.standard_normal((ncent, d))).astype(np.float16)
+    bw = np.linspace(-0.1, 0.1, 4).astype(np.float32)
+    Q = rng.standard_normal((7, 9, d)).astype(np.float32)
+    args = (dev(Q, torch.bfloat16), dev(codes), dev(res), dev(cu), dev(cent), dev(bw), nbits)
+    full = plaid.maxsim_residual_varlen(*args)
+    ws, wi = torch.topk(full, 25, dim=-1)
+    for chunk in (16, 64, 1000):
+        s, i = plaid.retrieve_residual_varlen(*args, 25, chunk=chunk)
+        assert torch.equal(s, ws), chunk
+        assert torch.equal(torch.gather(full, 1, i), ws), "indices point at the top scores"
+    want = O.maxsim_residual_varlen(f32(args[0]), codes, res, cu, cent, bw, nbits)
+    assert O.rel_err(f32(full), want) < 3e-2
+    # single-process "sharded" call degenerates to the local top-k
+    s, i = sharded.retrieve_plaid_sharded(*args, 25, doc_offset=0, n_docs_total=Nd, chunk=64)
+    assert torch.equal(s, ws)
+    s1, i1 = sharded.retrieve_sharded(dev(Q, torch.bfloat16), dev(rng.standard_normal((40, 12, d)).astype(np.float32), torch.bfloat16),
+                                      10, doc_offset=1000, n_docs_total=40)
+    assert s1.shape == (7, 10) and int(i1.min()) >= 1000
