@@ -16,6 +16,10 @@ import torch
 from . import _lib
 from ._lib import BwdArgs, FwdArgs, PlaidIndex, Seqs
 
+# The launchers hand raw pointers to a C library: keep torch.compile from tracing into them (it
+# breaks the graph around the call instead).
+_no_trace = getattr(getattr(torch, "compiler", None), "disable", None) or (lambda f: f)
+
 
 @dataclass
 class SeqSpec:
@@ -116,6 +120,7 @@ def n_scores(pairing, q: SeqSpec, d: SeqSpec, n_pairs) -> int:
     return n_pairs
 
 
+@_no_trace
 def forward(q: SeqSpec, d: SeqSpec, *, pairing=_lib.PAIR_CROSS, group=0, pair_q=None, pair_d=None,
             normalize=0, save_argmax=False, argmax_stride=None, engine=0):
     """Launch ``lik_maxsim_fwd``.  Returns (scores fp32 [n_scores], argmax int32 [n_scores, stride] | None)."""
@@ -148,6 +153,7 @@ def forward(q: SeqSpec, d: SeqSpec, *, pairing=_lib.PAIR_CROSS, group=0, pair_q=
     return scores, argmax
 
 
+@_no_trace
 def backward(q: SeqSpec, d: SeqSpec, grad_scores: torch.Tensor, argmax: torch.Tensor, *, pairing=_lib.PAIR_CROSS,
              group=0, pair_q=None, pair_d=None, normalize=0, deterministic=True, grad_dtype=None,
              need_q=True, need_d=True):
@@ -187,6 +193,7 @@ def backward(q: SeqSpec, d: SeqSpec, grad_scores: torch.Tensor, argmax: torch.Te
     return gq, gd
 
 
+@_no_trace
 def topk_rows(scores: torch.Tensor, k: int, *, largest=True, index_offset=0, out=None):
     """Per-row top-k of a [n_rows, n_cols] fp32 matrix; ``out=(scores, idx)`` merges into a running list."""
     lib = _lib.load()
@@ -210,6 +217,7 @@ def topk_rows(scores: torch.Tensor, k: int, *, largest=True, index_offset=0, out
     return out_s, out_i
 
 
+@_no_trace
 def topk_merge(cand_scores: torch.Tensor, cand_index: torch.Tensor, k: int, *, largest=True):
     """Merge candidate lists [n_lists, n_rows, k] into the per-row top k."""
     lib = _lib.load()
@@ -240,6 +248,7 @@ def plaid_index(codes, residuals, centroids, bucket_weights, nbits, dim) -> tupl
     return ix, (codes, residuals, centroids, bucket_weights)
 
 
+@_no_trace
 def plaid_decompress(ix: PlaidIndex, token_begin: int, token_count: int, normalize: bool, out_dtype, device):
     lib = _lib.load()
     out = torch.empty((token_count, ix.dim), dtype=out_dtype, device=device)

@@ -630,6 +630,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
             if (len > P.q_chunks * TILE_M && P.status) atomicOr(P.status, LIK_DEV_LEN_RANGE);
           }
           if ((off & 31) != 0 || l > 32) ctl->warp_aligned[wg] = 0;
+          if (ARGMAX && len > P.argmax_stride && P.status) atomicOr(P.status, LIK_DEV_ARGMAX_STRIDE);
           ctl->seg_off[wg][et] = off;
           ctl->seg_len[wg][et] = l;
           ctl->seg_q[wg][et] = ti.qa + et;

@@ -17,6 +17,7 @@ from . import _lib, _ops
 _DECOMPRESS_TOKENS = 1 << 22
 
 
+@_ops._no_trace
 def plaid_approx_score(query_centroid_scores, codes, doc_lengths):
     """``out[b] = sum_s max_{t < doc_lengths[b]} qcs[codes[b, t], s]`` -> fp32 ``[B]`` (plaid.py:82-136).
     Empty documents score 0; out-of-range codes read centroid 0."""

@@ -40,11 +40,12 @@ def _varlen_forward(Q_packed, D_packed, cu_seqlens_q, cu_seqlens_d, max_seqlen_q
     cu_q = cu_seqlens_q.to(torch.int32).contiguous()
     cu_d = cu_seqlens_d.to(torch.int32).contiguous()
     Nq, Nd = cu_q.numel() - 1, cu_d.numel() - 1
+    # the longest query sizes the query tiles (and the saved argmax); like the reference it costs one
+    # device->host sync when the caller does not pass it.  The longest document is only needed by the backward.
+    max_q = max_seqlen_from_cu(cu_q) if max_seqlen_q is None else int(max_seqlen_q)
     if save_argmax:
-        max_q = max_seqlen_from_cu(cu_q) if max_seqlen_q is None else int(max_seqlen_q)
         max_d = max_seqlen_from_cu(cu_d) if max_seqlen_d is None else int(max_seqlen_d)
-    else:  # inference never needs the maxima: no host sync
-        max_q = 0 if max_seqlen_q is None else int(max_seqlen_q)
+    else:
         max_d = 0 if max_seqlen_d is None else int(max_seqlen_d)
     dt = common_dtype(Q_packed, D_packed)
     q = _ops.packed_spec(Q_packed.to(dt), cu_q, max_q)
@@ -81,9 +82,9 @@ class _MaxSimVarlenFn(torch.autograd.Function):
 def maxsim_varlen(Q_packed, D_packed, cu_seqlens_q, cu_seqlens_d, max_seqlen_q=None, max_seqlen_d=None):
     """MaxSim on packed inputs -> fp32 ``[Nq, Nd]``; autograd-aware (varlen.py:452-493).
 
-    Empty sequences score 0.  ``max_seqlen_q`` / ``max_seqlen_d`` are only needed on the training
-    path (they size the saved argmax and the backward grid); when omitted there they are read from
-    ``cu_seqlens`` with one device->host sync.  Inference never synchronises."""
+    Empty sequences score 0.  ``max_seqlen_q`` sizes the query tiles and the saved argmax, ``max_seqlen_d``
+    the backward grid; when omitted they are read from ``cu_seqlens`` with one device->host sync (pass them
+    to stay sync-free, e.g. under CUDA-graph capture)."""
     if torch.is_grad_enabled() and (Q_packed.requires_grad or D_packed.requires_grad):
         _check_packed(Q_packed, D_packed)
         return _MaxSimVarlenFn.apply(
