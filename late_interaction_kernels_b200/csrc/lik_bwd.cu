@@ -586,10 +586,12 @@ __global__ void __launch_bounds__(256) bwd_dd_reduce_kernel(BwdParams P, DdSortO
   for (int c = 0; c < CH; ++c)
 #pragma unroll
     for (int e = 0; e < 4; ++e) acc[c][e] = 0.f;
-  const int cnt = O.tok_cnt[drow];
+  // both loads are issued together; tok_begin is only meaningful when the count is non-zero
+  const int cnt = __ldg(O.tok_cnt + drow);
+  const long long begin = __ldg(O.tok_begin + drow);
   const T* __restrict__ Qg = (const T*)P.q.data;
   if (cnt > 0) {
-    const int2* list = O.pairs + O.tok_begin[drow];
+    const int2* list = O.pairs + begin;
     for (int k0 = 0; k0 < cnt; k0 += 32) {
       const int n = min(32, cnt - k0);
       int2 mine = make_int2(0, 0);
