@@ -1,17 +1,21 @@
 // Blackwell tensor-core MaxSim forward (sm_100a: TMA + tcgen05.mma + TMEM).
 //
 // GEMM view: rows = query tokens (A operand, K-major, 128 per tile), columns = document tokens (B
-// operand, K-major, up to 128 per tile), K = embedding width.  A CTA is persistent: it keeps one or
+// operand, K-major, up to 256 per tile), K = embedding width.  A CTA is persistent: it keeps one or
 // two 128-row query tiles resident in shared memory and streams document tiles through a TMA ring.
 // Every document tile feeds one MMA group per resident query tile; the fp32 accumulator of query
-// tile m alternates between TMEM columns [256 m, +128) and [256 m + 128, +128).  A tile never spans two documents, so the
+// tile m lives in TMEM columns [256 m, 256 m + 256).  A tile never spans two documents, so the
 // epilogue is: per thread (= one query token = one TMEM lane) a running max over the tile's columns,
 // carried across the tiles of a document; at the end of the document the 128 row maxima are summed
 // per query (fixed order) into one score.  Scores for a (query, document) pair have exactly one
 // writer, so the forward is bitwise reproducible.
 //
-// Warp roles (320 threads): warp 0 = TMA producer, warp 1 = MMA issuer + TMEM owner, warps 2-5 =
-// epilogue group 0 (accumulator 0), warps 6-9 = epilogue group 1 (accumulator 1).
+// Warp roles (640 threads): warp 0 = TMA producer; warp 1 = MMA issuer + TMEM owner; warps 2-9 =
+// epilogue group 0 (accumulator 0), warps 10-17 = epilogue group 1 (accumulator 1); warps 18-19 idle
+// (they round the block up to the register-allocation granule).  The issuer is driven by one word
+// per ring stage that the producer writes, so the unit bookkeeping stays off its critical path.  An
+// accumulator is single-buffered (two 256-column accumulators fill TMEM), so the time an epilogue
+// group holds it bounds the tensor pipe; eight warps per group halve that time.
 //
 // Every mbarrier wait is bounded: on expiry the CTA raises LIK_DEV_WAIT_TIMEOUT in the status word,
 // sets a shared abort flag, drains its TMA copies, frees TMEM and returns.
@@ -27,14 +31,16 @@ constexpr int TILE_M = 128;
 #ifndef LIK_TILE_N
 #define LIK_TILE_N 256
 #endif
-constexpr int TILE_N = LIK_TILE_N;     // document tokens per tile
-constexpr int ACC_PER_GROUP = 256 / TILE_N;  // TMEM accumulators each epilogue group alternates between
-constexpr int BOX_ROWS = 64;        // rows per TMA box of the document ring
+constexpr int TILE_N = LIK_TILE_N;     // document tokens per TMA stage = columns of one accumulator
+constexpr int ACC_COLS = 256;          // TMEM columns reserved per accumulator
+static_assert(TILE_N <= ACC_COLS && TILE_N % 32 == 0, "a stage must fit one accumulator");
+constexpr int BOX_ROWS = 64;        // granule of the document TMA boxes (64, 128, 192 or 256 rows)
 constexpr int SLAB_BYTES_ROW = 128; // one swizzle span: 64 two-byte or 128 one-byte elements
 constexpr int MAX_SLABS = 2;
-constexpr int NUM_THREADS = 320;
-constexpr int EPI_THREADS = 128;
-constexpr int EPI_WARPS = 4;         // barrier arrivals are one per warp (elected lane), not one per thread
+constexpr int NUM_THREADS = 640;
+constexpr int EPI_THREADS = 128;     // threads per half of an epilogue group (one per accumulator row)
+constexpr int SUB_WARPS = 4;         // barrier arrivals are one per warp (elected lane), not one per thread
+constexpr int GROUP_WARPS = 8;
 constexpr long long WAIT_LIMIT_CYCLES = 4000000000ll;  // about 2 s per wait at 2 GHz
 constexpr int LEN_FLAG_MASKED = 1 << 30;
 
@@ -126,16 +132,6 @@ __device__ __forceinline__ void tmem_ld_wait(uint32_t (&r)[32]) {
                  "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
                :
                : "memory");
-}
-// 64-column variant: one TMEM round trip per 64 columns.
-__device__ __forceinline__ void tmem_ld64_issue(uint32_t taddr, uint32_t (&r)[64]) {
-  asm volatile("tcgen05.ld.sync.aligned.32x32b.x64.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32, %33, %34, %35, %36, %37, %38, %39, %40, %41, %42, %43, %44, %45, %46, %47, %48, %49, %50, %51, %52, %53, %54, %55, %56, %57, %58, %59, %60, %61, %62, %63}, [%64];"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31]), "=r"(r[32]), "=r"(r[33]), "=r"(r[34]), "=r"(r[35]), "=r"(r[36]), "=r"(r[37]), "=r"(r[38]), "=r"(r[39]), "=r"(r[40]), "=r"(r[41]), "=r"(r[42]), "=r"(r[43]), "=r"(r[44]), "=r"(r[45]), "=r"(r[46]), "=r"(r[47]), "=r"(r[48]), "=r"(r[49]), "=r"(r[50]), "=r"(r[51]), "=r"(r[52]), "=r"(r[53]), "=r"(r[54]), "=r"(r[55]), "=r"(r[56]), "=r"(r[57]), "=r"(r[58]), "=r"(r[59]), "=r"(r[60]), "=r"(r[61]), "=r"(r[62]), "=r"(r[63])
-               : "r"(taddr)
-               : "memory");
-}
-__device__ __forceinline__ void tmem_ld64_wait(uint32_t (&r)[64]) {
-  asm volatile("tcgen05.wait::ld.sync.aligned;" : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]), "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]), "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]), "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31]), "+r"(r[32]), "+r"(r[33]), "+r"(r[34]), "+r"(r[35]), "+r"(r[36]), "+r"(r[37]), "+r"(r[38]), "+r"(r[39]), "+r"(r[40]), "+r"(r[41]), "+r"(r[42]), "+r"(r[43]), "+r"(r[44]), "+r"(r[45]), "+r"(r[46]), "+r"(r[47]), "+r"(r[48]), "+r"(r[49]), "+r"(r[50]), "+r"(r[51]), "+r"(r[52]), "+r"(r[53]), "+r"(r[54]), "+r"(r[55]), "+r"(r[56]), "+r"(r[57]), "+r"(r[58]), "+r"(r[59]), "+r"(r[60]), "+r"(r[61]), "+r"(r[62]), "+r"(r[63]) : : "memory");
 }
 __device__ __forceinline__ void as_floats(const uint32_t (&r)[32], float (&v)[32]) {
 #pragma unroll
@@ -244,8 +240,9 @@ struct TcParams {
 struct SharedCtl {
   unsigned long long q_full, q_empty;
   unsigned long long d_full[8], d_empty[8];
-  unsigned long long acc_full[4], acc_empty[4];
-  unsigned long long wg_bar[2];
+  unsigned long long acc_full[2], acc_empty[2];
+  unsigned long long grp_bar[2], sub_bar[2];
+  uint32_t stage_info[8];
   uint32_t tmem_base;
   volatile int abort_flag;
   int seg_off[2][TILE_M], seg_len[2][TILE_M], seg_q[2][TILE_M];
@@ -253,14 +250,24 @@ struct SharedCtl {
   int n_seg[2];
   int warp_aligned[2];  // every query of the tile sits inside one warp's 32 rows, starting at its first row
   float emit[2][2][TILE_M];
+  float xch_m[2][2][TILE_M];  // half 1 -> half 0: per-row running maximum and its column
+  int xch_i[2][2][TILE_M];
   alignas(16) float col_scale[2][TILE_N];  // read as float4
   alignas(16) float col_bias[2][TILE_N];
 };
 
-#ifdef LIK_TC_PROFILE
+// Debug builds only: LIK_TC_PROFILE=1 sums the cycles every role spends in each phase, =2 records
+// raw event timestamps of CTA 0 instead (one array per role).
+#ifndef LIK_TC_PROFILE
+#define LIK_TC_PROFILE 0
+#endif
+#if LIK_TC_PROFILE
 }  // namespace
 __device__ unsigned long long g_prof[16];
+__device__ long long g_trace[5][4096];
 namespace {
+#endif
+#if LIK_TC_PROFILE == 1
 #define PROF_T0(var) long long var = clock64()
 #define PROF_ADD(slot, var) prof[slot] += clock64() - var
 #define PROF_DECL() unsigned long long prof[16] = {0}
@@ -270,6 +277,13 @@ namespace {
 #define PROF_ADD(slot, var)
 #define PROF_DECL()
 #define PROF_FLUSH(cond)
+#endif
+#if LIK_TC_PROFILE == 2
+#define TRACE_DECL() int trace_n = 0
+#define TRACE(role) do { if (blockIdx.x == 0 && trace_n < 4096) g_trace[role][trace_n++] = clock64(); } while (0)
+#else
+#define TRACE_DECL()
+#define TRACE(role)
 #endif
 
 // Bounded wait.  Returns false when the CTA is aborting.
@@ -331,20 +345,57 @@ __device__ __forceinline__ void unit_decode(const TcParams& P, long long u, int&
 }
 
 
-// First row and column count of document `doc`; `masked` tells whether its mask has holes.
+// Walks the work units of a CTA in order.  The length words of the next document are loaded one
+// unit ahead and left untouched until that unit starts, so that the load latency hides behind the
+// current unit's work; (group, document) advance by increments instead of a division per unit.
+struct UnitWalk {
+  int grp, doc, in_grp;  // the unit fetch() was last called for
+  int raw_a, raw_b;      // its unprocessed length words
+};
+
+__device__ __forceinline__ void walk_fetch(const TcParams& P, UnitWalk& w) {
+  if (P.d.cu) {
+    w.raw_a = P.d.cu[w.doc];
+    w.raw_b = P.d.cu[w.doc + 1];
+  } else if (P.d.lens) {
+    w.raw_a = P.d.lens[w.doc];
+  }
+}
+
+__device__ __forceinline__ void walk_init(const TcParams& P, long long u, UnitWalk& w) {
+  unit_decode(P, u, w.grp, w.doc);
+  w.in_grp = P.pairing == LIK_PAIR_CROSS ? 0 : w.doc - w.grp * P.group;
+  w.raw_a = w.raw_b = 0;
+  walk_fetch(P, w);
+}
+
+__device__ __forceinline__ void walk_advance(const TcParams& P, UnitWalk& w) {
+  ++w.doc;
+  if (P.pairing == LIK_PAIR_CROSS) {
+    if (w.doc == P.n_d) {
+      w.doc = 0;
+      ++w.grp;
+    }
+  } else if (++w.in_grp == P.group) {
+    w.in_grp = 0;
+    ++w.grp;
+  }
+}
+
+// First row and column count of the fetched document; `masked` tells whether its mask has holes.
 // Lengths come from the caller-validated views, clamped to the padded extent.
-__device__ __forceinline__ void doc_bounds(const TcParams& P, int doc, long long& row0, int& len, bool& masked) {
+__device__ __forceinline__ void walk_resolve(const TcParams& P, const UnitWalk& w, long long& row0, int& len, bool& masked) {
   masked = false;
   if (P.d.cu) {
-    const int a = P.d.cu[doc], b = P.d.cu[doc + 1];
+    const int a = w.raw_a, b = w.raw_b;
     row0 = a;
     len = b > a ? b - a : 0;
     if ((long long)a + len > P.d.n_rows) len = P.d.n_rows > a ? (int)(P.d.n_rows - a) : 0;
   } else {
-    row0 = (long long)doc * P.d.seq_stride;
+    row0 = (long long)w.doc * P.d.seq_stride;
     len = P.d.max_len;
     if (P.d.lens) {
-      int l = P.d.lens[doc];
+      int l = w.raw_a;
       if (P.d_len_flagged) {
         masked = (l & LEN_FLAG_MASKED) != 0;
         l &= ~LEN_FLAG_MASKED;
@@ -354,15 +405,27 @@ __device__ __forceinline__ void doc_bounds(const TcParams& P, int doc, long long
   }
 }
 
-#ifdef LIK_TC_PROFILE
+#if LIK_TC_PROFILE == 1
 __device__ __forceinline__ void prof_tiles(unsigned long long* prof) { prof[11] += 1; }
 #else
 #define prof_tiles(x)
 #endif
 
+struct DocMaps {
+  CUtensorMap m[4];  // document boxes of 64, 128, 192 and 256 rows: one copy per K slab whatever the tile height
+};
+
+// Word the producer leaves beside every ring stage for the MMA issuer.
+constexpr uint32_t STAGE_COLS_MASK = 0x1FFu;   // valid document rows in the stage
+constexpr uint32_t STAGE_ACC0 = 1u << 16;      // feed accumulator 0 / 1
+constexpr uint32_t STAGE_ACC1 = 1u << 17;
+constexpr uint32_t STAGE_FIRST = 1u << 18;     // first stage of a query-tile group: wait for the tiles
+constexpr uint32_t STAGE_LAST = 1u << 19;      // last stage of the group: hand the tiles back afterwards
+constexpr uint32_t STAGE_END = 1u << 20;       // no more work
+
 template <bool FP8, bool ARGMAX, bool SCALED>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
-fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap d_map, const TcParams P) {
+fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ DocMaps d_maps, const TcParams P) {
   extern __shared__ unsigned char smem_raw[];
   // operand tiles need 1024-byte alignment for the 128-byte swizzle
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -388,15 +451,16 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
       mbar_init(smem_u32(&ctl->d_full[s]), 1);
       mbar_init(smem_u32(&ctl->d_empty[s]), 1);
     }
-    for (int a = 0; a < 4; ++a) {
+    for (int a = 0; a < 2; ++a) {
       mbar_init(smem_u32(&ctl->acc_full[a]), 1);
-      mbar_init(smem_u32(&ctl->acc_empty[a]), EPI_WARPS);
+      mbar_init(smem_u32(&ctl->acc_empty[a]), GROUP_WARPS);
+      mbar_init(smem_u32(&ctl->grp_bar[a]), GROUP_WARPS);
+      mbar_init(smem_u32(&ctl->sub_bar[a]), SUB_WARPS);
     }
-    for (int a = 0; a < 2; ++a) mbar_init(smem_u32(&ctl->wg_bar[a]), EPI_WARPS);
     ctl->abort_flag = 0;
     fence_barrier_init();
     prefetch_tmap(&q_map);
-    prefetch_tmap(&d_map);
+    for (int i = 0; i < 4; ++i) prefetch_tmap(&d_maps.m[i]);
   }
   if (warp == 1) {
     tmem_alloc(smem_u32(&ctl->tmem_base), 512);
@@ -407,44 +471,48 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
   tc_fence_after();
   const uint32_t tmem_base = ctl->tmem_base;
 
-  // Every role walks the same unit sequence.  The bounds of the next document are fetched one
-  // iteration ahead so that the load latency hides behind the current document's work.
-  long long nx_row0 = 0;
-  int nx_len = 0, nx_grp = 0, nx_doc = 0;
-  bool nx_masked = false;
-  if (u_begin < u_end) {
-    unit_decode(P, u_begin, nx_grp, nx_doc);
-    doc_bounds(P, nx_doc, nx_row0, nx_len, nx_masked);
-  }
+  // The producer and the epilogue groups walk the same unit sequence.
+  UnitWalk wk{};
+  if (u_begin < u_end) walk_init(P, u_begin, wk);
 #define LIK_NEXT_UNIT()                                            \
-  const int grp = nx_grp, doc = nx_doc, dlen = nx_len;             \
-  const long long drow0 = nx_row0;                                 \
-  const bool dmasked = nx_masked;                                  \
+  const int grp = wk.grp, doc = wk.doc;                            \
+  long long drow0;                                                 \
+  int dlen;                                                        \
+  bool dmasked;                                                    \
+  walk_resolve(P, wk, drow0, dlen, dmasked);                       \
   (void)dmasked;                                                   \
+  (void)doc;                                                       \
   if (u + 1 < u_end) {                                             \
-    unit_decode(P, u + 1, nx_grp, nx_doc);                         \
-    doc_bounds(P, nx_doc, nx_row0, nx_len, nx_masked);             \
+    walk_advance(P, wk);                                           \
+    walk_fetch(P, wk);                                             \
   }
 
   if (warp == 0) {
     // =========================== TMA producer ===========================
     if (lane == 0) {
       int cur_grp = -1;
-      uint32_t n_qload = 0, n_dload = 0;
+      uint32_t n_qload = 0, st = 0, ph = 0, n_dload = 0;
+      long long uc = 0;
       const int x_per_slab = SLAB_BYTES_ROW / P.elt_bytes;
       bool ok = true;
+      int tiles_here = 0;
       PROF_DECL();
+      TRACE_DECL();
       PROF_T0(p_all);
-      for (long long u = u_begin; u < u_end && ok; ++u) {
+      for (long long u = u_begin; u < u_end && ok; ++u, ++uc) {
         LIK_NEXT_UNIT();
+        const bool last_unit_of_grp = (u + 1 >= u_end) || (wk.grp != grp);
+        uint32_t first = 0;
         if (grp != cur_grp) {
           cur_grp = grp;
+          first = STAGE_FIRST;
           // wait until the MMAs that read the previous query tiles are done
           PROF_T0(p_q);
           ok = wait_bar(&ctl->q_empty, (n_qload & 1) ^ 1, ctl, P.status);
           PROF_ADD(2, p_q);
           if (!ok) break;
           const int t0 = grp * P.mt, t1 = min(t0 + P.mt, n_tiles);
+          tiles_here = t1 - t0;
           mbar_arrive_expect_tx(smem_u32(&ctl->q_full), (uint32_t)((t1 - t0) * q_tile_bytes));
           for (int t = t0; t < t1; ++t) {
             TileInfo ti = tile_info(P, t);
@@ -454,21 +522,49 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
           }
           ++n_qload;
         }
+        // which accumulators this unit feeds: both resident tiles, or (one tile) alternating with the unit count
+        const uint32_t acc_bits = P.mt == 2 ? (tiles_here == 2 ? (STAGE_ACC0 | STAGE_ACC1) : STAGE_ACC0)
+                                            : ((uc & 1) ? STAGE_ACC1 : STAGE_ACC0);
+        if (dlen <= 0 && (first || last_unit_of_grp)) {
+          // an empty document carries no stage, but the group hand-shake it would have carried must still happen
+          PROF_T0(p_d0);
+          ok = wait_bar(&ctl->d_empty[st], ph ^ 1, ctl, P.status);
+          PROF_ADD(1, p_d0);
+          if (!ok) break;
+          ctl->stage_info[st] = first | (last_unit_of_grp ? STAGE_LAST : 0u);
+          mbar_arrive(smem_u32(&ctl->d_full[st]));
+          ++n_dload;
+          if (++st == (uint32_t)P.stages) { st = 0; ph ^= 1; }
+        }
         for (int c0 = 0; c0 < dlen; c0 += TILE_N) {
           const int ncols = min(TILE_N, dlen - c0);
           const int boxes = (ncols + BOX_ROWS - 1) / BOX_ROWS;
-          const int st = n_dload % P.stages;
           PROF_T0(p_d);
-          ok = wait_bar(&ctl->d_empty[st], ((n_dload / P.stages) & 1) ^ 1, ctl, P.status);
+          ok = wait_bar(&ctl->d_empty[st], ph ^ 1, ctl, P.status);
           PROF_ADD(1, p_d);
+          TRACE(0);
           if (!ok) break;
           const uint32_t full = smem_u32(&ctl->d_full[st]);
+          uint32_t info = (uint32_t)ncols | acc_bits;
+          if (c0 == 0) info |= first;
+          if (last_unit_of_grp && c0 + TILE_N >= dlen) info |= STAGE_LAST;
+          ctl->stage_info[st] = info;
           mbar_arrive_expect_tx(full, (uint32_t)(boxes * BOX_ROWS * SLAB_BYTES_ROW * P.n_slabs));
+          const CUtensorMap* map = &d_maps.m[boxes - 1];
           for (int sl = 0; sl < P.n_slabs; ++sl)
-            for (int b = 0; b < boxes; ++b)
-              tma_load_2d(smem_u32(d_smem + (size_t)st * d_stage_bytes + sl * TILE_N * SLAB_BYTES_ROW + b * BOX_ROWS * SLAB_BYTES_ROW),
-                          &d_map, sl * x_per_slab, (int)(drow0 + c0) + b * BOX_ROWS, full);
+            tma_load_2d(smem_u32(d_smem + (size_t)st * d_stage_bytes + sl * TILE_N * SLAB_BYTES_ROW), map, sl * x_per_slab,
+                        (int)(drow0 + c0), full);
           ++n_dload;
+          if (++st == (uint32_t)P.stages) { st = 0; ph ^= 1; }
+          TRACE(0);
+        }
+      }
+      if (ok) {
+        // tell the issuer that the stream has ended
+        ok = wait_bar(&ctl->d_empty[st], ph ^ 1, ctl, P.status);
+        if (ok) {
+          ctl->stage_info[st] = STAGE_END;
+          mbar_arrive(smem_u32(&ctl->d_full[st]));
         }
       }
       PROF_ADD(0, p_all);
@@ -491,55 +587,56 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
     }
   } else if (warp == 1) {
     // =========================== MMA issuer ===========================
+    // Driven by the stage words alone: between two MMA groups it runs a few dozen instructions, so the
+    // tensor pipe's queue never drains while work is available.
     if (lane == 0) {
-      int cur_grp = -1;
-      uint32_t n_qload = 0, n_dload = 0, n_acc[2] = {0, 0};
-      long long uc = 0;
+      uint32_t st = 0, ph = 0, q_ph = 0, acc_ph[2] = {0, 0};
       bool ok = true;
-      int mt_valid = 0;
-      const uint64_t q_desc0 = smem_desc_sw128(smem_u32(q_smem));
+      const uint32_t q_tile_desc = (uint32_t)(q_tile_bytes >> 4);
+      const uint64_t a_desc0 = smem_desc_sw128(smem_u32(q_smem));
+      const uint64_t b_desc0 = smem_desc_sw128(smem_u32(d_smem));
+      const uint32_t stage_desc = (uint32_t)(d_stage_bytes >> 4);
+      const uint32_t idesc0 = instr_desc(P.ab_format, 0);
       PROF_DECL();
+      TRACE_DECL();
       PROF_T0(m_all);
-      for (long long u = u_begin; u < u_end && ok; ++u, ++uc) {
-        LIK_NEXT_UNIT();
-        if (grp != cur_grp) {
-          if (cur_grp >= 0) tc_commit(smem_u32(&ctl->q_empty));  // previous query tiles are free once issued MMAs retire
-          cur_grp = grp;
-          mt_valid = min(P.mt, n_tiles - grp * P.mt);
+      while (ok) {
+        PROF_T0(m_d);
+        TRACE(1);
+        ok = wait_bar(&ctl->d_full[st], ph, ctl, P.status);
+        PROF_ADD(4, m_d);
+        TRACE(1);
+        if (!ok) break;
+        const uint32_t info = ctl->stage_info[st];
+        if (info & STAGE_END) break;
+        if (info & STAGE_FIRST) {
           PROF_T0(m_q);
-          ok = wait_bar(&ctl->q_full, n_qload & 1, ctl, P.status);
+          ok = wait_bar(&ctl->q_full, q_ph, ctl, P.status);
           PROF_ADD(6, m_q);
           if (!ok) break;
-          ++n_qload;
-          tc_fence_after();
+          q_ph ^= 1;
         }
-        for (int c0 = 0; c0 < dlen && ok; c0 += TILE_N) {
-          const int ncols = min(TILE_N, dlen - c0);
-          const int n_mma = (ncols + 15) & ~15;
-          const uint32_t idesc = instr_desc(P.ab_format, n_mma);
-          const int st = n_dload % P.stages;
-          PROF_T0(m_d);
-          ok = wait_bar(&ctl->d_full[st], (n_dload / P.stages) & 1, ctl, P.status);
-          PROF_ADD(4, m_d);
-          if (!ok) break;
-          tc_fence_after();
-          const uint64_t b_desc0 = smem_desc_sw128(smem_u32(d_smem + (size_t)st * d_stage_bytes));
-          for (int m = 0; m < mt_valid; ++m) {
-            // each epilogue group owns two accumulators and alternates between them, so the MMAs of
-            // the next tile run while the previous tile is still being drained
-            const int g = P.mt == 2 ? m : (int)(uc & 1);
-            const int a = g * ACC_PER_GROUP + (int)(n_acc[g] % ACC_PER_GROUP);
+        const uint32_t ncols = info & STAGE_COLS_MASK;
+        if (ncols) {
+          const uint32_t idesc = idesc0 | (((ncols + 15) >> 4) << 18);  // N / 8 in bits 17..22
+          const uint64_t b_stage = b_desc0 + (uint64_t)(st * stage_desc);
+#pragma unroll
+          for (int a = 0; a < 2; ++a) {
+            if (!(info & (a ? STAGE_ACC1 : STAGE_ACC0))) continue;
             PROF_T0(m_a);
-            ok = wait_bar(&ctl->acc_empty[a], ((n_acc[g] / ACC_PER_GROUP) & 1) ^ 1, ctl, P.status);
+            ok = wait_bar(&ctl->acc_empty[a], acc_ph[a] ^ 1, ctl, P.status);
             PROF_ADD(5, m_a);
+            TRACE(1);
             if (!ok) break;
+            acc_ph[a] ^= 1;
             tc_fence_after();
-            const uint32_t d_tmem = tmem_base + (uint32_t)(a * TILE_N);
+            const uint32_t d_tmem = tmem_base + (uint32_t)(a * ACC_COLS);
             // descriptors differ only in the 16-byte-unit start address: add offsets to a base descriptor
-            uint64_t a_desc = q_desc0 + (uint64_t)((m * q_tile_bytes) >> 4);
-            uint64_t b_desc = b_desc0;
+            uint64_t a_desc = a_desc0 + (uint64_t)((P.mt == 2 ? a : 0) * q_tile_desc);
+            uint64_t b_desc = b_stage;
             int left = P.k_steps;
             uint32_t accum = 0;
+            PROF_T0(m_i);
             for (int sl = 0; sl < P.n_slabs; ++sl) {
               tc_mma<FP8>(d_tmem, a_desc, b_desc, idesc, accum);
               accum = 1;
@@ -550,26 +647,36 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
               a_desc += (uint64_t)((TILE_M * SLAB_BYTES_ROW) >> 4);
               b_desc += (uint64_t)((TILE_N * SLAB_BYTES_ROW) >> 4);
             }
+            PROF_ADD(13, m_i);
+            TRACE(1);
             tc_commit(smem_u32(&ctl->acc_full[a]));
-            ++n_acc[g];
+            TRACE(1);
           }
-          tc_commit(smem_u32(&ctl->d_empty[st]));  // ring slot reusable once these MMAs retire
-          ++n_dload;
+          if (!ok) break;
         }
+        tc_commit(smem_u32(&ctl->d_empty[st]));  // ring slot reusable once these MMAs retire
+        if (info & STAGE_LAST) tc_commit(smem_u32(&ctl->q_empty));  // and so are the query tiles
+        TRACE(1);
+        if (++st == (uint32_t)P.stages) { st = 0; ph ^= 1; }
       }
       PROF_ADD(3, m_all);
       PROF_FLUSH(true);
     }
-  } else {
+  } else if (warp < 2 + 2 * GROUP_WARPS) {
     // =========================== epilogue groups ===========================
-    const int wg = (warp - 2) >> 2;          // 0 or 1
+    // Group g (eight warps) drains accumulator g.  Its two halves split the 32-column chunks of a tile
+    // between them (even chunks / odd chunks); half 1 hands its per-row result to half 0, which sums
+    // the rows of every query and writes the score.
+    const int e = warp - 2;
+    const int wg = e >> 3;                   // accumulator / epilogue group
+    const int sub = (e >> 2) & 1;            // half of the group
     const int quad = warp & 3;               // TMEM lane quadrant this warp may read
-    const int wq = (warp - 2) & 3;           // warp index inside the group
+    const int wq = e & 3;                    // warp index inside the half
     const int row = quad * 32 + lane;        // accumulator row == query token slot in the tile
-    const int et = wq * 32 + lane;           // thread index inside the group (0..127)
-    const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
+    const int et = wq * 32 + lane;           // thread index inside the half (0..127)
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(wg * ACC_COLS);
     int cur_grp = -1;
-    uint32_t n_acc = 0, n_wg = 0;
+    uint32_t n_acc = 0, n_grp_sync = 0, n_sub_sync = 0, n_doc = 0;
     long long uc = 0;
     bool ok = true;
     // per-row state for the resident query tile
@@ -577,16 +684,24 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
     int my_q = 0, my_s = 0;
     float my_qf = 1.f;
     int tile_id = 0;
-    // one group-wide rendezvous (bounded)
-#define LIK_WG_SYNC()                                             \
-  do {                                                            \
-    __syncwarp();                                                 \
-    if (lane == 0) mbar_arrive(smem_u32(&ctl->wg_bar[wg]));       \
-    ok = wait_bar(&ctl->wg_bar[wg], n_wg & 1, ctl, P.status);     \
-    ++n_wg;                                                       \
+    // bounded rendezvous of the whole group / of half 0
+#define LIK_GRP_SYNC()                                                \
+  do {                                                                \
+    __syncwarp();                                                     \
+    if (lane == 0) mbar_arrive(smem_u32(&ctl->grp_bar[wg]));          \
+    ok = wait_bar(&ctl->grp_bar[wg], n_grp_sync & 1, ctl, P.status);  \
+    ++n_grp_sync;                                                     \
+  } while (0)
+#define LIK_SUB_SYNC()                                                \
+  do {                                                                \
+    __syncwarp();                                                     \
+    if (lane == 0) mbar_arrive(smem_u32(&ctl->sub_bar[wg]));          \
+    ok = wait_bar(&ctl->sub_bar[wg], n_sub_sync & 1, ctl, P.status);  \
+    ++n_sub_sync;                                                     \
   } while (0)
 
     PROF_DECL();
+    TRACE_DECL();
     PROF_T0(e_all);
     for (long long u = u_begin; u < u_end && ok; ++u, ++uc) {
       LIK_NEXT_UNIT();
@@ -597,22 +712,24 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
         const int m = P.mt == 2 ? wg : 0;
         tile_id = grp * P.mt + m;
         have_tile = tile_id < n_tiles;
-        LIK_WG_SYNC();  // everyone in the group is done reading the old table
+        LIK_GRP_SYNC();  // everyone in the group is done reading the old table
         if (!ok) break;
         TileInfo ti{};
         int nseg = 0;
         if (have_tile) {
           ti = tile_info(P, tile_id);
           nseg = ti.qb - ti.qa;
-          ctl->row_seg[wg][et] = -1;
-          if (et == 0) {
-            ctl->n_seg[wg] = nseg;
-            ctl->warp_aligned[wg] = P.q_chunks == 1 ? 1 : 0;
+          if (sub == 0) {
+            ctl->row_seg[wg][et] = -1;
+            if (et == 0) {
+              ctl->n_seg[wg] = nseg;
+              ctl->warp_aligned[wg] = P.q_chunks == 1 ? 1 : 0;
+            }
           }
         }
-        LIK_WG_SYNC();
+        LIK_GRP_SYNC();
         if (!ok) break;
-        if (have_tile && et < nseg) {
+        if (have_tile && sub == 0 && et < nseg) {
           long long r0;
           int len;
           seq_bounds(P.q, ti.qa + et, r0, len, P.status);
@@ -636,7 +753,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
           ctl->seg_q[wg][et] = ti.qa + et;
           for (int i = 0; i < l; ++i) ctl->row_seg[wg][off + i] = (short)et;
         }
-        LIK_WG_SYNC();
+        LIK_GRP_SYNC();
         if (!ok) break;
         in_seg = false;
         row_ok = false;
@@ -664,9 +781,9 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
       for (int c0 = 0; c0 < dlen && ok; c0 += TILE_N) {
         const int ncols = min(TILE_N, dlen - c0);
         if (use_cols) {
-          LIK_WG_SYNC();  // the previous tile's readers are done with the column arrays
+          LIK_GRP_SYNC();  // the previous tile's readers are done with the column arrays
           if (!ok) break;
-          for (int c = et; c < ((ncols + 31) & ~31); c += EPI_THREADS) {
+          for (int c = sub * EPI_THREADS + et; c < ((ncols + 31) & ~31); c += 2 * EPI_THREADS) {
             float sc = 1.f, bi = -INFINITY;
             if (c < ncols) {
               const long long drow = drow0 + c0 + c;
@@ -676,57 +793,69 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
             ctl->col_scale[wg][c] = sc;
             ctl->col_bias[wg][c] = bi;
           }
-          LIK_WG_SYNC();
+          LIK_GRP_SYNC();
           if (!ok) break;
         }
-        const int abuf = wg * ACC_PER_GROUP + (int)(n_acc % ACC_PER_GROUP);
         PROF_T0(e_w);
-        ok = wait_bar(&ctl->acc_full[abuf], (n_acc / ACC_PER_GROUP) & 1, ctl, P.status);
+        ok = wait_bar(&ctl->acc_full[wg], n_acc & 1, ctl, P.status);
         PROF_ADD(8, e_w);
+        if (wq == 0 && lane == 0 && sub == 0) TRACE(3 + wg);
         prof_tiles(prof);
         PROF_T0(e_f);
         if (!ok) break;
         ++n_acc;
         tc_fence_after();
-        const uint32_t taddr = lane_addr + (uint32_t)(abuf * TILE_N);
-        for (int cc = 0; cc < ncols; cc += 64) {
-          // one TMEM round trip per 64 columns (a load that starts past ncols is skipped by the 32-wide tail)
+        // the accumulator goes back to the issuer as soon as this warp's last columns sit in registers
+#define LIK_RELEASE_ACC()                                          \
+  do {                                                             \
+    tc_fence_before();                                             \
+    __syncwarp();                                                  \
+    if (lane == 0) mbar_arrive(smem_u32(&ctl->acc_empty[wg]));     \
+  } while (0)
+        int cc = sub * 32;
+        if (cc >= ncols) LIK_RELEASE_ACC();
+        for (; cc < ncols; cc += 64) {
+          uint32_t r[32];
           float v[32];
-          if (ncols - cc > 32) {
-            uint32_t r[64];
-            tmem_ld64_issue(taddr + (uint32_t)cc, r);
-            tmem_ld64_wait(r);
-#pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
-            if (use_cols)  // columns past ncols carry bias -inf, so whole chunks can be folded
-              fold_chunk<ARGMAX, true>(v, 32, c0 + cc, &ctl->col_scale[wg][cc], &ctl->col_bias[wg][cc], run_m, run_i);
-            else
-              fold_chunk<ARGMAX, false>(v, 32, c0 + cc, nullptr, nullptr, run_m, run_i);
-#pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[32 + i]);
-            if (use_cols)
-              fold_chunk<ARGMAX, true>(v, 32, c0 + cc + 32, &ctl->col_scale[wg][cc + 32], &ctl->col_bias[wg][cc + 32], run_m, run_i);
-            else
-              fold_chunk<ARGMAX, false>(v, ncols - cc - 32, c0 + cc + 32, nullptr, nullptr, run_m, run_i);
-          } else {
-            uint32_t r[32];
-            tmem_ld32_issue(taddr + (uint32_t)cc, r);
-            tmem_ld_wait(r);
-            as_floats(r, v);
-            if (use_cols)
-              fold_chunk<ARGMAX, true>(v, 32, c0 + cc, &ctl->col_scale[wg][cc], &ctl->col_bias[wg][cc], run_m, run_i);
-            else
-              fold_chunk<ARGMAX, false>(v, ncols - cc, c0 + cc, nullptr, nullptr, run_m, run_i);
-          }
+          tmem_ld32_issue(lane_addr + (uint32_t)cc, r);
+          tmem_ld_wait(r);
+          if (cc + 64 >= ncols) LIK_RELEASE_ACC();
+          as_floats(r, v);
+          if (use_cols)  // columns past ncols carry bias -inf, so whole chunks can be folded
+            fold_chunk<ARGMAX, true>(v, 32, c0 + cc, &ctl->col_scale[wg][cc], &ctl->col_bias[wg][cc], run_m, run_i);
+          else
+            fold_chunk<ARGMAX, false>(v, ncols - cc, c0 + cc, nullptr, nullptr, run_m, run_i);
         }
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(&ctl->acc_empty[abuf]));
+#undef LIK_RELEASE_ACC
+        if (wq == 0 && lane == 0 && sub == 0) TRACE(3 + wg);
         PROF_ADD(9, e_f);
       }
       if (!ok) break;
       PROF_T0(e_e);
-      // ---- end of document: one value per row, summed per query in a fixed order ----
+      // ---- end of document: half 1 hands over, half 0 merges (lower column wins a tie) ----
+      float* xm = ctl->xch_m[wg][n_doc & 1];
+      int* xi = ctl->xch_i[wg][n_doc & 1];
+      ++n_doc;
+      if (sub == 1) {
+        xm[row] = run_m;
+        if (ARGMAX) xi[row] = run_i;
+      }
+      LIK_GRP_SYNC();
+      if (!ok) break;
+      if (sub == 1) continue;
+      {
+        const float m1 = xm[row];
+        if (ARGMAX) {
+          const int i1 = xi[row];
+          if (i1 >= 0 && (run_i < 0 || m1 > run_m || (m1 == run_m && i1 < run_i))) {
+            run_m = m1;
+            run_i = i1;
+          }
+        } else {
+          run_m = fmaxf(run_m, m1);
+        }
+      }
+      // one value per row, summed per query in a fixed order
       const bool has_winner = ARGMAX ? (run_i >= 0) : (run_m != -INFINITY);
       const float val = (in_seg && row_ok && has_winner) ? run_m * my_qf : 0.f;
       if (ARGMAX && in_seg && my_s < P.argmax_stride) {
@@ -743,11 +872,12 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
           P.scores[o] = sum;
         }
         PROF_ADD(10, e_e);
+        if (wq == 0 && lane == 0) TRACE(3 + wg);
         continue;
       }
-      float* ebuf = ctl->emit[wg][n_wg & 1];
+      float* ebuf = ctl->emit[wg][n_sub_sync & 1];
       ebuf[row] = val;
-      LIK_WG_SYNC();
+      LIK_SUB_SYNC();
       if (!ok) break;
       const int nseg = ctl->n_seg[wg];
       for (int sg = wq; sg < nseg; sg += 4) {
@@ -766,10 +896,12 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
         }
       }
       PROF_ADD(10, e_e);
+      if (wq == 0 && lane == 0) TRACE(3 + wg);
     }
     PROF_ADD(7, e_all);
     PROF_FLUSH(warp == 2 && lane == 0);
-#undef LIK_WG_SYNC
+#undef LIK_GRP_SYNC
+#undef LIK_SUB_SYNC
   }
 #undef LIK_NEXT_UNIT
 
@@ -965,11 +1097,14 @@ int launch_fwd_tc(const lik_fwd_args& a, const float* qn, const float* dn, void*
     set_error("not enough shared memory for the document ring");
     return LIK_ERR_UNSUPPORTED;
   }
-  CUtensorMap q_map, d_map;
+  CUtensorMap q_map;
+  DocMaps d_maps;
   int rc = make_map(&q_map, a.q, a.dtype, a.dim, TILE_M);
   if (rc) return rc;
-  rc = make_map(&d_map, a.d, a.dtype, a.dim, BOX_ROWS);
-  if (rc) return rc;
+  for (int i = 0; i < 4; ++i) {
+    rc = make_map(&d_maps.m[i], a.d, a.dtype, a.dim, (i + 1) * BOX_ROWS);
+    if (rc) return rc;
+  }
 
   TcParams P{};
   P.q = make_view(a.q, qn);
@@ -1028,7 +1163,7 @@ int launch_fwd_tc(const lik_fwd_args& a, const float* qn, const float* dn, void*
 #define LIK_TC_LAUNCH(F, A, X)                                                                                         \
   do {                                                                                                                 \
     LIK_CUDA_OK(cudaFuncSetAttribute(fwd_tc_kernel<F, A, X>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem_bytes)); \
-    fwd_tc_kernel<F, A, X><<<grid, block, pl.smem_bytes, st>>>(q_map, d_map, P);                                       \
+    fwd_tc_kernel<F, A, X><<<grid, block, pl.smem_bytes, st>>>(q_map, d_maps, P);                                       \
   } while (0)
   if (fp8) {
     if (argmax && affine) LIK_TC_LAUNCH(true, true, true);
@@ -1053,7 +1188,10 @@ int launch_fwd_tc(const lik_fwd_args& a, const float* qn, const float* dn, void*
 
 }  // namespace lik
 
-#ifdef LIK_TC_PROFILE
+#if LIK_TC_PROFILE
+extern "C" int lik_debug_trace(long long* out_host) {
+  return (int)cudaMemcpyFromSymbol(out_host, lik::g_trace, sizeof(long long) * 5 * 4096);
+}
 extern "C" int lik_debug_profile(unsigned long long* out_host, int reset) {
   cudaMemcpyFromSymbol(out_host, lik::g_prof, sizeof(unsigned long long) * 16);
   if (reset) {
