@@ -112,30 +112,14 @@ __device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t a_desc, uint64_
 // 32 lanes x 32 consecutive fp32 columns of TMEM -> 32 registers per thread.  The load is
 // asynchronous: the registers may only be read after tmem_ld_wait(), which takes them as in/out
 // operands so that no use can be scheduled ahead of it.
-__device__ __forceinline__ void tmem_ld32_issue(uint32_t taddr, uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr)
-      : "memory");
-}
-__device__ __forceinline__ void tmem_ld_wait(uint32_t (&r)[32]) {
-  asm volatile("tcgen05.wait::ld.sync.aligned;"
-               : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]), "+r"(r[8]),
-                 "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]), "+r"(r[16]),
-                 "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]), "+r"(r[24]),
-                 "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
-               :
+__device__ __forceinline__ void tmem_ld32_issue(uint32_t taddr, float (&v)[32]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+               : "=f"(v[0]), "=f"(v[1]), "=f"(v[2]), "=f"(v[3]), "=f"(v[4]), "=f"(v[5]), "=f"(v[6]), "=f"(v[7]), "=f"(v[8]), "=f"(v[9]), "=f"(v[10]), "=f"(v[11]), "=f"(v[12]), "=f"(v[13]), "=f"(v[14]), "=f"(v[15]), "=f"(v[16]), "=f"(v[17]), "=f"(v[18]), "=f"(v[19]), "=f"(v[20]), "=f"(v[21]), "=f"(v[22]), "=f"(v[23]), "=f"(v[24]), "=f"(v[25]), "=f"(v[26]), "=f"(v[27]), "=f"(v[28]), "=f"(v[29]), "=f"(v[30]), "=f"(v[31])
+               : "r"(taddr)
                : "memory");
 }
-__device__ __forceinline__ void as_floats(const uint32_t (&r)[32], float (&v)[32]) {
-#pragma unroll
-  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+__device__ __forceinline__ void tmem_ld_wait(float (&v)[32]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;" : "+f"(v[0]), "+f"(v[1]), "+f"(v[2]), "+f"(v[3]), "+f"(v[4]), "+f"(v[5]), "+f"(v[6]), "+f"(v[7]), "+f"(v[8]), "+f"(v[9]), "+f"(v[10]), "+f"(v[11]), "+f"(v[12]), "+f"(v[13]), "+f"(v[14]), "+f"(v[15]), "+f"(v[16]), "+f"(v[17]), "+f"(v[18]), "+f"(v[19]), "+f"(v[20]), "+f"(v[21]), "+f"(v[22]), "+f"(v[23]), "+f"(v[24]), "+f"(v[25]), "+f"(v[26]), "+f"(v[27]), "+f"(v[28]), "+f"(v[29]), "+f"(v[30]), "+f"(v[31]) : : "memory");
 }
 
 __device__ __forceinline__ float max3(float a, float b, float c) {
@@ -153,31 +137,14 @@ __device__ __forceinline__ float max32(const float (&v)[32]) {
   return fmaxf(max3(b0, b1, b2), b3);
 }
 
-// Fold one 32-column chunk of a score tile into the running (max, argmax) of a row.
-//   COLS: apply the per-column multiplier / additive mask staged in shared memory.
-//   lim:  number of valid columns in the chunk (1..32).
-template <bool ARGMAX, bool COLS>
-__device__ __forceinline__ void fold_chunk(float (&v)[32], int lim, int col0, const float* scale, const float* bias,
-                                           float& run_m, int& run_i) {
-  if (COLS) {
-#pragma unroll
-    for (int i = 0; i < 32; i += 4) {
-      const float4 sc = *reinterpret_cast<const float4*>(scale + i);
-      const float4 bi = *reinterpret_cast<const float4*>(bias + i);
-      v[i + 0] = fmaf(v[i + 0], sc.x, bi.x);
-      v[i + 1] = fmaf(v[i + 1], sc.y, bi.y);
-      v[i + 2] = fmaf(v[i + 2], sc.z, bi.z);
-      v[i + 3] = fmaf(v[i + 3], sc.w, bi.w);
-    }
-  }
-  if (lim < 32) {
-#pragma unroll
-    for (int i = 0; i < 32; ++i)
-      if (i >= lim) v[i] = -INFINITY;
-  }
+// Fold the maximum of one 32-column chunk into the running (max, argmax) of a row.  The column scan
+// only runs when the chunk beats the running maximum (strict: an equal value in a later chunk never
+// displaces an earlier winner) and returns the lowest matching column.
+template <bool ARGMAX>
+__device__ __forceinline__ void fold32(const float (&v)[32], int col0, float& run_m, int& run_i) {
   const float cmax = max32(v);
   if (ARGMAX) {
-    if (cmax > run_m) {  // strict: an equal value in a later chunk never displaces an earlier winner
+    if (cmax > run_m) {
       unsigned m0 = 0, m1 = 0, m2 = 0, m3 = 0;
 #pragma unroll
       for (int i = 0; i < 32; i += 4) {
@@ -186,11 +153,23 @@ __device__ __forceinline__ void fold_chunk(float (&v)[32], int lim, int col0, co
         if (v[i + 2] == cmax) m2 |= 1u << (i + 2);
         if (v[i + 3] == cmax) m3 |= 1u << (i + 3);
       }
-      run_i = col0 + __ffs((int)(m0 | m1 | m2 | m3)) - 1;  // lowest matching column
+      run_i = col0 + __ffs((int)(m0 | m1 | m2 | m3)) - 1;
       run_m = cmax;
     }
   } else {
     run_m = fmaxf(run_m, cmax);
+  }
+}
+// v[i] = v[i] * scale[i] + bias[i]: per-column multiplier and additive mask staged in shared memory
+__device__ __forceinline__ void affine32(float (&v)[32], const float* scale, const float* bias) {
+#pragma unroll
+  for (int i = 0; i < 32; i += 4) {
+    const float4 sc = *reinterpret_cast<const float4*>(scale + i);
+    const float4 bi = *reinterpret_cast<const float4*>(bias + i);
+    v[i + 0] = fmaf(v[i + 0], sc.x, bi.x);
+    v[i + 1] = fmaf(v[i + 1], sc.y, bi.y);
+    v[i + 2] = fmaf(v[i + 2], sc.z, bi.z);
+    v[i + 3] = fmaf(v[i + 3], sc.w, bi.w);
   }
 }
 
@@ -278,7 +257,10 @@ namespace {
 #define PROF_DECL()
 #define PROF_FLUSH(cond)
 #endif
-#if LIK_TC_PROFILE == 2
+#if LIK_TC_PROFILE == 3
+#define TRACE_DECL() int trace_n = 0
+#define TRACE(role)
+#elif LIK_TC_PROFILE == 2
 #define TRACE_DECL() int trace_n = 0
 #define TRACE(role) do { if (blockIdx.x == 0 && trace_n < 4096) g_trace[role][trace_n++] = clock64(); } while (0)
 #else
@@ -549,9 +531,15 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
           if (c0 == 0) info |= first;
           if (last_unit_of_grp && c0 + TILE_N >= dlen) info |= STAGE_LAST;
           ctl->stage_info[st] = info;
+#ifdef LIK_ABLATE_TMA
+          mbar_arrive(full);
+          const CUtensorMap* map = &d_maps.m[boxes - 1];
+          for (int sl = 0; sl < P.n_slabs - 2; ++sl)
+#else
           mbar_arrive_expect_tx(full, (uint32_t)(boxes * BOX_ROWS * SLAB_BYTES_ROW * P.n_slabs));
           const CUtensorMap* map = &d_maps.m[boxes - 1];
           for (int sl = 0; sl < P.n_slabs; ++sl)
+#endif
             tma_load_2d(smem_u32(d_smem + (size_t)st * d_stage_bytes + sl * TILE_N * SLAB_BYTES_ROW), map, sl * x_per_slab,
                         (int)(drow0 + c0), full);
           ++n_dload;
@@ -590,13 +578,15 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
     // Driven by the stage words alone: between two MMA groups it runs a few dozen instructions, so the
     // tensor pipe's queue never drains while work is available.
     if (lane == 0) {
-      uint32_t st = 0, ph = 0, q_ph = 0, acc_ph[2] = {0, 0};
+      uint32_t st = 0, ph = 0, q_ph = 0, acc_ph = 0;  // acc_ph: one phase bit per accumulator
       bool ok = true;
       const uint32_t q_tile_desc = (uint32_t)(q_tile_bytes >> 4);
       const uint64_t a_desc0 = smem_desc_sw128(smem_u32(q_smem));
       const uint64_t b_desc0 = smem_desc_sw128(smem_u32(d_smem));
       const uint32_t stage_desc = (uint32_t)(d_stage_bytes >> 4);
       const uint32_t idesc0 = instr_desc(P.ab_format, 0);
+      const int k_steps = P.k_steps, n_slabs = P.n_slabs;
+      const uint32_t a_tile1 = P.mt == 2 ? q_tile_desc : 0u;  // descriptor offset of the second resident tile
       PROF_DECL();
       TRACE_DECL();
       PROF_T0(m_all);
@@ -620,32 +610,54 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
         if (ncols) {
           const uint32_t idesc = idesc0 | (((ncols + 15) >> 4) << 18);  // N / 8 in bits 17..22
           const uint64_t b_stage = b_desc0 + (uint64_t)(st * stage_desc);
-#pragma unroll
+#pragma unroll 1  // one copy of the issue sequence: it stays in the instruction cache between the two groups
           for (int a = 0; a < 2; ++a) {
-            if (!(info & (a ? STAGE_ACC1 : STAGE_ACC0))) continue;
+            if (!(info & (STAGE_ACC0 << a))) continue;
             PROF_T0(m_a);
-            ok = wait_bar(&ctl->acc_empty[a], acc_ph[a] ^ 1, ctl, P.status);
+            ok = wait_bar(&ctl->acc_empty[a], ((acc_ph >> a) & 1u) ^ 1u, ctl, P.status);
             PROF_ADD(5, m_a);
             TRACE(1);
             if (!ok) break;
-            acc_ph[a] ^= 1;
+            acc_ph ^= 1u << a;
             tc_fence_after();
             const uint32_t d_tmem = tmem_base + (uint32_t)(a * ACC_COLS);
             // descriptors differ only in the 16-byte-unit start address: add offsets to a base descriptor
-            uint64_t a_desc = a_desc0 + (uint64_t)((P.mt == 2 ? a : 0) * q_tile_desc);
+            uint64_t a_desc = a_desc0 + (uint64_t)(a * a_tile1);
             uint64_t b_desc = b_stage;
-            int left = P.k_steps;
-            uint32_t accum = 0;
             PROF_T0(m_i);
-            for (int sl = 0; sl < P.n_slabs; ++sl) {
-              tc_mma<FP8>(d_tmem, a_desc, b_desc, idesc, accum);
-              accum = 1;
-              if (left > 1) tc_mma<FP8>(d_tmem, a_desc + 2, b_desc + 2, idesc, 1u);
-              if (left > 2) tc_mma<FP8>(d_tmem, a_desc + 4, b_desc + 4, idesc, 1u);
-              if (left > 3) tc_mma<FP8>(d_tmem, a_desc + 6, b_desc + 6, idesc, 1u);
-              left -= 4;
-              a_desc += (uint64_t)((TILE_M * SLAB_BYTES_ROW) >> 4);
-              b_desc += (uint64_t)((TILE_N * SLAB_BYTES_ROW) >> 4);
+#ifdef LIK_ABLATE_MMA
+            if (k_steps == 12345) {
+#else
+            if (k_steps == 8) {
+#endif
+              // the common width (128 two-byte or 256 one-byte elements): straight-line issue
+              const uint64_t a1 = a_desc + (uint64_t)((TILE_M * SLAB_BYTES_ROW) >> 4);
+              const uint64_t b1 = b_desc + (uint64_t)((TILE_N * SLAB_BYTES_ROW) >> 4);
+              tc_mma<FP8>(d_tmem, a_desc, b_desc, idesc, 0u);
+              tc_mma<FP8>(d_tmem, a_desc + 2, b_desc + 2, idesc, 1u);
+              tc_mma<FP8>(d_tmem, a_desc + 4, b_desc + 4, idesc, 1u);
+              tc_mma<FP8>(d_tmem, a_desc + 6, b_desc + 6, idesc, 1u);
+              tc_mma<FP8>(d_tmem, a1, b1, idesc, 1u);
+              tc_mma<FP8>(d_tmem, a1 + 2, b1 + 2, idesc, 1u);
+              tc_mma<FP8>(d_tmem, a1 + 4, b1 + 4, idesc, 1u);
+              tc_mma<FP8>(d_tmem, a1 + 6, b1 + 6, idesc, 1u);
+            } else {
+              int left = k_steps;
+              uint32_t accum = 0;
+#ifdef LIK_ABLATE_MMA
+              for (int sl = 0; sl < n_slabs - 2; ++sl) {
+#else
+              for (int sl = 0; sl < n_slabs; ++sl) {
+#endif
+                tc_mma<FP8>(d_tmem, a_desc, b_desc, idesc, accum);
+                accum = 1;
+                if (left > 1) tc_mma<FP8>(d_tmem, a_desc + 2, b_desc + 2, idesc, 1u);
+                if (left > 2) tc_mma<FP8>(d_tmem, a_desc + 4, b_desc + 4, idesc, 1u);
+                if (left > 3) tc_mma<FP8>(d_tmem, a_desc + 6, b_desc + 6, idesc, 1u);
+                left -= 4;
+                a_desc += (uint64_t)((TILE_M * SLAB_BYTES_ROW) >> 4);
+                b_desc += (uint64_t)((TILE_N * SLAB_BYTES_ROW) >> 4);
+              }
             }
             PROF_ADD(13, m_i);
             TRACE(1);
@@ -812,19 +824,37 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
     __syncwarp();                                                  \
     if (lane == 0) mbar_arrive(smem_u32(&ctl->acc_empty[wg]));     \
   } while (0)
+        // chunks of this half: cc, cc + 64, ...; only the tile's last chunk can be partial
         int cc = sub * 32;
         if (cc >= ncols) LIK_RELEASE_ACC();
-        for (; cc < ncols; cc += 64) {
-          uint32_t r[32];
-          float v[32];
-          tmem_ld32_issue(lane_addr + (uint32_t)cc, r);
-          tmem_ld_wait(r);
-          if (cc + 64 >= ncols) LIK_RELEASE_ACC();
-          as_floats(r, v);
-          if (use_cols)  // columns past ncols carry bias -inf, so whole chunks can be folded
-            fold_chunk<ARGMAX, true>(v, 32, c0 + cc, &ctl->col_scale[wg][cc], &ctl->col_bias[wg][cc], run_m, run_i);
-          else
-            fold_chunk<ARGMAX, false>(v, ncols - cc, c0 + cc, nullptr, nullptr, run_m, run_i);
+        if (use_cols) {
+          for (; cc < ncols; cc += 64) {
+            float v[32];
+            tmem_ld32_issue(lane_addr + (uint32_t)cc, v);
+            tmem_ld_wait(v);
+            if (cc + 64 >= ncols) LIK_RELEASE_ACC();
+            affine32(v, &ctl->col_scale[wg][cc], &ctl->col_bias[wg][cc]);  // bias is -inf past ncols
+            fold32<ARGMAX>(v, c0 + cc, run_m, run_i);
+          }
+        } else {
+          for (; cc + 32 <= ncols; cc += 64) {
+            float v[32];
+            tmem_ld32_issue(lane_addr + (uint32_t)cc, v);
+            tmem_ld_wait(v);
+            if (cc + 64 >= ncols) LIK_RELEASE_ACC();
+            fold32<ARGMAX>(v, c0 + cc, run_m, run_i);
+          }
+          if (cc < ncols) {
+            float v[32];
+            tmem_ld32_issue(lane_addr + (uint32_t)cc, v);
+            tmem_ld_wait(v);
+            LIK_RELEASE_ACC();
+            const int lim = ncols - cc;
+#pragma unroll
+            for (int i = 1; i < 32; ++i)
+              if (i >= lim) v[i] = -INFINITY;
+            fold32<ARGMAX>(v, c0 + cc, run_m, run_i);
+          }
         }
 #undef LIK_RELEASE_ACC
         if (wq == 0 && lane == 0 && sub == 0) TRACE(3 + wg);
