@@ -43,6 +43,8 @@ constexpr int SUB_WARPS = 4;         // barrier arrivals are one per warp (elect
 constexpr int GROUP_WARPS = 8;
 constexpr long long WAIT_LIMIT_CYCLES = 4000000000ll;  // about 2 s per wait at 2 GHz
 constexpr int LEN_FLAG_MASKED = 1 << 30;
+constexpr uint32_t TRY_WAIT_HINT_NS = 20000;  // how long one try_wait may keep the thread suspended
+constexpr int UNIT_RING = 8;                  // slots of the producer -> epilogue unit ring
 
 // ---------------------------------------------------------------------------------------------
 // PTX wrappers
@@ -62,10 +64,10 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
-      : "r"(bar), "r"(parity)
+      : "r"(bar), "r"(parity), "r"(TRY_WAIT_HINT_NS)
       : "memory");
   return ok != 0;
 }
@@ -173,6 +175,41 @@ __device__ __forceinline__ void affine32(float (&v)[32], const float* scale, con
   }
 }
 
+// Partial chunk of `lim` (1..31) columns: loaded as pieces of 16, 8, 4, 2 and 1 columns according to
+// the bits of lim into v[0..15], v[16..23], v[24..27], v[28..29], v[30]; pieces that are absent keep
+// the value the caller put there.  Piece n starts at column (lim with the bits below 2n cleared).
+__device__ __forceinline__ void tmem_ld_tail(uint32_t taddr, int lim, float (&v)[32]) {
+  if (lim & 16) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];" : "+f"(v[0]), "+f"(v[1]), "+f"(v[2]), "+f"(v[3]), "+f"(v[4]), "+f"(v[5]), "+f"(v[6]), "+f"(v[7]), "+f"(v[8]), "+f"(v[9]), "+f"(v[10]), "+f"(v[11]), "+f"(v[12]), "+f"(v[13]), "+f"(v[14]), "+f"(v[15]) : "r"(taddr + (uint32_t)(lim & 0)) : "memory");
+  }
+  if (lim & 8) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];" : "+f"(v[16]), "+f"(v[17]), "+f"(v[18]), "+f"(v[19]), "+f"(v[20]), "+f"(v[21]), "+f"(v[22]), "+f"(v[23]) : "r"(taddr + (uint32_t)(lim & 16)) : "memory");
+  }
+  if (lim & 4) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0, %1, %2, %3}, [%4];" : "+f"(v[24]), "+f"(v[25]), "+f"(v[26]), "+f"(v[27]) : "r"(taddr + (uint32_t)(lim & 24)) : "memory");
+  }
+  if (lim & 2) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x2.b32 {%0, %1}, [%2];" : "+f"(v[28]), "+f"(v[29]) : "r"(taddr + (uint32_t)(lim & 28)) : "memory");
+  }
+  if (lim & 1) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];" : "+f"(v[30]) : "r"(taddr + (uint32_t)(lim & 30)) : "memory");
+  }
+  asm volatile("tcgen05.wait::ld.sync.aligned;" : "+f"(v[0]), "+f"(v[1]), "+f"(v[2]), "+f"(v[3]), "+f"(v[4]), "+f"(v[5]), "+f"(v[6]), "+f"(v[7]), "+f"(v[8]), "+f"(v[9]), "+f"(v[10]), "+f"(v[11]), "+f"(v[12]), "+f"(v[13]), "+f"(v[14]), "+f"(v[15]), "+f"(v[16]), "+f"(v[17]), "+f"(v[18]), "+f"(v[19]), "+f"(v[20]), "+f"(v[21]), "+f"(v[22]), "+f"(v[23]), "+f"(v[24]), "+f"(v[25]), "+f"(v[26]), "+f"(v[27]), "+f"(v[28]), "+f"(v[29]), "+f"(v[30]) : : "memory");
+}
+// Column (relative to the chunk) of the first element of a tmem_ld_tail() array that equals cmax.
+__device__ __forceinline__ int tail_first_match(const float (&v)[32], float cmax, int lim) {
+  unsigned m = 0;
+#pragma unroll
+  for (int i = 0; i < 31; ++i)
+    if (v[i] == cmax) m |= 1u << i;
+  const int p = __ffs((int)m) - 1;  // array position; pieces are stored in ascending column order
+  if (p < 16) return p;
+  if (p < 24) return (lim & 16) + (p - 16);
+  if (p < 28) return (lim & 24) + (p - 24);
+  if (p < 30) return (lim & 28) + (p - 28);
+  return lim & 30;
+}
+
 // Shared-memory matrix descriptor: K-major operand, 128-byte swizzle, 8-row groups 1024 bytes apart.
 __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
   uint64_t d = 0;
@@ -222,6 +259,8 @@ struct SharedCtl {
   unsigned long long acc_full[2], acc_empty[2];
   unsigned long long grp_bar[2], sub_bar[2];
   uint32_t stage_info[8];
+  int2 unit_info[UNIT_RING];    // per work unit: x = document length | LEN_FLAG_MASKED, y = its first row
+  volatile int units_posted;    // units published in unit_info so far
   uint32_t tmem_base;
   volatile int abort_flag;
   int seg_off[2][TILE_M], seg_len[2][TILE_M], seg_q[2][TILE_M];
@@ -268,21 +307,42 @@ namespace {
 #define TRACE(role)
 #endif
 
-// Bounded wait.  Returns false when the CTA is aborting.
-__device__ __forceinline__ bool wait_bar(unsigned long long* bar, uint32_t parity, SharedCtl* ctl, int* status) {
-  const uint32_t b = smem_u32(bar);
-  if (mbar_try_wait(b, parity)) return true;
+// Bounded wait.  Returns false when the CTA is aborting.  The first probe lets the hardware suspend
+// the thread until the phase completes (or the hint expires), so the common case costs two
+// instructions; everything else lives in one out-of-line function.
+__device__ __noinline__ bool wait_bar_slow(uint32_t b, uint32_t parity, SharedCtl* ctl, int* status) {
   const long long t0 = clock64();
-  int spins = 0;
   while (true) {
     if (mbar_try_wait(b, parity)) return true;
     if (ctl->abort_flag) return false;
-    if ((++spins & 63) == 0 && clock64() - t0 > WAIT_LIMIT_CYCLES) {
+    if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
       ctl->abort_flag = 1;
       if (status) atomicOr(status, LIK_DEV_WAIT_TIMEOUT);
       return false;
     }
   }
+}
+__device__ __forceinline__ bool wait_bar(unsigned long long* bar, uint32_t parity, SharedCtl* ctl, int* status) {
+  const uint32_t b = smem_u32(bar);
+  if (mbar_try_wait(b, parity)) return true;
+  return wait_bar_slow(b, parity, ctl, status);
+}
+// Bounded wait until the producer has published unit `uc` of this CTA in the unit ring.
+__device__ __noinline__ bool wait_posted_slow(SharedCtl* ctl, int uc, int* status) {
+  const long long t0 = clock64();
+  while (true) {
+    if (ctl->units_posted > uc) return true;
+    if (ctl->abort_flag) return false;
+    if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
+      ctl->abort_flag = 1;
+      if (status) atomicOr(status, LIK_DEV_WAIT_TIMEOUT);
+      return false;
+    }
+  }
+}
+__device__ __forceinline__ bool wait_posted(SharedCtl* ctl, int uc, int* status) {
+  if (ctl->units_posted > uc) return true;
+  return wait_posted_slow(ctl, uc, status);
 }
 
 // Query tiles of tile-group g: tiles [g*mt, min((g+1)*mt, n_tiles)).
@@ -440,6 +500,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
       mbar_init(smem_u32(&ctl->sub_bar[a]), SUB_WARPS);
     }
     ctl->abort_flag = 0;
+    ctl->units_posted = 0;
     fence_barrier_init();
     prefetch_tmap(&q_map);
     for (int i = 0; i < 4; ++i) prefetch_tmap(&d_maps.m[i]);
@@ -507,19 +568,14 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
         // which accumulators this unit feeds: both resident tiles, or (one tile) alternating with the unit count
         const uint32_t acc_bits = P.mt == 2 ? (tiles_here == 2 ? (STAGE_ACC0 | STAGE_ACC1) : STAGE_ACC0)
                                             : ((uc & 1) ? STAGE_ACC1 : STAGE_ACC0);
-        if (dlen <= 0 && (first || last_unit_of_grp)) {
-          // an empty document carries no stage, but the group hand-shake it would have carried must still happen
-          PROF_T0(p_d0);
-          ok = wait_bar(&ctl->d_empty[st], ph ^ 1, ctl, P.status);
-          PROF_ADD(1, p_d0);
-          if (!ok) break;
-          ctl->stage_info[st] = first | (last_unit_of_grp ? STAGE_LAST : 0u);
-          mbar_arrive(smem_u32(&ctl->d_full[st]));
-          ++n_dload;
-          if (++st == (uint32_t)P.stages) { st = 0; ph ^= 1; }
-        }
-        for (int c0 = 0; c0 < dlen; c0 += TILE_N) {
-          const int ncols = min(TILE_N, dlen - c0);
+        // publish the unit for the epilogue groups, then its stages; an empty document still sends one
+        // (empty) stage so that every unit passes through the same hand-shakes
+        ctl->unit_info[uc & (UNIT_RING - 1)] = make_int2(dlen | (dmasked ? LEN_FLAG_MASKED : 0), (int)drow0);
+        __threadfence_block();
+        ctl->units_posted = (int)uc + 1;
+        int c0 = 0;
+        do {
+          const int ncols = max(0, min(TILE_N, dlen - c0));
           const int boxes = (ncols + BOX_ROWS - 1) / BOX_ROWS;
           PROF_T0(p_d);
           ok = wait_bar(&ctl->d_empty[st], ph ^ 1, ctl, P.status);
@@ -531,21 +587,20 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
           if (c0 == 0) info |= first;
           if (last_unit_of_grp && c0 + TILE_N >= dlen) info |= STAGE_LAST;
           ctl->stage_info[st] = info;
-#ifdef LIK_ABLATE_TMA
-          mbar_arrive(full);
-          const CUtensorMap* map = &d_maps.m[boxes - 1];
-          for (int sl = 0; sl < P.n_slabs - 2; ++sl)
-#else
-          mbar_arrive_expect_tx(full, (uint32_t)(boxes * BOX_ROWS * SLAB_BYTES_ROW * P.n_slabs));
-          const CUtensorMap* map = &d_maps.m[boxes - 1];
-          for (int sl = 0; sl < P.n_slabs; ++sl)
-#endif
-            tma_load_2d(smem_u32(d_smem + (size_t)st * d_stage_bytes + sl * TILE_N * SLAB_BYTES_ROW), map, sl * x_per_slab,
-                        (int)(drow0 + c0), full);
+          if (boxes > 0) {
+            mbar_arrive_expect_tx(full, (uint32_t)(boxes * BOX_ROWS * SLAB_BYTES_ROW * P.n_slabs));
+            const CUtensorMap* map = &d_maps.m[boxes - 1];
+            for (int sl = 0; sl < P.n_slabs; ++sl)
+              tma_load_2d(smem_u32(d_smem + (size_t)st * d_stage_bytes + sl * TILE_N * SLAB_BYTES_ROW), map, sl * x_per_slab,
+                          (int)(drow0 + c0), full);
+          } else {
+            mbar_arrive(full);
+          }
           ++n_dload;
           if (++st == (uint32_t)P.stages) { st = 0; ph ^= 1; }
           TRACE(0);
-        }
+          c0 += TILE_N;
+        } while (c0 < dlen);
       }
       if (ok) {
         // tell the issuer that the stream has ended
@@ -559,16 +614,16 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
       PROF_FLUSH(true);
       if (!ok) {
         // aborting: let the copies already issued land before the CTA goes away
-        const uint32_t issued = n_dload < (uint32_t)P.stages ? n_dload : (uint32_t)P.stages;
-        for (uint32_t i = 0; i < issued; ++i) {
-          const uint32_t n = n_dload - 1 - i;
-          const uint32_t bar = smem_u32(&ctl->d_full[n % P.stages]);
-          for (int spin = 0; spin < (1 << 20) && !mbar_try_wait(bar, (n / P.stages) & 1); ++spin) {
+        for (uint32_t i = 1; i <= (uint32_t)P.stages && i <= n_dload; ++i) {
+          const bool wrapped = i > st;  // that use lies before the last wrap of the ring
+          const uint32_t slot = wrapped ? st + (uint32_t)P.stages - i : st - i;
+          const uint32_t bar = smem_u32(&ctl->d_full[slot]);
+          for (int spin = 0; spin < (1 << 16) && !mbar_try_wait(bar, wrapped ? ph ^ 1 : ph); ++spin) {
           }
         }
         if (n_qload) {
           const uint32_t bar = smem_u32(&ctl->q_full);
-          for (int spin = 0; spin < (1 << 20) && !mbar_try_wait(bar, (n_qload - 1) & 1); ++spin) {
+          for (int spin = 0; spin < (1 << 16) && !mbar_try_wait(bar, (n_qload - 1) & 1); ++spin) {
           }
         }
       }
@@ -607,7 +662,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
           q_ph ^= 1;
         }
         const uint32_t ncols = info & STAGE_COLS_MASK;
-        if (ncols) {
+        {
           const uint32_t idesc = idesc0 | (((ncols + 15) >> 4) << 18);  // N / 8 in bits 17..22
           const uint64_t b_stage = b_desc0 + (uint64_t)(st * stage_desc);
 #pragma unroll 1  // one copy of the issue sequence: it stays in the instruction cache between the two groups
@@ -625,11 +680,9 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
             uint64_t a_desc = a_desc0 + (uint64_t)(a * a_tile1);
             uint64_t b_desc = b_stage;
             PROF_T0(m_i);
-#ifdef LIK_ABLATE_MMA
-            if (k_steps == 12345) {
-#else
-            if (k_steps == 8) {
-#endif
+            if (ncols == 0) {
+              // empty document: the accumulator still changes hands so that both sides keep their phase
+            } else if (k_steps == 8) {
               // the common width (128 two-byte or 256 one-byte elements): straight-line issue
               const uint64_t a1 = a_desc + (uint64_t)((TILE_M * SLAB_BYTES_ROW) >> 4);
               const uint64_t b1 = b_desc + (uint64_t)((TILE_N * SLAB_BYTES_ROW) >> 4);
@@ -644,11 +697,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
             } else {
               int left = k_steps;
               uint32_t accum = 0;
-#ifdef LIK_ABLATE_MMA
-              for (int sl = 0; sl < n_slabs - 2; ++sl) {
-#else
               for (int sl = 0; sl < n_slabs; ++sl) {
-#endif
                 tc_mma<FP8>(d_tmem, a_desc, b_desc, idesc, accum);
                 accum = 1;
                 if (left > 1) tc_mma<FP8>(d_tmem, a_desc + 2, b_desc + 2, idesc, 1u);
@@ -678,7 +727,8 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
     // =========================== epilogue groups ===========================
     // Group g (eight warps) drains accumulator g.  Its two halves split the 32-column chunks of a tile
     // between them (even chunks / odd chunks); half 1 hands its per-row result to half 0, which sums
-    // the rows of every query and writes the score.
+    // the rows of every query and writes the score.  (group, document) advance locally; a document's
+    // length and first row come from the producer's unit ring.
     const int e = warp - 2;
     const int wg = e >> 3;                   // accumulator / epilogue group
     const int sub = (e >> 2) & 1;            // half of the group
@@ -687,15 +737,18 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
     const int row = quad * 32 + lane;        // accumulator row == query token slot in the tile
     const int et = wq * 32 + lane;           // thread index inside the half (0..127)
     const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(wg * ACC_COLS);
+    const uint32_t acc_full_bar = smem_u32(&ctl->acc_full[wg]);
+    const uint32_t acc_empty_bar = smem_u32(&ctl->acc_empty[wg]);
     int cur_grp = -1;
     uint32_t n_acc = 0, n_grp_sync = 0, n_sub_sync = 0, n_doc = 0;
-    long long uc = 0;
+    int uc = 0;
     bool ok = true;
-    // per-row state for the resident query tile
+    // per-row / per-warp state for the resident query tile
     bool have_tile = false, in_seg = false, row_ok = false, aligned = false;
-    int my_q = 0, my_s = 0;
     float my_qf = 1.f;
     int tile_id = 0;
+    long long arg_off = -1;   // ARGMAX: offset of this row's slot for document 0 (-1: row stores nothing)
+    long long warp_out = -1;  // aligned tiles: offset of this warp's query score for document 0
     // bounded rendezvous of the whole group / of half 0
 #define LIK_GRP_SYNC()                                                \
   do {                                                                \
@@ -712,12 +765,29 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
     ++n_sub_sync;                                                     \
   } while (0)
 
+    int grp = 0, doc = 0, in_grp = 0;
+    if (u_begin < u_end) {
+      unit_decode(P, u_begin, grp, doc);
+      in_grp = P.pairing == LIK_PAIR_CROSS ? 0 : doc - grp * P.group;
+    }
+    const bool cross = P.pairing == LIK_PAIR_CROSS;
+    const int n_my_units = (int)(u_end - u_begin);
     PROF_DECL();
     TRACE_DECL();
     PROF_T0(e_all);
-    for (long long u = u_begin; u < u_end && ok; ++u, ++uc) {
-      LIK_NEXT_UNIT();
-      const int acc = P.mt == 2 ? wg : (int)(uc & 1);
+    for (; uc < n_my_units && ok; ++uc) {
+      if (uc > 0) {  // next (group, document)
+        ++doc;
+        if (cross) {
+          if (doc == P.n_d) {
+            doc = 0;
+            ++grp;
+          }
+        } else if (++in_grp == P.group) {
+          in_grp = 0;
+          ++grp;
+        }
+      }
       if (grp != cur_grp) {
         cur_grp = grp;
         // (re)build the segment table of this group's tile `wg` (mt == 2) or tile 0 (mt == 1: both groups)
@@ -769,31 +839,59 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
         if (!ok) break;
         in_seg = false;
         row_ok = false;
+        arg_off = -1;
+        warp_out = -1;
         aligned = have_tile && ctl->warp_aligned[wg] != 0;
         if (have_tile) {
           const int sg = ctl->row_seg[wg][row];
           if (sg >= 0) {
             in_seg = true;
-            my_q = ctl->seg_q[wg][sg];
-            my_s = row - ctl->seg_off[wg][sg] + ti.chunk * TILE_M;
+            const int my_q = ctl->seg_q[wg][sg];
+            const int my_s = row - ctl->seg_off[wg][sg] + ti.chunk * TILE_M;
             const long long qrow = ti.row0 + row;
             row_ok = row_valid(P.q, qrow);
             my_qf = row_factor(P.q, qrow);
+            if (ARGMAX && my_s < P.argmax_stride)
+              arg_off = (cross ? (long long)my_q * P.n_d : 0ll) * P.argmax_stride + my_s;
           }
+          const int sg0 = ctl->row_seg[wg][quad * 32];
+          if (aligned && sg0 >= 0) warp_out = cross ? (long long)ctl->seg_q[wg][sg0] * P.n_d : 0ll;
         }
       }
       // with two resident tiles each group handles its own tile for every document; with one tile the
       // groups alternate documents
-      const bool mine = P.mt == 2 ? have_tile : (acc == wg);
+      const bool mine = P.mt == 2 ? have_tile : ((uc & 1) == wg);
       if (!mine) continue;
 
-      const bool use_cols = SCALED || dmasked;  // per-column multiplier / additive mask needed for this document
+      // the first wait of the unit also makes sure the producer has published it
+      PROF_T0(e_w);
+      ok = wait_bar(&ctl->acc_full[wg], n_acc & 1, ctl, P.status);
+      if (ok) ok = wait_posted(ctl, uc, P.status);
+      PROF_ADD(8, e_w);
+      if (!ok) break;
+      __threadfence_block();
+      const int2 uinfo = ctl->unit_info[uc & (UNIT_RING - 1)];
+      const int dlen = uinfo.x & ~LEN_FLAG_MASKED;
+      const long long drow0 = uinfo.y;
+      const bool use_cols = SCALED || (uinfo.x & LEN_FLAG_MASKED) != 0;  // per-column multiplier / additive mask needed
       float run_m = -INFINITY;
       int run_i = -1;
-      for (int c0 = 0; c0 < dlen && ok; c0 += TILE_N) {
-        const int ncols = min(TILE_N, dlen - c0);
+      int c0 = 0;
+      do {
+        const int ncols = max(0, min(TILE_N, dlen - c0));
+        if (c0 > 0) {
+          PROF_T0(e_w2);
+          ok = wait_bar(&ctl->acc_full[wg], n_acc & 1, ctl, P.status);
+          PROF_ADD(8, e_w2);
+          if (!ok) break;
+        }
+        ++n_acc;
+        if (wq == 0 && lane == 0 && sub == 0) TRACE(3 + wg);
+        prof_tiles(prof);
+        PROF_T0(e_f);
         if (use_cols) {
-          LIK_GRP_SYNC();  // the previous tile's readers are done with the column arrays
+          // per-column arrays of this tile (the accumulator waits meanwhile: only masked / scaled documents pay)
+          LIK_GRP_SYNC();  // the previous tile's readers are done with the arrays
           if (!ok) break;
           for (int c = sub * EPI_THREADS + et; c < ((ncols + 31) & ~31); c += 2 * EPI_THREADS) {
             float sc = 1.f, bi = -INFINITY;
@@ -808,21 +906,13 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
           LIK_GRP_SYNC();
           if (!ok) break;
         }
-        PROF_T0(e_w);
-        ok = wait_bar(&ctl->acc_full[wg], n_acc & 1, ctl, P.status);
-        PROF_ADD(8, e_w);
-        if (wq == 0 && lane == 0 && sub == 0) TRACE(3 + wg);
-        prof_tiles(prof);
-        PROF_T0(e_f);
-        if (!ok) break;
-        ++n_acc;
         tc_fence_after();
         // the accumulator goes back to the issuer as soon as this warp's last columns sit in registers
 #define LIK_RELEASE_ACC()                                          \
   do {                                                             \
     tc_fence_before();                                             \
     __syncwarp();                                                  \
-    if (lane == 0) mbar_arrive(smem_u32(&ctl->acc_empty[wg]));     \
+    if (lane == 0) mbar_arrive(acc_empty_bar);                     \
   } while (0)
         // chunks of this half: cc, cc + 64, ...; only the tile's last chunk can be partial
         int cc = sub * 32;
@@ -845,21 +935,30 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
             fold32<ARGMAX>(v, c0 + cc, run_m, run_i);
           }
           if (cc < ncols) {
-            float v[32];
-            tmem_ld32_issue(lane_addr + (uint32_t)cc, v);
-            tmem_ld_wait(v);
-            LIK_RELEASE_ACC();
+            // partial chunk: pieces of 16, 8, 4, 2 and 1 columns as the bits of its width say, absent
+            // pieces stay at -inf, so nothing needs masking
             const int lim = ncols - cc;
+            float v[32];
 #pragma unroll
-            for (int i = 1; i < 32; ++i)
-              if (i >= lim) v[i] = -INFINITY;
-            fold32<ARGMAX>(v, c0 + cc, run_m, run_i);
+            for (int i = 0; i < 32; ++i) v[i] = -INFINITY;
+            tmem_ld_tail(lane_addr + (uint32_t)cc, lim, v);
+            LIK_RELEASE_ACC();
+            const float cmax = max32(v);
+            if (ARGMAX) {
+              if (cmax > run_m) {
+                run_i = c0 + cc + tail_first_match(v, cmax, lim);
+                run_m = cmax;
+              }
+            } else {
+              run_m = fmaxf(run_m, cmax);
+            }
           }
         }
 #undef LIK_RELEASE_ACC
         if (wq == 0 && lane == 0 && sub == 0) TRACE(3 + wg);
         PROF_ADD(9, e_f);
-      }
+        c0 += TILE_N;
+      } while (c0 < dlen);
       if (!ok) break;
       PROF_T0(e_e);
       // ---- end of document: half 1 hands over, half 0 merges (lower column wins a tie) ----
@@ -888,19 +987,11 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
       // one value per row, summed per query in a fixed order
       const bool has_winner = ARGMAX ? (run_i >= 0) : (run_m != -INFINITY);
       const float val = (in_seg && row_ok && has_winner) ? run_m * my_qf : 0.f;
-      if (ARGMAX && in_seg && my_s < P.argmax_stride) {
-        const long long slot = P.pairing == LIK_PAIR_CROSS ? (long long)my_q * P.n_d + doc : (long long)doc;
-        P.argmax[slot * P.argmax_stride + my_s] = has_winner ? run_i : -1;
-      }
+      if (ARGMAX && arg_off >= 0) P.argmax[arg_off + (long long)doc * P.argmax_stride] = has_winner ? run_i : -1;
       if (aligned) {
         // one query per warp: a shuffle tree (fixed order) replaces the shared-memory pass
         const float sum = warp_sum(val);
-        const int sg0 = ctl->row_seg[wg][quad * 32];
-        if (lane == 0 && sg0 >= 0) {
-          const int qq = ctl->seg_q[wg][sg0];
-          const long long o = P.pairing == LIK_PAIR_CROSS ? (long long)qq * P.n_d + doc : (long long)doc;
-          P.scores[o] = sum;
-        }
+        if (lane == 0 && warp_out >= 0) P.scores[warp_out + doc] = sum;
         PROF_ADD(10, e_e);
         if (wq == 0 && lane == 0) TRACE(3 + wg);
         continue;
@@ -918,7 +1009,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
         if (lane == 0) {
           const int qq = ctl->seg_q[wg][sg];
           if (P.q_chunks == 1) {
-            const long long o = P.pairing == LIK_PAIR_CROSS ? (long long)qq * P.n_d + doc : (long long)doc;
+            const long long o = cross ? (long long)qq * P.n_d + doc : (long long)doc;
             P.scores[o] = sum;
           } else {
             P.partial[(long long)tile_id * P.n_d + doc] = sum;
