@@ -139,6 +139,30 @@ __device__ __forceinline__ float max32(const float (&v)[32]) {
   return fmaxf(max3(b0, b1, b2), b3);
 }
 
+__device__ __forceinline__ float min3(float a, float b, float c) {
+  float d;
+  asm("min.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+// Position (0..31) of the first element of v that equals cmax, where cmax is the maximum of v.
+// Compare / select / logic instructions share one half-rate pipe, which a per-element equality scan
+// would saturate, so the scan is arithmetic instead: key_i = (cmax - v_i) * 2^154 + i is exactly i
+// for a match and at least 32 (or +inf) otherwise, because two different floats never differ by
+// less than 2^-149; the scaling is split in two exact powers of two that cannot overflow for
+// |cmax| < 2^64.  The minimum key is the answer.
+__device__ __forceinline__ int first_match32(const float (&v)[32], float cmax) {
+  const float c2 = cmax * 0x1p64f;
+  float k[32];
+#pragma unroll
+  for (int i = 0; i < 32; ++i) k[i] = fmaf(fmaf(v[i], -0x1p64f, c2), 0x1p90f, (float)i);
+  float a0 = min3(k[0], k[1], k[2]), a1 = min3(k[3], k[4], k[5]), a2 = min3(k[6], k[7], k[8]);
+  float a3 = min3(k[9], k[10], k[11]), a4 = min3(k[12], k[13], k[14]), a5 = min3(k[15], k[16], k[17]);
+  float a6 = min3(k[18], k[19], k[20]), a7 = min3(k[21], k[22], k[23]), a8 = min3(k[24], k[25], k[26]);
+  float a9 = min3(k[27], k[28], k[29]);
+  float b0 = min3(a0, a1, a2), b1 = min3(a3, a4, a5), b2 = min3(a6, a7, a8), b3 = min3(a9, k[30], k[31]);
+  return (int)fminf(min3(b0, b1, b2), b3);
+}
+
 // Fold the maximum of one 32-column chunk into the running (max, argmax) of a row.  The column scan
 // only runs when the chunk beats the running maximum (strict: an equal value in a later chunk never
 // displaces an earlier winner) and returns the lowest matching column.
@@ -147,15 +171,7 @@ __device__ __forceinline__ void fold32(const float (&v)[32], int col0, float& ru
   const float cmax = max32(v);
   if (ARGMAX) {
     if (cmax > run_m) {
-      unsigned m0 = 0, m1 = 0, m2 = 0, m3 = 0;
-#pragma unroll
-      for (int i = 0; i < 32; i += 4) {
-        if (v[i + 0] == cmax) m0 |= 1u << (i + 0);
-        if (v[i + 1] == cmax) m1 |= 1u << (i + 1);
-        if (v[i + 2] == cmax) m2 |= 1u << (i + 2);
-        if (v[i + 3] == cmax) m3 |= 1u << (i + 3);
-      }
-      run_i = col0 + __ffs((int)(m0 | m1 | m2 | m3)) - 1;
+      run_i = col0 + first_match32(v, cmax);
       run_m = cmax;
     }
   } else {
@@ -198,11 +214,7 @@ __device__ __forceinline__ void tmem_ld_tail(uint32_t taddr, int lim, float (&v)
 }
 // Column (relative to the chunk) of the first element of a tmem_ld_tail() array that equals cmax.
 __device__ __forceinline__ int tail_first_match(const float (&v)[32], float cmax, int lim) {
-  unsigned m = 0;
-#pragma unroll
-  for (int i = 0; i < 31; ++i)
-    if (v[i] == cmax) m |= 1u << i;
-  const int p = __ffs((int)m) - 1;  // array position; pieces are stored in ascending column order
+  const int p = first_match32(v, cmax);  // array position; pieces are stored in ascending column order
   if (p < 16) return p;
   if (p < 24) return (lim & 16) + (p - 16);
   if (p < 28) return (lim & 24) + (p - 24);
@@ -299,12 +311,17 @@ namespace {
 #if LIK_TC_PROFILE == 3
 #define TRACE_DECL() int trace_n = 0
 #define TRACE(role)
+// per-chunk timestamps of one epilogue warp; `dep` makes the read wait for the value it names
+#define TRACE3(dep) do { if (blockIdx.x == 0 && warp == 2 && trace_n < 4096) { const long long t_ = clock64() + ((dep) == 12345.f ? 1 : 0); if (lane == 0) g_trace[3][trace_n] = t_; ++trace_n; } } while (0)
 #elif LIK_TC_PROFILE == 2
 #define TRACE_DECL() int trace_n = 0
 #define TRACE(role) do { if (blockIdx.x == 0 && trace_n < 4096) g_trace[role][trace_n++] = clock64(); } while (0)
 #else
 #define TRACE_DECL()
 #define TRACE(role)
+#endif
+#ifndef TRACE3
+#define TRACE3(dep)
 #endif
 
 // Bounded wait.  Returns false when the CTA is aborting.  The first probe lets the hardware suspend
@@ -929,10 +946,13 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
         } else {
           for (; cc + 32 <= ncols; cc += 64) {
             float v[32];
+            TRACE3(0.f);
             tmem_ld32_issue(lane_addr + (uint32_t)cc, v);
             tmem_ld_wait(v);
+            TRACE3(v[0] + v[31]);
             if (cc + 64 >= ncols) LIK_RELEASE_ACC();
             fold32<ARGMAX>(v, c0 + cc, run_m, run_i);
+            TRACE3(run_m);
           }
           if (cc < ncols) {
             // partial chunk: pieces of 16, 8, 4, 2 and 1 columns as the bits of its width say, absent
