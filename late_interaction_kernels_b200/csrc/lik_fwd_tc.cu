@@ -95,19 +95,25 @@ __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::
 __device__ __forceinline__ void tc_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
+// Both operand descriptors share their upper word (stride, version, swizzle mode); only the 14-bit
+// start-address field in the lower word moves, so the issuer carries 32-bit values and the 64-bit
+// descriptors are put together next to the instruction.
 template <bool FP8>
-__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t desc_hi, uint32_t idesc,
+                                       uint32_t accumulate) {
   if (FP8) {
     asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
-        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\tsetp.ne.b32 p, %5, 0;\n\t"
+        "mov.b64 da, {%1, %3};\n\tmov.b64 db, {%2, %3};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], da, db, %4, p;\n\t}" ::"r"(d_tmem),
+        "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "r"(accumulate)
         : "memory");
   } else {
     asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
-        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\tsetp.ne.b32 p, %5, 0;\n\t"
+        "mov.b64 da, {%1, %3};\n\tmov.b64 db, {%2, %3};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n\t}" ::"r"(d_tmem),
+        "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "r"(accumulate)
         : "memory");
   }
 }
@@ -653,8 +659,9 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
       uint32_t st = 0, ph = 0, q_ph = 0, acc_ph = 0;  // acc_ph: one phase bit per accumulator
       bool ok = true;
       const uint32_t q_tile_desc = (uint32_t)(q_tile_bytes >> 4);
-      const uint64_t a_desc0 = smem_desc_sw128(smem_u32(q_smem));
-      const uint64_t b_desc0 = smem_desc_sw128(smem_u32(d_smem));
+      const uint32_t desc_hi = (uint32_t)(smem_desc_sw128(0) >> 32);
+      const uint32_t a_desc0 = (uint32_t)smem_desc_sw128(smem_u32(q_smem));
+      const uint32_t b_desc0 = (uint32_t)smem_desc_sw128(smem_u32(d_smem));
       const uint32_t stage_desc = (uint32_t)(d_stage_bytes >> 4);
       const uint32_t idesc0 = instr_desc(P.ab_format, 0);
       const int k_steps = P.k_steps, n_slabs = P.n_slabs;
@@ -681,7 +688,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
         const uint32_t ncols = info & STAGE_COLS_MASK;
         {
           const uint32_t idesc = idesc0 | (((ncols + 15) >> 4) << 18);  // N / 8 in bits 17..22
-          const uint64_t b_stage = b_desc0 + (uint64_t)(st * stage_desc);
+          const uint32_t b_stage = b_desc0 + st * stage_desc;
 #pragma unroll 1  // one copy of the issue sequence: it stays in the instruction cache between the two groups
           for (int a = 0; a < 2; ++a) {
             if (!(info & (STAGE_ACC0 << a))) continue;
@@ -694,35 +701,35 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
             tc_fence_after();
             const uint32_t d_tmem = tmem_base + (uint32_t)(a * ACC_COLS);
             // descriptors differ only in the 16-byte-unit start address: add offsets to a base descriptor
-            uint64_t a_desc = a_desc0 + (uint64_t)(a * a_tile1);
-            uint64_t b_desc = b_stage;
+            uint32_t a_desc = a_desc0 + a * a_tile1;
+            uint32_t b_desc = b_stage;
             PROF_T0(m_i);
             if (ncols == 0) {
               // empty document: the accumulator still changes hands so that both sides keep their phase
             } else if (k_steps == 8) {
               // the common width (128 two-byte or 256 one-byte elements): straight-line issue
-              const uint64_t a1 = a_desc + (uint64_t)((TILE_M * SLAB_BYTES_ROW) >> 4);
-              const uint64_t b1 = b_desc + (uint64_t)((TILE_N * SLAB_BYTES_ROW) >> 4);
-              tc_mma<FP8>(d_tmem, a_desc, b_desc, idesc, 0u);
-              tc_mma<FP8>(d_tmem, a_desc + 2, b_desc + 2, idesc, 1u);
-              tc_mma<FP8>(d_tmem, a_desc + 4, b_desc + 4, idesc, 1u);
-              tc_mma<FP8>(d_tmem, a_desc + 6, b_desc + 6, idesc, 1u);
-              tc_mma<FP8>(d_tmem, a1, b1, idesc, 1u);
-              tc_mma<FP8>(d_tmem, a1 + 2, b1 + 2, idesc, 1u);
-              tc_mma<FP8>(d_tmem, a1 + 4, b1 + 4, idesc, 1u);
-              tc_mma<FP8>(d_tmem, a1 + 6, b1 + 6, idesc, 1u);
+              const uint32_t a1 = a_desc + (uint32_t)((TILE_M * SLAB_BYTES_ROW) >> 4);
+              const uint32_t b1 = b_desc + (uint32_t)((TILE_N * SLAB_BYTES_ROW) >> 4);
+              tc_mma<FP8>(d_tmem, a_desc, b_desc, desc_hi, idesc, 0u);
+              tc_mma<FP8>(d_tmem, a_desc + 2, b_desc + 2, desc_hi, idesc, 1u);
+              tc_mma<FP8>(d_tmem, a_desc + 4, b_desc + 4, desc_hi, idesc, 1u);
+              tc_mma<FP8>(d_tmem, a_desc + 6, b_desc + 6, desc_hi, idesc, 1u);
+              tc_mma<FP8>(d_tmem, a1, b1, desc_hi, idesc, 1u);
+              tc_mma<FP8>(d_tmem, a1 + 2, b1 + 2, desc_hi, idesc, 1u);
+              tc_mma<FP8>(d_tmem, a1 + 4, b1 + 4, desc_hi, idesc, 1u);
+              tc_mma<FP8>(d_tmem, a1 + 6, b1 + 6, desc_hi, idesc, 1u);
             } else {
               int left = k_steps;
               uint32_t accum = 0;
               for (int sl = 0; sl < n_slabs; ++sl) {
-                tc_mma<FP8>(d_tmem, a_desc, b_desc, idesc, accum);
+                tc_mma<FP8>(d_tmem, a_desc, b_desc, desc_hi, idesc, accum);
                 accum = 1;
-                if (left > 1) tc_mma<FP8>(d_tmem, a_desc + 2, b_desc + 2, idesc, 1u);
-                if (left > 2) tc_mma<FP8>(d_tmem, a_desc + 4, b_desc + 4, idesc, 1u);
-                if (left > 3) tc_mma<FP8>(d_tmem, a_desc + 6, b_desc + 6, idesc, 1u);
+                if (left > 1) tc_mma<FP8>(d_tmem, a_desc + 2, b_desc + 2, desc_hi, idesc, 1u);
+                if (left > 2) tc_mma<FP8>(d_tmem, a_desc + 4, b_desc + 4, desc_hi, idesc, 1u);
+                if (left > 3) tc_mma<FP8>(d_tmem, a_desc + 6, b_desc + 6, desc_hi, idesc, 1u);
                 left -= 4;
-                a_desc += (uint64_t)((TILE_M * SLAB_BYTES_ROW) >> 4);
-                b_desc += (uint64_t)((TILE_N * SLAB_BYTES_ROW) >> 4);
+                a_desc += (uint32_t)((TILE_M * SLAB_BYTES_ROW) >> 4);
+                b_desc += (uint32_t)((TILE_N * SLAB_BYTES_ROW) >> 4);
               }
             }
             PROF_ADD(13, m_i);
