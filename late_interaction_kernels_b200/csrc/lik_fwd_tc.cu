@@ -39,7 +39,6 @@ constexpr int SLAB_BYTES_ROW = 128; // one swizzle span: 64 two-byte or 128 one-
 constexpr int MAX_SLABS = 2;
 constexpr int NUM_THREADS = 640;
 constexpr int EPI_THREADS = 128;     // threads per half of an epilogue group (one per accumulator row)
-constexpr int SUB_WARPS = 4;         // barrier arrivals are one per warp (elected lane), not one per thread
 constexpr int GROUP_WARPS = 8;
 constexpr long long WAIT_LIMIT_CYCLES = 4000000000ll;  // about 2 s per wait at 2 GHz
 constexpr int LEN_FLAG_MASKED = 1 << 30;
@@ -275,7 +274,7 @@ struct SharedCtl {
   unsigned long long q_full, q_empty;
   unsigned long long d_full[8], d_empty[8];
   unsigned long long acc_full[2], acc_empty[2];
-  unsigned long long grp_bar[2], sub_bar[2];
+  int grp_abort[2];             // set by a group's first warp when its bounded wait gave up
   uint32_t stage_info[8];
   int2 unit_info[UNIT_RING];    // per work unit: x = document length | LEN_FLAG_MASKED, y = its first row
   volatile int units_posted;    // units published in unit_info so far
@@ -519,8 +518,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
     for (int a = 0; a < 2; ++a) {
       mbar_init(smem_u32(&ctl->acc_full[a]), 1);
       mbar_init(smem_u32(&ctl->acc_empty[a]), GROUP_WARPS);
-      mbar_init(smem_u32(&ctl->grp_bar[a]), GROUP_WARPS);
-      mbar_init(smem_u32(&ctl->sub_bar[a]), SUB_WARPS);
+      ctl->grp_abort[a] = 0;
     }
     ctl->abort_flag = 0;
     ctl->units_posted = 0;
@@ -761,10 +759,9 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
     const int row = quad * 32 + lane;        // accumulator row == query token slot in the tile
     const int et = wq * 32 + lane;           // thread index inside the half (0..127)
     const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(wg * ACC_COLS);
-    const uint32_t acc_full_bar = smem_u32(&ctl->acc_full[wg]);
     const uint32_t acc_empty_bar = smem_u32(&ctl->acc_empty[wg]);
     int cur_grp = -1;
-    uint32_t n_acc = 0, n_grp_sync = 0, n_sub_sync = 0, n_doc = 0;
+    uint32_t n_acc = 0, n_emit = 0, n_doc = 0;
     int uc = 0;
     bool ok = true;
     // per-row / per-warp state for the resident query tile
@@ -773,20 +770,22 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
     int tile_id = 0;
     long long arg_off = -1;   // ARGMAX: offset of this row's slot for document 0 (-1: row stores nothing)
     long long warp_out = -1;  // aligned tiles: offset of this warp's query score for document 0
-    // bounded rendezvous of the whole group / of half 0
-#define LIK_GRP_SYNC()                                                \
-  do {                                                                \
-    __syncwarp();                                                     \
-    if (lane == 0) mbar_arrive(smem_u32(&ctl->grp_bar[wg]));          \
-    ok = wait_bar(&ctl->grp_bar[wg], n_grp_sync & 1, ctl, P.status);  \
-    ++n_grp_sync;                                                     \
-  } while (0)
-#define LIK_SUB_SYNC()                                                \
-  do {                                                                \
-    __syncwarp();                                                     \
-    if (lane == 0) mbar_arrive(smem_u32(&ctl->sub_bar[wg]));          \
-    ok = wait_bar(&ctl->sub_bar[wg], n_sub_sync & 1, ctl, P.status);  \
-    ++n_sub_sync;                                                     \
+    // Rendezvous of the whole group / of half 0 on hardware named barriers: a waiting warp issues
+    // nothing.  Nobody waits on anything else between two of them, so every warp of the group always
+    // arrives; the only bounded waits of a group (on the accumulator) are done by its first warp, which
+    // then tells the others through grp_abort whether to go on.
+    const bool leader = (e & 7) == 0;
+#define LIK_GRP_SYNC() asm volatile("bar.sync %0, %1;" ::"r"(1 + wg), "r"(2 * EPI_THREADS) : "memory")
+#define LIK_SUB_SYNC() asm volatile("bar.sync %0, %1;" ::"r"(3 + wg), "r"(EPI_THREADS) : "memory")
+#define LIK_GROUP_WAIT_ACC(also_posted)                                              \
+  do {                                                                               \
+    if (leader) {                                                                    \
+      bool ok_ = wait_bar(&ctl->acc_full[wg], n_acc & 1, ctl, P.status);             \
+      if (ok_ && (also_posted)) ok_ = wait_posted(ctl, uc, P.status);                \
+      if (!ok_ && lane == 0) ctl->grp_abort[wg] = 1;                                 \
+    }                                                                                \
+    LIK_GRP_SYNC();                                                                  \
+    ok = ctl->grp_abort[wg] == 0;                                                    \
   } while (0)
 
     int grp = 0, doc = 0, in_grp = 0;
@@ -819,7 +818,6 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
         tile_id = grp * P.mt + m;
         have_tile = tile_id < n_tiles;
         LIK_GRP_SYNC();  // everyone in the group is done reading the old table
-        if (!ok) break;
         TileInfo ti{};
         int nseg = 0;
         if (have_tile) {
@@ -834,7 +832,6 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
           }
         }
         LIK_GRP_SYNC();
-        if (!ok) break;
         if (have_tile && sub == 0 && et < nseg) {
           long long r0;
           int len;
@@ -860,7 +857,6 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
           for (int i = 0; i < l; ++i) ctl->row_seg[wg][off + i] = (short)et;
         }
         LIK_GRP_SYNC();
-        if (!ok) break;
         in_seg = false;
         row_ok = false;
         arg_off = -1;
@@ -889,11 +885,9 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
 
       // the first wait of the unit also makes sure the producer has published it
       PROF_T0(e_w);
-      ok = wait_bar(&ctl->acc_full[wg], n_acc & 1, ctl, P.status);
-      if (ok) ok = wait_posted(ctl, uc, P.status);
+      LIK_GROUP_WAIT_ACC(true);
       PROF_ADD(8, e_w);
       if (!ok) break;
-      __threadfence_block();
       const int2 uinfo = ctl->unit_info[uc & (UNIT_RING - 1)];
       const int dlen = uinfo.x & ~LEN_FLAG_MASKED;
       const long long drow0 = uinfo.y;
@@ -905,7 +899,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
         const int ncols = max(0, min(TILE_N, dlen - c0));
         if (c0 > 0) {
           PROF_T0(e_w2);
-          ok = wait_bar(&ctl->acc_full[wg], n_acc & 1, ctl, P.status);
+          LIK_GROUP_WAIT_ACC(false);
           PROF_ADD(8, e_w2);
           if (!ok) break;
         }
@@ -916,7 +910,6 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
         if (use_cols) {
           // per-column arrays of this tile (the accumulator waits meanwhile: only masked / scaled documents pay)
           LIK_GRP_SYNC();  // the previous tile's readers are done with the arrays
-          if (!ok) break;
           for (int c = sub * EPI_THREADS + et; c < ((ncols + 31) & ~31); c += 2 * EPI_THREADS) {
             float sc = 1.f, bi = -INFINITY;
             if (c < ncols) {
@@ -928,7 +921,6 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
             ctl->col_bias[wg][c] = bi;
           }
           LIK_GRP_SYNC();
-          if (!ok) break;
         }
         tc_fence_after();
         // the accumulator goes back to the issuer as soon as this warp's last columns sit in registers
@@ -997,7 +989,6 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
         if (ARGMAX) xi[row] = run_i;
       }
       LIK_GRP_SYNC();
-      if (!ok) break;
       if (sub == 1) continue;
       {
         const float m1 = xm[row];
@@ -1023,10 +1014,10 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
         if (wq == 0 && lane == 0) TRACE(3 + wg);
         continue;
       }
-      float* ebuf = ctl->emit[wg][n_sub_sync & 1];
+      float* ebuf = ctl->emit[wg][n_emit & 1];
+      ++n_emit;
       ebuf[row] = val;
       LIK_SUB_SYNC();
-      if (!ok) break;
       const int nseg = ctl->n_seg[wg];
       for (int sg = wq; sg < nseg; sg += 4) {
         const int off = ctl->seg_off[wg][sg], len = ctl->seg_len[wg][sg];
@@ -1048,6 +1039,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
     }
     PROF_ADD(7, e_all);
     PROF_FLUSH(warp == 2 && lane == 0);
+#undef LIK_GROUP_WAIT_ACC
 #undef LIK_GRP_SYNC
 #undef LIK_SUB_SYNC
   }
