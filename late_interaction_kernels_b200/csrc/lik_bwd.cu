@@ -346,9 +346,9 @@ constexpr int DQ_JC = 32;
 
 template <typename T, typename G, int CH>
 __global__ void __launch_bounds__(256) bwd_dq_fast_kernel(BwdParams P) {
-  __shared__ int s_t[DQ_JC][8];
-  __shared__ float s_g[DQ_JC];
-  __shared__ long long s_row0[DQ_JC];
+  // per (document of the chunk, query token of the CTA): winning document row (-1: none) and the weight
+  // g * row factor, prepared once by the whole CTA so that the gather loop is load + fma only
+  __shared__ int2 s_e[DQ_JC][8];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int i = blockIdx.x;
   const int s0 = blockIdx.y * 8;
@@ -369,47 +369,48 @@ __global__ void __launch_bounds__(256) bwd_dq_fast_kernel(BwdParams P) {
   long long p0;
   int count, j0;
   query_slots(P.pm, i, p0, count, j0);
-  const T* __restrict__ Dg = (const T*)P.d.data;
   const int lq = P.argmax_stride;
+  const long long pitch = P.d.row_stride;
+  const T* __restrict__ Dlane = (const T*)P.d.data + lane * 4;
+  bool lane_on[CH];
+#pragma unroll
+  for (int c = 0; c < CH; ++c) lane_on[c] = c * 128 + lane * 4 < P.dim;
+  const bool d_factor = P.d.inv_norm || P.d.scale || P.d.scale_scalar != 1.f;
   for (int jb = 0; jb < count; jb += DQ_JC) {
     __syncthreads();
     {
       // thread (jj, r): winner of document jb + jj for query token s0 + r
       const int jj = tid >> 3, r = tid & 7;
-      int t = -1;
-      if (jb + jj < count && s0 + r < lq) t = P.argmax[(p0 + jb + jj) * lq + s0 + r];
-      s_t[jj][r] = t;
-      if (tid < DQ_JC) {
-        const int j = jb + tid;
-        float g = 0.f;
-        long long r0 = 0;
-        if (j < count) {
-          g = P.g[p0 + j];
+      int2 e = make_int2(-1, 0);
+      if (jb + jj < count && s0 + r < lq) {
+        const int t = P.argmax[(p0 + jb + jj) * lq + s0 + r];
+        if (t >= 0) {
+          long long r0;
           int dl;
-          seq_bounds(P.d, j0 + j, r0, dl, nullptr);
+          seq_bounds(P.d, j0 + jb + jj, r0, dl, nullptr);
+          const long long drow = r0 + t;
+          float f = P.g[p0 + jb + jj];
+          if (d_factor) f *= row_factor(P.d, drow);
+          e = make_int2((int)drow, __float_as_int(f));
         }
-        s_g[tid] = g;
-        s_row0[tid] = r0;
       }
+      s_e[jj][r] = e;
     }
     __syncthreads();
     if (active) {
 #pragma unroll 8
       for (int jj = 0; jj < DQ_JC; ++jj) {
-        const int t = s_t[jj][warp];
-        if (t < 0) continue;
-        const long long drow = s_row0[jj] + t;
-        float f = s_g[jj];
-        if (P.d.inv_norm || P.d.scale || P.d.scale_scalar != 1.f) f *= row_factor(P.d, drow);
-        const T* src = Dg + drow * P.d.row_stride;
+        const int2 e = s_e[jj][warp];
+        if (e.x < 0) continue;
+        const float f = __int_as_float(e.y);
+        const T* src = Dlane + e.x * pitch;
 #pragma unroll
         for (int c = 0; c < CH; ++c) {
-          const int k = c * 128 + lane * 4;
-          if (k < P.dim) {
+          if (lane_on[c]) {
             float v[4];
-            load4<T>(src + k, v);
+            load4<T>(src + c * 128, v);
 #pragma unroll
-            for (int e = 0; e < 4; ++e) acc[c][e] = fmaf(f, v[e], acc[c][e]);
+            for (int x = 0; x < 4; ++x) acc[c][x] = fmaf(f, v[x], acc[c][x]);
           }
         }
       }
@@ -450,6 +451,10 @@ __global__ void __launch_bounds__(256) bwd_dq_fast_kernel(BwdParams P) {
 // rows with independent vector loads, accumulates in list order and stores the row once.
 // ---------------------------------------------------------------------------------
 constexpr int DDS_WARPS = 16;
+#ifndef LIK_DD_UNROLL
+#define LIK_DD_UNROLL 4
+#endif
+constexpr int DD_UNROLL = LIK_DD_UNROLL;  // independent list entries in flight per warp of the reduce kernel
 
 struct DdSortOut {
   int2* pairs;            // [n_scores * lq] (query row, weight bits), grouped by document then token
@@ -591,38 +596,50 @@ __global__ void __launch_bounds__(256) bwd_dd_reduce_kernel(BwdParams P, DdSortO
   const long long begin = __ldg(O.tok_begin + drow);
   const T* __restrict__ Qg = (const T*)P.q.data;
   if (cnt > 0) {
-    const int2* list = O.pairs + begin;
-    for (int k0 = 0; k0 < cnt; k0 += 32) {
-      const int n = min(32, cnt - k0);
-      int2 mine = make_int2(0, 0);
-      if (lane < n) mine = list[k0 + lane];
-      // gather in groups of 8 independent row loads, accumulate in list order
-      for (int k = 0; k < n; k += 8) {
-        float v[8][CH][4];
-        float w[8];
+    // every lane reads the same list entry (one broadcast transaction), then its own slice of the query row:
+    // DD_UNROLL independent entries per round, accumulated in list order
+    const int2* __restrict__ list = O.pairs + begin;
+    const long long pitch = P.q.row_stride;
+    const T* __restrict__ Qlane = Qg + lane * 4;
+    bool lane_on[CH];
 #pragma unroll
-        for (int u = 0; u < 8; ++u) {
-          const int row = __shfl_sync(0xffffffffu, mine.x, (k + u) & 31);
-          w[u] = __int_as_float(__shfl_sync(0xffffffffu, mine.y, (k + u) & 31));
-          if (k + u >= n) w[u] = 0.f;  // row 0 is a valid address; its weight is zero
-          const T* src = Qg + (long long)(k + u < n ? row : 0) * P.q.row_stride;
+    for (int c = 0; c < CH; ++c) lane_on[c] = c * 128 + lane * 4 < P.dim;
+    int k = 0;
+    for (; k + DD_UNROLL <= cnt; k += DD_UNROLL) {
+      int2 e[DD_UNROLL];
 #pragma unroll
-          for (int c = 0; c < CH; ++c) {
-            const int kk = c * 128 + lane * 4;
-            if (kk < P.dim) load4<T>(src + kk, v[u][c]);
-          }
-        }
+      for (int u = 0; u < DD_UNROLL; ++u) e[u] = __ldg(list + k + u);
+      float v[DD_UNROLL][CH][4];
 #pragma unroll
-        for (int u = 0; u < 8; ++u)
+      for (int u = 0; u < DD_UNROLL; ++u) {
+        const T* src = Qlane + e[u].x * pitch;
 #pragma unroll
-          for (int c = 0; c < CH; ++c) {
-            const int kk = c * 128 + lane * 4;
-            if (kk < P.dim) {
+        for (int c = 0; c < CH; ++c)
+          if (lane_on[c]) load4<T>(src + c * 128, v[u][c]);
+      }
 #pragma unroll
-              for (int x = 0; x < 4; ++x) acc[c][x] = fmaf(w[u], v[u][c][x], acc[c][x]);
-            }
+      for (int u = 0; u < DD_UNROLL; ++u) {
+        const float w = __int_as_float(e[u].y);
+#pragma unroll
+        for (int c = 0; c < CH; ++c)
+          if (lane_on[c]) {
+#pragma unroll
+            for (int x = 0; x < 4; ++x) acc[c][x] = fmaf(w, v[u][c][x], acc[c][x]);
           }
       }
+    }
+    for (; k < cnt; ++k) {
+      const int2 e = __ldg(list + k);
+      const float w = __int_as_float(e.y);
+      const T* src = Qlane + e.x * pitch;
+#pragma unroll
+      for (int c = 0; c < CH; ++c)
+        if (lane_on[c]) {
+          float v[4];
+          load4<T>(src + c * 128, v);
+#pragma unroll
+          for (int x = 0; x < 4; ++x) acc[c][x] = fmaf(w, v[x], acc[c][x]);
+        }
     }
   }
   if (P.normalize) {
@@ -718,7 +735,7 @@ bool bwd_fast_ok(const lik_bwd_args& a) {
   const size_t eb = dtype_size(a.dtype);
   return a.dim % 4 == 0 && a.dim <= 256 && (a.q.row_stride * eb) % (4 * eb) == 0 && (a.d.row_stride * eb) % (4 * eb) == 0 &&
          ((uintptr_t)a.q.data % (4 * eb)) == 0 && ((uintptr_t)a.d.data % (4 * eb)) == 0 && ((uintptr_t)a.grad_q % 16) == 0 &&
-         ((uintptr_t)a.grad_d % 16) == 0;
+         ((uintptr_t)a.grad_d % 16) == 0 && a.q.n_rows < (1ll << 31) && a.d.n_rows < (1ll << 31);  // row indices travel as int
 }
 
 BwdPlan plan_bwd(const lik_bwd_args& a) {
