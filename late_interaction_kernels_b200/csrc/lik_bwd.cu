@@ -8,6 +8,8 @@
 // reduces them in registers: no atomics, one store per output row, bitwise
 // reproducible) and an fp32-atomic scatter followed by a finalise pass.  The
 // L2-normalise Jacobian is applied in the same kernels.
+#include <mutex>
+
 #include "lik_common.cuh"
 
 namespace lik {
@@ -773,9 +775,51 @@ BwdPlan plan_bwd(const lik_bwd_args& a) {
   return pl;
 }
 
+// grad_Q and grad_D are independent, and both are bound by gather latency rather than by any
+// throughput limit, so when both are wanted the grad_Q kernel runs on a second stream beside the
+// grad_D kernels: fork after everything already enqueued on the caller's stream, join before returning
+// to it.  One auxiliary stream and two events per device, created on first use; the enqueue sequence
+// holds a lock because the events are shared by every caller on that device.
+struct ForkJoin {
+  cudaStream_t aux = nullptr;
+  cudaEvent_t fork = nullptr, join = nullptr;
+  bool ok = false;
+};
+std::mutex g_fork_mutex;
+ForkJoin g_fork[64];
+
+ForkJoin* fork_join_locked() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  ForkJoin& f = g_fork[dev];
+  if (!f.aux) {
+    f.ok = cudaStreamCreateWithFlags(&f.aux, cudaStreamNonBlocking) == cudaSuccess &&
+           cudaEventCreateWithFlags(&f.fork, cudaEventDisableTiming) == cudaSuccess &&
+           cudaEventCreateWithFlags(&f.join, cudaEventDisableTiming) == cudaSuccess;
+    if (!f.ok) (void)cudaGetLastError();
+  }
+  return f.ok ? &f : nullptr;
+}
+
 template <typename T, typename G>
-int run_bwd(const lik_bwd_args& a, BwdParams& P, const BwdPlan& pl, cudaStream_t st) {
+int run_bwd(const lik_bwd_args& a, BwdParams& P, const BwdPlan& pl, cudaStream_t st_main) {
   const bool list = a.pairing == LIK_PAIR_LIST;
+  // fork only when both gradients run the gather kernels and the problem is large enough to matter
+  const bool want_fork = a.grad_q && a.grad_d && !list && a.deterministic && pl.fast && pl.sorted &&
+                         P.pm.n_scores * (long long)a.argmax_stride >= (1ll << 20);
+  std::unique_lock<std::mutex> fork_lock(g_fork_mutex, std::defer_lock);
+  ForkJoin* fj = nullptr;
+  if (want_fork) {
+    fork_lock.lock();
+    fj = fork_join_locked();
+    if (fj) {
+      LIK_CUDA_OK(cudaEventRecord(fj->fork, st_main));
+      LIK_CUDA_OK(cudaStreamWaitEvent(fj->aux, fj->fork, 0));
+    } else {
+      fork_lock.unlock();
+    }
+  }
+  cudaStream_t st = fj ? fj->aux : st_main;  // stream of the grad_Q kernel; grad_D switches back below
   const int cmax = (a.dim + 31) / 32;
   char* ws = (char*)a.workspace;
 #define LIK_BY_CMAX(KERNEL, GRID, ...)                                          \
@@ -802,6 +846,10 @@ int run_bwd(const lik_bwd_args& a, BwdParams& P, const BwdPlan& pl, cudaStream_t
       LIK_BY_CMAX(bwd_dq_kernel, grid, P);
     }
     LIK_CUDA_OK(cudaGetLastError());
+  }
+  if (fj) {
+    LIK_CUDA_OK(cudaEventRecord(fj->join, fj->aux));
+    st = st_main;
   }
   if (a.grad_d && !list && a.deterministic && a.d.n_seq > 0 && a.d.max_len > 0) {
     if (pl.sorted) {
@@ -850,6 +898,7 @@ int run_bwd(const lik_bwd_args& a, BwdParams& P, const BwdPlan& pl, cudaStream_t
       LIK_CUDA_OK(cudaGetLastError());
     }
   }
+  if (fj) LIK_CUDA_OK(cudaStreamWaitEvent(st_main, fj->join, 0));
   return LIK_OK;
 }
 
