@@ -17,7 +17,8 @@ sys.path.insert(0, os.path.join(ROOT, "tests"))
 
 def main():
     from golden import cases
-    from late_interaction_kernels_b200 import plaid, retrieve as retrieve_mod, sharded
+    import late_interaction_kernels_b200 as lik
+    from late_interaction_kernels_b200 import plaid, sharded
     from oracle import maxsim_oracle as O
 
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
@@ -37,7 +38,7 @@ def main():
 
     lo, hi = sharded.shard_bounds(Nd, world, rank)
     s, i = sharded.retrieve_sharded(tq, tD[lo:hi], k, d_mask=tm[lo:hi], doc_offset=lo, n_docs_total=Nd, normalize=False, chunk=50)
-    ws, wi = retrieve_mod.retrieve(tq, tD, k, d_mask=tm, normalize=False, chunk=50)
+    ws, wi = lik.retrieve(tq, tD, k, d_mask=tm, normalize=False, chunk=50)
     assert torch.equal(s, ws), "sharded scores differ from the single-GPU retrieve"
     assert torch.equal(i, wi), "sharded indices differ from the single-GPU retrieve"
     if rank == 0:
