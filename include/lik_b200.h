@@ -174,6 +174,10 @@ typedef struct lik_bwd_args {
 } lik_bwd_args;
 
 size_t lik_maxsim_bwd_workspace(const lik_bwd_args* args);
+/* All work is ordered after what `stream` already holds and before anything enqueued on it afterwards.
+ * When both gradients are requested on a large problem, the grad_q kernel is enqueued on a stream the
+ * library creates once per device (event fork from `stream`, event join back into it), so that it runs
+ * beside the grad_d kernels; callers only ever synchronise with `stream`. */
 int lik_maxsim_bwd(const lik_bwd_args* args, lik_stream_t stream);
 
 /* ------------------------------------------------------------------------- */
