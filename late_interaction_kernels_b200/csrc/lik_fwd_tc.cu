@@ -943,40 +943,15 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
             fold32<ARGMAX>(v, c0 + cc, run_m, run_i);
           }
         } else {
-          if (!ARGMAX) {
-            // two register buffers: the next chunk of this warp is in flight while the current one is
-            // folded, and the accumulator is released after the last load, before the last folds
-            float va[32], vb[32];
-            bool more = cc + 32 <= ncols;
-            if (more) tmem_ld32_issue(lane_addr + (uint32_t)cc, va);
-            while (more) {
-              int cn = cc + 64;
-              more = cn + 32 <= ncols;
-              tmem_ld_wait(va);
-              if (more) tmem_ld32_issue(lane_addr + (uint32_t)cn, vb);
-              else if (cn >= ncols) LIK_RELEASE_ACC();
-              fold32<false>(va, c0 + cc, run_m, run_i);
-              cc = cn;
-              if (!more) break;
-              cn = cc + 64;
-              more = cn + 32 <= ncols;
-              tmem_ld_wait(vb);
-              if (more) tmem_ld32_issue(lane_addr + (uint32_t)cn, va);
-              else if (cn >= ncols) LIK_RELEASE_ACC();
-              fold32<false>(vb, c0 + cc, run_m, run_i);
-              cc = cn;
-            }
-          } else {
-            for (; cc + 32 <= ncols; cc += 64) {
-              float v[32];
-              TRACE3(0.f);
-              tmem_ld32_issue(lane_addr + (uint32_t)cc, v);
-              tmem_ld_wait(v);
-              TRACE3(v[0] + v[31]);
-              if (cc + 64 >= ncols) LIK_RELEASE_ACC();
-              fold32<ARGMAX>(v, c0 + cc, run_m, run_i);
-              TRACE3(run_m);
-            }
+          for (; cc + 32 <= ncols; cc += 64) {
+            float v[32];
+            TRACE3(0.f);
+            tmem_ld32_issue(lane_addr + (uint32_t)cc, v);
+            tmem_ld_wait(v);
+            TRACE3(v[0] + v[31]);
+            if (cc + 64 >= ncols) LIK_RELEASE_ACC();
+            fold32<ARGMAX>(v, c0 + cc, run_m, run_i);
+            TRACE3(run_m);
           }
           if (cc < ncols) {
             // partial chunk: pieces of 16, 8, 4, 2 and 1 columns as the bits of its width say, absent
