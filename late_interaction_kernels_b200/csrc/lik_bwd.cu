@@ -667,7 +667,7 @@ __global__ void __launch_bounds__(256) bwd_dd_reduce_kernel(BwdParams P, DdSortO
 // Atomic scatter: one warp per (score slot, query token).  Adds into fp32 buffers.
 // WITH_DQ also scatters grad_q (pair lists, where a query's slots are not contiguous).
 // ---------------------------------------------------------------------------------
-template <typename T, bool WITH_DQ>
+template <typename T, bool WITH_DQ, bool VEC>
 __global__ void __launch_bounds__(256) bwd_scatter_kernel(BwdParams P) {
   const int lane = threadIdx.x & 31;
   const long long w = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
@@ -693,9 +693,24 @@ __global__ void __launch_bounds__(256) bwd_scatter_kernel(BwdParams P) {
   const T* dsrc = (const T*)P.d.data + drow * P.d.row_stride;
   const float fq = g * row_factor(P.q, qrow);
   const float fd = g * row_factor(P.d, drow);
-  for (int k = lane; k < P.dim; k += 32) {
-    if (P.gd32) atomicAdd(P.gd32 + drow * P.dim + k, fq * to_f32(qsrc[k]));
-    if (WITH_DQ && P.gq32) atomicAdd(P.gq32 + qrow * P.dim + k, fd * to_f32(dsrc[k]));
+  if (VEC) {
+    // four consecutive elements per lane and one 16-byte reduction per lane (rows and width are multiples of 4)
+    for (int k = lane * 4; k < P.dim; k += 128) {
+      float v[4];
+      if (P.gd32) {
+        load4<T>(qsrc + k, v);
+        atomicAdd(reinterpret_cast<float4*>(P.gd32 + drow * P.dim + k), make_float4(fq * v[0], fq * v[1], fq * v[2], fq * v[3]));
+      }
+      if (WITH_DQ && P.gq32) {
+        load4<T>(dsrc + k, v);
+        atomicAdd(reinterpret_cast<float4*>(P.gq32 + qrow * P.dim + k), make_float4(fd * v[0], fd * v[1], fd * v[2], fd * v[3]));
+      }
+    }
+  } else {
+    for (int k = lane; k < P.dim; k += 32) {
+      if (P.gd32) atomicAdd(P.gd32 + drow * P.dim + k, fq * to_f32(qsrc[k]));
+      if (WITH_DQ && P.gq32) atomicAdd(P.gq32 + qrow * P.dim + k, fd * to_f32(dsrc[k]));
+    }
   }
 }
 
@@ -883,10 +898,14 @@ int run_bwd(const lik_bwd_args& a, BwdParams& P, const BwdPlan& pl, cudaStream_t
     long long warps = P.pm.n_scores * (long long)a.argmax_stride;
     if (warps > 0) {
       unsigned grid = (unsigned)ceil_div(warps, 8);
-      if (scatter_q)
-        bwd_scatter_kernel<T, true><<<grid, 256, 0, st>>>(P);
+      if (scatter_q && fast)
+        bwd_scatter_kernel<T, true, true><<<grid, 256, 0, st>>>(P);
+      else if (scatter_q)
+        bwd_scatter_kernel<T, true, false><<<grid, 256, 0, st>>>(P);
+      else if (fast)
+        bwd_scatter_kernel<T, false, true><<<grid, 256, 0, st>>>(P);
       else
-        bwd_scatter_kernel<T, false><<<grid, 256, 0, st>>>(P);
+        bwd_scatter_kernel<T, false, false><<<grid, 256, 0, st>>>(P);
       LIK_CUDA_OK(cudaGetLastError());
     }
     if (P.gq32 && a.q.n_rows > 0) {
