@@ -207,6 +207,135 @@ def retrieve_bench(n_docs, world, rank, dev):
             "tflops_valid": flops / (ms * 1e-3) / 1e12, "best_index_q0": int(i[0, 0])}
 
 
+def _time_us(fn, dev, iters=10, warm=3, graph=False):
+    """Mean device time of fn() in microseconds.  With graph=True the call is captured once into a CUDA
+    graph and replayed, so that host launch overhead does not hide the device time of a small problem."""
+    import torch
+
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize(dev)
+    run = fn
+    if graph:
+        try:
+            gr = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gr):
+                fn()
+            run = gr.replay
+            run()
+            torch.cuda.synchronize(dev)
+        except Exception:  # noqa: BLE001  (not capturable: time it eagerly)
+            torch.cuda.synchronize(dev)
+            run = fn
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        run()
+    e1.record()
+    torch.cuda.synchronize(dev)
+    return e0.elapsed_time(e1) / iters * 1e3
+
+
+def other_configs(dev):
+    """Kernel timings of the other BASELINE shapes (rank 0, one GPU): the KD layout in bf16 and e4m3
+    (HBM-bound: GB/s over the document bytes read once), the packed ColPali-shaped batch forward and
+    forward + backward (TFLOP/s on valid tokens), and the PLAID candidate score (GB/s over codes + table rows)."""
+    import torch
+    import torch.nn.functional as F
+
+    import late_interaction_kernels_b200 as lik
+    from late_interaction_kernels_b200 import fp8, plaid
+
+    out = {}
+    g = torch.Generator(device=dev).manual_seed(7)
+    # KD: Q[64,32,128] x D[64,32,300,128], lengths U[64,300] per candidate
+    Q = F.normalize(torch.randn((64, 32, 128), generator=g, device=dev), dim=-1)
+    D = F.normalize(torch.randn((64, 32, 300, 128), generator=g, device=dev), dim=-1)
+    lens = torch.randint(64, 301, (64, 32), generator=g, device=dev)
+    dm = torch.arange(300, device=dev)[None, None, :] < lens[..., None]
+    qb, db = Q.bfloat16(), D.bfloat16()
+    t = _time_us(lambda: lik.maxsim(qb, db, d_mask=dm), dev, graph=True)
+    out["kd_bf16_fwd"] = {"us": t, "GBps_document_bytes": db.numel() * 2 / t / 1e3, "shape": "Q[64,32,128] x D[64,32,300,128]"}
+    q8, sq = fp8.quantize_fp8_per_token(Q)
+    d8, sd = fp8.quantize_fp8_per_token(D)
+    t = _time_us(lambda: fp8.maxsim_inference_fp8(q8, d8, scale_Q=sq, scale_D=sd, d_mask=dm), dev, graph=True)
+    out["kd_e4m3_fwd"] = {"us": t, "GBps_document_bytes": (d8.numel() + sd.numel() * 4) / t / 1e3}
+    del D, db, d8
+    # packed: 128 queries of U[16,32] tokens x 128 documents of U[900,1030] tokens
+    ql = torch.randint(16, 33, (128,), generator=g, device=dev)
+    dl = torch.randint(900, 1031, (128,), generator=g, device=dev)
+    cq = F.pad(ql.cumsum(0), (1, 0)).int()
+    cd = F.pad(dl.cumsum(0), (1, 0)).int()
+    Qp = F.normalize(torch.randn((int(ql.sum()), 128), generator=g, device=dev), dim=-1).bfloat16()
+    Dp = F.normalize(torch.randn((int(dl.sum()), 128), generator=g, device=dev), dim=-1).bfloat16()
+    fl = 2.0 * 128 * float(ql.sum()) * float(dl.sum())
+    t = _time_us(lambda: lik.maxsim_varlen(Qp, Dp, cq, cd, 32, 1030), dev, graph=True)
+    out["varlen_fwd"] = {"us": t, "tflops_valid": fl / t / 1e6, "shape": "128 q U[16,32] x 128 docs U[900,1030]"}
+    Qr, Dr = Qp.clone().requires_grad_(), Dp.clone().requires_grad_()
+    go = torch.randn((128, 128), generator=g, device=dev)
+
+    def fb():
+        Qr.grad = None
+        Dr.grad = None
+        lik.maxsim_varlen(Qr, Dr, cq, cd, 32, 1030).backward(go)
+
+    t = _time_us(fb, dev)
+    out["varlen_fwd_bwd"] = {"us": t, "tflops_valid": (fl + 4.0 * 128 * float(ql.sum()) * 128) / t / 1e6}
+    # PLAID candidate score: 65536 centroids, 8192 candidate documents of up to 300 codes
+    qcs = torch.randn((65536, 32), generator=g, device=dev)
+    codes = torch.randint(0, 65536, (8192, 300), generator=g, device=dev, dtype=torch.int32)
+    cl = torch.randint(32, 301, (8192,), generator=g, device=dev)
+    t = _time_us(lambda: plaid.plaid_approx_score(qcs, codes, cl), dev, graph=True)
+    out["plaid_approx"] = {"us": t, "GBps_codes_and_rows": float(cl.sum()) * (4 + 32 * 4) / t / 1e3, "shape": "8192 docs x <=300 codes, 32 query tokens"}
+    return out
+
+
+def plaid_retrieve_bench(n_docs, world, rank, dev):
+    """Sharded top-k over a PLAID index (2-bit residuals, d=128, 65536 fp16 centroids): the shard's
+    codes and residual bytes are decompressed chunk by chunk, scored and merged; 1024 queries, top-100."""
+    import torch
+    import torch.distributed as dist
+    import torch.nn.functional as F
+
+    from late_interaction_kernels_b200 import sharded
+
+    lo, hi = sharded.shard_bounds(n_docs, world, rank)
+    g = torch.Generator(device=dev).manual_seed(4321 + rank)
+    lens = torch.randint(32, 301, (hi - lo,), generator=g, device=dev)
+    T = int(lens.sum())
+    codes = torch.randint(0, 65536, (T,), generator=g, device=dev, dtype=torch.int32)
+    res = torch.randint(0, 256, (T, 32), generator=g, device=dev, dtype=torch.uint8)
+    cu = F.pad(lens.cumsum(0), (1, 0)).int()
+    g.manual_seed(5)
+    cent = F.normalize(torch.randn((65536, 128), generator=g, device=dev), dim=-1).half()
+    bw = torch.linspace(-0.1, 0.1, 4, device=dev)
+    Q = F.normalize(torch.randn((1024, 32, 128), generator=g, device=dev), dim=-1).bfloat16()
+    tok = torch.tensor([float(T)], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(tok)
+
+    def run():
+        return sharded.retrieve_plaid_sharded(Q, codes, res, cu, cent, bw, 2, 100, doc_offset=lo, n_docs_total=n_docs, chunk=4096)
+
+    run()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    s, i = run()
+    e1.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    n_tok = float(tok.item())
+    return {"metric": "PLAID retrieve queries/s", "value": 1024 / (ms * 1e-3), "unit": "queries/s", "ms_per_batch": ms, "n_docs": n_docs,
+            "queries": 1024, "top_k": 100, "nbits": 2, "scaling": "strong", "tflops_valid": 2.0 * 128 * 1024 * 32 * n_tok / (ms * 1e-3) / 1e12,
+            "compressed_GBps": n_tok * 36 / (ms * 1e-3) / 1e9}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -403,6 +532,11 @@ def main():
         del Qr, Dr, flush
         torch.cuda.empty_cache()
         line["extra"] = {"retrieve": retrieve_bench(args.retrieve_docs, world, rank, dev)}
+        torch.cuda.empty_cache()
+        line["extra"]["plaid_retrieve"] = plaid_retrieve_bench(args.retrieve_docs, world, rank, dev)
+        torch.cuda.empty_cache()
+        if world == 1:
+            line["extra"]["other_configs"] = other_configs(dev)
     if rank == 0:
         if not args.no_cpu_baseline and world == 1:
             sample_q = 16

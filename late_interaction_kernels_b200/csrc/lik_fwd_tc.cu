@@ -883,9 +883,20 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
       const bool mine = P.mt == 2 ? have_tile : ((uc & 1) == wg);
       if (!mine) continue;
 
-      // the first wait of the unit also makes sure the producer has published it
+      // Unit data (length, first row) comes from the producer's ring.  Kernels with per-column
+      // multipliers wait for the publication alone (it precedes the unit's loads) so that they can stage
+      // the column arrays while the MMAs run; the others take it with their first accumulator wait.
       PROF_T0(e_w);
-      LIK_GROUP_WAIT_ACC(true);
+      if (SCALED) {
+        if (leader) {
+          const bool ok_ = wait_posted(ctl, uc, P.status);
+          if (!ok_ && lane == 0) ctl->grp_abort[wg] = 1;
+        }
+        LIK_GRP_SYNC();
+        ok = ctl->grp_abort[wg] == 0;
+      } else {
+        LIK_GROUP_WAIT_ACC(true);
+      }
       PROF_ADD(8, e_w);
       if (!ok) break;
       const int2 uinfo = ctl->unit_info[uc & (UNIT_RING - 1)];
@@ -897,7 +908,24 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
       int c0 = 0;
       do {
         const int ncols = max(0, min(TILE_N, dlen - c0));
-        if (c0 > 0) {
+        // per-column arrays of this tile; the first rendezvous says the previous tile's readers are done with them
+#define LIK_STAGE_COLUMNS()                                                                               \
+  do {                                                                                                    \
+    LIK_GRP_SYNC();                                                                                       \
+    for (int c = sub * EPI_THREADS + et; c < ((ncols + 31) & ~31); c += 2 * EPI_THREADS) {                \
+      float sc = 1.f, bi = -INFINITY;                                                                     \
+      if (c < ncols) {                                                                                    \
+        const long long drow = drow0 + c0 + c;                                                            \
+        sc = row_factor(P.d, drow);                                                                       \
+        bi = row_valid(P.d, drow) ? 0.f : -INFINITY;                                                      \
+      }                                                                                                   \
+      ctl->col_scale[wg][c] = sc;                                                                         \
+      ctl->col_bias[wg][c] = bi;                                                                          \
+    }                                                                                                     \
+    LIK_GRP_SYNC();                                                                                       \
+  } while (0)
+        if (SCALED) LIK_STAGE_COLUMNS();  // before the accumulator wait: overlaps the MMAs
+        if (SCALED || c0 > 0) {
           PROF_T0(e_w2);
           LIK_GROUP_WAIT_ACC(false);
           PROF_ADD(8, e_w2);
@@ -907,21 +935,8 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
         if (wq == 0 && lane == 0 && sub == 0) TRACE(3 + wg);
         prof_tiles(prof);
         PROF_T0(e_f);
-        if (use_cols) {
-          // per-column arrays of this tile (the accumulator waits meanwhile: only masked / scaled documents pay)
-          LIK_GRP_SYNC();  // the previous tile's readers are done with the arrays
-          for (int c = sub * EPI_THREADS + et; c < ((ncols + 31) & ~31); c += 2 * EPI_THREADS) {
-            float sc = 1.f, bi = -INFINITY;
-            if (c < ncols) {
-              const long long drow = drow0 + c0 + c;
-              sc = row_factor(P.d, drow);
-              bi = row_valid(P.d, drow) ? 0.f : -INFINITY;
-            }
-            ctl->col_scale[wg][c] = sc;
-            ctl->col_bias[wg][c] = bi;
-          }
-          LIK_GRP_SYNC();
-        }
+        if (!SCALED && use_cols) LIK_STAGE_COLUMNS();  // a document whose mask has holes: known only now
+#undef LIK_STAGE_COLUMNS
         tc_fence_after();
         // the accumulator goes back to the issuer as soon as this warp's last columns sit in registers
 #define LIK_RELEASE_ACC()                                          \
