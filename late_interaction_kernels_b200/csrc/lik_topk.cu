@@ -4,7 +4,9 @@
 // shared memory.  New candidates arrive KP at a time (a slice of a score row, or
 // one of several already-selected lists), are bitonic-sorted, combined with the
 // kept list by the "best of top[i] and block[KP-1-i]" step (which leaves the KP
-// best of the union as a bitonic sequence) and re-sorted by a bitonic merge.
+// best of the union as a bitonic sequence) and re-sorted by a bitonic merge.  Blocks
+// of a score row in which nothing beats the current k-th best are skipped after one
+// read of their values.
 // Order: better score first, ties to the lower document index; padding
 // (index < 0) last.
 #include <climits>
@@ -108,6 +110,18 @@ __global__ void __launch_bounds__(256) topk_kernel(TopkParams P) {
 
   const long long n_blocks = P.mode == 0 ? (P.n_cols + P.KP - 1) / P.KP : P.n_lists;
   for (long long b = 0; b < n_blocks; ++b) {
+    // A block of new candidates matters only if one of them beats the current k-th best: the kept list
+    // never gets worse, so anything behind that entry can never reach the output.  Once the list is warm
+    // almost every block is dismissed by this one pass over its values.
+    if (P.mode == 0) {
+      const Cand kth{top_k[P.k - 1], top_i[P.k - 1]};
+      int hit = 0;
+      for (int t = tid; t < P.KP; t += nt) {
+        const long long c = b * P.KP + t;
+        if (c < P.n_cols && before(Cand{sgn * P.scores[row * P.ld + c], c + P.index_offset}, kth)) hit = 1;
+      }
+      if (!__syncthreads_or(hit)) continue;
+    }
     for (int t = tid; t < P.KP; t += nt) {
       float key = -INFINITY;
       long long id = kPadIdx;
