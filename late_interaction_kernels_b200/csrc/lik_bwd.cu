@@ -289,6 +289,47 @@ __device__ __forceinline__ void load4<__nv_bfloat16>(const __nv_bfloat16* p, flo
   v[0] = __uint_as_float(x.x << 16); v[1] = __uint_as_float(x.x & 0xffff0000u);
   v[2] = __uint_as_float(x.y << 16); v[3] = __uint_as_float(x.y & 0xffff0000u);
 }
+// Four elements as they sit in memory (two 32-bit words for 16-bit types): gather loops keep several
+// of these in flight and unpack only when they multiply, which halves the registers a load in flight costs.
+template <typename T>
+struct Raw4 {
+  uint2 x;
+};
+template <>
+struct Raw4<float> {
+  float4 x;
+};
+template <typename T>
+__device__ __forceinline__ Raw4<T> load4_raw(const T* p) {
+  Raw4<T> r;
+  r.x = __ldg(reinterpret_cast<const decltype(r.x)*>(p));
+  return r;
+}
+template <typename T>
+__device__ __forceinline__ Raw4<T> zero4_raw() {
+  Raw4<T> r;
+  r.x = decltype(r.x){};
+  return r;
+}
+__device__ __forceinline__ void unpack4(const Raw4<float>& r, float (&v)[4]) {
+  v[0] = r.x.x; v[1] = r.x.y; v[2] = r.x.z; v[3] = r.x.w;
+}
+__device__ __forceinline__ void unpack4(const Raw4<__half>& r, float (&v)[4]) {
+  const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&r.x.x)), b = __half22float2(*reinterpret_cast<const __half2*>(&r.x.y));
+  v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+}
+__device__ __forceinline__ void unpack4(const Raw4<__nv_bfloat16>& r, float (&v)[4]) {
+  v[0] = __uint_as_float(r.x.x << 16); v[1] = __uint_as_float(r.x.x & 0xffff0000u);
+  v[2] = __uint_as_float(r.x.y << 16); v[3] = __uint_as_float(r.x.y & 0xffff0000u);
+}
+template <typename T>
+__device__ __forceinline__ void fma4_raw(float (&acc)[4], float w, const Raw4<T>& r) {
+  float v[4];
+  unpack4(r, v);
+#pragma unroll
+  for (int x = 0; x < 4; ++x) acc[x] = fmaf(w, v[x], acc[x]);
+}
+
 template <typename G>
 __device__ __forceinline__ void store4(G* p, const float (&v)[4]);
 template <>
@@ -345,6 +386,11 @@ __device__ __forceinline__ void normalize_jacobian_row(float (&acc)[CH][4], cons
 // (coalesced), then every warp gathers its 32 winning rows with independent loads.
 // ---------------------------------------------------------------------------------
 constexpr int DQ_JC = 32;
+#ifndef LIK_DQ_UNROLL
+#define LIK_DQ_UNROLL 8
+#endif
+constexpr int DQ_UNROLL = LIK_DQ_UNROLL;  // row loads in flight per warp of the grad_Q gather
+static_assert(DQ_JC % DQ_UNROLL == 0, "the chunk is walked in whole groups");
 
 template <typename T, typename G, int CH>
 __global__ void __launch_bounds__(256) bwd_dq_fast_kernel(BwdParams P) {
@@ -400,20 +446,26 @@ __global__ void __launch_bounds__(256) bwd_dq_fast_kernel(BwdParams P) {
     }
     __syncthreads();
     if (active) {
-#pragma unroll 8
-      for (int jj = 0; jj < DQ_JC; ++jj) {
-        const int2 e = s_e[jj][warp];
-        if (e.x < 0) continue;
-        const float f = __int_as_float(e.y);
-        const T* src = Dlane + e.x * pitch;
+      // DQ_UNROLL winners at a time: all their row loads are issued before the first one is used (an
+      // entry without a winner loads nothing and multiplies zeros)
+#pragma unroll 1
+      for (int j0g = 0; j0g < DQ_JC; j0g += DQ_UNROLL) {
+        int2 e[DQ_UNROLL];
 #pragma unroll
-        for (int c = 0; c < CH; ++c) {
-          if (lane_on[c]) {
-            float v[4];
-            load4<T>(src + c * 128, v);
+        for (int u = 0; u < DQ_UNROLL; ++u) e[u] = s_e[j0g + u][warp];
+        Raw4<T> v[DQ_UNROLL][CH];
 #pragma unroll
-            for (int x = 0; x < 4; ++x) acc[c][x] = fmaf(f, v[x], acc[c][x]);
-          }
+        for (int u = 0; u < DQ_UNROLL; ++u) {
+          const bool on = e[u].x >= 0;
+          const T* src = Dlane + (on ? e[u].x : 0) * pitch;
+#pragma unroll
+          for (int c = 0; c < CH; ++c) v[u][c] = (on && lane_on[c]) ? load4_raw<T>(src + c * 128) : zero4_raw<T>();
+        }
+#pragma unroll
+        for (int u = 0; u < DQ_UNROLL; ++u) {
+          const float f = e[u].x >= 0 ? __int_as_float(e[u].y) : 0.f;
+#pragma unroll
+          for (int c = 0; c < CH; ++c) fma4_raw<T>(acc[c], f, v[u][c]);
         }
       }
     }
@@ -454,7 +506,7 @@ __global__ void __launch_bounds__(256) bwd_dq_fast_kernel(BwdParams P) {
 // ---------------------------------------------------------------------------------
 constexpr int DDS_WARPS = 16;
 #ifndef LIK_DD_UNROLL
-#define LIK_DD_UNROLL 4
+#define LIK_DD_UNROLL 8
 #endif
 constexpr int DD_UNROLL = LIK_DD_UNROLL;  // independent list entries in flight per warp of the reduce kernel
 
@@ -611,23 +663,18 @@ __global__ void __launch_bounds__(256) bwd_dd_reduce_kernel(BwdParams P, DdSortO
       int2 e[DD_UNROLL];
 #pragma unroll
       for (int u = 0; u < DD_UNROLL; ++u) e[u] = __ldg(list + k + u);
-      float v[DD_UNROLL][CH][4];
+      Raw4<T> v[DD_UNROLL][CH];
 #pragma unroll
       for (int u = 0; u < DD_UNROLL; ++u) {
         const T* src = Qlane + e[u].x * pitch;
 #pragma unroll
-        for (int c = 0; c < CH; ++c)
-          if (lane_on[c]) load4<T>(src + c * 128, v[u][c]);
+        for (int c = 0; c < CH; ++c) v[u][c] = lane_on[c] ? load4_raw<T>(src + c * 128) : zero4_raw<T>();
       }
 #pragma unroll
       for (int u = 0; u < DD_UNROLL; ++u) {
         const float w = __int_as_float(e[u].y);
 #pragma unroll
-        for (int c = 0; c < CH; ++c)
-          if (lane_on[c]) {
-#pragma unroll
-            for (int x = 0; x < 4; ++x) acc[c][x] = fmaf(w, v[u][c][x], acc[c][x]);
-          }
+        for (int c = 0; c < CH; ++c) fma4_raw<T>(acc[c], w, v[u][c]);
       }
     }
     for (; k < cnt; ++k) {
