@@ -664,6 +664,12 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
       const uint32_t idesc0 = instr_desc(P.ab_format, 0);
       const int k_steps = P.k_steps, n_slabs = P.n_slabs;
       const uint32_t a_tile1 = P.mt == 2 ? q_tile_desc : 0u;  // descriptor offset of the second resident tile
+      uint32_t a_lo0[8], a_lo1[8];  // the eight K steps of either resident tile never move
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        a_lo0[k] = a_desc0 + (uint32_t)((k & 3) * 2 + (k >> 2) * ((TILE_M * SLAB_BYTES_ROW) >> 4));
+        a_lo1[k] = a_lo0[k] + a_tile1;
+      }
       PROF_DECL();
       TRACE_DECL();
       PROF_T0(m_all);
@@ -687,7 +693,10 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
         {
           const uint32_t idesc = idesc0 | (((ncols + 15) >> 4) << 18);  // N / 8 in bits 17..22
           const uint32_t b_stage = b_desc0 + st * stage_desc;
-#pragma unroll 1  // one copy of the issue sequence: it stays in the instruction cache between the two groups
+          uint32_t b_lo[8];
+#pragma unroll
+          for (int k = 0; k < 8; ++k) b_lo[k] = b_stage + (uint32_t)((k & 3) * 2 + (k >> 2) * ((TILE_N * SLAB_BYTES_ROW) >> 4));
+#pragma unroll
           for (int a = 0; a < 2; ++a) {
             if (!(info & (STAGE_ACC0 << a))) continue;
             PROF_T0(m_a);
@@ -705,17 +714,17 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
             if (ncols == 0) {
               // empty document: the accumulator still changes hands so that both sides keep their phase
             } else if (k_steps == 8) {
-              // the common width (128 two-byte or 256 one-byte elements): straight-line issue
-              const uint32_t a1 = a_desc + (uint32_t)((TILE_M * SLAB_BYTES_ROW) >> 4);
-              const uint32_t b1 = b_desc + (uint32_t)((TILE_N * SLAB_BYTES_ROW) >> 4);
-              tc_mma<FP8>(d_tmem, a_desc, b_desc, desc_hi, idesc, 0u);
-              tc_mma<FP8>(d_tmem, a_desc + 2, b_desc + 2, desc_hi, idesc, 1u);
-              tc_mma<FP8>(d_tmem, a_desc + 4, b_desc + 4, desc_hi, idesc, 1u);
-              tc_mma<FP8>(d_tmem, a_desc + 6, b_desc + 6, desc_hi, idesc, 1u);
-              tc_mma<FP8>(d_tmem, a1, b1, desc_hi, idesc, 1u);
-              tc_mma<FP8>(d_tmem, a1 + 2, b1 + 2, desc_hi, idesc, 1u);
-              tc_mma<FP8>(d_tmem, a1 + 4, b1 + 4, desc_hi, idesc, 1u);
-              tc_mma<FP8>(d_tmem, a1 + 6, b1 + 6, desc_hi, idesc, 1u);
+              // the common width (128 two-byte or 256 one-byte elements): straight-line issue from
+              // descriptor words prepared ahead of the accumulator wait
+              const uint32_t* al = a ? a_lo1 : a_lo0;
+              tc_mma<FP8>(d_tmem, al[0], b_lo[0], desc_hi, idesc, 0u);
+              tc_mma<FP8>(d_tmem, al[1], b_lo[1], desc_hi, idesc, 1u);
+              tc_mma<FP8>(d_tmem, al[2], b_lo[2], desc_hi, idesc, 1u);
+              tc_mma<FP8>(d_tmem, al[3], b_lo[3], desc_hi, idesc, 1u);
+              tc_mma<FP8>(d_tmem, al[4], b_lo[4], desc_hi, idesc, 1u);
+              tc_mma<FP8>(d_tmem, al[5], b_lo[5], desc_hi, idesc, 1u);
+              tc_mma<FP8>(d_tmem, al[6], b_lo[6], desc_hi, idesc, 1u);
+              tc_mma<FP8>(d_tmem, al[7], b_lo[7], desc_hi, idesc, 1u);
             } else {
               int left = k_steps;
               uint32_t accum = 0;
