@@ -512,8 +512,8 @@ def main():
     achieved = fwd_flops / (fwd_ms * 1e-3) / 1e12
     roofline = {"bound": "tensor", "achieved": achieved, "peak": peak_tf, "unit": "TFLOP/s", "frac": achieved / peak_tf,
                 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel on this workload, from the
-                # ncu capture summarised in profiles/fwd_tc_kernel_argmax_c2.txt (31.56 MB + 4.82 MB)
-                "traffic": 36.38e6, "traffic_unit": "bytes per launch",
+                # ncu capture summarised in profiles/fwd_tc_kernel_argmax_c2.txt (31.55 MB + 4.02 MB)
+                "traffic": 35.57e6, "traffic_unit": "bytes per launch",
                 "kernel": "fwd_tc_kernel (bf16, argmax, masked)", "kernel_ms": fwd_ms, "peak_source": which}
 
     line = {
