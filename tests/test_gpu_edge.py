@@ -186,3 +186,38 @@ def test_plaid_retrieve_matches_score_then_topk():
     s1, i1 = sharded.retrieve_sharded(dev(Q, torch.bfloat16), dev(rng.standard_normal((40, 12, d)).astype(np.float32), torch.bfloat16),
                                       10, doc_offset=1000, n_docs_total=40)
     assert s1.shape == (7, 10) and int(i1.min()) >= 1000
+
+
+def test_exact_ties_pick_the_lowest_column_everywhere():
+    """Integer-valued embeddings make the scores exact, so duplicated document tokens tie exactly: the saved
+    winner must be the lowest column wherever the copies sit — inside one 32-column chunk, in chunks read by
+    different warps, in the partial last chunk, and in the second tile of a document longer than 256 tokens
+    (reference contract: lowest index wins, forward.py:168-169)."""
+    from late_interaction_kernels_b200 import _ops
+
+    rng = np.random.default_rng(17)
+    nq, lq, d, ld = 5, 32, 64, 300
+    lens = np.array([300, 257, 256, 255, 97, 33, 31, 1])
+    nd = len(lens)
+    Q = rng.integers(-2, 3, size=(nq, lq, d)).astype(np.float32)
+    D = rng.integers(-2, 3, size=(nd, ld, d)).astype(np.float32)
+    # copies of one row at columns chosen to straddle chunk, warp-half and tile boundaries
+    for j, cols in enumerate(([3, 35, 64, 131, 255, 256, 299], [40, 8, 256], [255, 0, 31, 32], [254, 224, 200], [96, 64, 65],
+                              [32, 1], [30, 29, 2], [0])):
+        for c in cols[1:]:
+            D[j, c] = D[j, cols[0]]
+    D[2, :256] = D[2, 17]  # a document whose tokens are all the same: every winner is column 0
+    D[2, 0] = D[2, 17]
+    dm = np.arange(ld)[None, :] < lens[:, None]
+    S = np.einsum("isk,jtk->ijst", Q, D)
+    S = np.where(dm[None, :, None, :], S, -np.inf)
+    want_arg = S.argmax(-1).astype(np.int32)  # first occurrence of the maximum
+    want = S.max(-1).sum(-1)
+    for dtype in (torch.bfloat16, torch.float16):
+        q, dd = _ops.padded_spec(dev(Q, dtype)), _ops.padded_spec(dev(D, dtype), dev(dm))
+        for engine in (1, 2):
+            s, a = _ops.forward(q, dd, save_argmax=True, engine=engine)
+            assert np.array_equal(f32(s).reshape(nq, nd), want), (dtype, engine)
+            assert np.array_equal(a.cpu().numpy().reshape(nq, nd, lq), want_arg), (dtype, engine)
+        s0, _ = _ops.forward(q, dd, engine=2)  # the path without argmax gives the same bits
+        assert torch.equal(s0, s)
