@@ -1102,26 +1102,42 @@ __global__ void mask_lens_kernel(const unsigned char* __restrict__ mask, const i
   if (lane == 0) out[j] = (last + 1) | (cnt != last + 1 ? LEN_FLAG_MASKED : 0);
 }
 
+constexpr int PACK_MAX_QUERIES = 8192;  // offsets are staged in shared memory; larger batches use fixed groups
+
 // Greedy packing of ragged queries into 128-row tiles: a tile takes whole consecutive queries until the next
-// one would not fit.  out[0] = tile count, out[1 + m] = first query of tile m (out[1 + count] = n_q).
-__global__ void pack_query_tiles_kernel(const int* __restrict__ cu, int n_q, int* __restrict__ out) {
-  if (threadIdx.x != 0 || blockIdx.x != 0) return;
-  int tiles = 0, rows = 0, count = 0;  // a tile also holds at most TILE_M queries (empty ones take no rows)
-  out[1] = 0;
-  for (int q = 0; q < n_q; ++q) {
-    const int len = max(cu[q + 1] - cu[q], 0);
-    if (count > 0 && (rows + len > TILE_M || count == TILE_M)) {
+// one would not fit (or it holds 128 queries; empty ones take no rows).  out[0] = tile count, out[1 + m] =
+// first query of tile m (out[1 + count] = n_q).  One CTA: the offsets go to shared memory, every thread finds
+// by bisection where a tile starting at its query would end, then one thread follows those links.
+__global__ void __launch_bounds__(256) pack_query_tiles_kernel(const int* __restrict__ cu, int n_q, int* __restrict__ out) {
+  __shared__ int s_cu[PACK_MAX_QUERIES + 1];
+  __shared__ unsigned char s_span[PACK_MAX_QUERIES];  // queries in the tile that starts at query i (1..128)
+  for (int i = threadIdx.x; i <= n_q; i += blockDim.x) s_cu[i] = cu[i];
+  __syncthreads();
+  for (int i = threadIdx.x; i < n_q; i += blockDim.x) {
+    int lo = i + 1, hi = min(i + TILE_M, n_q);  // the tile ends at some j in [lo, hi]; a lone long query still gets one
+    const int base = s_cu[i];
+    while (lo < hi) {
+      const int mid = (lo + hi + 1) >> 1;
+      if (s_cu[mid] - base <= TILE_M) lo = mid;
+      else hi = mid - 1;
+    }
+    s_span[i] = (unsigned char)(lo - i - 1);  // stored minus one so that 128 fits a byte
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int tiles = 0, q = 0;
+    out[1] = 0;
+    while (q < n_q) {
+      q += (int)s_span[q] + 1;
       ++tiles;
       out[1 + tiles] = q;
-      rows = 0;
-      count = 0;
     }
-    rows += len;
-    ++count;
+    if (tiles == 0) {  // n_q == 0 cannot reach this kernel; keep the table well formed anyway
+      tiles = 1;
+      out[2] = n_q;
+    }
+    out[0] = tiles;
   }
-  ++tiles;
-  out[1 + tiles] = n_q;
-  out[0] = tiles;
 }
 
 // scores[q, j] = sum over the chunks of query q, in chunk order
@@ -1178,7 +1194,6 @@ int make_map(CUtensorMap* map, const lik_seqs& s, int dtype, int dim, int box_ro
   return LIK_OK;
 }
 
-constexpr int PACK_MAX_QUERIES = 8192;  // the packing scan is serial; larger batches use fixed groups
 
 struct TcPlan {
   bool pack_tiles;  // ragged queries packed greedily into tiles by pack_query_tiles_kernel
@@ -1294,7 +1309,7 @@ int launch_fwd_tc(const lik_fwd_args& a, const float* qn, const float* dn, void*
   if (pl.pack_tiles) {
     const size_t lens_bytes = (a.d.mask && !a.d.cu) ? align_up((size_t)a.d.n_seq * sizeof(int), 256) : 0;
     int* tbl = (int*)((char*)ws + partial_bytes(pl, a) + lens_bytes);
-    pack_query_tiles_kernel<<<1, 32, 0, st>>>(a.q.cu, a.q.n_seq, tbl);
+    pack_query_tiles_kernel<<<1, 256, 0, st>>>(a.q.cu, a.q.n_seq, tbl);
     LIK_CUDA_OK(cudaGetLastError());
     P.tile_q0 = tbl + 1;
   }
