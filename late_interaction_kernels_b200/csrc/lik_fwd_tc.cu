@@ -183,6 +183,17 @@ __device__ __forceinline__ void fold32(const float (&v)[32], int col0, float& ru
     run_m = fmaxf(run_m, cmax);
   }
 }
+// v[i] *= scale[i]: per-column multiplier staged in shared memory
+__device__ __forceinline__ void scale32(float (&v)[32], const float* scale) {
+#pragma unroll
+  for (int i = 0; i < 32; i += 4) {
+    const float4 sc = *reinterpret_cast<const float4*>(scale + i);
+    v[i + 0] *= sc.x;
+    v[i + 1] *= sc.y;
+    v[i + 2] *= sc.z;
+    v[i + 3] *= sc.w;
+  }
+}
 // v[i] = v[i] * scale[i] + bias[i]: per-column multiplier and additive mask staged in shared memory
 __device__ __forceinline__ void affine32(float (&v)[32], const float* scale, const float* bias) {
 #pragma unroll
@@ -911,7 +922,8 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
       const int2 uinfo = ctl->unit_info[uc & (UNIT_RING - 1)];
       const int dlen = uinfo.x & ~LEN_FLAG_MASKED;
       const long long drow0 = uinfo.y;
-      const bool use_cols = SCALED || (uinfo.x & LEN_FLAG_MASKED) != 0;  // per-column multiplier / additive mask needed
+      const bool holes = (uinfo.x & LEN_FLAG_MASKED) != 0;  // the document's mask is not a plain prefix
+      const bool use_cols = SCALED || holes;                // per-column multiplier / additive mask needed
       float run_m = -INFINITY;
       int run_i = -1;
       int c0 = 0;
@@ -963,7 +975,8 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
             tmem_ld32_issue(lane_addr + (uint32_t)cc, v);
             tmem_ld_wait(v);
             if (cc + 64 >= ncols) LIK_RELEASE_ACC();
-            affine32(v, &ctl->col_scale[wg][cc], &ctl->col_bias[wg][cc]);  // bias is -inf past ncols
+            if (!holes && cc + 32 <= ncols) scale32(v, &ctl->col_scale[wg][cc]);  // whole chunk valid: multiplier only
+            else affine32(v, &ctl->col_scale[wg][cc], &ctl->col_bias[wg][cc]);    // bias is -inf past ncols and in holes
             fold32<ARGMAX>(v, c0 + cc, run_m, run_i);
           }
         } else {
