@@ -6,6 +6,8 @@
 namespace lik {
 int launch_row_inv_norm(const void* data, int dtype, long long n_rows, int dim, long long stride, float eps, float* out,
                         cudaStream_t st);
+int launch_row_normalize(const void* data, int dtype, long long n_rows, int dim, long long stride, float eps, void* out,
+                         cudaStream_t st);
 int launch_fwd_generic(const lik_fwd_args& a, const float* qn, const float* dn, cudaStream_t st);
 // tcgen05 path (lik_fwd_tc.cu)
 bool fwd_tc_supported(const lik_fwd_args& a);
@@ -16,8 +18,9 @@ namespace {
 constexpr float kFwdNormEps = 1e-12f;
 
 struct FwdPlan {
-  size_t qn_off, dn_off, tc_off, total;
+  size_t qn_off, dn_off, qcopy_off, dcopy_off, tc_off, total;
   bool use_tc;
+  bool copies;  // fused normalisation through normalised operand copies instead of per-row multipliers
 };
 
 int validate_seqs(const lik_seqs& s, const char* name) {
@@ -49,6 +52,11 @@ int validate_fwd(const lik_fwd_args& a) {
   return LIK_OK;
 }
 
+// With 16-bit inputs the fused L2 normalisation is done the way the reference kernel does it (forward.py:120-126):
+// the operands are normalised in fp32 and rounded back to their dtype, here once per call into workspace copies,
+// and then scored like pre-normalised inputs, which keeps the scoring kernel on its multiplier-free path.
+// fp32 inputs keep per-row multipliers (4 bytes per row, no rounding).  Every entry point plans the same way, so
+// the same call gives the same bits whichever one runs it.
 FwdPlan plan_fwd(const lik_fwd_args& a) {
   FwdPlan pl{};
   size_t off = 0;
@@ -57,13 +65,63 @@ FwdPlan plan_fwd(const lik_fwd_args& a) {
     off = align_up(off + bytes, 256);
     return o;
   };
-  pl.qn_off = pl.dn_off = pl.tc_off = (size_t)-1;
-  if (a.normalize & LIK_NORM_Q) pl.qn_off = take((size_t)a.q.n_rows * 4);
-  if (a.normalize & LIK_NORM_D) pl.dn_off = take((size_t)a.d.n_rows * 4);
-  pl.use_tc = a.engine != 1 && fwd_tc_supported(a);
-  if (pl.use_tc) pl.tc_off = take(fwd_tc_workspace(a));
+  pl.qn_off = pl.dn_off = pl.qcopy_off = pl.dcopy_off = pl.tc_off = (size_t)-1;
+  pl.copies = a.normalize && (a.dtype == LIK_BF16 || a.dtype == LIK_F16);
+  const size_t eb = dtype_size(a.dtype);
+  if (a.normalize & LIK_NORM_Q) {
+    if (pl.copies) pl.qcopy_off = take((size_t)a.q.n_rows * a.dim * eb);
+    else pl.qn_off = take((size_t)a.q.n_rows * 4);
+  }
+  if (a.normalize & LIK_NORM_D) {
+    if (pl.copies) pl.dcopy_off = take((size_t)a.d.n_rows * a.dim * eb);
+    else pl.dn_off = take((size_t)a.d.n_rows * 4);
+  }
+  lik_fwd_args b = a;
+  if (pl.copies) {  // what the scoring kernel will see: dense rows, nothing left to normalise
+    if (a.normalize & LIK_NORM_Q) b.q.row_stride = a.dim;
+    if (a.normalize & LIK_NORM_D) b.d.row_stride = a.dim;
+    b.normalize = 0;
+  }
+  pl.use_tc = a.engine != 1 && fwd_tc_supported(b);
+  if (pl.use_tc) pl.tc_off = take(fwd_tc_workspace(b));
   pl.total = off;
   return pl;
+}
+
+int run_fwd(const lik_fwd_args& a, const FwdPlan& pl, cudaStream_t st) {
+  char* ws = (char*)a.workspace;
+  int rc;
+  lik_fwd_args b = a;
+  const float *qn = nullptr, *dn = nullptr;
+  if (a.normalize & LIK_NORM_Q) {
+    if (pl.copies) {
+      rc = launch_row_normalize(a.q.data, a.dtype, a.q.n_rows, a.dim, a.q.row_stride, kFwdNormEps, ws + pl.qcopy_off, st);
+      if (rc) return rc;
+      b.q.data = ws + pl.qcopy_off;
+      b.q.row_stride = a.dim;
+    } else {
+      float* w = (float*)(ws + pl.qn_off);
+      rc = launch_row_inv_norm(a.q.data, a.dtype, a.q.n_rows, a.dim, a.q.row_stride, kFwdNormEps, w, st);
+      if (rc) return rc;
+      qn = w;
+    }
+  }
+  if (a.normalize & LIK_NORM_D) {
+    if (pl.copies) {
+      rc = launch_row_normalize(a.d.data, a.dtype, a.d.n_rows, a.dim, a.d.row_stride, kFwdNormEps, ws + pl.dcopy_off, st);
+      if (rc) return rc;
+      b.d.data = ws + pl.dcopy_off;
+      b.d.row_stride = a.dim;
+    } else {
+      float* w = (float*)(ws + pl.dn_off);
+      rc = launch_row_inv_norm(a.d.data, a.dtype, a.d.n_rows, a.dim, a.d.row_stride, kFwdNormEps, w, st);
+      if (rc) return rc;
+      dn = w;
+    }
+  }
+  if (pl.copies) b.normalize = 0;
+  if (pl.use_tc) return launch_fwd_tc(b, qn, dn, ws + pl.tc_off, fwd_tc_workspace(b), st);
+  return launch_fwd_generic(b, qn, dn, st);
 }
 }  // namespace
 }  // namespace lik
@@ -73,8 +131,9 @@ extern "C" size_t lik_maxsim_fwd_workspace(const lik_fwd_args* a) {
   return lik::plan_fwd(*a).total;
 }
 
-extern "C" int lik_maxsim_fwd(const lik_fwd_args* a, lik_stream_t stream) {
-  using namespace lik;
+namespace lik {
+namespace {
+int fwd_entry(const lik_fwd_args* a, lik_stream_t stream) {
   LIK_REQUIRE(a != nullptr, "args is NULL");
   int rc = validate_fwd(*a);
   if (rc) return rc;
@@ -87,24 +146,12 @@ extern "C" int lik_maxsim_fwd(const lik_fwd_args* a, lik_stream_t stream) {
     set_error("workspace too small: need %zu bytes, got %zu", pl.total, a->workspace_bytes);
     return LIK_ERR_WORKSPACE;
   }
-  cudaStream_t st = (cudaStream_t)stream;
-  char* ws = (char*)a->workspace;
-  const float *qn = nullptr, *dn = nullptr;
-  if (a->normalize & LIK_NORM_Q) {
-    float* w = (float*)(ws + pl.qn_off);
-    rc = launch_row_inv_norm(a->q.data, a->dtype, a->q.n_rows, a->dim, a->q.row_stride, kFwdNormEps, w, st);
-    if (rc) return rc;
-    qn = w;
-  }
-  if (a->normalize & LIK_NORM_D) {
-    float* w = (float*)(ws + pl.dn_off);
-    rc = launch_row_inv_norm(a->d.data, a->dtype, a->d.n_rows, a->dim, a->d.row_stride, kFwdNormEps, w, st);
-    if (rc) return rc;
-    dn = w;
-  }
-  if (pl.use_tc) return launch_fwd_tc(*a, qn, dn, ws + pl.tc_off, fwd_tc_workspace(*a), st);
-  return launch_fwd_generic(*a, qn, dn, st);
+  return run_fwd(*a, pl, (cudaStream_t)stream);
 }
+}  // namespace
+}  // namespace lik
+
+extern "C" int lik_maxsim_fwd(const lik_fwd_args* a, lik_stream_t stream) { return lik::fwd_entry(a, stream); }
 
 // ---------------------------------------------------------------------------------------------
 // Forward without a caller workspace: the scratch lives in this library's device image.
@@ -153,7 +200,7 @@ extern "C" int lik_maxsim_fwd_static(const lik_fwd_args* a, lik_stream_t stream)
   lik_fwd_args b = *a;
   b.workspace = scratch;
   b.workspace_bytes = LIK_STATIC_SCRATCH_BYTES;
-  return lik_maxsim_fwd(&b, stream);
+  return fwd_entry(&b, stream);
 }
 
 extern "C" int lik_row_inv_norm(const void* data, int32_t dtype, int64_t n_rows, int32_t dim, int64_t row_stride, float eps,

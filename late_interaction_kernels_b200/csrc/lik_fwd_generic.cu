@@ -69,6 +69,59 @@ int launch_row_inv_norm(const void* data, int dtype, long long n_rows, int dim, 
   return LIK_OK;
 }
 
+// y[row] = round_to_T(x[row] / max(||x[row]||, eps)), dense rows of `dim` elements.  One warp per row; the row is
+// read once (it stays in registers between the norm and the scaling for widths up to 256).
+template <typename T>
+__global__ void row_normalize_kernel(const T* __restrict__ x, long long n_rows, int dim, long long stride, float eps,
+                                     T* __restrict__ y) {
+  const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= n_rows) return;
+  const int lane = threadIdx.x & 31;
+  const T* p = x + row * stride;
+  T* o = y + row * dim;
+  float v[8];
+  float ss = 0.f;
+#pragma unroll
+  for (int c = 0; c < 8; ++c) {
+    const int k = c * 32 + lane;
+    v[c] = k < dim ? to_f32(p[k]) : 0.f;
+    ss = fmaf(v[c], v[c], ss);
+  }
+  for (int k = 256 + lane; k < dim; k += 32) {
+    const float w = to_f32(p[k]);
+    ss = fmaf(w, w, ss);
+  }
+  ss = warp_sum(ss);
+  const float inv = 1.0f / fmaxf(sqrtf(ss), eps);
+#pragma unroll
+  for (int c = 0; c < 8; ++c) {
+    const int k = c * 32 + lane;
+    if (k < dim) o[k] = from_f32<T>(v[c] * inv);
+  }
+  for (int k = 256 + lane; k < dim; k += 32) o[k] = from_f32<T>(to_f32(p[k]) * inv);
+}
+
+// Normalised copy of a 16-bit matrix (dense output rows).
+int launch_row_normalize(const void* data, int dtype, long long n_rows, int dim, long long stride, float eps, void* out,
+                         cudaStream_t st) {
+  if (n_rows <= 0) return LIK_OK;
+  const int warps = 8;
+  dim3 grid((unsigned)ceil_div(n_rows, warps)), block(warps * 32);
+  switch (dtype) {
+    case LIK_F16:
+      row_normalize_kernel<<<grid, block, 0, st>>>((const __half*)data, n_rows, dim, stride, eps, (__half*)out);
+      break;
+    case LIK_BF16:
+      row_normalize_kernel<<<grid, block, 0, st>>>((const __nv_bfloat16*)data, n_rows, dim, stride, eps, (__nv_bfloat16*)out);
+      break;
+    default:
+      set_error("normalised copies exist for 16-bit inputs only (dtype %d)", dtype);
+      return LIK_ERR_INVALID;
+  }
+  LIK_CUDA_OK(cudaGetLastError());
+  return LIK_OK;
+}
+
 // ---------------------------------------------------------------------------------
 // Generic forward.  One CTA (4 warps) per score slot.  Tiles: 32 query tokens
 // (lane = token) x 64 document tokens (16 per warp) x 32 embedding columns.
