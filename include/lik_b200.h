@@ -89,7 +89,10 @@ typedef struct lik_seqs {
 /*   document for every query token, relative to the document start; -1 when    */
 /*   the document has no valid token, and for positions >= the query length.    */
 /* normalize: bit 0 (LIK_NORM_Q) / bit 1 (LIK_NORM_D): divide the query /       */
-/* document tokens by max(||x||, 1e-12) inside the kernel (fused L2 norm).     */
+/* document tokens by max(||x||, 1e-12) as part of the call (fused L2 norm).   */
+/* 16-bit inputs are normalised in fp32 and rounded back to their type into a  */
+/* workspace copy (what the reference kernel does, forward.py:120-126); fp32   */
+/* inputs are scaled by fp32 inverse norms inside the scoring kernel.          */
 /* ------------------------------------------------------------------------- */
 typedef struct lik_fwd_args {
   lik_seqs q, d;
