@@ -50,7 +50,7 @@ enum lik_dev_status {
   LIK_DEV_LEN_RANGE = 16    /* a length exceeds the padded extent (clamped) */
 };
 
-enum lik_normalize { LIK_NORM_NONE = 0, LIK_NORM_Q = 1, LIK_NORM_D = 2, LIK_NORM_BOTH = 3 };
+enum lik_normalize { LIK_NORM_NONE = 0, LIK_NORM_Q = 1, LIK_NORM_D = 2, LIK_NORM_BOTH = 3, LIK_NORM_ROUNDED = 4 };
 
 enum lik_pairing {
   LIK_PAIR_CROSS = 0,   /* every query against every document: scores[i * d.n_seq + j] */
@@ -90,9 +90,12 @@ typedef struct lik_seqs {
 /*   the document has no valid token, and for positions >= the query length.    */
 /* normalize: bit 0 (LIK_NORM_Q) / bit 1 (LIK_NORM_D): divide the query /       */
 /* document tokens by max(||x||, 1e-12) as part of the call (fused L2 norm).   */
-/* 16-bit inputs are normalised in fp32 and rounded back to their type into a  */
-/* workspace copy (what the reference kernel does, forward.py:120-126); fp32   */
-/* inputs are scaled by fp32 inverse norms inside the scoring kernel.          */
+/* By default the scoring kernel multiplies the raw dot products by fp32       */
+/* inverse norms, so scores and winners follow the fp32 oracle (reference.py). */
+/* With LIK_NORM_ROUNDED (bit 2) and 16-bit inputs the operands are instead    */
+/* normalised in fp32 and rounded back to their type into workspace copies,    */
+/* which is what the reference's GPU kernel does (forward.py:120-126) and is   */
+/* faster; near-ties may then pick another winner, so it is meant for search.  */
 /* ------------------------------------------------------------------------- */
 typedef struct lik_fwd_args {
   lik_seqs q, d;

@@ -18,6 +18,7 @@ LIB_PATH = os.path.join(_PKG_DIR, "liblik_b200.so")
 LIK_F32, LIK_F16, LIK_BF16, LIK_E4M3 = 0, 1, 2, 3
 PAIR_CROSS, PAIR_GROUPED, PAIR_LIST = 0, 1, 2
 NORM_NONE, NORM_Q, NORM_D, NORM_BOTH = 0, 1, 2, 3
+NORM_ROUNDED = 4  # search paths: normalised operands rounded to the input dtype (workspace copies), see lik_b200.h
 TOPK_MAX = 1024
 STATIC_SCRATCH_BYTES = 16 << 20
 

@@ -52,11 +52,11 @@ int validate_fwd(const lik_fwd_args& a) {
   return LIK_OK;
 }
 
-// With 16-bit inputs the fused L2 normalisation is done the way the reference kernel does it (forward.py:120-126):
-// the operands are normalised in fp32 and rounded back to their dtype, here once per call into workspace copies,
-// and then scored like pre-normalised inputs, which keeps the scoring kernel on its multiplier-free path.
-// fp32 inputs keep per-row multipliers (4 bytes per row, no rounding).  Every entry point plans the same way, so
-// the same call gives the same bits whichever one runs it.
+// Fused L2 normalisation.  Default: fp32 inverse norms per row, applied to the raw dot products inside the scoring
+// kernel (the fp32 oracle's arithmetic).  With LIK_NORM_ROUNDED and 16-bit inputs: the way the reference kernel does
+// it (forward.py:120-126) — operands normalised in fp32 and rounded back to their dtype, here once per call into
+// workspace copies, then scored like pre-normalised inputs on the kernel's multiplier-free path.  Every entry point
+// plans the same way, so the same call gives the same bits whichever one runs it.
 FwdPlan plan_fwd(const lik_fwd_args& a) {
   FwdPlan pl{};
   size_t off = 0;
@@ -66,7 +66,7 @@ FwdPlan plan_fwd(const lik_fwd_args& a) {
     return o;
   };
   pl.qn_off = pl.dn_off = pl.qcopy_off = pl.dcopy_off = pl.tc_off = (size_t)-1;
-  pl.copies = a.normalize && (a.dtype == LIK_BF16 || a.dtype == LIK_F16);
+  pl.copies = (a.normalize & LIK_NORM_ROUNDED) && (a.normalize & LIK_NORM_BOTH) && (a.dtype == LIK_BF16 || a.dtype == LIK_F16);
   const size_t eb = dtype_size(a.dtype);
   if (a.normalize & LIK_NORM_Q) {
     if (pl.copies) pl.qcopy_off = take((size_t)a.q.n_rows * a.dim * eb);
@@ -81,6 +81,8 @@ FwdPlan plan_fwd(const lik_fwd_args& a) {
     if (a.normalize & LIK_NORM_Q) b.q.row_stride = a.dim;
     if (a.normalize & LIK_NORM_D) b.d.row_stride = a.dim;
     b.normalize = 0;
+  } else {
+    b.normalize = a.normalize & LIK_NORM_BOTH;
   }
   pl.use_tc = a.engine != 1 && fwd_tc_supported(b);
   if (pl.use_tc) pl.tc_off = take(fwd_tc_workspace(b));
@@ -119,7 +121,7 @@ int run_fwd(const lik_fwd_args& a, const FwdPlan& pl, cudaStream_t st) {
       dn = w;
     }
   }
-  if (pl.copies) b.normalize = 0;
+  b.normalize = pl.copies ? 0 : (a.normalize & LIK_NORM_BOTH);
   if (pl.use_tc) return launch_fwd_tc(b, qn, dn, ws + pl.tc_off, fwd_tc_workspace(b), st);
   return launch_fwd_generic(b, qn, dn, st);
 }

@@ -221,3 +221,19 @@ def test_exact_ties_pick_the_lowest_column_everywhere():
             assert np.array_equal(a.cpu().numpy().reshape(nq, nd, lq), want_arg), (dtype, engine)
         s0, _ = _ops.forward(q, dd, engine=2)  # the path without argmax gives the same bits
         assert torch.equal(s0, s)
+
+
+def test_opt_in_rounded_normalisation_stays_within_tolerance():
+    """LIK_NORM_ROUNDED (normalised 16-bit operand copies, the reference GPU kernel's arithmetic) is opt-in: it
+    must stay within the bf16 tolerance of the oracle and of the default fp32-inverse-norm path."""
+    from late_interaction_kernels_b200.forward import maxsim_forward
+
+    Q, D, _, dm = cases.dense_case(21, 9, 40, 32, 77, 128, d_len=(1, 77), normalized=False)
+    for dtype in (torch.bfloat16, torch.float16):
+        Qt, Dt = dev(Q * 3.0, dtype), dev(D * 0.25, dtype)
+        want = O.maxsim(f32(Qt), f32(Dt), None, dm, normalize=True)
+        base, _ = maxsim_forward(Qt, Dt, d_mask=dev(dm), normalize=True)
+        fast, _ = maxsim_forward(Qt, Dt, d_mask=dev(dm), normalize=True, _rounded_norm=True)
+        assert O.rel_err(f32(base), want) < 1e-3
+        assert O.rel_err(f32(fast), want) < 2e-2
+        assert not torch.equal(fast, base), "the two forms are different arithmetic"
