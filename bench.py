@@ -30,6 +30,15 @@ import numpy as np
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
+_JSON_OUT = None  # the process's original stdout once main() has redirected descriptor 1 (see there)
+
+
+def emit(obj):
+    out = _JSON_OUT if _JSON_OUT is not None else sys.stdout
+    out.write(json.dumps(obj) + "\n")
+    out.flush()
+
+
 METRIC = "MaxSim fwd+bwd TFLOP/s (bf16)"
 WORKLOAD = "colbert_inbatch_train_bf16: Q[512,32,128] x D[512,300,128], d_len U[64,300], fwd+bwd"
 NQ, ND, LQ, LD, DIM = 512, 512, 32, 300, 128
@@ -357,6 +366,13 @@ def main():
         run_reference(args, rank)
         return
 
+    # stdout carries exactly one JSON line: libraries that write to file descriptor 1 on their own (NCCL's version
+    # banner does) are sent to stderr for the whole run, and the line is written to the saved descriptor at the end
+    global _JSON_OUT
+    sys.stdout.flush()
+    _JSON_OUT = os.fdopen(os.dup(1), "w")
+    os.dup2(2, 1)
+
     import torch
     import torch.distributed as dist
 
@@ -415,7 +431,7 @@ def main():
             part()
         b.record()
         torch.cuda.synchronize()
-        print(json.dumps({"only": args.only, "ms": a.elapsed_time(b) / args.steps, "steps": args.steps}), flush=True)
+        emit({"only": args.only, "ms": a.elapsed_time(b) / args.steps, "steps": args.steps})
         return
 
     for _ in range(args.warmup):
@@ -551,7 +567,7 @@ def main():
             dt = time.perf_counter() - t0
             line["cpu_baseline"] = {"value": (cf + cb) * reps / dt / 1e12, "unit": "TFLOP/s", "cores": os.cpu_count() or 1,
                                     "kind": "port", "sample": f"{reps} x ({sample_q} queries x {ND} docs fwd+bwd), numpy oracle, all host threads"}
-        print(json.dumps(line), flush=True)
+        emit(line)
     if world > 1:
         dist.destroy_process_group()
 
