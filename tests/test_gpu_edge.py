@@ -237,3 +237,30 @@ def test_opt_in_rounded_normalisation_stays_within_tolerance():
         assert O.rel_err(f32(base), want) < 1e-3
         assert O.rel_err(f32(fast), want) < 2e-2
         assert not torch.equal(fast, base), "the two forms are different arithmetic"
+
+
+def test_backward_with_forked_stream_is_graph_capturable():
+    """Both gradients on a large enough problem: the grad_Q kernel runs on the library's second stream
+    between an event fork and join.  That pattern must survive CUDA-graph capture and replay, and give the
+    same bits as the eager call."""
+    from late_interaction_kernels_b200 import _ops
+
+    g = torch.Generator().manual_seed(3)
+    Q = torch.nn.functional.normalize(torch.randn(192, 32, 64, generator=g), dim=-1).cuda().bfloat16()
+    D = torch.nn.functional.normalize(torch.randn(192, 200, 64, generator=g), dim=-1).cuda().bfloat16()
+    go = torch.randn(192, 192, generator=g).cuda()
+    q, d = _ops.padded_spec(Q), _ops.padded_spec(D)
+    _, am = _ops.forward(q, d, save_argmax=True)
+    assert am.numel() >= 1 << 20  # large enough for the fork
+    eq, ed = _ops.backward(q, d, go, am)
+    torch.cuda.synchronize()
+    st = torch.cuda.Stream()
+    with torch.cuda.stream(st):
+        gr = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(gr, stream=st):
+            gq, gd = _ops.backward(q, d, go, am)
+    gq.zero_()
+    gd.zero_()
+    gr.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(gq, eq) and torch.equal(gd, ed)
