@@ -10,7 +10,11 @@
  * Conventions
  *   - every pointer is a DEVICE pointer unless the name ends in _host;
  *   - the caller allocates inputs, outputs and workspaces; the library never
- *     allocates device memory, never synchronises and keeps no per-call state;
+ *     allocates device memory and never synchronises.  State it keeps per
+ *     process: the error text of each thread, one auxiliary stream and two events
+ *     per device for the backward (created on first use, see lik_maxsim_bwd), a
+ *     count of the kernels it launched (lik_launch_count), and the device address
+ *     of the built-in scratch array of lik_maxsim_fwd_static;
  *   - launches go to the cudaStream_t passed as lik_stream_t;
  *   - return value: LIK_OK or a negative lik_status; lik_last_error() gives the
  *     text for the calling thread;
@@ -238,12 +242,68 @@ int lik_plaid_bwd_dq(const lik_plaid_index* index, int32_t max_ld, int64_t n_doc
                      float* grad_q, lik_stream_t stream);
 
 /* ------------------------------------------------------------------------- */
+/* Scoring fused with the per-query top-k.  Replaces the chunk loop of          */
+/* maxsim_topk (topk.py:41-86: score a chunk, torch.topk, cat, torch.topk) and  */
+/* of retrieve (retrieve.py:194-310) by ONE pass of the scoring kernel over all */
+/* documents: no [n_q, n_docs] and no [n_q, chunk] score matrix exists; every   */
+/* (query, document) score is offered to a candidate list of its query straight */
+/* from the accumulator epilogue, lists are cut back to their k best as they    */
+/* fill, and a merge kernel writes the k best per query, best first, ties to    */
+/* the lower document index (the order lik_topk_rows uses).                     */
+/* args: a lik_fwd_args with LIK_PAIR_CROSS pairing; scores / argmax unused.    */
+/* Supported (lik_maxsim_fwd_topk_supported() == 1): bf16 / fp16 / e4m3 inputs  */
+/* the tcgen05 kernel takes, padded queries of at most 128 tokens, k <= 128.    */
+/* Anything else: use lik_maxsim_fwd per chunk + lik_topk_rows.                 */
+/* out_index = document index + index_offset.  Fewer than k documents: the      */
+/* remaining entries are (-inf / +inf, -1).                                     */
+/* ------------------------------------------------------------------------- */
+/* A corpus that does not sit in memory as one matrix is scored piece by piece into the SAME workspace:  */
+/* every call but the first sets LIK_TOPK_CONTINUE (keep the candidate lists of the earlier pieces),     */
+/* every call but the last sets LIK_TOPK_PARTIAL (no merge, nothing written to out_*); doc_base is the   */
+/* index of the piece's first document (pieces in ascending order, same queries, same k).                */
+enum lik_topk_flags { LIK_TOPK_CONTINUE = 1, LIK_TOPK_PARTIAL = 2 };
+typedef struct lik_topk_spec {
+  int32_t k;
+  int32_t largest;      /* 0: the k smallest scores */
+  int64_t index_offset;
+  float* out_scores;    /* [q.n_seq, k] */
+  int64_t* out_index;   /* [q.n_seq, k] */
+  int32_t flags;        /* lik_topk_flags */
+  int32_t doc_base;     /* added to the document index of this call's documents */
+} lik_topk_spec;
+
+int lik_maxsim_fwd_topk_supported(const lik_fwd_args* args, const lik_topk_spec* topk);
+size_t lik_maxsim_fwd_topk_workspace(const lik_fwd_args* args, const lik_topk_spec* topk);
+int lik_maxsim_fwd_topk(const lik_fwd_args* args, const lik_topk_spec* topk, lik_stream_t stream);
+
+/* ------------------------------------------------------------------------- */
+/* Scoring straight from a compressed index: ONE kernel gathers centroid rows,  */
+/* unpacks the residual codes, adds bucket weights, normalises, rounds to the   */
+/* operand type and feeds the tensor cores (the decode stage runs in the        */
+/* kernel's producer warps and writes the operand tiles into shared memory).    */
+/* Replaces _maxsim_residual_forward (plaid.py:404-515) and the launcher of     */
+/* maxsim_residual_varlen (plaid.py:832-963); with topk != NULL the scores go   */
+/* into the same fused top-k as above instead of a [n_q, n_docs] matrix.        */
+/* args: q = the queries (bf16 or fp16); d describes the document layout only   */
+/* (d.data == NULL, rows = tokens of the index: packed cu or padded lens);      */
+/* normalize bit LIK_NORM_D = normalise the decoded tokens, LIK_NORM_Q = the    */
+/* queries.  Supported: width a multiple of 16 and at most 128, 16-byte aligned */
+/* centroid rows.  Otherwise decode with lik_plaid_decompress and score the     */
+/* rows with lik_maxsim_fwd: both ways give the same bits.                      */
+/* ------------------------------------------------------------------------- */
+int lik_plaid_fwd_supported(const lik_fwd_args* args, const lik_plaid_index* index, const lik_topk_spec* topk);
+size_t lik_plaid_fwd_workspace(const lik_fwd_args* args, const lik_plaid_index* index, const lik_topk_spec* topk);
+int lik_plaid_fwd(const lik_fwd_args* args, const lik_plaid_index* index, const lik_topk_spec* topk, lik_stream_t stream);
+
+/* ------------------------------------------------------------------------- */
 /* Utilities                                                                    */
 /* ------------------------------------------------------------------------- */
 /* out[r] = 1 / max(||x_r||, eps) for every row; the fused-normalise kernels take these. */
 int lik_row_inv_norm(const void* data, int32_t dtype, int64_t n_rows, int32_t dim, int64_t row_stride, float eps,
                      float* out, lik_stream_t stream);
 const char* lik_last_error(void);
+/* kernels this library has launched in this process so far (all threads, all devices) */
+uint64_t lik_launch_count(void);
 int lik_version(void);
 /* 1 when the device the calling thread has current is sm_100 (tcgen05 kernels usable) */
 int lik_device_supported(void);

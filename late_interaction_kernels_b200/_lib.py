@@ -20,6 +20,8 @@ PAIR_CROSS, PAIR_GROUPED, PAIR_LIST = 0, 1, 2
 NORM_NONE, NORM_Q, NORM_D, NORM_BOTH = 0, 1, 2, 3
 NORM_ROUNDED = 4  # search paths: normalised operands rounded to the input dtype (workspace copies), see lik_b200.h
 TOPK_MAX = 1024
+TOPK_CONTINUE, TOPK_PARTIAL = 1, 2
+TOPK_FUSED_MAX = 128  # largest k of the fused scoring + top-k kernel
 STATIC_SCRATCH_BYTES = 16 << 20
 
 DEV_STATUS_TEXT = {
@@ -71,6 +73,13 @@ class BwdArgs(C.Structure):
     ]
 
 
+class TopkSpec(C.Structure):
+    _fields_ = [
+        ("k", C.c_int32), ("largest", C.c_int32), ("index_offset", C.c_int64), ("out_scores", C.c_void_p),
+        ("out_index", C.c_void_p), ("flags", C.c_int32), ("doc_base", C.c_int32),
+    ]
+
+
 class PlaidIndex(C.Structure):
     _fields_ = [
         ("codes", C.c_void_p), ("residuals", C.c_void_p), ("n_tokens", C.c_int64), ("centroids", C.c_void_p),
@@ -95,6 +104,20 @@ def _declare(lib):
     lib.lik_maxsim_bwd_workspace.restype = sz
     lib.lik_maxsim_bwd.argtypes = [C.POINTER(BwdArgs), vp]
     lib.lik_maxsim_bwd.restype = i32
+    lib.lik_maxsim_fwd_topk_supported.argtypes = [C.POINTER(FwdArgs), C.POINTER(TopkSpec)]
+    lib.lik_maxsim_fwd_topk_supported.restype = i32
+    lib.lik_maxsim_fwd_topk_workspace.argtypes = [C.POINTER(FwdArgs), C.POINTER(TopkSpec)]
+    lib.lik_maxsim_fwd_topk_workspace.restype = sz
+    lib.lik_maxsim_fwd_topk.argtypes = [C.POINTER(FwdArgs), C.POINTER(TopkSpec), vp]
+    lib.lik_maxsim_fwd_topk.restype = i32
+    lib.lik_plaid_fwd_supported.argtypes = [C.POINTER(FwdArgs), C.POINTER(PlaidIndex), C.POINTER(TopkSpec)]
+    lib.lik_plaid_fwd_supported.restype = i32
+    lib.lik_plaid_fwd_workspace.argtypes = [C.POINTER(FwdArgs), C.POINTER(PlaidIndex), C.POINTER(TopkSpec)]
+    lib.lik_plaid_fwd_workspace.restype = sz
+    lib.lik_plaid_fwd.argtypes = [C.POINTER(FwdArgs), C.POINTER(PlaidIndex), C.POINTER(TopkSpec), vp]
+    lib.lik_plaid_fwd.restype = i32
+    lib.lik_launch_count.argtypes = []
+    lib.lik_launch_count.restype = C.c_uint64
     lib.lik_topk_rows.argtypes = [vp, i64, i64, i64, i32, i32, i64, i32, vp, vp, vp]
     lib.lik_topk_rows.restype = i32
     lib.lik_topk_merge.argtypes = [vp, vp, i32, i64, i32, i32, vp, vp, vp]
@@ -115,6 +138,8 @@ def _declare(lib):
 
 EXPORTED_SYMBOLS = (
     "lik_maxsim_fwd_workspace", "lik_maxsim_fwd", "lik_maxsim_fwd_static", "lik_maxsim_bwd_workspace", "lik_maxsim_bwd", "lik_topk_rows",
+    "lik_maxsim_fwd_topk_supported", "lik_maxsim_fwd_topk_workspace", "lik_maxsim_fwd_topk",
+    "lik_plaid_fwd_supported", "lik_plaid_fwd_workspace", "lik_plaid_fwd", "lik_launch_count",
     "lik_topk_merge", "lik_plaid_decompress", "lik_plaid_approx", "lik_plaid_bwd_dq", "lik_row_inv_norm",
     "lik_last_error", "lik_version", "lik_device_supported",
 )

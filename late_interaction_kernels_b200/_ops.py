@@ -14,7 +14,7 @@ from dataclasses import dataclass
 import torch
 
 from . import _lib
-from ._lib import BwdArgs, FwdArgs, PlaidIndex, Seqs
+from ._lib import BwdArgs, FwdArgs, PlaidIndex, Seqs, TopkSpec
 
 # The launchers hand raw pointers to a C library: keep torch.compile from tracing into them (it
 # breaks the graph around the call instead).
@@ -150,6 +150,83 @@ def forward(q: SeqSpec, d: SeqSpec, *, pairing=_lib.PAIR_CROSS, group=0, pair_q=
         a.workspace, a.workspace_bytes = ws.data_ptr(), nbytes
     with torch.cuda.device(dev):
         _lib.check(lib.lik_maxsim_fwd(C.byref(a), _lib.stream_ptr(dev)), "lik_maxsim_fwd")
+    return scores, argmax
+
+
+def layout_spec(n_tokens: int, n_seq: int, max_len: int, *, cu=None, lens=None, seq_stride=0) -> Seqs:
+    """Document layout without a token matrix (the documents are a compressed index): rows = tokens."""
+    return Seqs(data=None, row_stride=0, n_rows=n_tokens, n_seq=n_seq, max_len=max_len, seq_stride=seq_stride,
+                cu=_lib.ptr(cu), lens=_lib.ptr(lens), mask=None, scale=None, scale_scalar=1.0, reserved=0)
+
+
+class TopkState:
+    """Workspace of a fused top-k that runs over several pieces of a corpus (same queries, same k)."""
+
+    def __init__(self):
+        self.ws = None
+        self.started = False
+
+
+@_no_trace
+def forward_fused(q: SeqSpec, d, *, normalize=0, plaid: PlaidIndex | None = None, topk=None, largest=True, index_offset=0,
+                  doc_base=0, state: TopkState | None = None, last=True, save_argmax=False, argmax_stride=None):
+    """The fused forms of the forward: scores fused with the per-query top-k (``topk=k``), and / or documents
+    decoded from a PLAID index inside the scoring kernel (``plaid=``; ``d`` is then a ``layout_spec``).
+
+    Returns ``None`` when the library does not take the problem on this path (the caller then scores chunks
+    with :func:`forward`).  Otherwise ``(scores, argmax)`` or, with ``topk``, ``(scores [n_q, k], index
+    [n_q, k])`` -- ``None`` for every piece but the last when ``state`` carries a corpus scored in pieces."""
+    lib = _lib.load()
+    dev = q.data.device
+    _lib.require_cuda(q.data, op="maxsim fused forward")
+    d_struct = d if isinstance(d, Seqs) else d.c_struct()
+    n_d = d_struct.n_seq
+    dim = q.data.shape[1]
+    ns = q.n_seq * n_d
+    tk = None
+    out_s = out_i = scores = argmax = None
+    stride = q.max_len if argmax_stride is None else int(argmax_stride)
+    if topk is not None:
+        flags = (_lib.TOPK_CONTINUE if (state is not None and state.started) else 0) | (0 if last else _lib.TOPK_PARTIAL)
+        if last:
+            out_s = torch.empty((q.n_seq, topk), dtype=torch.float32, device=dev)
+            out_i = torch.empty((q.n_seq, topk), dtype=torch.int64, device=dev)
+        tk = TopkSpec(k=topk, largest=int(bool(largest)), index_offset=index_offset, out_scores=_lib.ptr(out_s),
+                      out_index=_lib.ptr(out_i), flags=flags, doc_base=doc_base)
+    else:
+        scores = torch.empty(ns, dtype=torch.float32, device=dev)
+        argmax = torch.empty((ns, stride), dtype=torch.int32, device=dev) if save_argmax else None
+    a = FwdArgs(
+        q=q.c_struct(), d=d_struct, dtype=_lib.lik_dtype(q.data.dtype), dim=dim, pairing=_lib.PAIR_CROSS, group=0,
+        pair_q=None, pair_d=None, n_pairs=0, normalize=int(normalize), engine=0, scores=_lib.ptr(scores),
+        argmax=_lib.ptr(argmax) if (argmax is not None and argmax.numel()) else None, argmax_stride=stride, reserved=0,
+        workspace=None, workspace_bytes=0, status=status_word(dev).data_ptr(),
+    )
+    tkp = C.byref(tk) if tk is not None else None
+    with torch.cuda.device(dev):
+        if plaid is not None:
+            if not lib.lik_plaid_fwd_supported(C.byref(a), C.byref(plaid), tkp):
+                return None
+            nbytes = lib.lik_plaid_fwd_workspace(C.byref(a), C.byref(plaid), tkp)
+        else:
+            if not lib.lik_maxsim_fwd_topk_supported(C.byref(a), tkp):
+                return None
+            nbytes = lib.lik_maxsim_fwd_topk_workspace(C.byref(a), tkp)
+        if state is not None and state.ws is not None and state.ws.numel() >= nbytes:
+            ws = state.ws  # the candidate lists of the earlier pieces live here
+        else:
+            if state is not None and state.started:
+                raise RuntimeError("the workspace of a top-k in pieces must not grow: score the largest piece first")
+            ws = torch.empty(max(nbytes, 1), dtype=torch.uint8, device=dev)
+        a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
+        if plaid is not None:
+            _lib.check(lib.lik_plaid_fwd(C.byref(a), C.byref(plaid), tkp, _lib.stream_ptr(dev)), "lik_plaid_fwd")
+        else:
+            _lib.check(lib.lik_maxsim_fwd_topk(C.byref(a), tkp, _lib.stream_ptr(dev)), "lik_maxsim_fwd_topk")
+    if state is not None:
+        state.ws, state.started = ws, True
+    if topk is not None:
+        return (out_s, out_i) if last else (None, None)
     return scores, argmax
 
 

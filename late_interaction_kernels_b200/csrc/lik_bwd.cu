@@ -437,9 +437,11 @@ __global__ void __launch_bounds__(256) bwd_dq_fast_kernel(BwdParams P) {
           int dl;
           seq_bounds(P.d, j0 + jb + jj, r0, dl, nullptr);
           const long long drow = r0 + t;
-          float f = P.g[p0 + jb + jj];
-          if (d_factor) f *= row_factor(P.d, drow);
-          e = make_int2((int)drow, __float_as_int(f));
+          if (t < dl && drow < P.d.n_rows) {  // a saved winner outside its document contributes nothing
+            float f = P.g[p0 + jb + jj];
+            if (d_factor) f *= row_factor(P.d, drow);
+            e = make_int2((int)drow, __float_as_int(f));
+          }
         }
       }
       s_e[jj][r] = e;
@@ -490,6 +492,207 @@ __global__ void __launch_bounds__(256) bwd_dq_fast_kernel(BwdParams P) {
     const int k = c * 128 + lane * 4;
     if (k < P.dim) store4<G>(out + k, acc[c]);
   }
+}
+
+
+// =================================================================================
+// 16-byte gathers.  A row of the operand matrix is covered by 16 lanes that each move 16 bytes per
+// 256-byte chunk, so one warp-wide load instruction fetches two different rows (one per half-warp):
+// half the load instructions per gathered byte of the 8-byte version above, and twice the bytes in
+// flight per instruction slot.  Every half-warp owns one output row from start to finish, so nothing
+// is combined across lanes except the normalisation dot product.
+// Needs 16-byte-aligned rows and a width that is a multiple of 16 bytes.
+// =================================================================================
+template <typename T>
+struct Vec16 {
+  static constexpr int N = 16 / (int)sizeof(T);  // elements per 16-byte load
+};
+
+// volatile: the loads of a round keep their program order, i.e. all of them are issued before the
+// first multiply-add that consumes one (the compiler otherwise interleaves them to save registers,
+// which serialises the round trips to L2)
+template <typename T>
+__device__ __forceinline__ uint4 load16_raw(const T* p) {
+  uint4 r;
+  asm volatile("ld.global.nc.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(p));
+  return r;
+}
+__device__ __forceinline__ void unpack16(const uint4& r, float (&v)[4], const float*) {
+  v[0] = __uint_as_float(r.x); v[1] = __uint_as_float(r.y); v[2] = __uint_as_float(r.z); v[3] = __uint_as_float(r.w);
+}
+__device__ __forceinline__ void unpack16(const uint4& r, float (&v)[8], const __nv_bfloat16*) {
+  v[0] = __uint_as_float(r.x << 16); v[1] = __uint_as_float(r.x & 0xffff0000u);
+  v[2] = __uint_as_float(r.y << 16); v[3] = __uint_as_float(r.y & 0xffff0000u);
+  v[4] = __uint_as_float(r.z << 16); v[5] = __uint_as_float(r.z & 0xffff0000u);
+  v[6] = __uint_as_float(r.w << 16); v[7] = __uint_as_float(r.w & 0xffff0000u);
+}
+__device__ __forceinline__ void unpack16(const uint4& r, float (&v)[8], const __half*) {
+  const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&r.x)), b = __half22float2(*reinterpret_cast<const __half2*>(&r.y));
+  const float2 c = __half22float2(*reinterpret_cast<const __half2*>(&r.z)), d = __half22float2(*reinterpret_cast<const __half2*>(&r.w));
+  v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y; v[4] = c.x; v[5] = c.y; v[6] = d.x; v[7] = d.y;
+}
+template <typename T>
+__device__ __forceinline__ void fma16_raw(float (&acc)[Vec16<T>::N], float w, const uint4& r) {
+  float v[Vec16<T>::N];
+  unpack16(r, v, (const T*)nullptr);
+#pragma unroll
+  for (int x = 0; x < Vec16<T>::N; ++x) acc[x] = fmaf(w, v[x], acc[x]);
+}
+__device__ __forceinline__ float half_warp_sum(float v) {
+#pragma unroll
+  for (int o = 8; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+// element offset of chunk c for lane hl of the half-warp
+template <typename T>
+__device__ __forceinline__ int elt16(int c, int hl) {
+  return (c * 16 + hl) * Vec16<T>::N;
+}
+
+// (g - <g, x_hat> x_hat) * inv for a row held by one half-warp
+template <typename T, int CH>
+__device__ __forceinline__ void normalize_jacobian_row16(float (&acc)[CH][Vec16<T>::N], const T* src, float inv, int dim, int hl) {
+  constexpr int N = Vec16<T>::N;
+  float xh[CH][N];
+  float dot = 0.f;
+#pragma unroll
+  for (int c = 0; c < CH; ++c) {
+    const int k = elt16<T>(c, hl);
+    if (k < dim) {
+      unpack16(load16_raw<T>(src + k), xh[c], (const T*)nullptr);
+#pragma unroll
+      for (int e = 0; e < N; ++e) {
+        xh[c][e] *= inv;
+        dot = fmaf(acc[c][e], xh[c][e], dot);
+      }
+    } else {
+#pragma unroll
+      for (int e = 0; e < N; ++e) xh[c][e] = 0.f;
+    }
+  }
+  dot = half_warp_sum(dot);
+#pragma unroll
+  for (int c = 0; c < CH; ++c)
+#pragma unroll
+    for (int e = 0; e < N; ++e) acc[c][e] = (acc[c][e] - dot * xh[c][e]) * inv;
+}
+
+template <typename T, typename G, int CH>
+__device__ __forceinline__ void store_row16(G* out, const float (&acc)[CH][Vec16<T>::N], int dim, int hl) {
+  constexpr int N = Vec16<T>::N;
+#pragma unroll
+  for (int c = 0; c < CH; ++c) {
+    const int k = elt16<T>(c, hl);
+    if (k < dim) {
+#pragma unroll
+      for (int q = 0; q < N; q += 4) {
+        const float v[4] = {acc[c][q], acc[c][q + 1], acc[c][q + 2], acc[c][q + 3]};
+        store4<G>(out + k + q, v);
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------
+// grad_q, 16-byte gathers: grid = (n_q, ceil(rows / 16)); half-warp = query token.  The winners and
+// weights of 32 documents at a time are staged through shared memory by the whole CTA.
+// ---------------------------------------------------------------------------------
+constexpr int DQ16_TOK = 16;  // query tokens per CTA (one per half-warp)
+
+template <typename T, typename G, int CH>
+__global__ void __launch_bounds__(256) bwd_dq16_kernel(BwdParams P) {
+  constexpr int N = Vec16<T>::N;
+  constexpr int U = 8 / CH;  // rows in flight per half-warp
+  __shared__ int2 s_e[DQ_JC][DQ16_TOK];
+  const int tid = threadIdx.x, hl = tid & 15, hw = tid >> 4;
+  const int i = blockIdx.x;
+  const int s0 = blockIdx.y * DQ16_TOK;
+  const int s = s0 + hw;
+  long long qrow0;
+  int qlen;
+  seq_bounds(P.q, i, qrow0, qlen, nullptr);
+  const int q_rows = P.q.cu ? qlen : P.q.max_len;
+  if (s0 >= q_rows) return;  // whole CTA out of range
+  const long long qrow = qrow0 + s;
+  const bool owns = s < q_rows;
+  const bool active = owns && s < qlen && s < P.argmax_stride && row_valid(P.q, qrow);
+  float acc[CH][N];
+#pragma unroll
+  for (int c = 0; c < CH; ++c)
+#pragma unroll
+    for (int e = 0; e < N; ++e) acc[c][e] = 0.f;
+  long long p0;
+  int count, j0;
+  query_slots(P.pm, i, p0, count, j0);
+  const int lq = P.argmax_stride;
+  const long long pitch = P.d.row_stride;
+  const T* __restrict__ Dlane = (const T*)P.d.data + hl * N;
+  bool lane_on[CH];
+#pragma unroll
+  for (int c = 0; c < CH; ++c) lane_on[c] = elt16<T>(c, hl) < P.dim;
+  const bool d_factor = P.d.inv_norm || P.d.scale || P.d.scale_scalar != 1.f;
+  for (int jb = 0; jb < count; jb += DQ_JC) {
+    __syncthreads();
+#pragma unroll
+    for (int x = tid; x < DQ_JC * DQ16_TOK; x += 256) {
+      // entry (jj, r): winner of document jb + jj for query token s0 + r
+      const int jj = x >> 4, r = x & 15;
+      int2 e = make_int2(-1, 0);
+      if (jb + jj < count && s0 + r < lq) {
+        const int t = P.argmax[(p0 + jb + jj) * lq + s0 + r];
+        if (t >= 0) {
+          long long r0;
+          int dl;
+          seq_bounds(P.d, j0 + jb + jj, r0, dl, nullptr);
+          const long long drow = r0 + t;
+          if (t < dl && drow < P.d.n_rows) {  // a saved winner outside its document contributes nothing
+            float f = P.g[p0 + jb + jj];
+            if (d_factor) f *= row_factor(P.d, drow);
+            e = make_int2((int)drow, __float_as_int(f));
+          }
+        }
+      }
+      s_e[jj][r] = e;
+    }
+    __syncthreads();
+    if (active) {
+#pragma unroll 1
+      for (int j0g = 0; j0g < DQ_JC; j0g += U) {
+        int2 e[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) e[u] = s_e[j0g + u][hw];
+        uint4 v[U][CH];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const bool on = e[u].x >= 0;
+          const T* src = Dlane + (on ? e[u].x : 0) * pitch;
+#pragma unroll
+          for (int c = 0; c < CH; ++c) v[u][c] = (on && lane_on[c]) ? load16_raw<T>(src + c * 16 * N) : make_uint4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const float f = e[u].x >= 0 ? __int_as_float(e[u].y) : 0.f;
+#pragma unroll
+          for (int c = 0; c < CH; ++c) fma16_raw<T>(acc[c], f, v[u][c]);
+        }
+      }
+    }
+  }
+  if (!owns) return;
+  if (active) {
+    if (P.normalize) {
+      normalize_jacobian_row16<T, CH>(acc, (const T*)P.q.data + qrow * P.q.row_stride, P.q.inv_norm[qrow], P.dim, hl);
+    } else {
+      const float qf = P.q.scale_scalar * (P.q.scale ? P.q.scale[qrow] : 1.f);
+      if (qf != 1.f) {
+#pragma unroll
+        for (int c = 0; c < CH; ++c)
+#pragma unroll
+          for (int e = 0; e < N; ++e) acc[c][e] *= qf;
+      }
+    }
+  }
+  store_row16<T, G, CH>((G*)P.grad_q + qrow * P.dim, acc, P.dim, hl);
 }
 
 // ---------------------------------------------------------------------------------
@@ -710,6 +913,215 @@ __global__ void __launch_bounds__(256) bwd_dd_reduce_kernel(BwdParams P, DdSortO
   }
 }
 
+
+// The same sort for argmax strides that are a multiple of four: a lane reads four consecutive winners with
+// one 16-byte load and a warp keeps eight such loads in flight, so a pass over the document's winners is a
+// few round trips to L2 instead of one per 32 entries.  The order inside a token's list is (warp, round,
+// load, word, lane): fixed by the data alone, hence reproducible.
+constexpr int DDS_LOADS = 8;  // 16-byte loads in flight per lane
+
+__global__ void __launch_bounds__(DDS_WARPS * 32) bwd_dd_sort4_kernel(BwdParams P, DdSortOut O, int ld_pad) {
+  extern __shared__ int dds_raw[];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int j = blockIdx.x;
+  long long drow0;
+  int dlen;
+  seq_bounds(P.d, j, drow0, dlen, nullptr);
+  if (dlen <= 0) return;
+  if (dlen >= ld_pad) {  // max_len understated the longest document: report instead of overrunning shared memory
+    if (tid == 0 && P.status) atomicOr(P.status, LIK_DEV_LEN_RANGE);
+    return;
+  }
+  int i_begin, i_end;
+  if (P.pm.pairing == LIK_PAIR_CROSS) {
+    i_begin = 0;
+    i_end = P.pm.n_q;
+  } else {
+    i_begin = j / P.pm.group;
+    i_end = i_begin + 1;
+  }
+  const int lq = P.argmax_stride;          // multiple of 4
+  const int qpr = lq >> 2;                 // 16-byte groups per (query, document) slot
+  const int n_quad = (i_end - i_begin) * qpr;
+  const int n_ent = n_quad * 4;
+  const long long base = (long long)j * n_ent;
+  int* hist = dds_raw;                          // [DDS_WARPS][ld_pad]
+  int* tok_off = hist + DDS_WARPS * ld_pad;     // [ld_pad + 1] (kept for the layout shared with the scalar kernel)
+  float* gcol = reinterpret_cast<float*>(tok_off + ld_pad + 1);  // [i_end - i_begin]
+
+  for (int x = tid; x < DDS_WARPS * ld_pad; x += blockDim.x) hist[x] = 0;
+  for (int x = tid; x < i_end - i_begin; x += blockDim.x) {
+    const long long p = P.pm.pairing == LIK_PAIR_CROSS ? (long long)(i_begin + x) * P.pm.n_d + j : (long long)j;
+    gcol[x] = P.g[p];
+  }
+  __syncthreads();
+
+  // slice of this warp in 16-byte groups, a multiple of 32 * DDS_LOADS so that rounds stay whole
+  const int round_quads = 32 * DDS_LOADS;
+  const int per_warp = (((n_quad + DDS_WARPS - 1) / DDS_WARPS + round_quads - 1) / round_quads) * round_quads;
+  const int m_lo = warp * per_warp, m_hi = min(n_quad, m_lo + per_warp);
+  const int4 none = make_int4(-1, -1, -1, -1);
+
+  auto load_quad = [&](int m) -> int4 {
+    if (m >= m_hi) return none;
+    const int ii = m / qpr, sq = m - ii * qpr;
+    const long long p = P.pm.pairing == LIK_PAIR_CROSS ? (long long)(i_begin + ii) * P.pm.n_d + j : (long long)j;
+    return __ldg(reinterpret_cast<const int4*>(P.argmax + p * lq) + sq);
+  };
+  // query row of entry (ii, s) or -1 when that query token takes no part
+  auto query_row = [&](int ii, int s) -> int {
+    long long qrow0;
+    int qlen;
+    seq_bounds(P.q, i_begin + ii, qrow0, qlen, nullptr);
+    if (s >= qlen || !row_valid(P.q, qrow0 + s)) return -1;
+    return (int)(qrow0 + s);
+  };
+
+  // ---- pass 1: per-warp histogram of the winners per token ----
+  for (int mb = m_lo; mb < m_hi; mb += round_quads) {
+    int4 w[DDS_LOADS];
+#pragma unroll
+    for (int u = 0; u < DDS_LOADS; ++u) w[u] = load_quad(mb + u * 32 + lane);
+#pragma unroll
+    for (int u = 0; u < DDS_LOADS; ++u) {
+      const int m = mb + u * 32 + lane;
+      if (m >= m_hi) continue;
+      const int ii = m / qpr, s4 = (m - ii * qpr) * 4;
+      const int t4[4] = {w[u].x, w[u].y, w[u].z, w[u].w};
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int t = t4[k];
+        if (t >= 0 && t < dlen && query_row(ii, s4 + k) >= 0) atomicAdd(&hist[warp * ld_pad + t], 1);
+      }
+    }
+  }
+  __syncthreads();
+  // ---- offsets: warp w takes tokens w*32 .. in steps of DDS_WARPS*32; a running total per 32 tokens is
+  // needed first, so warp 0 scans the per-token totals and the other warps wait ----
+  if (warp == 0) {
+    int running = 0;
+    for (int tb = 0; tb < dlen; tb += 32) {
+      const int t = tb + lane;
+      int tot = 0;
+      if (t < dlen)
+        for (int w = 0; w < DDS_WARPS; ++w) tot += hist[w * ld_pad + t];
+      int incl = tot;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        int v = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += v;
+      }
+      const int excl = running + incl - tot;
+      if (t < dlen) {
+        O.tok_begin[drow0 + t] = base + excl;
+        O.tok_cnt[drow0 + t] = tot;
+        int b = excl;
+        for (int w = 0; w < DDS_WARPS; ++w) {
+          const int c = hist[w * ld_pad + t];
+          hist[w * ld_pad + t] = b;
+          b += c;
+        }
+      }
+      running += __shfl_sync(0xffffffffu, incl, 31);
+    }
+  }
+  __syncthreads();
+  // ---- pass 2: placement (the winners come from L2 this time) ----
+  for (int mb = m_lo; mb < m_hi; mb += round_quads) {
+    int4 w[DDS_LOADS];
+#pragma unroll
+    for (int u = 0; u < DDS_LOADS; ++u) w[u] = load_quad(mb + u * 32 + lane);
+#pragma unroll
+    for (int u = 0; u < DDS_LOADS; ++u) {
+      const int m = mb + u * 32 + lane;
+      const bool in = m < m_hi;
+      const int ii = in ? m / qpr : 0, s4 = in ? (m - ii * qpr) * 4 : 0;
+      const float gi = in ? gcol[ii] : 0.f;
+      const int t4[4] = {w[u].x, w[u].y, w[u].z, w[u].w};
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        int t = t4[k];
+        int qrow = -1;
+        if (in && t >= 0 && t < dlen) qrow = query_row(ii, s4 + k);
+        if (qrow < 0) t = -1;
+        const unsigned peers = __match_any_sync(0xffffffffu, t);
+        if (t >= 0) {
+          const int rank = __popc(peers & ((1u << lane) - 1u));
+          const int pos = hist[warp * ld_pad + t] + rank;
+          O.pairs[base + pos] = make_int2(qrow, __float_as_int(gi * row_factor(P.q, qrow)));
+        }
+        __syncwarp();
+        if (t >= 0 && (peers & ((1u << lane) - 1u)) == 0) hist[warp * ld_pad + t] += __popc(peers);
+        __syncwarp();
+      }
+    }
+  }
+}
+
+// grad_d reduce with 16-byte gathers: one half-warp per document token, 16 tokens per CTA.
+template <typename T, typename G, int CH>
+__global__ void __launch_bounds__(256) bwd_dd_reduce16_kernel(BwdParams P, DdSortOut O) {
+  constexpr int N = Vec16<T>::N;
+  constexpr int U = 8 / CH;
+  const int hl = threadIdx.x & 15;
+  const long long drow = (long long)blockIdx.x * 16 + (threadIdx.x >> 4);
+  if (drow >= P.d.n_rows) return;
+  float acc[CH][N];
+#pragma unroll
+  for (int c = 0; c < CH; ++c)
+#pragma unroll
+    for (int e = 0; e < N; ++e) acc[c][e] = 0.f;
+  const int cnt = __ldg(O.tok_cnt + drow);
+  const long long begin = __ldg(O.tok_begin + drow);
+  if (cnt > 0) {
+    const int2* __restrict__ list = O.pairs + begin;
+    const long long pitch = P.q.row_stride;
+    const T* __restrict__ Qlane = (const T*)P.q.data + hl * N;
+    bool lane_on[CH];
+#pragma unroll
+    for (int c = 0; c < CH; ++c) lane_on[c] = elt16<T>(c, hl) < P.dim;
+    int k = 0;
+    for (; k + U <= cnt; k += U) {
+      int2 e[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) e[u] = __ldg(list + k + u);
+      uint4 v[U][CH];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const T* src = Qlane + e[u].x * pitch;
+#pragma unroll
+        for (int c = 0; c < CH; ++c) v[u][c] = lane_on[c] ? load16_raw<T>(src + c * 16 * N) : make_uint4(0, 0, 0, 0);
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const float w = __int_as_float(e[u].y);
+#pragma unroll
+        for (int c = 0; c < CH; ++c) fma16_raw<T>(acc[c], w, v[u][c]);
+      }
+    }
+    for (; k < cnt; ++k) {
+      const int2 e = __ldg(list + k);
+      const float w = __int_as_float(e.y);
+      const T* src = Qlane + e.x * pitch;
+#pragma unroll
+      for (int c = 0; c < CH; ++c)
+        if (lane_on[c]) fma16_raw<T>(acc[c], w, load16_raw<T>(src + c * 16 * N));
+    }
+  }
+  if (P.normalize) {
+    normalize_jacobian_row16<T, CH>(acc, (const T*)P.d.data + drow * P.d.row_stride, P.d.inv_norm[drow], P.dim, hl);
+  } else {
+    const float df = P.d.scale_scalar * (P.d.scale ? P.d.scale[drow] : 1.f);
+    if (df != 1.f) {
+#pragma unroll
+      for (int c = 0; c < CH; ++c)
+#pragma unroll
+        for (int x = 0; x < N; ++x) acc[c][x] *= df;
+    }
+  }
+  store_row16<T, G, CH>((G*)P.grad_d + drow * P.dim, acc, P.dim, hl);
+}
+
 // ---------------------------------------------------------------------------------
 // Atomic scatter: one warp per (score slot, query token).  Adds into fp32 buffers.
 // WITH_DQ also scatters grad_q (pair lists, where a query's slots are not contiguous).
@@ -790,6 +1202,7 @@ namespace {
 struct BwdPlan {
   size_t qn_off, dn_off, gq32_off, gd32_off, pairs_off, begin_off, cnt_off, total;
   bool fast, sorted;
+  bool row16;  // 16-byte gathers: rows 16-byte aligned, width a multiple of 16 bytes, at most 1024 bytes
   int ld_pad;
   size_t sort_smem;
 };
@@ -802,6 +1215,12 @@ bool bwd_fast_ok(const lik_bwd_args& a) {
          ((uintptr_t)a.grad_d % 16) == 0 && a.q.n_rows < (1ll << 31) && a.d.n_rows < (1ll << 31);  // row indices travel as int
 }
 
+bool bwd_row16_ok(const lik_bwd_args& a) {
+  const size_t eb = dtype_size(a.dtype);
+  return bwd_fast_ok(a) && (a.dim * eb) % 16 == 0 && a.dim * eb <= 1024 && (a.q.row_stride * eb) % 16 == 0 &&
+         (a.d.row_stride * eb) % 16 == 0 && ((uintptr_t)a.q.data % 16) == 0 && ((uintptr_t)a.d.data % 16) == 0;
+}
+
 BwdPlan plan_bwd(const lik_bwd_args& a) {
   BwdPlan pl{};
   size_t off = 0;
@@ -812,6 +1231,7 @@ BwdPlan plan_bwd(const lik_bwd_args& a) {
   };
   pl.qn_off = pl.dn_off = pl.gq32_off = pl.gd32_off = pl.pairs_off = pl.begin_off = pl.cnt_off = (size_t)-1;
   pl.fast = bwd_fast_ok(a);
+  pl.row16 = bwd_row16_ok(a);
   pl.sorted = false;
   if (a.normalize) {
     pl.qn_off = take((size_t)a.q.n_rows * 4);
@@ -887,23 +1307,32 @@ int run_bwd(const lik_bwd_args& a, BwdParams& P, const BwdPlan& pl, cudaStream_t
 #define LIK_BY_CMAX(KERNEL, GRID, ...)                                          \
   do {                                                                          \
     if (cmax <= 4)                                                              \
-      KERNEL<T, G, 4><<<GRID, 256, 0, st>>>(__VA_ARGS__);                        \
+      KERNEL<T, G, 4><<<GRID, 256, 0, st>>>(__VA_ARGS__), ::lik::count_launch();                        \
     else if (cmax <= 8)                                                         \
-      KERNEL<T, G, 8><<<GRID, 256, 0, st>>>(__VA_ARGS__);                        \
+      KERNEL<T, G, 8><<<GRID, 256, 0, st>>>(__VA_ARGS__), ::lik::count_launch();                        \
     else if (cmax <= 16)                                                        \
-      KERNEL<T, G, 16><<<GRID, 256, 0, st>>>(__VA_ARGS__);                       \
+      KERNEL<T, G, 16><<<GRID, 256, 0, st>>>(__VA_ARGS__), ::lik::count_launch();                       \
     else                                                                        \
-      KERNEL<T, G, 32><<<GRID, 256, 0, st>>>(__VA_ARGS__);                       \
+      KERNEL<T, G, 32><<<GRID, 256, 0, st>>>(__VA_ARGS__), ::lik::count_launch();                       \
   } while (0)
 
   const bool fast = pl.fast;
   if (a.grad_q && !list && a.q.n_seq > 0 && a.q.max_len > 0) {
     dim3 grid((unsigned)a.q.n_seq, (unsigned)ceil_div(a.q.max_len, 8));
-    if (fast) {
-      if (a.dim <= 128)
-        bwd_dq_fast_kernel<T, G, 1><<<grid, 256, 0, st>>>(P);
+    if (pl.row16) {
+      const dim3 grid16((unsigned)a.q.n_seq, (unsigned)ceil_div(a.q.max_len, DQ16_TOK));
+      const size_t row_bytes = (size_t)a.dim * sizeof(T);
+      if (row_bytes <= 256)
+        bwd_dq16_kernel<T, G, 1><<<grid16, 256, 0, st>>>(P), ::lik::count_launch();
+      else if (row_bytes <= 512)
+        bwd_dq16_kernel<T, G, 2><<<grid16, 256, 0, st>>>(P), ::lik::count_launch();
       else
-        bwd_dq_fast_kernel<T, G, 2><<<grid, 256, 0, st>>>(P);
+        bwd_dq16_kernel<T, G, 4><<<grid16, 256, 0, st>>>(P), ::lik::count_launch();
+    } else if (fast) {
+      if (a.dim <= 128)
+        bwd_dq_fast_kernel<T, G, 1><<<grid, 256, 0, st>>>(P), ::lik::count_launch();
+      else
+        bwd_dq_fast_kernel<T, G, 2><<<grid, 256, 0, st>>>(P), ::lik::count_launch();
     } else {
       LIK_BY_CMAX(bwd_dq_kernel, grid, P);
     }
@@ -920,14 +1349,31 @@ int run_bwd(const lik_bwd_args& a, BwdParams& P, const BwdPlan& pl, cudaStream_t
       O.tok_begin = (long long*)(ws + pl.begin_off);
       O.tok_cnt = (int*)(ws + pl.cnt_off);
       LIK_CUDA_OK(cudaMemsetAsync(O.tok_cnt, 0, (size_t)a.d.n_rows * sizeof(int), st));
-      LIK_CUDA_OK(cudaFuncSetAttribute(bwd_dd_sort_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.sort_smem));
-      bwd_dd_sort_kernel<<<(unsigned)a.d.n_seq, DDS_WARPS * 32, pl.sort_smem, st>>>(P, O, pl.ld_pad);
+      const bool quads = a.argmax_stride % 4 == 0 && ((uintptr_t)a.argmax % 16) == 0;
+      if (quads) {
+        LIK_CUDA_OK(cudaFuncSetAttribute(bwd_dd_sort4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.sort_smem));
+        bwd_dd_sort4_kernel<<<(unsigned)a.d.n_seq, DDS_WARPS * 32, pl.sort_smem, st>>>(P, O, pl.ld_pad), ::lik::count_launch();
+      } else {
+        LIK_CUDA_OK(cudaFuncSetAttribute(bwd_dd_sort_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.sort_smem));
+        bwd_dd_sort_kernel<<<(unsigned)a.d.n_seq, DDS_WARPS * 32, pl.sort_smem, st>>>(P, O, pl.ld_pad), ::lik::count_launch();
+      }
       LIK_CUDA_OK(cudaGetLastError());
-      const unsigned rgrid = (unsigned)ceil_div(a.d.n_rows, 8);
-      if (a.dim <= 128)
-        bwd_dd_reduce_kernel<T, G, 1><<<rgrid, 256, 0, st>>>(P, O);
-      else
-        bwd_dd_reduce_kernel<T, G, 2><<<rgrid, 256, 0, st>>>(P, O);
+      if (pl.row16) {
+        const unsigned rgrid = (unsigned)ceil_div(a.d.n_rows, 16);
+        const size_t row_bytes = (size_t)a.dim * sizeof(T);
+        if (row_bytes <= 256)
+          bwd_dd_reduce16_kernel<T, G, 1><<<rgrid, 256, 0, st>>>(P, O), ::lik::count_launch();
+        else if (row_bytes <= 512)
+          bwd_dd_reduce16_kernel<T, G, 2><<<rgrid, 256, 0, st>>>(P, O), ::lik::count_launch();
+        else
+          bwd_dd_reduce16_kernel<T, G, 4><<<rgrid, 256, 0, st>>>(P, O), ::lik::count_launch();
+      } else {
+        const unsigned rgrid = (unsigned)ceil_div(a.d.n_rows, 8);
+        if (a.dim <= 128)
+          bwd_dd_reduce_kernel<T, G, 1><<<rgrid, 256, 0, st>>>(P, O), ::lik::count_launch();
+        else
+          bwd_dd_reduce_kernel<T, G, 2><<<rgrid, 256, 0, st>>>(P, O), ::lik::count_launch();
+      }
     } else {
       dim3 grid((unsigned)a.d.n_seq, (unsigned)ceil_div(a.d.max_len, DD_TOK));
       LIK_BY_CMAX(bwd_dd_owned_kernel, grid, P);
@@ -946,21 +1392,21 @@ int run_bwd(const lik_bwd_args& a, BwdParams& P, const BwdPlan& pl, cudaStream_t
     if (warps > 0) {
       unsigned grid = (unsigned)ceil_div(warps, 8);
       if (scatter_q && fast)
-        bwd_scatter_kernel<T, true, true><<<grid, 256, 0, st>>>(P);
+        bwd_scatter_kernel<T, true, true><<<grid, 256, 0, st>>>(P), ::lik::count_launch();
       else if (scatter_q)
-        bwd_scatter_kernel<T, true, false><<<grid, 256, 0, st>>>(P);
+        bwd_scatter_kernel<T, true, false><<<grid, 256, 0, st>>>(P), ::lik::count_launch();
       else if (fast)
-        bwd_scatter_kernel<T, false, true><<<grid, 256, 0, st>>>(P);
+        bwd_scatter_kernel<T, false, true><<<grid, 256, 0, st>>>(P), ::lik::count_launch();
       else
-        bwd_scatter_kernel<T, false, false><<<grid, 256, 0, st>>>(P);
+        bwd_scatter_kernel<T, false, false><<<grid, 256, 0, st>>>(P), ::lik::count_launch();
       LIK_CUDA_OK(cudaGetLastError());
     }
     if (P.gq32 && a.q.n_rows > 0) {
-      bwd_finalize_kernel<T, G><<<(unsigned)ceil_div(a.q.n_rows, 8), 256, 0, st>>>(P.gq32, P.q, a.dim, a.normalize, (G*)a.grad_q);
+      bwd_finalize_kernel<T, G><<<(unsigned)ceil_div(a.q.n_rows, 8), 256, 0, st>>>(P.gq32, P.q, a.dim, a.normalize, (G*)a.grad_q), ::lik::count_launch();
       LIK_CUDA_OK(cudaGetLastError());
     }
     if (P.gd32 && a.d.n_rows > 0) {
-      bwd_finalize_kernel<T, G><<<(unsigned)ceil_div(a.d.n_rows, 8), 256, 0, st>>>(P.gd32, P.d, a.dim, a.normalize, (G*)a.grad_d);
+      bwd_finalize_kernel<T, G><<<(unsigned)ceil_div(a.d.n_rows, 8), 256, 0, st>>>(P.gd32, P.d, a.dim, a.normalize, (G*)a.grad_d), ::lik::count_launch();
       LIK_CUDA_OK(cudaGetLastError());
     }
   }

@@ -38,6 +38,9 @@ const char* get_error();
 inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
 inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 int sm_count();
+// every kernel launch of the library is followed by this (read back through lik_launch_count)
+void count_launch();
+unsigned long long launch_count();
 
 // ---- element types -------------------------------------------------------------
 struct e4m3_t {

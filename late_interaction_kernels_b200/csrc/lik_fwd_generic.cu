@@ -2,13 +2,19 @@
 // width, every layout and pairing.  It is the exact path (fp32 FMA in a fixed
 // order, so fp32 inputs keep fp32 accuracy) and the home of shapes the tcgen05
 // kernel does not take (odd widths, pair lists).
+#include <atomic>
+
 #include "lik_common.cuh"
 
 namespace lik {
 
 namespace {
 thread_local char g_err[512] = "";
+std::atomic<unsigned long long> g_launches{0};
 }
+
+void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
+unsigned long long launch_count() { return g_launches.load(std::memory_order_relaxed); }
 
 void set_error(const char* fmt, ...) {
   va_list ap;
@@ -50,16 +56,16 @@ int launch_row_inv_norm(const void* data, int dtype, long long n_rows, int dim, 
   dim3 grid((unsigned)ceil_div(n_rows, warps)), block(warps * 32);
   switch (dtype) {
     case LIK_F32:
-      row_inv_norm_kernel<<<grid, block, 0, st>>>((const float*)data, n_rows, dim, stride, eps, out);
+      row_inv_norm_kernel<<<grid, block, 0, st>>>((const float*)data, n_rows, dim, stride, eps, out), ::lik::count_launch();
       break;
     case LIK_F16:
-      row_inv_norm_kernel<<<grid, block, 0, st>>>((const __half*)data, n_rows, dim, stride, eps, out);
+      row_inv_norm_kernel<<<grid, block, 0, st>>>((const __half*)data, n_rows, dim, stride, eps, out), ::lik::count_launch();
       break;
     case LIK_BF16:
-      row_inv_norm_kernel<<<grid, block, 0, st>>>((const __nv_bfloat16*)data, n_rows, dim, stride, eps, out);
+      row_inv_norm_kernel<<<grid, block, 0, st>>>((const __nv_bfloat16*)data, n_rows, dim, stride, eps, out), ::lik::count_launch();
       break;
     case LIK_E4M3:
-      row_inv_norm_kernel<<<grid, block, 0, st>>>((const e4m3_t*)data, n_rows, dim, stride, eps, out);
+      row_inv_norm_kernel<<<grid, block, 0, st>>>((const e4m3_t*)data, n_rows, dim, stride, eps, out), ::lik::count_launch();
       break;
     default:
       set_error("unknown dtype %d", dtype);
@@ -109,10 +115,10 @@ int launch_row_normalize(const void* data, int dtype, long long n_rows, int dim,
   dim3 grid((unsigned)ceil_div(n_rows, warps)), block(warps * 32);
   switch (dtype) {
     case LIK_F16:
-      row_normalize_kernel<<<grid, block, 0, st>>>((const __half*)data, n_rows, dim, stride, eps, (__half*)out);
+      row_normalize_kernel<<<grid, block, 0, st>>>((const __half*)data, n_rows, dim, stride, eps, (__half*)out), ::lik::count_launch();
       break;
     case LIK_BF16:
-      row_normalize_kernel<<<grid, block, 0, st>>>((const __nv_bfloat16*)data, n_rows, dim, stride, eps, (__nv_bfloat16*)out);
+      row_normalize_kernel<<<grid, block, 0, st>>>((const __nv_bfloat16*)data, n_rows, dim, stride, eps, (__nv_bfloat16*)out), ::lik::count_launch();
       break;
     default:
       set_error("normalised copies exist for 16-bit inputs only (dtype %d)", dtype);
@@ -282,7 +288,7 @@ int launch_fwd_generic(const lik_fwd_args& a, const float* qn, const float* dn, 
 #define LIK_LAUNCH_GENERIC(T)                                                                                    \
   do {                                                                                                           \
     LIK_CUDA_OK(cudaFuncSetAttribute(fwd_generic_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
-    fwd_generic_kernel<T><<<grid, 128, smem, st>>>(P);                                                           \
+    fwd_generic_kernel<T><<<grid, 128, smem, st>>>(P), ::lik::count_launch();                                                           \
   } while (0)
   switch (a.dtype) {
     case LIK_F32:

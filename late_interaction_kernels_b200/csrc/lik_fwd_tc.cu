@@ -21,7 +21,11 @@
 // sets a shared abort flag, drains its TMA copies, frees TMEM and returns.
 #include <cuda.h>
 
+#include <cstring>
+
 #include "lik_common.cuh"
+#include "lik_plaid_row.cuh"
+#include "lik_tc.cuh"
 
 namespace lik {
 
@@ -70,6 +74,8 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// generic-proxy writes to shared memory become visible to the async proxy (the tensor core's operand reads)
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
   asm volatile(
@@ -257,9 +263,30 @@ __device__ __forceinline__ uint32_t instr_desc(int ab_format, int n) {
 // ---------------------------------------------------------------------------------------------
 // Kernel parameters
 // ---------------------------------------------------------------------------------------------
+// Fused top-k (retrieve).  Instead of a score matrix the epilogue keeps candidate lists: one list per
+// (CTA, query) for every query of the tile groups the CTA works on.  A CTA meets the documents of a
+// group in ascending order, so a list is append-only in document order; a score enters when it beats the
+// list's threshold (strictly: an equal score that arrives later has a higher index and loses the tie).
+// A full list (TOPK_CAP entries) is cut back to its k best by the warp that owns it, which also raises
+// the threshold to the k-th best.  The lists of a query are merged by lik::launch_topk_slots afterwards.
+// List slot of (CTA c, group g) is c + g: a CTA works on a contiguous range of groups and the ranges of
+// consecutive CTAs are ordered, so c + g is unique among the pairs that occur.
+constexpr int TOPK_CAP = 256;  // entries per list: eight per lane of the owning warp
+struct TopkOut {
+  float* cand_key;  // [n_slots * qpg][TOPK_CAP]: score (negated when the smallest are wanted)
+  int* cand_idx;    // same shape: document index
+  int2* hdr;        // [n_slots * qpg]: x = entries in the list, y = threshold as an ordered key (0: none yet)
+  int k;
+  int qpg;          // lists per slot: two query tiles' worth
+  int largest;
+  int doc_base;     // added to the document index stored with a candidate
+};
+
+// One row of the pair-list table (LIK_PAIR_LIST): written by list_units_kernel, read by the producer.
+//   x = query (0 for a pair that is out of range), y = first document row, z = document length, w = unused
 struct TcParams {
   SeqView q, d;
-  int pairing;       // CROSS or GROUPED
+  int pairing;       // CROSS, GROUPED or LIST
   int group;         // GROUPED: documents per query
   int n_q, n_d;
   int elt_bytes;     // 1 or 2
@@ -271,7 +298,10 @@ struct TcParams {
   int q_chunks;      // 128-row chunks per query (> 1: one query chunk per tile)
   int n_tiles;       // query tiles
   int mt;            // query tiles resident per CTA (1 or 2)
-  long long n_units; // work units (tile group, document)
+  int n_sb;          // CROSS: the documents are walked in n_sb super-blocks of sb_docs documents (L2-sized)
+  int sb_docs;
+  long long n_flat;  // GROUPED / LIST: number of units
+  const int4* list_tab;  // LIST: one row per pair
   float* scores;
   float* partial;    // [n_tiles, n_d] when q_chunks > 1
   int* argmax;
@@ -279,7 +309,14 @@ struct TcParams {
   int* status;
   const int* tile_q0;  // packed queries: tile m holds queries [tile_q0[m], tile_q0[m+1]); tile_q0[-1] is the tile count
   int d_len_flagged;  // d.lens carries LEN_FLAG_MASKED on documents whose mask is not a plain prefix
+  int d_full_count;   // arrivals that complete a ring stage: 1 (TMA) or the number of decompress warps
+  TopkOut topk;       // cand_key == nullptr: scores are written instead
+  PlaidSrc plaid;     // PLAID kernels: the compressed documents
+  int plaid_f16;      // PLAID kernels: operand type fp16 instead of bf16
 };
+
+constexpr int PLAID_WARPS = 3;  // warps 0, 18 and 19 decode compressed tokens in the PLAID kernels
+constexpr int PLAID_UNROLL = 4; // tokens in flight per half-warp
 
 struct SharedCtl {
   unsigned long long q_full, q_empty;
@@ -287,7 +324,7 @@ struct SharedCtl {
   unsigned long long acc_full[2], acc_empty[2];
   int grp_abort[2];             // set by a group's first warp when its bounded wait gave up
   uint32_t stage_info[8];
-  int2 unit_info[UNIT_RING];    // per work unit: x = document length | LEN_FLAG_MASKED, y = its first row
+  int4 unit_info[UNIT_RING];    // per work unit: x = document length | LEN_FLAG_MASKED, y = its first row, z = query (LIST)
   volatile int units_posted;    // units published in unit_info so far
   uint32_t tmem_base;
   volatile int abort_flag;
@@ -300,45 +337,12 @@ struct SharedCtl {
   int xch_i[2][2][TILE_M];
   alignas(16) float col_scale[2][TILE_N];  // read as float4
   alignas(16) float col_bias[2][TILE_N];
+  // fused top-k: state of the candidate list of every query of the resident tiles
+  int seg_cnt[2][TILE_M];
+  unsigned seg_thr[2][TILE_M];
+  int seg_list[2][TILE_M];      // list number (slot * qpg + query within the group)
+  float plaid_bw[256];          // PLAID kernels: the bucket weights
 };
-
-// Debug builds only: LIK_TC_PROFILE=1 sums the cycles every role spends in each phase, =2 records
-// raw event timestamps of CTA 0 instead (one array per role).
-#ifndef LIK_TC_PROFILE
-#define LIK_TC_PROFILE 0
-#endif
-#if LIK_TC_PROFILE
-}  // namespace
-__device__ unsigned long long g_prof[16];
-__device__ long long g_trace[5][4096];
-namespace {
-#endif
-#if LIK_TC_PROFILE == 1
-#define PROF_T0(var) long long var = clock64()
-#define PROF_ADD(slot, var) prof[slot] += clock64() - var
-#define PROF_DECL() unsigned long long prof[16] = {0}
-#define PROF_FLUSH(cond) if (cond) { for (int i_ = 0; i_ < 16; ++i_) if (prof[i_]) atomicAdd(&g_prof[i_], prof[i_]); }
-#else
-#define PROF_T0(var)
-#define PROF_ADD(slot, var)
-#define PROF_DECL()
-#define PROF_FLUSH(cond)
-#endif
-#if LIK_TC_PROFILE == 3
-#define TRACE_DECL() int trace_n = 0
-#define TRACE(role)
-// per-chunk timestamps of one epilogue warp; `dep` makes the read wait for the value it names
-#define TRACE3(dep) do { if (blockIdx.x == 0 && warp == 2 && trace_n < 4096) { const long long t_ = clock64() + ((dep) == 12345.f ? 1 : 0); if (lane == 0) g_trace[3][trace_n] = t_; ++trace_n; } } while (0)
-#elif LIK_TC_PROFILE == 2
-#define TRACE_DECL() int trace_n = 0
-#define TRACE(role) do { if (blockIdx.x == 0 && trace_n < 4096) g_trace[role][trace_n++] = clock64(); } while (0)
-#else
-#define TRACE_DECL()
-#define TRACE(role)
-#endif
-#ifndef TRACE3
-#define TRACE3(dep)
-#endif
 
 // Bounded wait.  Returns false when the CTA is aborting.  The first probe lets the hardware suspend
 // the thread until the phase completes (or the hint expires), so the common case costs two
@@ -407,70 +411,119 @@ __device__ __forceinline__ TileInfo tile_info(const TcParams& P, int tile) {
   return t;
 }
 
-// Work unit u -> (tile group, document).  CROSS: group-major over all documents.  GROUPED: one
-// query per tile, unit == document, group == owning query.
-__device__ __forceinline__ void unit_decode(const TcParams& P, long long u, int& grp, int& doc) {
-  if (P.pairing == LIK_PAIR_CROSS) {
-    grp = (int)(u / P.n_d);
-    doc = (int)(u - (long long)grp * P.n_d);
-  } else {
-    doc = (int)u;
-    grp = doc / P.group;
-  }
-}
-
-
-// Walks the work units of a CTA in order.  The length words of the next document are loaded one
-// unit ahead and left untouched until that unit starts, so that the load latency hides behind the
-// current unit's work; (group, document) advance by increments instead of a division per unit.
-struct UnitWalk {
-  int grp, doc, in_grp;  // the unit fetch() was last called for
-  int raw_a, raw_b;      // its unprocessed length words
+// ---------------------------------------------------------------------------------------------
+// The units of a CTA, in the order every role walks them.
+//   CROSS: the documents are cut into super-blocks (one unless the caller asked for more: a super-block is
+//   sized to stay in L2 while every tile group passes over it); inside a super-block the units are (tile
+//   group, document), group-major, and CTA c of G takes the c-th of G equal shares.  A CTA therefore sees
+//   the same one to three groups in every super-block, each with an ascending document range.
+//   GROUPED: unit = document, group = its query.  LIST: unit = pair, group = its query (from the table).
+// `doc` is the global document index (LIST: the pair).
+// ---------------------------------------------------------------------------------------------
+struct UnitIter {
+  int sb;               // super-block
+  int doc_lo, doc_hi;   // its documents
+  long long u, u_end;   // position and end of this CTA's share of the super-block
+  int grp, doc, in_grp;
 };
 
-__device__ __forceinline__ void walk_fetch(const TcParams& P, UnitWalk& w) {
-  if (P.d.cu) {
-    w.raw_a = P.d.cu[w.doc];
-    w.raw_b = P.d.cu[w.doc + 1];
-  } else if (P.d.lens) {
-    w.raw_a = P.d.lens[w.doc];
-  }
-}
-
-__device__ __forceinline__ void walk_init(const TcParams& P, long long u, UnitWalk& w) {
-  unit_decode(P, u, w.grp, w.doc);
-  w.in_grp = P.pairing == LIK_PAIR_CROSS ? 0 : w.doc - w.grp * P.group;
-  w.raw_a = w.raw_b = 0;
-  walk_fetch(P, w);
-}
-
-__device__ __forceinline__ void walk_advance(const TcParams& P, UnitWalk& w) {
-  ++w.doc;
-  if (P.pairing == LIK_PAIR_CROSS) {
-    if (w.doc == P.n_d) {
-      w.doc = 0;
-      ++w.grp;
+__device__ __forceinline__ bool iter_enter(const TcParams& P, int n_groups, UnitIter& it) {
+  const long long c = blockIdx.x, G = gridDim.x;
+  while (it.sb < P.n_sb) {
+    long long units;
+    if (P.pairing == LIK_PAIR_CROSS) {
+      it.doc_lo = (int)min((long long)it.sb * P.sb_docs, (long long)P.n_d);
+      it.doc_hi = (int)min((long long)it.doc_lo + P.sb_docs, (long long)P.n_d);
+      units = (long long)n_groups * (it.doc_hi - it.doc_lo);
+    } else {
+      it.doc_lo = 0;
+      it.doc_hi = P.n_d;
+      units = P.n_flat;
     }
-  } else if (++w.in_grp == P.group) {
-    w.in_grp = 0;
-    ++w.grp;
+    it.u = units * c / G;
+    it.u_end = units * (c + 1) / G;
+    if (it.u < it.u_end) {
+      if (P.pairing == LIK_PAIR_CROSS) {
+        const int nd_b = it.doc_hi - it.doc_lo;
+        it.grp = (int)(it.u / nd_b);
+        it.doc = it.doc_lo + (int)(it.u - (long long)it.grp * nd_b);
+        it.in_grp = 0;
+      } else if (P.pairing == LIK_PAIR_GROUPED) {
+        it.doc = (int)it.u;
+        it.grp = it.doc / P.group;
+        it.in_grp = it.doc - it.grp * P.group;
+      } else {
+        it.doc = (int)it.u;
+        it.grp = -1;  // comes from the table
+        it.in_grp = 0;
+      }
+      return true;
+    }
+    ++it.sb;
   }
+  return false;
+}
+__device__ __forceinline__ bool iter_begin(const TcParams& P, int n_groups, UnitIter& it) {
+  it.sb = 0;
+  return iter_enter(P, n_groups, it);
+}
+__device__ __forceinline__ bool iter_next(const TcParams& P, int n_groups, UnitIter& it) {
+  if (++it.u < it.u_end) {
+    ++it.doc;
+    if (P.pairing == LIK_PAIR_CROSS) {
+      if (it.doc == it.doc_hi) {
+        it.doc = it.doc_lo;
+        ++it.grp;
+      }
+    } else if (P.pairing == LIK_PAIR_GROUPED) {
+      if (++it.in_grp == P.group) {
+        it.in_grp = 0;
+        ++it.grp;
+      }
+    }
+    return true;
+  }
+  ++it.sb;
+  return iter_enter(P, n_groups, it);
 }
 
+// Length words of a unit's document, loaded one unit ahead of their use.
+struct UnitRaw {
+  int a, b, q;
+};
+__device__ __forceinline__ UnitRaw unit_fetch(const TcParams& P, const UnitIter& it) {
+  UnitRaw r{0, 0, 0};
+  if (P.pairing == LIK_PAIR_LIST) {
+    const int4 t = __ldg(P.list_tab + it.doc);
+    r.q = t.x;
+    r.a = t.y;
+    r.b = t.z;
+  } else if (P.d.cu) {
+    r.a = P.d.cu[it.doc];
+    r.b = P.d.cu[it.doc + 1];
+  } else if (P.d.lens) {
+    r.a = P.d.lens[it.doc];
+  }
+  return r;
+}
 // First row and column count of the fetched document; `masked` tells whether its mask has holes.
 // Lengths come from the caller-validated views, clamped to the padded extent.
-__device__ __forceinline__ void walk_resolve(const TcParams& P, const UnitWalk& w, long long& row0, int& len, bool& masked) {
+__device__ __forceinline__ void unit_resolve(const TcParams& P, const UnitIter& it, const UnitRaw& r, long long& row0, int& len,
+                                             bool& masked) {
   masked = false;
-  if (P.d.cu) {
-    const int a = w.raw_a, b = w.raw_b;
+  if (P.pairing == LIK_PAIR_LIST) {
+    row0 = r.a;
+    len = r.b;
+  } else if (P.d.cu) {
+    const int a = r.a, b = r.b;
     row0 = a;
     len = b > a ? b - a : 0;
     if ((long long)a + len > P.d.n_rows) len = P.d.n_rows > a ? (int)(P.d.n_rows - a) : 0;
   } else {
-    row0 = (long long)w.doc * P.d.seq_stride;
+    row0 = (long long)it.doc * P.d.seq_stride;
     len = P.d.max_len;
     if (P.d.lens) {
-      int l = w.raw_a;
+      int l = r.a;
       if (P.d_len_flagged) {
         masked = (l & LEN_FLAG_MASKED) != 0;
         l &= ~LEN_FLAG_MASKED;
@@ -479,12 +532,6 @@ __device__ __forceinline__ void walk_resolve(const TcParams& P, const UnitWalk& 
     }
   }
 }
-
-#if LIK_TC_PROFILE == 1
-__device__ __forceinline__ void prof_tiles(unsigned long long* prof) { prof[11] += 1; }
-#else
-#define prof_tiles(x)
-#endif
 
 struct DocMaps {
   CUtensorMap m[4];  // document boxes of 64, 128, 192 and 256 rows: one copy per K slab whatever the tile height
@@ -498,7 +545,62 @@ constexpr uint32_t STAGE_FIRST = 1u << 18;     // first stage of a query-tile gr
 constexpr uint32_t STAGE_LAST = 1u << 19;      // last stage of the group: hand the tiles back afterwards
 constexpr uint32_t STAGE_END = 1u << 20;       // no more work
 
-template <bool FP8, bool ARGMAX, bool SCALED>
+// Monotone map float -> unsigned (larger float, larger key); 0 is below every float.
+__device__ __forceinline__ unsigned ordered_key(float f) {
+  const unsigned u = __float_as_uint(f);
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+
+// Cut a full candidate list (TOPK_CAP entries, in arrival = ascending document order) back to its k best
+// and return the k-th best as an ordered key.  One warp; lane l holds entries l, l + 32, ...  The k-th
+// largest key is found by bisection on its bits (32 warp-wide counts); entries above it stay, and of the
+// entries equal to it the earliest ones (lowest document indices), so that exactly k remain, in order.
+__device__ __noinline__ unsigned topk_compact(float* keys, int* idx, int k, int lane) {
+  constexpr int PER = TOPK_CAP / 32;
+  unsigned uk[PER];
+  float fk[PER];
+  int id[PER];
+#pragma unroll
+  for (int j = 0; j < PER; ++j) {
+    fk[j] = keys[j * 32 + lane];
+    id[j] = idx[j * 32 + lane];
+    uk[j] = ordered_key(fk[j]);
+  }
+  unsigned kth = 0;
+  for (int bit = 31; bit >= 0; --bit) {
+    const unsigned cand = kth | (1u << bit);
+    int c = 0;
+#pragma unroll
+    for (int j = 0; j < PER; ++j) c += uk[j] >= cand ? 1 : 0;
+    c = __reduce_add_sync(0xffffffffu, c);
+    if (c >= k) kth = cand;
+  }
+  int n_gt = 0;
+#pragma unroll
+  for (int j = 0; j < PER; ++j) n_gt += uk[j] > kth ? 1 : 0;
+  n_gt = __reduce_add_sync(0xffffffffu, n_gt);
+  const int need = k - n_gt;  // ties to keep (at least one)
+  const unsigned lt = (1u << lane) - 1u;
+  int out = 0, ties = 0;
+#pragma unroll
+  for (int j = 0; j < PER; ++j) {
+    const bool eq = uk[j] == kth;
+    const unsigned m_eq = __ballot_sync(0xffffffffu, eq);
+    const bool keep = uk[j] > kth || (eq && ties + __popc(m_eq & lt) < need);
+    const unsigned m_keep = __ballot_sync(0xffffffffu, keep);
+    if (keep) {
+      const int pos = out + __popc(m_keep & lt);
+      keys[pos] = fk[j];
+      idx[pos] = id[j];
+    }
+    out += __popc(m_keep);
+    ties += __popc(m_eq);
+  }
+  __syncwarp();
+  return kth;
+}
+
+template <bool FP8, bool ARGMAX, bool SCALED, bool PLAID>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ DocMaps d_maps, const TcParams P) {
   extern __shared__ unsigned char smem_raw[];
@@ -512,18 +614,17 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
-  // contiguous range of work units for this CTA
   // greedy-packed query tiles are counted on the device (the count sits in front of the table)
   const int n_tiles = P.tile_q0 ? P.tile_q0[-1] : P.n_tiles;
-  const long long n_units = P.tile_q0 ? (long long)((n_tiles + P.mt - 1) / P.mt) * P.n_d : P.n_units;
-  const long long u_begin = n_units * (long long)blockIdx.x / gridDim.x;
-  const long long u_end = n_units * (long long)(blockIdx.x + 1) / gridDim.x;
+  const int n_groups = (n_tiles + P.mt - 1) / P.mt;
+  const bool list = P.pairing == LIK_PAIR_LIST;
+  const bool topk = P.topk.cand_key != nullptr;
 
   if (tid == 0) {
     mbar_init(smem_u32(&ctl->q_full), 1);
     mbar_init(smem_u32(&ctl->q_empty), 1);
     for (int s = 0; s < P.stages; ++s) {
-      mbar_init(smem_u32(&ctl->d_full[s]), 1);
+      mbar_init(smem_u32(&ctl->d_full[s]), (uint32_t)P.d_full_count);
       mbar_init(smem_u32(&ctl->d_empty[s]), 1);
     }
     for (int a = 0; a < 2; ++a) {
@@ -535,8 +636,11 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
     ctl->units_posted = 0;
     fence_barrier_init();
     prefetch_tmap(&q_map);
-    for (int i = 0; i < 4; ++i) prefetch_tmap(&d_maps.m[i]);
+    if (!PLAID)
+      for (int i = 0; i < 4; ++i) prefetch_tmap(&d_maps.m[i]);
   }
+  if (PLAID)
+    for (int b = tid; b < (1 << P.plaid.nbits); b += NUM_THREADS) ctl->plaid_bw[b] = P.plaid.bucket_weights[b];
   if (warp == 1) {
     tmem_alloc(smem_u32(&ctl->tmem_base), 512);
     tmem_relinquish();
@@ -546,111 +650,170 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
   tc_fence_after();
   const uint32_t tmem_base = ctl->tmem_base;
 
-  // The producer and the epilogue groups walk the same unit sequence.
-  UnitWalk wk{};
-  if (u_begin < u_end) walk_init(P, u_begin, wk);
-#define LIK_NEXT_UNIT()                                            \
-  const int grp = wk.grp, doc = wk.doc;                            \
-  long long drow0;                                                 \
-  int dlen;                                                        \
-  bool dmasked;                                                    \
-  walk_resolve(P, wk, drow0, dlen, dmasked);                       \
-  (void)dmasked;                                                   \
-  (void)doc;                                                       \
-  if (u + 1 < u_end) {                                             \
-    walk_advance(P, wk);                                           \
-    walk_fetch(P, wk);                                             \
-  }
-
-  if (warp == 0) {
-    // =========================== TMA producer ===========================
-    if (lane == 0) {
+  const bool producer_warp = warp == 0 || (PLAID && warp >= 2 + 2 * GROUP_WARPS);
+  if (producer_warp) {
+    // =========================== producer ===========================
+    // TMA kernels: one thread (warp 0, lane 0) walks the units, loads the query tiles and the document
+    // stages with TMA and leaves the stage words and the unit ring.  PLAID kernels: three whole warps walk
+    // the units in step; each decodes its share of every stage's tokens into the swizzled operand layout
+    // (generic-proxy stores, fenced for the tensor core's reads), and arrives on the stage barrier; the
+    // elected thread of warp 0 still does everything else.
+    const bool elect = warp == 0 && lane == 0;
+    if (PLAID || lane == 0) {
+      const int pw = warp == 0 ? 0 : warp - (2 + 2 * GROUP_WARPS) + 1;  // decoder warp number 0..2
       int cur_grp = -1;
       uint32_t n_qload = 0, st = 0, ph = 0, n_dload = 0;
       long long uc = 0;
       const int x_per_slab = SLAB_BYTES_ROW / P.elt_bytes;
       bool ok = true;
       int tiles_here = 0;
-      PROF_DECL();
-      TRACE_DECL();
-      PROF_T0(p_all);
-      for (long long u = u_begin; u < u_end && ok; ++u, ++uc) {
-        LIK_NEXT_UNIT();
-        const bool last_unit_of_grp = (u + 1 >= u_end) || (wk.grp != grp);
+      UnitIter cur, nxt;
+      bool have = iter_begin(P, n_groups, cur);
+      UnitRaw raw_cur{0, 0, 0}, raw_nxt{0, 0, 0};
+      bool have_nxt = false;
+      if (have) {
+        raw_cur = unit_fetch(P, cur);
+        nxt = cur;
+        have_nxt = iter_next(P, n_groups, nxt);
+        if (have_nxt) raw_nxt = unit_fetch(P, nxt);
+      }
+      while (have && ok) {
+        const int grp = list ? raw_cur.q : cur.grp;
+        const int next_grp = have_nxt ? (list ? raw_nxt.q : nxt.grp) : -1;
+        long long drow0;
+        int dlen;
+        bool dmasked;
+        unit_resolve(P, cur, raw_cur, drow0, dlen, dmasked);
+        // step the look-ahead now so that the next unit's length words are in flight during this unit
+        cur = nxt;
+        raw_cur = raw_nxt;
+        have = have_nxt;
+        if (have) {
+          have_nxt = iter_next(P, n_groups, nxt);
+          if (have_nxt) raw_nxt = unit_fetch(P, nxt);
+        }
+        const bool last_unit_of_grp = next_grp != grp;
         uint32_t first = 0;
         if (grp != cur_grp) {
           cur_grp = grp;
           first = STAGE_FIRST;
-          // wait until the MMAs that read the previous query tiles are done
-          PROF_T0(p_q);
-          ok = wait_bar(&ctl->q_empty, (n_qload & 1) ^ 1, ctl, P.status);
-          PROF_ADD(2, p_q);
-          if (!ok) break;
           const int t0 = grp * P.mt, t1 = min(t0 + P.mt, n_tiles);
           tiles_here = t1 - t0;
-          mbar_arrive_expect_tx(smem_u32(&ctl->q_full), (uint32_t)((t1 - t0) * q_tile_bytes));
-          for (int t = t0; t < t1; ++t) {
-            TileInfo ti = tile_info(P, t);
-            for (int sl = 0; sl < P.n_slabs; ++sl)
-              tma_load_2d(smem_u32(q_smem + (t - t0) * q_tile_bytes + sl * TILE_M * SLAB_BYTES_ROW), &q_map, sl * x_per_slab,
-                          (int)ti.row0, smem_u32(&ctl->q_full));
+          if (elect) {
+            // wait until the MMAs that read the previous query tiles are done
+            ok = wait_bar(&ctl->q_empty, (n_qload & 1) ^ 1, ctl, P.status);
+            if (ok) {
+              mbar_arrive_expect_tx(smem_u32(&ctl->q_full), (uint32_t)((t1 - t0) * q_tile_bytes));
+              for (int t = t0; t < t1; ++t) {
+                TileInfo ti = tile_info(P, t);
+                for (int sl = 0; sl < P.n_slabs; ++sl)
+                  tma_load_2d(smem_u32(q_smem + (t - t0) * q_tile_bytes + sl * TILE_M * SLAB_BYTES_ROW), &q_map, sl * x_per_slab,
+                              (int)ti.row0, smem_u32(&ctl->q_full));
+              }
+            }
           }
           ++n_qload;
+          if (PLAID && warp == 0) ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+          if (!ok) break;
         }
         // which accumulators this unit feeds: both resident tiles, or (one tile) alternating with the unit count
         const uint32_t acc_bits = P.mt == 2 ? (tiles_here == 2 ? (STAGE_ACC0 | STAGE_ACC1) : STAGE_ACC0)
                                             : ((uc & 1) ? STAGE_ACC1 : STAGE_ACC0);
         // publish the unit for the epilogue groups, then its stages; an empty document still sends one
         // (empty) stage so that every unit passes through the same hand-shakes
-        ctl->unit_info[uc & (UNIT_RING - 1)] = make_int2(dlen | (dmasked ? LEN_FLAG_MASKED : 0), (int)drow0);
-        __threadfence_block();
-        ctl->units_posted = (int)uc + 1;
+        if (elect) {
+          ctl->unit_info[uc & (UNIT_RING - 1)] = make_int4(dlen | (dmasked ? LEN_FLAG_MASKED : 0), (int)drow0, grp, 0);
+          __threadfence_block();
+          ctl->units_posted = (int)uc + 1;
+        }
         int c0 = 0;
         do {
           const int ncols = max(0, min(TILE_N, dlen - c0));
-          const int boxes = (ncols + BOX_ROWS - 1) / BOX_ROWS;
-          PROF_T0(p_d);
           ok = wait_bar(&ctl->d_empty[st], ph ^ 1, ctl, P.status);
-          PROF_ADD(1, p_d);
-          TRACE(0);
           if (!ok) break;
           const uint32_t full = smem_u32(&ctl->d_full[st]);
-          uint32_t info = (uint32_t)ncols | acc_bits;
-          if (c0 == 0) info |= first;
-          if (last_unit_of_grp && c0 + TILE_N >= dlen) info |= STAGE_LAST;
-          ctl->stage_info[st] = info;
-          if (boxes > 0) {
-            mbar_arrive_expect_tx(full, (uint32_t)(boxes * BOX_ROWS * SLAB_BYTES_ROW * P.n_slabs));
-            const CUtensorMap* map = &d_maps.m[boxes - 1];
-            for (int sl = 0; sl < P.n_slabs; ++sl)
-              tma_load_2d(smem_u32(d_smem + (size_t)st * d_stage_bytes + sl * TILE_N * SLAB_BYTES_ROW), map, sl * x_per_slab,
-                          (int)(drow0 + c0), full);
+          if (elect) {
+            uint32_t info = (uint32_t)ncols | acc_bits;
+            if (c0 == 0) info |= first;
+            if (last_unit_of_grp && c0 + TILE_N >= dlen) info |= STAGE_LAST;
+            ctl->stage_info[st] = info;
+          }
+          if (PLAID) {
+            // tokens of the stage go round-robin to the six half-warps of the three decoder warps
+            const int hl = lane & 15;
+            const int hw6 = pw * 2 + (lane >> 4);
+            const bool lane_on = hl * 8 < P.plaid.dim;
+            unsigned char* stage = d_smem + (size_t)st * d_stage_bytes + (hl >> 3) * (TILE_N * SLAB_BYTES_ROW);
+            for (int tb = 0; tb < ncols; tb += 2 * PLAID_WARPS * PLAID_UNROLL) {  // same trip count on every lane
+              const int t0 = tb + hw6;
+              int code[PLAID_UNROLL];
+#pragma unroll
+              for (int u = 0; u < PLAID_UNROLL; ++u) {
+                const int t = t0 + u * 2 * PLAID_WARPS;
+                code[u] = t < ncols ? plaid_code(P.plaid, drow0 + c0 + t, P.status) : 0;
+              }
+              PlaidRaw r[PLAID_UNROLL];
+#pragma unroll
+              for (int u = 0; u < PLAID_UNROLL; ++u) {
+                const int t = t0 + u * 2 * PLAID_WARPS;
+                if (t < ncols && lane_on) r[u] = plaid_load(P.plaid, drow0 + c0 + t, code[u], hl);
+                else r[u] = PlaidRaw{make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), 0ull};
+              }
+#pragma unroll
+              for (int u = 0; u < PLAID_UNROLL; ++u) {
+                const int t = t0 + u * 2 * PLAID_WARPS;
+                // the shuffles of the norm need the whole half-warp: a token past the end is computed and dropped
+                float e[8];
+                plaid_features(P.plaid, r[u], ctl->plaid_bw, e);
+                if (!lane_on) {
+#pragma unroll
+                  for (int i = 0; i < 8; ++i) e[i] = 0.f;
+                }
+                const float inv = plaid_inv_norm(P.plaid, e);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) e[i] *= inv;
+                if (t < ncols && lane_on)
+                  *reinterpret_cast<uint4*>(stage + t * SLAB_BYTES_ROW + (((hl & 7) ^ (t & 7)) << 4)) = plaid_pack16(e, P.plaid_f16 != 0);
+              }
+            }
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(full);
           } else {
-            mbar_arrive(full);
+            const int boxes = (ncols + BOX_ROWS - 1) / BOX_ROWS;
+            if (boxes > 0) {
+              mbar_arrive_expect_tx(full, (uint32_t)(boxes * BOX_ROWS * SLAB_BYTES_ROW * P.n_slabs));
+              const CUtensorMap* map = &d_maps.m[boxes - 1];
+              for (int sl = 0; sl < P.n_slabs; ++sl)
+                tma_load_2d(smem_u32(d_smem + (size_t)st * d_stage_bytes + sl * TILE_N * SLAB_BYTES_ROW), map, sl * x_per_slab,
+                            (int)(drow0 + c0), full);
+            } else {
+              mbar_arrive(full);
+            }
           }
           ++n_dload;
           if (++st == (uint32_t)P.stages) { st = 0; ph ^= 1; }
-          TRACE(0);
           c0 += TILE_N;
         } while (c0 < dlen);
+        ++uc;
       }
       if (ok) {
         // tell the issuer that the stream has ended
         ok = wait_bar(&ctl->d_empty[st], ph ^ 1, ctl, P.status);
         if (ok) {
-          ctl->stage_info[st] = STAGE_END;
-          mbar_arrive(smem_u32(&ctl->d_full[st]));
+          if (elect) ctl->stage_info[st] = STAGE_END;
+          if (lane == 0) mbar_arrive(smem_u32(&ctl->d_full[st]));
         }
       }
-      PROF_ADD(0, p_all);
-      PROF_FLUSH(true);
-      if (!ok) {
+      if (!ok && elect) {
         // aborting: let the copies already issued land before the CTA goes away
-        for (uint32_t i = 1; i <= (uint32_t)P.stages && i <= n_dload; ++i) {
-          const bool wrapped = i > st;  // that use lies before the last wrap of the ring
-          const uint32_t slot = wrapped ? st + (uint32_t)P.stages - i : st - i;
-          const uint32_t bar = smem_u32(&ctl->d_full[slot]);
-          for (int spin = 0; spin < (1 << 16) && !mbar_try_wait(bar, wrapped ? ph ^ 1 : ph); ++spin) {
+        if (!PLAID) {
+          for (uint32_t i = 1; i <= (uint32_t)P.stages && i <= n_dload; ++i) {
+            const bool wrapped = i > st;  // that use lies before the last wrap of the ring
+            const uint32_t slot = wrapped ? st + (uint32_t)P.stages - i : st - i;
+            const uint32_t bar = smem_u32(&ctl->d_full[slot]);
+            for (int spin = 0; spin < (1 << 16) && !mbar_try_wait(bar, wrapped ? ph ^ 1 : ph); ++spin) {
+            }
           }
         }
         if (n_qload) {
@@ -681,22 +844,13 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
         a_lo0[k] = a_desc0 + (uint32_t)((k & 3) * 2 + (k >> 2) * ((TILE_M * SLAB_BYTES_ROW) >> 4));
         a_lo1[k] = a_lo0[k] + a_tile1;
       }
-      PROF_DECL();
-      TRACE_DECL();
-      PROF_T0(m_all);
       while (ok) {
-        PROF_T0(m_d);
-        TRACE(1);
         ok = wait_bar(&ctl->d_full[st], ph, ctl, P.status);
-        PROF_ADD(4, m_d);
-        TRACE(1);
         if (!ok) break;
         const uint32_t info = ctl->stage_info[st];
         if (info & STAGE_END) break;
         if (info & STAGE_FIRST) {
-          PROF_T0(m_q);
           ok = wait_bar(&ctl->q_full, q_ph, ctl, P.status);
-          PROF_ADD(6, m_q);
           if (!ok) break;
           q_ph ^= 1;
         }
@@ -710,10 +864,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
 #pragma unroll
           for (int a = 0; a < 2; ++a) {
             if (!(info & (STAGE_ACC0 << a))) continue;
-            PROF_T0(m_a);
             ok = wait_bar(&ctl->acc_empty[a], ((acc_ph >> a) & 1u) ^ 1u, ctl, P.status);
-            PROF_ADD(5, m_a);
-            TRACE(1);
             if (!ok) break;
             acc_ph ^= 1u << a;
             tc_fence_after();
@@ -721,7 +872,6 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
             // descriptors differ only in the 16-byte-unit start address: add offsets to a base descriptor
             uint32_t a_desc = a_desc0 + a * a_tile1;
             uint32_t b_desc = b_stage;
-            PROF_T0(m_i);
             if (ncols == 0) {
               // empty document: the accumulator still changes hands so that both sides keep their phase
             } else if (k_steps == 8) {
@@ -750,20 +900,14 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
                 b_desc += (uint32_t)((TILE_N * SLAB_BYTES_ROW) >> 4);
               }
             }
-            PROF_ADD(13, m_i);
-            TRACE(1);
             tc_commit(smem_u32(&ctl->acc_full[a]));
-            TRACE(1);
           }
           if (!ok) break;
         }
         tc_commit(smem_u32(&ctl->d_empty[st]));  // ring slot reusable once these MMAs retire
         if (info & STAGE_LAST) tc_commit(smem_u32(&ctl->q_empty));  // and so are the query tiles
-        TRACE(1);
         if (++st == (uint32_t)P.stages) { st = 0; ph ^= 1; }
       }
-      PROF_ADD(3, m_all);
-      PROF_FLUSH(true);
     }
   } else if (warp < 2 + 2 * GROUP_WARPS) {
     // =========================== epilogue groups ===========================
@@ -790,6 +934,8 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
     int tile_id = 0;
     long long arg_off = -1;   // ARGMAX: offset of this row's slot for document 0 (-1: row stores nothing)
     long long warp_out = -1;  // aligned tiles: offset of this warp's query score for document 0
+    int my_list = -1;         // top-k: the list whose state thread `et` (half 0) loaded into shared memory
+    int warp_seg = -1;        // aligned tiles: the query (segment) of this warp's rows
     // Rendezvous of the whole group / of half 0 on hardware named barriers: a waiting warp issues
     // nothing.  Nobody waits on anything else between two of them, so every warp of the group always
     // arrives; the only bounded waits of a group (on the accumulator) are done by its first warp, which
@@ -807,29 +953,61 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
     LIK_GRP_SYNC();                                                                  \
     ok = ctl->grp_abort[wg] == 0;                                                    \
   } while (0)
+    // top-k: write the state of the lists this thread loaded back to their headers
+#define LIK_TOPK_STORE_BACK()                                                                          \
+  do {                                                                                                 \
+    if (topk && sub == 0 && my_list >= 0) {                                                            \
+      P.topk.hdr[my_list] = make_int2(ctl->seg_cnt[wg][et], (int)ctl->seg_thr[wg][et]);                \
+      my_list = -1;                                                                                    \
+    }                                                                                                  \
+  } while (0)
+    // one (query, document) score: stored, or offered to the query's candidate list (warp-uniform)
+#define LIK_EMIT_SCORE(sg_, value_, offset_)                                                           \
+  do {                                                                                                 \
+    if (!topk) {                                                                                       \
+      if (lane == 0) P.scores[offset_] = (value_);                                                     \
+    } else {                                                                                           \
+      const float key_ = (P.topk.largest ? (value_) : -(value_)) + 0.f;                                \
+      const unsigned ukey_ = ordered_key(key_);                                                        \
+      if (ukey_ > ctl->seg_thr[wg][sg_]) {                                                             \
+        int cnt_ = ctl->seg_cnt[wg][sg_];                                                              \
+        float* keys_ = P.topk.cand_key + (long long)ctl->seg_list[wg][sg_] * TOPK_CAP;                 \
+        int* idx_ = P.topk.cand_idx + (long long)ctl->seg_list[wg][sg_] * TOPK_CAP;                    \
+        if (lane == 0) {                                                                               \
+          keys_[cnt_] = key_;                                                                          \
+          idx_[cnt_] = doc + P.topk.doc_base;                                                          \
+        }                                                                                              \
+        ++cnt_;                                                                                        \
+        __syncwarp();                                                                                  \
+        if (cnt_ == TOPK_CAP) {                                                                        \
+          const unsigned thr_ = topk_compact(keys_, idx_, P.topk.k, lane);                             \
+          cnt_ = P.topk.k;                                                                             \
+          if (lane == 0) ctl->seg_thr[wg][sg_] = thr_;                                                 \
+        }                                                                                              \
+        if (lane == 0) ctl->seg_cnt[wg][sg_] = cnt_;                                                   \
+        __syncwarp();                                                                                  \
+      }                                                                                                \
+    }                                                                                                  \
+  } while (0)
 
-    int grp = 0, doc = 0, in_grp = 0;
-    if (u_begin < u_end) {
-      unit_decode(P, u_begin, grp, doc);
-      in_grp = P.pairing == LIK_PAIR_CROSS ? 0 : doc - grp * P.group;
-    }
+    UnitIter it;
+    bool have_unit = iter_begin(P, n_groups, it);
     const bool cross = P.pairing == LIK_PAIR_CROSS;
-    const int n_my_units = (int)(u_end - u_begin);
-    PROF_DECL();
-    TRACE_DECL();
-    PROF_T0(e_all);
-    for (; uc < n_my_units && ok; ++uc) {
-      if (uc > 0) {  // next (group, document)
-        ++doc;
-        if (cross) {
-          if (doc == P.n_d) {
-            doc = 0;
-            ++grp;
-          }
-        } else if (++in_grp == P.group) {
-          in_grp = 0;
-          ++grp;
+    for (; have_unit && ok; ++uc, have_unit = iter_next(P, n_groups, it)) {
+      int grp = it.grp;
+      const int doc = it.doc;
+      bool waited = false;
+      if (list) {
+        // the query of a pair is only known from the unit ring
+        if (leader) {
+          const bool ok_ = wait_posted(ctl, uc, P.status);
+          if (!ok_ && lane == 0) ctl->grp_abort[wg] = 1;
         }
+        LIK_GRP_SYNC();
+        ok = ctl->grp_abort[wg] == 0;
+        if (!ok) break;
+        grp = ctl->unit_info[uc & (UNIT_RING - 1)].z;
+        waited = true;
       }
       if (grp != cur_grp) {
         cur_grp = grp;
@@ -838,6 +1016,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
         tile_id = grp * P.mt + m;
         have_tile = tile_id < n_tiles;
         LIK_GRP_SYNC();  // everyone in the group is done reading the old table
+        LIK_TOPK_STORE_BACK();
         TileInfo ti{};
         int nseg = 0;
         if (have_tile) {
@@ -869,18 +1048,29 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
             l = min(TILE_M, max(0, len - ti.chunk * TILE_M));
             if (len > P.q_chunks * TILE_M && P.status) atomicOr(P.status, LIK_DEV_LEN_RANGE);
           }
-          if ((off & 31) != 0 || l > 32) ctl->warp_aligned[wg] = 0;
+          // an empty query owns no accumulator row, so only the per-query pass below can write its zero
+          if ((off & 31) != 0 || l > 32 || l == 0) ctl->warp_aligned[wg] = 0;
           if (ARGMAX && len > P.argmax_stride && P.status) atomicOr(P.status, LIK_DEV_ARGMAX_STRIDE);
           ctl->seg_off[wg][et] = off;
           ctl->seg_len[wg][et] = l;
           ctl->seg_q[wg][et] = ti.qa + et;
           for (int i = 0; i < l; ++i) ctl->row_seg[wg][off + i] = (short)et;
+          if (topk) {
+            // the candidate list of (this CTA, this group, this query)
+            // (with one resident tile the two epilogue groups take alternate documents: a list each)
+            my_list = ((int)blockIdx.x + grp) * P.topk.qpg + (P.mt == 2 ? m : wg) * P.q_per_tile + et;
+            const int2 hd = P.topk.hdr[my_list];
+            ctl->seg_list[wg][et] = my_list;
+            ctl->seg_cnt[wg][et] = hd.x;
+            ctl->seg_thr[wg][et] = (unsigned)hd.y;
+          }
         }
         LIK_GRP_SYNC();
         in_seg = false;
         row_ok = false;
         arg_off = -1;
         warp_out = -1;
+        warp_seg = -1;
         aligned = have_tile && ctl->warp_aligned[wg] != 0;
         if (have_tile) {
           const int sg = ctl->row_seg[wg][row];
@@ -895,7 +1085,10 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
               arg_off = (cross ? (long long)my_q * P.n_d : 0ll) * P.argmax_stride + my_s;
           }
           const int sg0 = ctl->row_seg[wg][quad * 32];
-          if (aligned && sg0 >= 0) warp_out = cross ? (long long)ctl->seg_q[wg][sg0] * P.n_d : 0ll;
+          if (aligned && sg0 >= 0) {
+            warp_seg = sg0;
+            warp_out = cross ? (long long)ctl->seg_q[wg][sg0] * P.n_d : 0ll;
+          }
         }
       }
       // with two resident tiles each group handles its own tile for every document; with one tile the
@@ -906,24 +1099,27 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
       // Unit data (length, first row) comes from the producer's ring.  Kernels with per-column
       // multipliers wait for the publication alone (it precedes the unit's loads) so that they can stage
       // the column arrays while the MMAs run; the others take it with their first accumulator wait.
-      PROF_T0(e_w);
-      if (SCALED) {
-        if (leader) {
-          const bool ok_ = wait_posted(ctl, uc, P.status);
-          if (!ok_ && lane == 0) ctl->grp_abort[wg] = 1;
+      if (SCALED || waited) {
+        if (!waited) {
+          if (leader) {
+            const bool ok_ = wait_posted(ctl, uc, P.status);
+            if (!ok_ && lane == 0) ctl->grp_abort[wg] = 1;
+          }
+          LIK_GRP_SYNC();
+          ok = ctl->grp_abort[wg] == 0;
         }
-        LIK_GRP_SYNC();
-        ok = ctl->grp_abort[wg] == 0;
+        if (ok && !SCALED) LIK_GROUP_WAIT_ACC(false);
       } else {
         LIK_GROUP_WAIT_ACC(true);
       }
-      PROF_ADD(8, e_w);
       if (!ok) break;
-      const int2 uinfo = ctl->unit_info[uc & (UNIT_RING - 1)];
+      const int4 uinfo = ctl->unit_info[uc & (UNIT_RING - 1)];
       const int dlen = uinfo.x & ~LEN_FLAG_MASKED;
       const long long drow0 = uinfo.y;
       const bool holes = (uinfo.x & LEN_FLAG_MASKED) != 0;  // the document's mask is not a plain prefix
       const bool use_cols = SCALED || holes;                // per-column multiplier / additive mask needed
+      // where this unit's results go: CROSS / GROUPED index by document, LIST by pair (== unit)
+      const long long out_col = doc;
       float run_m = -INFINITY;
       int run_i = -1;
       int c0 = 0;
@@ -947,15 +1143,10 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
   } while (0)
         if (SCALED) LIK_STAGE_COLUMNS();  // before the accumulator wait: overlaps the MMAs
         if (SCALED || c0 > 0) {
-          PROF_T0(e_w2);
           LIK_GROUP_WAIT_ACC(false);
-          PROF_ADD(8, e_w2);
           if (!ok) break;
         }
         ++n_acc;
-        if (wq == 0 && lane == 0 && sub == 0) TRACE(3 + wg);
-        prof_tiles(prof);
-        PROF_T0(e_f);
         if (!SCALED && use_cols) LIK_STAGE_COLUMNS();  // a document whose mask has holes: known only now
 #undef LIK_STAGE_COLUMNS
         tc_fence_after();
@@ -982,13 +1173,10 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
         } else {
           for (; cc + 32 <= ncols; cc += 64) {
             float v[32];
-            TRACE3(0.f);
             tmem_ld32_issue(lane_addr + (uint32_t)cc, v);
             tmem_ld_wait(v);
-            TRACE3(v[0] + v[31]);
             if (cc + 64 >= ncols) LIK_RELEASE_ACC();
             fold32<ARGMAX>(v, c0 + cc, run_m, run_i);
-            TRACE3(run_m);
           }
           if (cc < ncols) {
             // partial chunk: pieces of 16, 8, 4, 2 and 1 columns as the bits of its width say, absent
@@ -1011,12 +1199,9 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
           }
         }
 #undef LIK_RELEASE_ACC
-        if (wq == 0 && lane == 0 && sub == 0) TRACE(3 + wg);
-        PROF_ADD(9, e_f);
         c0 += TILE_N;
       } while (c0 < dlen);
       if (!ok) break;
-      PROF_T0(e_e);
       // ---- end of document: half 1 hands over, half 0 merges (lower column wins a tie) ----
       float* xm = ctl->xch_m[wg][n_doc & 1];
       int* xi = ctl->xch_i[wg][n_doc & 1];
@@ -1042,13 +1227,11 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
       // one value per row, summed per query in a fixed order
       const bool has_winner = ARGMAX ? (run_i >= 0) : (run_m != -INFINITY);
       const float val = (in_seg && row_ok && has_winner) ? run_m * my_qf : 0.f;
-      if (ARGMAX && arg_off >= 0) P.argmax[arg_off + (long long)doc * P.argmax_stride] = has_winner ? run_i : -1;
+      if (ARGMAX && arg_off >= 0) P.argmax[arg_off + out_col * P.argmax_stride] = has_winner ? run_i : -1;
       if (aligned) {
         // one query per warp: a shuffle tree (fixed order) replaces the shared-memory pass
         const float sum = warp_sum(val);
-        if (lane == 0 && warp_out >= 0) P.scores[warp_out + doc] = sum;
-        PROF_ADD(10, e_e);
-        if (wq == 0 && lane == 0) TRACE(3 + wg);
+        if (warp_out >= 0) LIK_EMIT_SCORE(warp_seg, sum, warp_out + out_col);
         continue;
       }
       float* ebuf = ctl->emit[wg][n_emit & 1];
@@ -1061,26 +1244,26 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
         float sum = 0.f;
         for (int i = lane; i < len; i += 32) sum += ebuf[off + i];
         sum = warp_sum(sum);
-        if (lane == 0) {
-          const int qq = ctl->seg_q[wg][sg];
-          if (P.q_chunks == 1) {
-            const long long o = cross ? (long long)qq * P.n_d + doc : (long long)doc;
-            P.scores[o] = sum;
-          } else {
-            P.partial[(long long)tile_id * P.n_d + doc] = sum;
-          }
+        const int qq = ctl->seg_q[wg][sg];
+        if (P.q_chunks == 1) {
+          const long long o = cross ? (long long)qq * P.n_d + out_col : out_col;
+          LIK_EMIT_SCORE(sg, sum, o);
+        } else if (lane == 0) {
+          P.partial[(long long)tile_id * P.n_d + doc] = sum;
         }
       }
-      PROF_ADD(10, e_e);
-      if (wq == 0 && lane == 0) TRACE(3 + wg);
     }
-    PROF_ADD(7, e_all);
-    PROF_FLUSH(warp == 2 && lane == 0);
+    // top-k: leave the lists' state where the next launch stage (the merge) finds it
+    if (sub == 0) {
+      LIK_SUB_SYNC();
+      LIK_TOPK_STORE_BACK();
+    }
+#undef LIK_EMIT_SCORE
+#undef LIK_TOPK_STORE_BACK
 #undef LIK_GROUP_WAIT_ACC
 #undef LIK_GRP_SYNC
 #undef LIK_SUB_SYNC
   }
-#undef LIK_NEXT_UNIT
 
   // ---- teardown (also reached when aborting: every wait above is bounded) ----
   tc_fence_before();
@@ -1089,6 +1272,26 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
     tc_fence_after();
     tmem_dealloc(tmem_base, 512);
   }
+}
+
+// One row of the pair-list table per pair: the query (0 when the pair is out of range, which is reported
+// through the status word and scores 0 because its document is then empty), the first row and the length of
+// the document.
+__global__ void list_units_kernel(SeqView q, SeqView d, const int* __restrict__ pair_q, const int* __restrict__ pair_d,
+                                  long long n_pairs, int4* __restrict__ tab, int* status) {
+  const long long p = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (p >= n_pairs) return;
+  const int i = pair_q[p], j = pair_d[p];
+  int4 t = make_int4(0, 0, 0, 0);
+  if (i < 0 || i >= q.n_seq || j < 0 || j >= d.n_seq) {
+    if (status) atomicOr(status, LIK_DEV_PAIR_RANGE);
+  } else {
+    long long r0;
+    int len;
+    seq_bounds(d, j, r0, len, status);
+    t = make_int4(i, (int)r0, len, 0);
+  }
+  tab[p] = t;
 }
 
 // Effective length of every padded document under its token mask: 1 + index of the last valid
@@ -1207,26 +1410,34 @@ int make_map(CUtensorMap* map, const lik_seqs& s, int dtype, int dim, int box_ro
   return LIK_OK;
 }
 
+constexpr size_t SB_WINDOW_BYTES = 48u << 20;   // documents of one super-block: stays in L2 while every group passes
+constexpr size_t SB_MIN_BYTES = 96u << 20;      // smaller document sets are walked as one block
 
 struct TcPlan {
   bool pack_tiles;  // ragged queries packed greedily into tiles by pack_query_tiles_kernel
   int q_per_tile, q_chunks, n_tiles, mt, n_slabs, k_steps, stages;
-  long long n_units;
+  int n_sb, sb_docs, n_groups;
+  long long n_flat, n_units_total;
+  int grid;
   size_t smem_bytes;
 };
 
-TcPlan plan_tc(const lik_fwd_args& a) {
+TcPlan plan_tc(const lik_fwd_args& a, const TcExtra& x) {
   TcPlan pl{};
   const int eb = (int)dtype_size(a.dtype);
   pl.n_slabs = (a.dim * eb + SLAB_BYTES_ROW - 1) / SLAB_BYTES_ROW;
   pl.k_steps = (a.dim * eb + 31) / 32;
   const int ml = a.q.max_len > 0 ? a.q.max_len : 1;
-  if (a.pairing == LIK_PAIR_GROUPED) {
+  pl.n_sb = 1;
+  pl.sb_docs = a.d.n_seq > 0 ? a.d.n_seq : 1;
+  if (a.pairing != LIK_PAIR_CROSS) {
     pl.q_per_tile = 1;
     pl.q_chunks = 1;
     pl.n_tiles = a.q.n_seq;
     pl.mt = 1;
-    pl.n_units = a.d.n_seq;
+    pl.n_groups = a.q.n_seq;
+    pl.n_flat = a.pairing == LIK_PAIR_GROUPED ? a.d.n_seq : a.n_pairs;
+    pl.n_units_total = pl.n_flat;
   } else {
     if (ml <= TILE_M) {
       pl.q_per_tile = TILE_M / ml;
@@ -1240,8 +1451,26 @@ TcPlan plan_tc(const lik_fwd_args& a) {
     pl.mt = pl.n_tiles >= 2 ? 2 : 1;
     // packed queries shorter than the fixed slot: let the device pack them tightly (n_tiles becomes an upper bound)
     pl.pack_tiles = a.q.cu && ml < TILE_M && pl.q_per_tile > 1 && a.q.n_seq > 1 && a.q.n_seq <= PACK_MAX_QUERIES;
-    pl.n_units = ceil_div(pl.n_tiles, pl.mt) * (long long)a.d.n_seq;
+    pl.n_groups = (int)ceil_div(pl.n_tiles, pl.mt);
+    pl.n_flat = 0;
+    pl.n_units_total = (long long)pl.n_groups * a.d.n_seq;
+    // large document sets are walked in L2-sized super-blocks (several tile groups read every document)
+    const size_t row_bytes = x.plaid ? (size_t)(4 + x.plaid->packed_dim) : (size_t)a.dim * eb;
+    const size_t d_bytes = (size_t)a.d.n_rows * row_bytes;
+    if (a.d.n_seq > 0 && pl.n_groups > 1 && d_bytes > SB_MIN_BYTES) {
+      const size_t per_doc = d_bytes / (size_t)a.d.n_seq + 1;
+      long long sb = (long long)(SB_WINDOW_BYTES / per_doc);
+      if (sb < 64) sb = 64;
+      if (sb < a.d.n_seq) {
+        pl.sb_docs = (int)sb;
+        pl.n_sb = (int)ceil_div(a.d.n_seq, sb);
+      }
+    }
   }
+  const long long g = pl.n_units_total < sm_count() ? pl.n_units_total : sm_count();
+  pl.grid = (int)(g < 0 ? 0 : g);
+  // the fused top-k numbers its candidate lists by CTA: the same grid whatever the piece of the corpus
+  if (x.topk_k > 0 && pl.grid > 0) pl.grid = sm_count();
   const size_t q_bytes = 2 * (size_t)pl.n_slabs * TILE_M * SLAB_BYTES_ROW;
   const size_t stage = (size_t)pl.n_slabs * TILE_N * SLAB_BYTES_ROW;
   const size_t fixed = q_bytes + sizeof(SharedCtl) + 1024;
@@ -1254,48 +1483,113 @@ TcPlan plan_tc(const lik_fwd_args& a) {
 
 }  // namespace
 
-bool fwd_tc_supported(const lik_fwd_args& a) {
-  static int dev_ok = -1;
-  if (dev_ok < 0) dev_ok = lik_device_supported();
-  if (!dev_ok) return false;
+// What the tcgen05 kernel takes.  `plaid`: the documents are a compressed index (a.d.data is NULL).
+static bool tc_problem_ok(const lik_fwd_args& a, bool plaid) {
+  // per device ordinal: a process may hold GPUs of different architectures
+  static signed char dev_ok[64] = {0};  // 0 = not asked yet, 1 = usable, -1 = not usable
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return false;
+  if (dev < 0 || dev >= 64) {
+    if (!lik_device_supported()) return false;
+  } else {
+    if (dev_ok[dev] == 0) dev_ok[dev] = lik_device_supported() ? 1 : -1;
+    if (dev_ok[dev] < 0) return false;
+  }
   if (a.dtype != LIK_BF16 && a.dtype != LIK_F16 && a.dtype != LIK_E4M3) return false;
-  if (a.pairing != LIK_PAIR_CROSS && a.pairing != LIK_PAIR_GROUPED) return false;
+  if (plaid && a.dtype == LIK_E4M3) return false;
+  if (a.pairing < LIK_PAIR_CROSS || a.pairing > LIK_PAIR_LIST) return false;
   const int eb = (int)dtype_size(a.dtype);
   if ((a.dim * eb) % 16 != 0 || a.dim * eb > MAX_SLABS * SLAB_BYTES_ROW) return false;
   if (a.q.n_seq <= 0 || a.d.n_seq <= 0 || a.q.n_rows <= 0 || a.d.n_rows <= 0) return false;
   if (a.q.max_len <= 0) return false;  // packed queries need their longest length to form tiles
-  if (a.pairing == LIK_PAIR_GROUPED && a.q.max_len > TILE_M) return false;
-  if ((a.q.row_stride * eb) % 16 != 0 || (a.d.row_stride * eb) % 16 != 0) return false;
-  if (((uintptr_t)a.q.data & 15) || ((uintptr_t)a.d.data & 15)) return false;
+  if (a.pairing != LIK_PAIR_CROSS && a.q.max_len > TILE_M) return false;  // one query per tile
+  if (a.pairing == LIK_PAIR_LIST) {
+    if (a.n_pairs <= 0 || a.n_pairs >= (1ll << 31) || !a.pair_q || !a.pair_d) return false;
+    if (a.d.mask) return false;  // token masks with holes are not carried by the pair table
+  }
+  if ((a.q.row_stride * eb) % 16 != 0 || ((uintptr_t)a.q.data & 15)) return false;
+  if (!plaid && ((a.d.row_stride * eb) % 16 != 0 || ((uintptr_t)a.d.data & 15))) return false;
   if (a.q.n_rows >= (1ll << 31) || a.d.n_rows >= (1ll << 31)) return false;
   if (a.argmax && a.argmax_stride < 0) return false;
   return get_encode_fn() != nullptr;
 }
 
-static size_t partial_bytes(const TcPlan& pl, const lik_fwd_args& a) {
-  return pl.q_chunks > 1 ? align_up((size_t)pl.n_tiles * a.d.n_seq * sizeof(float), 256) : 0;
+bool fwd_tc_supported(const lik_fwd_args& a) { return tc_problem_ok(a, false); }
+
+// The fused top-k needs fixed query slots (padded queries of at most 128 tokens) and k within the list size.
+bool fwd_tc_topk_supported(const lik_fwd_args& a, const TcExtra& x) {
+  if (!tc_problem_ok(a, x.plaid != nullptr)) return false;
+  if (a.pairing != LIK_PAIR_CROSS || a.q.cu || a.q.max_len > TILE_M || a.argmax) return false;
+  return x.topk_k >= 1 && x.topk_k <= TOPK_CAP / 2;
 }
 
-size_t fwd_tc_workspace(const lik_fwd_args& a) {
-  TcPlan pl = plan_tc(a);
-  const size_t lens_bytes = (a.d.mask && !a.d.cu) ? align_up((size_t)a.d.n_seq * sizeof(int), 256) : 0;
-  const size_t tiles_bytes = pl.pack_tiles ? align_up((size_t)(a.q.n_seq + 3) * sizeof(int), 256) : 0;
-  return partial_bytes(pl, a) + lens_bytes + tiles_bytes;
+bool fwd_tc_plaid_supported(const lik_fwd_args& a, const TcExtra& x) {
+  if (!x.plaid || !tc_problem_ok(a, true)) return false;
+  if (x.plaid->dim != a.dim || a.dim % 16 != 0 || a.dim > 128 || a.d.mask || a.d.scale) return false;
+  return plaid_row16_ok(*x.plaid);
 }
 
-int launch_fwd_tc(const lik_fwd_args& a, const float* qn, const float* dn, void* ws, size_t ws_bytes, cudaStream_t st) {
-  TcPlan pl = plan_tc(a);
+namespace {
+struct TcWs {
+  size_t partial, lens, tiles, list, hdr, keys, idx, total;
+  long long n_lists;
+};
+TcWs tc_ws_layout(const TcPlan& pl, const lik_fwd_args& a, const TcExtra& x) {
+  TcWs w{};
+  size_t off = 0;
+  auto take = [&](size_t bytes) {
+    const size_t o = off;
+    off += align_up(bytes, 256);
+    return o;
+  };
+  // the candidate lists first: their size depends on the queries and the machine only, so they keep their place
+  // when the documents come in pieces
+  w.n_lists = 0;
+  if (x.topk_k > 0) {
+    w.n_lists = (long long)(pl.grid + pl.n_groups) * 2 * pl.q_per_tile;
+    w.hdr = take((size_t)w.n_lists * sizeof(int2));
+    w.keys = take((size_t)w.n_lists * TOPK_CAP * sizeof(float));
+    w.idx = take((size_t)w.n_lists * TOPK_CAP * sizeof(int));
+  }
+  w.partial = take(pl.q_chunks > 1 ? (size_t)pl.n_tiles * a.d.n_seq * sizeof(float) : 0);
+  w.lens = take((a.d.mask && !a.d.cu) ? (size_t)a.d.n_seq * sizeof(int) : 0);
+  w.tiles = take(pl.pack_tiles ? (size_t)(a.q.n_seq + 3) * sizeof(int) : 0);
+  w.list = take(a.pairing == LIK_PAIR_LIST ? (size_t)a.n_pairs * sizeof(int4) : 0);
+  w.total = off;
+  return w;
+}
+}  // namespace
+
+size_t fwd_tc_workspace(const lik_fwd_args& a, const TcExtra& x) { return tc_ws_layout(plan_tc(a, x), a, x).total; }
+
+int launch_topk_slots(const float* keys, const int* idx, const int2* hdr, int cap, int n_ctas, int n_groups, int mt, int qpt,
+                      long long n_q, int k, int largest, long long index_offset, float* out_scores, long long* out_index,
+                      cudaStream_t st);
+
+int launch_fwd_tc(const lik_fwd_args& a, const float* qn, const float* dn, void* ws, size_t ws_bytes, cudaStream_t st,
+                  const TcExtra& x) {
+  TcPlan pl = plan_tc(a, x);
   if (pl.stages < 1) {
     set_error("not enough shared memory for the document ring");
     return LIK_ERR_UNSUPPORTED;
   }
+  const TcWs w = tc_ws_layout(pl, a, x);
+  if (ws_bytes < w.total || (w.total && !ws)) {  // before anything that writes into the workspace is enqueued
+    set_error("tcgen05 forward: workspace too small");
+    return LIK_ERR_WORKSPACE;
+  }
+  if (pl.grid < 1) return LIK_OK;
+  const bool plaid = x.plaid != nullptr;
   CUtensorMap q_map;
   DocMaps d_maps;
+  memset(&d_maps, 0, sizeof(d_maps));
   int rc = make_map(&q_map, a.q, a.dtype, a.dim, TILE_M);
   if (rc) return rc;
-  for (int i = 0; i < 4; ++i) {
-    rc = make_map(&d_maps.m[i], a.d, a.dtype, a.dim, (i + 1) * BOX_ROWS);
-    if (rc) return rc;
+  if (!plaid) {
+    for (int i = 0; i < 4; ++i) {
+      rc = make_map(&d_maps.m[i], a.d, a.dtype, a.dim, (i + 1) * BOX_ROWS);
+      if (rc) return rc;
+    }
   }
 
   TcParams P{};
@@ -1314,82 +1608,94 @@ int launch_fwd_tc(const lik_fwd_args& a, const float* qn, const float* dn, void*
   P.q_chunks = pl.q_chunks;
   P.n_tiles = pl.n_tiles;
   P.mt = pl.mt;
-  P.n_units = pl.n_units;
+  P.n_sb = pl.n_sb;
+  P.sb_docs = pl.sb_docs;
+  P.n_flat = pl.n_flat;
   P.scores = a.scores;
-  P.partial = pl.q_chunks > 1 ? (float*)ws : nullptr;
+  P.partial = pl.q_chunks > 1 ? (float*)((char*)ws + w.partial) : nullptr;
   P.d_len_flagged = 0;
   P.tile_q0 = nullptr;
+  P.list_tab = nullptr;
+  P.d_full_count = plaid ? PLAID_WARPS : 1;
+  if (plaid) {
+    P.plaid = *x.plaid;
+    P.plaid_f16 = a.dtype == LIK_F16;
+  }
   if (pl.pack_tiles) {
-    const size_t lens_bytes = (a.d.mask && !a.d.cu) ? align_up((size_t)a.d.n_seq * sizeof(int), 256) : 0;
-    int* tbl = (int*)((char*)ws + partial_bytes(pl, a) + lens_bytes);
-    pack_query_tiles_kernel<<<1, 256, 0, st>>>(a.q.cu, a.q.n_seq, tbl);
+    int* tbl = (int*)((char*)ws + w.tiles);
+    pack_query_tiles_kernel<<<1, 256, 0, st>>>(a.q.cu, a.q.n_seq, tbl), ::lik::count_launch();
     LIK_CUDA_OK(cudaGetLastError());
     P.tile_q0 = tbl + 1;
   }
   if (a.d.mask && !a.d.cu) {
     // trim every document to its last valid token; only documents with holes pay for per-column masking
-    int* eff = (int*)((char*)ws + partial_bytes(pl, a));
-    mask_lens_kernel<<<(unsigned)ceil_div(a.d.n_seq, 8), 256, 0, st>>>(a.d.mask, a.d.lens, a.d.n_seq, a.d.max_len, a.d.seq_stride, eff);
+    int* eff = (int*)((char*)ws + w.lens);
+    mask_lens_kernel<<<(unsigned)ceil_div(a.d.n_seq, 8), 256, 0, st>>>(a.d.mask, a.d.lens, a.d.n_seq, a.d.max_len, a.d.seq_stride, eff), ::lik::count_launch();
     LIK_CUDA_OK(cudaGetLastError());
     P.d.lens = eff;
     P.d_len_flagged = 1;
   }
+  if (a.pairing == LIK_PAIR_LIST) {
+    int4* tab = (int4*)((char*)ws + w.list);
+    list_units_kernel<<<(unsigned)ceil_div(a.n_pairs, 256), 256, 0, st>>>(P.q, P.d, a.pair_q, a.pair_d, a.n_pairs, tab, a.status), ::lik::count_launch();
+    LIK_CUDA_OK(cudaGetLastError());
+    P.list_tab = tab;
+  }
   P.argmax = a.argmax;
   P.argmax_stride = a.argmax_stride;
   P.status = a.status;
-  if (ws_bytes < fwd_tc_workspace(a)) {
-    set_error("tcgen05 forward: workspace too small");
-    return LIK_ERR_WORKSPACE;
+  if (x.topk_k > 0) {
+    P.topk.hdr = (int2*)((char*)ws + w.hdr);
+    P.topk.cand_key = (float*)((char*)ws + w.keys);
+    P.topk.cand_idx = (int*)((char*)ws + w.idx);
+    P.topk.k = x.topk_k;
+    P.topk.qpg = 2 * pl.q_per_tile;
+    P.topk.largest = x.topk_largest;
+    P.topk.doc_base = x.topk_doc_base;
+    if (!(x.topk_flags & LIK_TOPK_CONTINUE))
+      LIK_CUDA_OK(cudaMemsetAsync(P.topk.hdr, 0, (size_t)w.n_lists * sizeof(int2), st));  // empty lists, no threshold
   }
-  // positions of the saved argmax that no accumulator row covers (packed queries shorter than the stride)
-  if (a.argmax && (a.q.cu || a.q.lens))
+  // positions of the saved argmax that no accumulator row covers (queries shorter than the stride)
+  if (a.argmax && (a.q.cu || a.q.lens || a.argmax_stride > a.q.max_len))
     LIK_CUDA_OK(cudaMemsetAsync(a.argmax, 0xFF,
-                                (size_t)n_scores_of(a.pairing, a.q.n_seq, a.d.n_seq, 0) * a.argmax_stride * sizeof(int), st));
+                                (size_t)n_scores_of(a.pairing, a.q.n_seq, a.d.n_seq, a.n_pairs) * a.argmax_stride * sizeof(int), st));
 
   const bool fp8 = a.dtype == LIK_E4M3;
   const bool argmax = a.argmax != nullptr;
   const bool affine = a.d.scale || dn;  // a per-column multiplier for every document
-  long long grid_ll = pl.n_units < sm_count() ? pl.n_units : sm_count();
-  if (grid_ll < 1) return LIK_OK;
-  dim3 grid((unsigned)grid_ll), block(NUM_THREADS);
-#define LIK_TC_LAUNCH(F, A, X)                                                                                         \
+  dim3 grid((unsigned)pl.grid), block(NUM_THREADS);
+#define LIK_TC_LAUNCH(F, A, X, PL)                                                                                     \
   do {                                                                                                                 \
-    LIK_CUDA_OK(cudaFuncSetAttribute(fwd_tc_kernel<F, A, X>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem_bytes)); \
-    fwd_tc_kernel<F, A, X><<<grid, block, pl.smem_bytes, st>>>(q_map, d_maps, P);                                       \
+    LIK_CUDA_OK(cudaFuncSetAttribute(fwd_tc_kernel<F, A, X, PL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem_bytes)); \
+    fwd_tc_kernel<F, A, X, PL><<<grid, block, pl.smem_bytes, st>>>(q_map, d_maps, P), ::lik::count_launch();                                   \
   } while (0)
-  if (fp8) {
-    if (argmax && affine) LIK_TC_LAUNCH(true, true, true);
-    else if (argmax) LIK_TC_LAUNCH(true, true, false);
-    else if (affine) LIK_TC_LAUNCH(true, false, true);
-    else LIK_TC_LAUNCH(true, false, false);
+  if (plaid) {
+    if (argmax) LIK_TC_LAUNCH(false, true, false, true);
+    else LIK_TC_LAUNCH(false, false, false, true);
+  } else if (fp8) {
+    if (argmax && affine) LIK_TC_LAUNCH(true, true, true, false);
+    else if (argmax) LIK_TC_LAUNCH(true, true, false, false);
+    else if (affine) LIK_TC_LAUNCH(true, false, true, false);
+    else LIK_TC_LAUNCH(true, false, false, false);
   } else {
-    if (argmax && affine) LIK_TC_LAUNCH(false, true, true);
-    else if (argmax) LIK_TC_LAUNCH(false, true, false);
-    else if (affine) LIK_TC_LAUNCH(false, false, true);
-    else LIK_TC_LAUNCH(false, false, false);
+    if (argmax && affine) LIK_TC_LAUNCH(false, true, true, false);
+    else if (argmax) LIK_TC_LAUNCH(false, true, false, false);
+    else if (affine) LIK_TC_LAUNCH(false, false, true, false);
+    else LIK_TC_LAUNCH(false, false, false, false);
   }
 #undef LIK_TC_LAUNCH
   LIK_CUDA_OK(cudaGetLastError());
   if (pl.q_chunks > 1) {
     const long long n = (long long)a.q.n_seq * a.d.n_seq;
-    reduce_chunks_kernel<<<(unsigned)ceil_div(n, 256), 256, 0, st>>>(P.partial, a.q.n_seq, a.d.n_seq, pl.q_chunks, a.scores);
+    reduce_chunks_kernel<<<(unsigned)ceil_div(n, 256), 256, 0, st>>>(P.partial, a.q.n_seq, a.d.n_seq, pl.q_chunks, a.scores), ::lik::count_launch();
     LIK_CUDA_OK(cudaGetLastError());
+  }
+  if (x.topk_k > 0 && !(x.topk_flags & LIK_TOPK_PARTIAL)) {
+    rc = launch_topk_slots(P.topk.cand_key, P.topk.cand_idx, P.topk.hdr, TOPK_CAP, pl.grid, pl.n_groups, pl.mt, pl.q_per_tile,
+                           a.q.n_seq, x.topk_k, x.topk_largest, x.topk_index_offset, x.topk_scores, (long long*)x.topk_index, st);
+    if (rc) return rc;
   }
   return LIK_OK;
 }
 
 }  // namespace lik
-
-#if LIK_TC_PROFILE
-extern "C" int lik_debug_trace(long long* out_host) {
-  return (int)cudaMemcpyFromSymbol(out_host, lik::g_trace, sizeof(long long) * 5 * 4096);
-}
-extern "C" int lik_debug_profile(unsigned long long* out_host, int reset) {
-  cudaMemcpyFromSymbol(out_host, lik::g_prof, sizeof(unsigned long long) * 16);
-  if (reset) {
-    unsigned long long z[16] = {0};
-    cudaMemcpyToSymbol(lik::g_prof, z, sizeof(z));
-  }
-  return 0;
-}
-#endif

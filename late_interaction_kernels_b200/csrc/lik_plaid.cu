@@ -2,6 +2,7 @@
 // residual bit-unpack + bucket lookup + optional L2 norm), the IVF-prune
 // approximate score, and the grad_Q backward of the residual scorer.
 #include "lik_common.cuh"
+#include "lik_plaid_row.cuh"
 
 namespace lik {
 
@@ -81,6 +82,61 @@ __global__ void __launch_bounds__(256) plaid_decompress_kernel(PlaidView v, long
   for (int c = 0; c < FMAX; ++c) {
     int f = c * 32 + lane;
     if (f < v.dim) out[w * v.dim + f] = from_f32<O>(e[c] * inv);
+  }
+}
+
+// Half-warp per token, the arithmetic of lik_plaid_row.cuh (the scoring kernel's producer warps decode
+// tokens with the same functions, so rows written here and tiles decoded there hold the same bits):
+// 16-byte centroid loads, one load for a lane's eight bucket codes, 16-byte stores.
+constexpr int PD_UNROLL = 4;  // tokens in flight per half-warp
+
+template <typename O>
+__global__ void __launch_bounds__(256) plaid_decompress16_kernel(PlaidSrc S, long long tok0, long long count, O* __restrict__ out,
+                                                               int* status) {
+  __shared__ float bw[256];
+  for (int b = threadIdx.x; b < (1 << S.nbits); b += blockDim.x) bw[b] = S.bucket_weights[b];
+  __syncthreads();
+  const int hl = threadIdx.x & 15;
+  const long long hw = (long long)blockIdx.x * 16 + (threadIdx.x >> 4);  // half-warp number
+  const long long n_hw = (long long)gridDim.x * 16;
+  const bool lane_on = hl * 8 < S.dim;
+  // every thread runs the same number of rounds (the norm's shuffles are warp-wide)
+  for (long long base = 0; base < count; base += n_hw * PD_UNROLL) {
+    int code[PD_UNROLL];
+#pragma unroll
+    for (int u = 0; u < PD_UNROLL; ++u) {
+      const long long w = base + u * n_hw + hw;
+      code[u] = w < count ? plaid_code(S, tok0 + w, status) : 0;
+    }
+    PlaidRaw r[PD_UNROLL];
+#pragma unroll
+    for (int u = 0; u < PD_UNROLL; ++u) {
+      const long long w = base + u * n_hw + hw;
+      if (w < count && lane_on) r[u] = plaid_load(S, tok0 + w, code[u], hl);
+      else r[u] = PlaidRaw{make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), 0ull};
+    }
+#pragma unroll
+    for (int u = 0; u < PD_UNROLL; ++u) {
+      const long long w = base + u * n_hw + hw;
+      float e[8];
+      plaid_features(S, r[u], bw, e);
+      if (!lane_on) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) e[i] = 0.f;
+      }
+      const float inv = plaid_inv_norm(S, e);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) e[i] *= inv;
+      if (w < count && lane_on) {
+        O* dst = out + w * S.dim + hl * 8;
+        if (sizeof(O) == 4) {
+          reinterpret_cast<float4*>(dst)[0] = make_float4(e[0], e[1], e[2], e[3]);
+          reinterpret_cast<float4*>(dst)[1] = make_float4(e[4], e[5], e[6], e[7]);
+        } else {
+          *reinterpret_cast<uint4*>(dst) = plaid_pack16(e, dtype_of<O>::value == LIK_F16);
+        }
+      }
+    }
   }
 }
 
@@ -207,9 +263,27 @@ extern "C" int lik_plaid_decompress(const lik_plaid_index* index, int64_t token_
   if (token_count == 0) return LIK_OK;
   PlaidView v = make_plaid_view(*index);
   cudaStream_t st = (cudaStream_t)stream;
+  {
+    PlaidSrc S{index->codes, index->residuals, index->centroids, index->bucket_weights, index->centroid_dtype, index->n_centroids,
+               index->nbits, v.packed_dim, index->dim, normalize ? 1 : 0};
+    if (plaid_row16_ok(S) && ((uintptr_t)out % 16) == 0 && (out_dtype == LIK_F32 || out_dtype == LIK_F16 || out_dtype == LIK_BF16)) {
+      // enough half-warps to fill the machine, PD_UNROLL tokens in flight each
+      long long blocks = ceil_div(token_count, 16 * PD_UNROLL);
+      const long long cap = (long long)sm_count() * 16;
+      if (blocks > cap) blocks = cap;
+      if (out_dtype == LIK_F32)
+        plaid_decompress16_kernel<float><<<(unsigned)blocks, 256, 0, st>>>(S, token_begin, token_count, (float*)out, status), ::lik::count_launch();
+      else if (out_dtype == LIK_F16)
+        plaid_decompress16_kernel<__half><<<(unsigned)blocks, 256, 0, st>>>(S, token_begin, token_count, (__half*)out, status), ::lik::count_launch();
+      else
+        plaid_decompress16_kernel<__nv_bfloat16><<<(unsigned)blocks, 256, 0, st>>>(S, token_begin, token_count, (__nv_bfloat16*)out, status), ::lik::count_launch();
+      LIK_CUDA_OK(cudaGetLastError());
+      return LIK_OK;
+    }
+  }
   unsigned grid = (unsigned)ceil_div(token_count, 8);
   const int fm = (v.dim + 31) / 32;
-#define LIK_DEC(O, F) plaid_decompress_kernel<O, F><<<grid, 256, 0, st>>>(v, token_begin, token_count, normalize, (O*)out, status)
+#define LIK_DEC(O, F) plaid_decompress_kernel<O, F><<<grid, 256, 0, st>>>(v, token_begin, token_count, normalize, (O*)out, status), ::lik::count_launch()
   switch (out_dtype) {
     case LIK_F32:
       LIK_BY_FMAX(fm, LIK_DEC(float, 4), LIK_DEC(float, 8), LIK_DEC(float, 16), LIK_DEC(float, 32));
@@ -237,7 +311,7 @@ extern "C" int lik_plaid_approx(const float* qcs, int32_t n_centroids, int32_t l
   if (n_docs == 0) return LIK_OK;
   LIK_REQUIRE(qcs && codes && doc_lengths && out, "NULL pointer");
   plaid_approx_kernel<<<(unsigned)ceil_div(n_docs, 8), 256, 0, (cudaStream_t)stream>>>(
-      qcs, n_centroids, lq, codes, n_docs, max_ld, (const long long*)doc_lengths, out);
+      qcs, n_centroids, lq, codes, n_docs, max_ld, (const long long*)doc_lengths, out), ::lik::count_launch();
   LIK_CUDA_OK(cudaGetLastError());
   return LIK_OK;
 }
@@ -256,7 +330,7 @@ extern "C" int lik_plaid_bwd_dq(const lik_plaid_index* index, int32_t max_ld, in
   unsigned grid = (unsigned)ceil_div((int64_t)n_q * lq, 8);
   const int fm = (v.dim + 31) / 32;
 #define LIK_PB(T, F) \
-  plaid_bwd_dq_kernel<T, F><<<grid, 256, 0, st>>>(v, max_ld, n_docs, (const T*)q, n_q, lq, grad_scores, argmax, normalize, grad_q)
+  plaid_bwd_dq_kernel<T, F><<<grid, 256, 0, st>>>(v, max_ld, n_docs, (const T*)q, n_q, lq, grad_scores, argmax, normalize, grad_q), ::lik::count_launch()
   switch (q_dtype) {
     case LIK_F32:
       LIK_BY_FMAX(fm, LIK_PB(float, 4), LIK_PB(float, 8), LIK_PB(float, 16), LIK_PB(float, 32));

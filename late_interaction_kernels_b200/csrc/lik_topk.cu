@@ -159,6 +159,89 @@ __global__ void __launch_bounds__(256) topk_kernel(TopkParams P) {
   }
 }
 
+// Merge of the candidate lists the fused scoring kernel leaves (lik_fwd_tc.cu): list slot of (CTA c, tile
+// group g) is c + g, each slot holds 2 * qpt lists of up to `cap` entries (unsorted), and CTA c of n_ctas can
+// only have worked on the groups [n_groups * c / n_ctas, n_groups * (c + 1) / n_ctas] (a superset of the ones
+// it really met; lists it never touched are empty).  A group is `mt` query tiles of `qpt` queries; with two
+// tiles a query has one list per slot (tile * qpt + position), with one tile it has two (the kernel's two
+// epilogue groups take alternate documents).  One CTA per query.
+struct SlotParams {
+  const float* keys;
+  const int* idx;
+  const int2* hdr;
+  int cap, n_ctas, n_groups, mt, qpt;
+  long long n_q, index_offset;
+  int k, KP, largest;
+  float* out_scores;
+  long long* out_index;
+};
+
+__global__ void __launch_bounds__(256) topk_slots_kernel(SlotParams P) {
+  extern __shared__ unsigned char raw[];
+  long long* top_i = reinterpret_cast<long long*>(raw);
+  long long* blk_i = top_i + P.KP;
+  float* top_k = reinterpret_cast<float*>(blk_i + P.KP);
+  float* blk_k = top_k + P.KP;
+  const int tid = threadIdx.x, nt = blockDim.x;
+  const long long q = blockIdx.x;
+  const int tile = (int)(q / P.qpt), et = (int)(q - (long long)tile * P.qpt);
+  const int g = tile / P.mt, m = tile - g * P.mt;
+  const int n_sub = P.mt == 2 ? 1 : 2;
+  for (int t = tid; t < P.KP; t += nt) {
+    top_k[t] = -INFINITY;
+    top_i[t] = kPadIdx;
+  }
+  __syncthreads();
+  for (int c = 0; c < P.n_ctas; ++c) {
+    const long long g_lo = (long long)P.n_groups * c / P.n_ctas, g_hi = (long long)P.n_groups * (c + 1) / P.n_ctas;
+    if (g < g_lo || g > g_hi) continue;
+    for (int sub = 0; sub < n_sub; ++sub) {
+    const long long list = (long long)(c + g) * (2 * P.qpt) + (P.mt == 2 ? m : sub) * P.qpt + et;
+    int cnt = P.hdr[list].x;
+    if (cnt > P.cap) cnt = P.cap;
+    for (int b0 = 0; b0 < cnt; b0 += P.KP) {
+      for (int t = tid; t < P.KP; t += nt) {
+        float key = -INFINITY;
+        long long id = kPadIdx;
+        if (b0 + t < cnt) {
+          key = P.keys[list * P.cap + b0 + t];
+          id = P.idx[list * P.cap + b0 + t];
+        }
+        blk_k[t] = key;
+        blk_i[t] = id;
+      }
+      bitonic_sort(blk_k, blk_i, P.KP, tid, nt);
+      for (int t = tid; t < P.KP; t += nt) {
+        Cand a{top_k[t], top_i[t]}, cnd{blk_k[P.KP - 1 - t], blk_i[P.KP - 1 - t]};
+        if (before(cnd, a)) {
+          top_k[t] = cnd.key;
+          top_i[t] = cnd.idx;
+        }
+      }
+      bitonic_merge(top_k, top_i, P.KP, tid, nt);
+    }
+    }
+  }
+  const float sgn = P.largest ? 1.f : -1.f;
+  for (int t = tid; t < P.k; t += nt) {
+    const bool pad = top_i[t] == kPadIdx;
+    P.out_scores[q * P.k + t] = pad ? -sgn * INFINITY : sgn * top_k[t];
+    P.out_index[q * P.k + t] = pad ? -1 : top_i[t] + P.index_offset;
+  }
+}
+
+int launch_topk_slots(const float* keys, const int* idx, const int2* hdr, int cap, int n_ctas, int n_groups, int mt, int qpt,
+                      long long n_q, int k, int largest, long long index_offset, float* out_scores, long long* out_index,
+                      cudaStream_t st) {
+  if (n_q <= 0 || k <= 0) return LIK_OK;
+  SlotParams P{keys, idx, hdr, cap, n_ctas, n_groups, mt, qpt, n_q, index_offset, k, 2, largest, out_scores, out_index};
+  while (P.KP < k) P.KP <<= 1;
+  const size_t smem = (size_t)P.KP * 2 * (sizeof(long long) + sizeof(float));
+  topk_slots_kernel<<<(unsigned)n_q, 256, smem, st>>>(P), ::lik::count_launch();
+  LIK_CUDA_OK(cudaGetLastError());
+  return LIK_OK;
+}
+
 static int launch_topk(TopkParams& P, cudaStream_t st) {
   if (P.n_rows <= 0 || P.k <= 0) return LIK_OK;
   int KP = 1;
@@ -166,7 +249,7 @@ static int launch_topk(TopkParams& P, cudaStream_t st) {
   if (KP < 2) KP = 2;
   P.KP = KP;
   size_t smem = (size_t)KP * 2 * (sizeof(long long) + sizeof(float));
-  topk_kernel<<<(unsigned)P.n_rows, 256, smem, st>>>(P);
+  topk_kernel<<<(unsigned)P.n_rows, 256, smem, st>>>(P), ::lik::count_launch();
   LIK_CUDA_OK(cudaGetLastError());
   return LIK_OK;
 }

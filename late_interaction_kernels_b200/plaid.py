@@ -15,6 +15,16 @@ from . import _lib, _ops
 
 # decompressed tokens held at once (rows of `dim` operand-dtype values)
 _DECOMPRESS_TOKENS = 1 << 22
+# Up to this many query-tile groups (a group = 256 query-token rows = eight 32-token queries) the index is decoded
+# inside the scoring kernel (``lik_plaid_fwd``): every group decodes the tokens it scores, which beats writing
+# and re-reading operand rows while few groups share them.  Beyond it the tokens are decoded once per call
+# (``lik_plaid_decompress``) and scored by every group.  Both ways produce the same bits.
+_FUSED_DECODE_MAX_GROUPS = 4
+
+
+def _tile_groups(Nq: int, Lq: int) -> int:
+    tiles = -(-Nq // (128 // Lq)) if Lq <= 128 else Nq * -(-Lq // 128)
+    return -(-tiles // 2)
 
 
 @_ops._no_trace
@@ -73,6 +83,18 @@ def _residual_scores(Q, ix, cu_or_lens, max_ld, padded, normalize, save_argmax):
     Qo = Q.to(odt)
     q = _ops.padded_spec(Qo)
     norm = _lib.NORM_Q if normalize else _lib.NORM_NONE
+    if Nq > 0 and _tile_groups(Nq, Lq) <= _FUSED_DECODE_MAX_GROUPS and ix.n_tokens > 0:
+        if padded:
+            nd = cu_or_lens.numel()
+            lay = _ops.layout_spec(nd * max_ld, nd, max_ld, lens=cu_or_lens, seq_stride=max_ld)
+        else:
+            nd = cu_or_lens.numel() - 1
+            lay = _ops.layout_spec(ix.n_tokens, nd, max(int(max_ld), 0), cu=cu_or_lens)
+        fused = _ops.forward_fused(q, lay, normalize=(_lib.NORM_BOTH if normalize else _lib.NORM_NONE), plaid=ix,
+                                   save_argmax=save_argmax, argmax_stride=Lq)
+        if fused is not None:
+            s, am = fused
+            return s.view(Nq, nd), (am.view(Nq, nd, Lq) if am is not None else None)
     if padded:
         lens = cu_or_lens
         Nd = lens.numel()
@@ -260,25 +282,45 @@ def retrieve_residual_varlen(Q, codes_flat, residuals_flat, cu_seqlens_d, centro
     if Nd <= 0:
         out = (torch.empty((Nq, 0), dtype=torch.float32, device=dev), torch.empty((Nq, 0), dtype=torch.int64, device=dev))
         return (out[0].squeeze(0), out[1].squeeze(0)) if q2 else out
-    if doc_lengths_host is not None:
-        cu_host = torch.zeros(Nd + 1, dtype=torch.int64)
-        cu_host[1:] = doc_lengths_host.to(torch.int64).cumsum(0)
-    else:
-        cu_host = cu.cpu().to(torch.int64)
     ix, keep = _ops.plaid_index(codes_flat, residuals_flat, centroids, bucket_weights, nbits, d)
     odt = _operand_dtype(Q)
     q = _ops.padded_spec(Q.to(odt))
     norm = _lib.NORM_Q if normalize else _lib.NORM_NONE
     out = None
     with torch.no_grad():
-        for j0 in range(0, Nd, chunk):
-            j1 = min(Nd, j0 + chunk)
+        if k <= _lib.TOPK_FUSED_MAX and _tile_groups(Nq, Lq) <= _FUSED_DECODE_MAX_GROUPS:
+            # few queries: one kernel decodes, scores and keeps the candidates; nothing is read on the host
+            lay = _ops.layout_spec(ix.n_tokens, Nd, 0, cu=cu)
+            out = _ops.forward_fused(q, lay, normalize=(_lib.NORM_BOTH if normalize else _lib.NORM_NONE), plaid=ix, topk=k,
+                                     largest=largest)
+            if out is not None:
+                return (out[0].squeeze(0), out[1].squeeze(0)) if q2 else out
+        if doc_lengths_host is not None:
+            cu_host = torch.zeros(Nd + 1, dtype=torch.int64)
+            cu_host[1:] = doc_lengths_host.to(torch.int64).cumsum(0)
+        else:
+            cu_host = cu.cpu().to(torch.int64)
+        # many queries: every token is decoded once (in pieces of `chunk` documents, sized so that a piece's operand
+        # rows stay small) and the scoring kernel carries its candidate lists from piece to piece
+        state = _ops.TopkState() if k <= _lib.TOPK_FUSED_MAX else None
+        pieces = [(j0, min(Nd, j0 + chunk)) for j0 in range(0, Nd, chunk)]
+        for n, (j0, j1) in enumerate(pieces):
             t0, t1 = int(cu_host[j0]), int(cu_host[j1])
             emb = _ops.plaid_decompress(ix, t0, t1 - t0, normalize, odt, dev)
             max_ld = int((cu_host[j0 + 1 : j1 + 1] - cu_host[j0:j1]).max())
             dd = _ops.packed_spec(emb, cu[j0 : j1 + 1] - t0, max_ld)
-            s, _ = _ops.forward(q, dd, normalize=norm)
-            out = _ops.topk_rows(s.view(Nq, j1 - j0), k, largest=largest, index_offset=j0, out=out)
+            if state is not None:
+                r = _ops.forward_fused(q, dd, normalize=norm, topk=k, largest=largest, doc_base=j0, state=state,
+                                       last=n == len(pieces) - 1)
+                if r is None:
+                    if state.started:
+                        raise RuntimeError("the fused top-k refused a later piece of a corpus it had started on")
+                    state = None
+                elif n == len(pieces) - 1:
+                    out = r
+            if state is None:
+                s, _ = _ops.forward(q, dd, normalize=norm)
+                out = _ops.topk_rows(s.view(Nq, j1 - j0), k, largest=largest, index_offset=j0, out=out)
     ts, ti = out
     return (ts.squeeze(0), ti.squeeze(0)) if q2 else (ts, ti)
 

@@ -10,11 +10,12 @@ from ._utils import common_dtype, max_seqlen_from_cu
 
 
 def _scatter_forward(Q, D, cu_q, cu_d, pair_q, pair_d, max_q, max_d, save_argmax):
+    # the longest query sizes the query tiles of the tensor-core path (and the saved winners); like the reference it
+    # costs one device->host sync when the caller does not pass it.  The longest document is only needed by the backward.
+    max_q = max_seqlen_from_cu(cu_q) if max_q is None else int(max_q)
     if save_argmax:
-        max_q = max_seqlen_from_cu(cu_q) if max_q is None else int(max_q)
         max_d = max_seqlen_from_cu(cu_d) if max_d is None else int(max_d)
     else:
-        max_q = 0 if max_q is None else int(max_q)
         max_d = 0 if max_d is None else int(max_d)
     dt = common_dtype(Q, D)
     q = _ops.packed_spec(Q.to(dt), cu_q, max_q)

@@ -1,9 +1,11 @@
 """Top-k MaxSim (reference: topk.py:12-91).
 
 The reference scores a chunk, calls ``torch.topk``, concatenates with the running list and calls
-``torch.topk`` again.  Here each chunk's scores go through ``lik_topk_rows``, which merges them
-into the running ``[Nq, k]`` list in one kernel; ties are broken by the lower document index, so
-chunked and unchunked calls return identical indices.
+``torch.topk`` again.  Here the scoring kernel itself keeps the candidates (``lik_maxsim_fwd_topk``): one
+launch walks all documents, no ``[Nq, chunk]`` score matrix is written, and a merge kernel returns the
+``k`` best per query.  Problems that path does not take (fp32 inputs, packed or very long queries,
+``k > 128``) score chunks with ``lik_maxsim_fwd`` and merge them with ``lik_topk_rows``.  Either way ties
+go to the lower document index, so chunked and unchunked calls return identical indices.
 """
 
 from __future__ import annotations
@@ -11,6 +13,7 @@ from __future__ import annotations
 import torch
 
 from . import _lib, _ops
+from ._utils import common_dtype, ensure_contiguous_last
 from .forward import maxsim_forward
 
 
@@ -36,7 +39,12 @@ def maxsim_topk(Q, D, k, q_mask=None, d_mask=None, *, normalize=False, chunk_siz
     step = Nd if (chunk_size is None or chunk_size >= Nd) else int(chunk_size)
     out = None
     with torch.no_grad():
-        for start in range(0, Nd, max(step, 1)):
+        if Nd > 0 and Q.shape[0] > 0 and k <= _lib.TOPK_FUSED_MAX and Q.shape[-1] == D.shape[-1]:
+            dt = common_dtype(Q, D)
+            q = _ops.padded_spec(ensure_contiguous_last(Q).to(dt), q_mask)
+            dd = _ops.padded_spec(ensure_contiguous_last(D).to(dt), d_mask)
+            out = _ops.forward_fused(q, dd, normalize=_lib.NORM_BOTH if normalize else _lib.NORM_NONE, topk=k, largest=largest)
+        for start in range(0, Nd if out is None else 0, max(step, 1)):
             end = min(start + step, Nd)
             dm = d_mask[start:end] if d_mask is not None else None
             s, _ = maxsim_forward(Q, D[start:end], q_mask=q_mask, d_mask=dm, save_argmax=False, normalize=normalize)

@@ -27,7 +27,7 @@ def test_header_symbols_are_exported(lib):
     for sym in declared:
         assert hasattr(lib, sym), f"{sym} declared in the header but not exported"
     assert declared == set(_lib.EXPORTED_SYMBOLS)
-    assert lib.lik_version() >= 100
+    assert lib.lik_version() >= 200
 
 
 def test_struct_sizes_match_the_header_layout():
@@ -38,6 +38,7 @@ def test_struct_sizes_match_the_header_layout():
     assert C.sizeof(_lib.Seqs) == 80
     assert C.sizeof(_lib.FwdArgs) == 2 * 80 + 96
     assert C.sizeof(_lib.PlaidIndex) == 56
+    assert C.sizeof(_lib.TopkSpec) == 40
 
 
 def test_argument_validation_without_a_gpu(lib):
