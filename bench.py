@@ -3,16 +3,17 @@
     python bench.py --gpus N --steps K --warmup W            # this engine
     python bench.py --impl reference ...                       # the reference algorithm on host cores
 
-Workload (BASELINE config 2, "ColBERTv2-shaped in-batch training"): bf16 Q[512,32,128] and
-D[512,300,128] ~N(0,1) L2-normalised, document lengths U[64,300] as a boolean d_mask, full q_mask,
-one step = forward + backward (gradients w.r.t. Q and D) through the autograd path.  Inputs are
-seeded synthetic data.  With N > 1 every rank runs its own replica of the step (MaxSim training does
-not shard; data parallelism is the caller's), so the whole-job figure is N times the per-rank work
-over the slowest rank's time ("weak" scaling).
+Headline workload ("ColBERTv2-shaped in-batch training"): bf16 Q[512,32,128] and D[512,300,128] ~N(0,1)
+L2-normalised, document lengths U[64,300] as a boolean d_mask, full q_mask, one step = forward + backward
+(gradients w.r.t. Q and D) through the autograd path.  Inputs are seeded synthetic data.  With N > 1 every
+rank runs its own replica of the step (MaxSim training does not shard; data parallelism is the caller's),
+so the whole-job figure is N times the per-rank work over the slowest rank's time ("weak" scaling).
 
 Metric: TFLOP/s counting only algorithmic work on valid tokens:
     forward  2 * d * sum_{(i,j)} lq_i * ld_j        backward  4 * d * sum_{(i,j)} lq_i
-One JSON line is printed by rank 0.
+Before anything is timed a sampled block of scores and gradients is compared with the CPU oracle; the run
+stops if it is off.  One JSON line is printed by rank 0; `extra` carries the retrieve / PLAID / other-shape
+legs, each with the roofline that bounds it.
 """
 
 from __future__ import annotations
@@ -42,6 +43,7 @@ def emit(obj):
 METRIC = "MaxSim fwd+bwd TFLOP/s (bf16)"
 WORKLOAD = "colbert_inbatch_train_bf16: Q[512,32,128] x D[512,300,128], d_len U[64,300], fwd+bwd"
 NQ, ND, LQ, LD, DIM = 512, 512, 32, 300, 128
+CHUNK = 4096  # documents per seeded chunk of the synthetic corpora
 
 
 def make_inputs(seed=0):
@@ -69,6 +71,31 @@ def measured_peaks():
             d = json.load(f)
         return float(d["bf16_tflops"]), float(d["hbm_gbs"]), "measured"
     return 1590.0, 6650.0, "fallback"
+
+
+def profiled_traffic(kernel_key):
+    """DRAM bytes per launch of a kernel from the committed ncu capture (profiles/dram_traffic.json); None when
+    that capture is absent."""
+    p = os.path.join(ROOT, "profiles", "dram_traffic.json")
+    try:
+        with open(p) as f:
+            return json.load(f).get(kernel_key)
+    except (OSError, ValueError):
+        return None
+
+
+def roofline(bound, work, seconds, *, kernel, note=None, traffic=None):
+    """One roofline entry: achieved = algorithmic FLOPs (bound "tensor") or bytes (bound "hbm") / time."""
+    peak_tf, peak_gb, which = measured_peaks()
+    if bound == "tensor":
+        achieved, peak, unit = work / seconds / 1e12, peak_tf, "TFLOP/s"
+    else:
+        achieved, peak, unit = work / seconds / 1e9, peak_gb, "GB/s"
+    r = {"bound": bound, "achieved": achieved, "peak": peak, "unit": unit, "frac": achieved / peak, "traffic": traffic,
+         "kernel": kernel, "kernel_ms": seconds * 1e3, "peak_source": which, "algorithmic_work": work}
+    if note:
+        r["note"] = note
+    return r
 
 
 class ClockSampler:
@@ -129,14 +156,75 @@ class ClockSampler:
                 "samples": len(sm)}
 
 
+# --------------------------------------------------------------------------------------------------------
+# CPU legs (the oracle = the reference algorithm restated in numpy; the only place bench.py runs it)
+# --------------------------------------------------------------------------------------------------------
 def cpu_reference_step(sample_q, Q, D, dm, g):
-    """One forward + backward of the reference algorithm (the CPU oracle, a port of the reference's
-    reference.py) on the first `sample_q` queries against all documents."""
+    """One forward + backward of the reference algorithm on the first `sample_q` queries against all documents."""
     from oracle import maxsim_oracle as O
 
     s = O.maxsim(Q[:sample_q], D, None, dm)
     gq, gd = O.maxsim_grads(g[:sample_q], Q[:sample_q], D, None, dm)
     return float(s.sum()) + float(gq.sum()) + float(gd.sum())
+
+
+def _best_of(fn, reps, budget_s):
+    fn()
+    best, n, t_all = float("inf"), 0, time.perf_counter()
+    while n < reps and (n == 0 or time.perf_counter() - t_all < budget_s):
+        t0 = time.perf_counter()
+        fn()
+        best = min(best, time.perf_counter() - t0)
+        n += 1
+    return best, n
+
+
+def cpu_other_workloads():
+    """The other workload shapes on host cores, each bounded to a few seconds (oracle port, all host threads)."""
+    from oracle import maxsim_oracle as O
+
+    out = {}
+    rng = np.random.default_rng(0)
+    # fp32 in-batch forward with both masks and fused normalisation, in full
+    Q = rng.standard_normal((32, 32, 128)).astype(np.float32)
+    D = rng.standard_normal((32, 180, 128)).astype(np.float32)
+    qm = np.arange(32)[None] < rng.integers(8, 33, size=32)[:, None]
+    dmk = np.arange(180)[None] < rng.integers(32, 181, size=32)[:, None]
+    t, n = _best_of(lambda: O.maxsim(Q, D, qm, dmk, normalize=True), 5, 5.0)
+    fl = 2.0 * 128 * float(qm.sum()) * float(dmk.sum())
+    out["inbatch_fp32_fwd_32x32"] = {"ms": t * 1e3, "tflops_valid": fl / t / 1e12, "sample": f"whole workload, best of {n}"}
+    # KD layout forward, in full
+    Qk = rng.standard_normal((64, 32, 128)).astype(np.float32)
+    Dk = rng.standard_normal((64, 32, 300, 128)).astype(np.float32)
+    lk = rng.integers(64, 301, size=(64, 32))
+    dk = np.arange(300)[None, None] < lk[..., None]
+    t, n = _best_of(lambda: O.maxsim_kd(Qk, Dk, None, dk), 2, 8.0)
+    out["kd_fwd_64x32"] = {"ms": t * 1e3, "tflops_valid": 2.0 * 128 * 32 * float(lk.sum()) / t / 1e12, "sample": f"whole workload, best of {n}"}
+    # packed ColPali shape: 16 x 16 of the 128 x 128 pairs, forward + backward
+    ql = rng.integers(16, 33, size=16)
+    dl = rng.integers(900, 1031, size=16)
+    Qp = rng.standard_normal((int(ql.sum()), 128)).astype(np.float32)
+    Dp = rng.standard_normal((int(dl.sum()), 128)).astype(np.float32)
+    cq, cd = np.concatenate([[0], np.cumsum(ql)]), np.concatenate([[0], np.cumsum(dl)])
+    gg = rng.standard_normal((16, 16)).astype(np.float32)
+
+    def packed():
+        O.maxsim_varlen(Qp, Dp, cq, cd)
+        O.varlen_grads(gg, Qp, Dp, cq, cd)
+
+    t, n = _best_of(packed, 2, 8.0)
+    fl = 2.0 * 128 * float(ql.sum()) * float(dl.sum()) + 4.0 * 128 * float(ql.sum()) * 16
+    out["packed_colpali_fwd_bwd"] = {"ms": t * 1e3, "tflops_valid": fl / t / 1e12, "sample": f"16 x 16 of 128 x 128 pairs, best of {n}"}
+    # retrieve: 8 queries against one 4096-document chunk of the corpus, top-100
+    Qr = rng.standard_normal((8, 32, 128)).astype(np.float32)
+    Dr = rng.standard_normal((CHUNK, 300, 128)).astype(np.float32)
+    lr = rng.integers(32, 301, size=CHUNK)
+    dr = np.arange(300)[None] < lr[:, None]
+    t, n = _best_of(lambda: O.retrieve(Qr, Dr, 100, d_mask=dr, normalize=False, chunk=1024), 1, 10.0)
+    out["retrieve_chunk"] = {"ms": t * 1e3, "queries_per_s_on_4096_docs": 8 / t,
+                             "queries_per_s_extrapolated_to_1M_docs": 8 / t * CHUNK / 1e6,
+                             "sample": "8 queries x one 4096-document chunk, top-100 (the 1M figure is an extrapolation)"}
+    return out
 
 
 def run_reference(args, rank):
@@ -165,55 +253,294 @@ def run_reference(args, rank):
     print(json.dumps(line), flush=True)
 
 
-def retrieve_bench(n_docs, world, rank, dev):
-    """Sharded top-k retrieve (BASELINE config 5 shape): `n_docs` documents of U[32,300] tokens, d=128, bf16
-    normalised, split by document over the ranks; 1024 queries x 32 tokens, top_k=100, chunk=4096.
-    Strong scaling: the corpus is fixed, every rank scores its slice, one all-gather + merge."""
+# --------------------------------------------------------------------------------------------------------
+# Parity before timing
+# --------------------------------------------------------------------------------------------------------
+def assert_step_parity(lik, dQ, dD, dM, dG, Q, D, dm, g):
+    """Sampled scores and gradients of the timed step against the oracle (bf16 tolerance 2e-2).  Raises SystemExit."""
+    import torch
+
+    from oracle import maxsim_oracle as O
+
+    f32 = lambda t: t.detach().float().cpu().numpy()  # noqa: E731
+    Qt, Dt = dQ.clone().requires_grad_(), dD.clone().requires_grad_()
+    s = lik.maxsim(Qt, Dt, d_mask=dM)
+    qi = [0, 1, 255, 511]
+    gm = torch.zeros_like(dG)
+    gm[qi] = dG[qi]
+    s.backward(gm)
+    Qr, Dr = f32(dQ), f32(dD)
+    errs = {"scores": O.rel_err(f32(s)[:8, :16], O.maxsim(Qr[:8], Dr[:16], None, dm[:16]))}
+    wq, wd = O.maxsim_grads(g[qi], Qr[qi], Dr, None, dm)
+    errs["grad_q"] = O.rel_err(f32(Qt.grad)[qi], wq)
+    errs["grad_d"] = O.rel_err(f32(Dt.grad), wd)
+    bad = {k: v for k, v in errs.items() if not v < 2e-2}
+    if bad:
+        raise SystemExit(f"bench.py: parity check failed before timing: {bad}")
+    return errs
+
+
+def verify_topk(Q, score_docs, n_docs, result, *, n_queries=4, n_random=2000, tol=2e-2, seed=0):
+    """Re-score, on the CPU oracle, the returned top-k of a few queries plus random documents: the returned
+    scores must match, and no sampled document outside the list may beat its k-th score by more than the
+    tolerance.  `score_docs(q_rows, doc_ids)` -> oracle scores [len(q_rows), len(doc_ids)]."""
+    s, i = result
+    rng = np.random.default_rng(seed)
+    qs = sorted(rng.choice(s.shape[0], size=min(n_queries, s.shape[0]), replace=False).tolist())
+    worst = {"score_rel_err": 0.0, "outsider_margin": -float("inf")}
+    for q in qs:
+        top = i[q].cpu().numpy()
+        rand = rng.choice(n_docs, size=min(n_random, n_docs), replace=False)
+        ids = np.unique(np.concatenate([top, rand]))
+        sc = score_docs([q], ids)[0]
+        pos = {int(d): n for n, d in enumerate(ids)}
+        got = s[q].cpu().numpy()
+        want = np.array([sc[pos[int(d)]] for d in top])
+        scale = max(1e-6, float(np.abs(want).max()))
+        worst["score_rel_err"] = max(worst["score_rel_err"], float(np.abs(got - want).max() / scale))
+        kth = float(want.min())
+        outsiders = np.setdiff1d(ids, top)
+        if outsiders.size:
+            best_out = max(float(sc[pos[int(d)]]) for d in outsiders)
+            worst["outsider_margin"] = max(worst["outsider_margin"], (best_out - kth) / scale)
+    if not worst["score_rel_err"] < tol or not worst["outsider_margin"] < tol:
+        raise SystemExit(f"bench.py: retrieve verification failed: {worst}")
+    worst["queries_checked"] = len(qs)
+    worst["random_docs_per_query"] = int(min(n_random, n_docs))
+    return worst
+
+
+# --------------------------------------------------------------------------------------------------------
+# Seeded synthetic corpora (chunk-addressable: any rank can build any chunk; the tests use the same ones)
+# --------------------------------------------------------------------------------------------------------
+def dense_corpus(lo, hi, dev, Ld=300, d=DIM):
+    """Documents [lo, hi) of the dense corpus: bf16 [n, Ld, d] L2-normalised rows and lengths U[32, Ld]."""
+    import torch
+
+    nd = hi - lo
+    D = torch.empty((nd, Ld, d), dtype=torch.bfloat16, device=dev)
+    lens = torch.empty(nd, dtype=torch.int64, device=dev)
+    g = torch.Generator(device=dev)
+    c = lo // CHUNK
+    while c * CHUNK < hi:
+        a, b = c * CHUNK, (c + 1) * CHUNK
+        g.manual_seed(1234 + c)
+        x = torch.randn((CHUNK, Ld, d), generator=g, device=dev, dtype=torch.float32)
+        ln = torch.randint(32, Ld + 1, (CHUNK,), generator=g, device=dev)
+        s0, s1 = max(a, lo), min(b, hi)
+        D[s0 - lo:s1 - lo] = torch.nn.functional.normalize(x[s0 - a:s1 - a], dim=-1).to(torch.bfloat16)
+        lens[s0 - lo:s1 - lo] = ln[s0 - a:s1 - a]
+        c += 1
+    return D, lens
+
+
+def plaid_corpus(lo, hi, dev, d=DIM):
+    """Documents [lo, hi) of the PLAID corpus: lengths U[32,300], uniform codes over 65536 centroids, uniform 2-bit
+    residual bytes; returns (codes int32 [T], residuals uint8 [T, d/4], lens int64 [n])."""
+    import torch
+
+    g = torch.Generator(device=dev)
+    codes, res, lens = [], [], []
+    c = lo // CHUNK
+    while c * CHUNK < hi:
+        a, b = c * CHUNK, (c + 1) * CHUNK
+        g.manual_seed(4321 + c)
+        ln = torch.randint(32, 301, (CHUNK,), generator=g, device=dev)
+        T = int(ln.sum())
+        cc = torch.randint(0, 65536, (T,), generator=g, device=dev, dtype=torch.int32)
+        rr = torch.randint(0, 256, (T, d // 4), generator=g, device=dev, dtype=torch.uint8)
+        s0, s1 = max(a, lo), min(b, hi)
+        cu = torch.nn.functional.pad(ln.cumsum(0), (1, 0))
+        t0, t1 = int(cu[s0 - a]), int(cu[s1 - a])
+        codes.append(cc[t0:t1])
+        res.append(rr[t0:t1])
+        lens.append(ln[s0 - a:s1 - a])
+        c += 1
+    return torch.cat(codes), torch.cat(res), torch.cat(lens)
+
+
+def plaid_tables(dev, d=DIM):
+    import torch
+
+    g = torch.Generator(device=dev).manual_seed(5)
+    cent = torch.nn.functional.normalize(torch.randn((65536, d), generator=g, device=dev), dim=-1).half()
+    bw = torch.linspace(-0.1, 0.1, 4, device=dev)
+    return cent, bw
+
+
+def retrieve_queries(n, dev, d=DIM):
+    import torch
+
+    g = torch.Generator(device=dev).manual_seed(99)
+    return torch.nn.functional.normalize(torch.randn((n, 32, d), generator=g, device=dev), dim=-1).to(torch.bfloat16)
+
+
+def _timed(run, dev, reps, world):
+    """Device time of run() per repetition: every repetition between its own event pair, max over ranks per repetition."""
     import torch
     import torch.distributed as dist
+
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(reps)]
+    last = None
+    for a, b in ev:
+        a.record()
+        last = run()
+        b.record()
+    torch.cuda.synchronize(dev)
+    t = torch.tensor([a.elapsed_time(b) for a, b in ev], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = t.cpu().numpy()
+    return float(ms.min()), float(np.median(ms)), last
+
+
+def retrieve_bench(n_docs, world, rank, dev, verify):
+    """Sharded top-k retrieve: `n_docs` documents of U[32,300] tokens, d=128, bf16 normalised, split by document over
+    the ranks; 1024 queries x 32 tokens, top_k=100.  Strong scaling: the corpus is fixed, every rank scores its slice
+    in one pass of the fused scoring + top-k kernel, then one all-gather + merge."""
+    import torch
+    import torch.distributed as dist
+
+    from late_interaction_kernels_b200 import _lib, sharded
+
+    lo, hi = sharded.shard_bounds(n_docs, world, rank)
+    D, lens = dense_corpus(lo, hi, dev)
+    dm = torch.arange(300, device=dev)[None, :] < lens[:, None]
+    Q = retrieve_queries(1024, dev)
+    valid_tokens = torch.tensor([float(lens.sum())], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(valid_tokens)
+    n_tok = float(valid_tokens.item())
+
+    def run(q=Q, normalize=False):
+        return sharded.retrieve_sharded(q, D, 100, d_mask=dm, doc_offset=lo, n_docs_total=n_docs, normalize=normalize, chunk=CHUNK)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    lib = _lib.load()
+    n0 = lib.lik_launch_count()
+    res = run()
+    launches = lib.lik_launch_count() - n0
+    barrier()
+    ms_min, ms_med, res = _timed(run, dev, 3, world)
+    flops = 2.0 * DIM * 1024 * 32 * n_tok
+    out = {"metric": "retrieve queries/s", "value": 1024 / (ms_med * 1e-3), "unit": "queries/s", "ms_per_batch": ms_med,
+           "ms_per_batch_min": ms_min, "repetitions": 3, "n_docs": n_docs, "queries": 1024, "top_k": 100, "scaling": "strong",
+           "tflops_valid": flops / (ms_med * 1e-3) / 1e12, "launches_per_batch_per_rank": int(launches),
+           "roofline": roofline("tensor", flops / world, ms_med * 1e-3, kernel="fwd_tc_kernel (bf16, fused top-k)",
+                                note="per GPU: valid FLOPs of the shard over the batch time")}
+    # the default of retrieve(): fused L2 normalisation of both sides
+    barrier()
+    run(normalize=True)
+    ms_min, ms_med, _ = _timed(lambda: run(normalize=True), dev, 2, world)
+    out["normalize_true"] = {"ms_per_batch": ms_med, "queries_per_s": 1024 / (ms_med * 1e-3), "tflops_valid": flops / (ms_med * 1e-3) / 1e12}
+    # end to end: queries from pinned host memory, [Nq, k] scores and indices back to the host
+    hQ = Q.cpu().pin_memory()
+    hS = torch.empty((1024, 100), dtype=torch.float32).pin_memory()
+    hI = torch.empty((1024, 100), dtype=torch.int64).pin_memory()
+    dQ = torch.empty_like(Q)
+
+    def e2e():
+        dQ.copy_(hQ, non_blocking=True)
+        s, i = run(q=dQ)
+        hS.copy_(s, non_blocking=True)
+        hI.copy_(i, non_blocking=True)
+        return s, i
+
+    e2e()
+    barrier()
+    ms_min, ms_med, _ = _timed(e2e, dev, 2, world)
+    out["e2e"] = {"value": 1024 / (ms_med * 1e-3), "unit": "queries/s", "h2d_bytes_per_batch": hQ.numel() * 2,
+                  "d2h_bytes_per_batch": hS.numel() * 4 + hI.numel() * 8}
+    # few queries: the documents are read once, so the bound is HBM
+    if world == 1:
+        Q8 = retrieve_queries(8, dev)
+        run(q=Q8)
+        ms_min, ms_med, _ = _timed(lambda: run(q=Q8), dev, 3, world)
+        out["eight_queries"] = {"ms_per_batch": ms_med, "queries_per_s": 8 / (ms_med * 1e-3),
+                                "roofline": roofline("hbm", n_tok * DIM * 2, ms_med * 1e-3, kernel="fwd_tc_kernel (bf16, fused top-k)",
+                                                     note="valid document bytes read once; 256 rows of queries make it tensor work "
+                                                          "at the same time (256 FLOP per byte)")}
+    if verify and world == 1:
+        from oracle import maxsim_oracle as O
+
+        Qh = Q.float().cpu().numpy()
+
+        def score_docs(q_rows, ids):
+            sub = D[torch.as_tensor(ids, device=dev)].float().cpu().numpy()
+            sm = dm[torch.as_tensor(ids, device=dev)].cpu().numpy()
+            return O.maxsim(Qh[q_rows], sub, None, sm)
+
+        out["verified"] = verify_topk(Q, score_docs, n_docs, res)
+    out["best_index_q0"] = int(res[1][0, 0])
+    return out
+
+
+def plaid_retrieve_bench(n_docs, world, rank, dev, verify):
+    """Sharded top-k over a PLAID index (2-bit residuals, d=128, 65536 fp16 centroids): 1024 queries, top-100.  With
+    this many queries every token is decoded once per call, in pieces, and the scoring kernel carries its candidate
+    lists from piece to piece."""
+    import torch
+    import torch.distributed as dist
+    import torch.nn.functional as F
 
     from late_interaction_kernels_b200 import sharded
 
     lo, hi = sharded.shard_bounds(n_docs, world, rank)
-    nd, Ld, d, chunk = hi - lo, 300, 128, 4096
-    D = torch.empty((nd, Ld, d), dtype=torch.bfloat16, device=dev)
-    lens = torch.empty(nd, dtype=torch.int64, device=dev)
-    g = torch.Generator(device=dev)
-    for c0 in range(0, nd, chunk):  # chunk-addressable seeds: any rank can regenerate any chunk
-        c1 = min(nd, c0 + chunk)
-        g.manual_seed(1234 + (lo + c0) // chunk)
-        x = torch.randn((c1 - c0, Ld, d), generator=g, device=dev, dtype=torch.float32)
-        D[c0:c1] = torch.nn.functional.normalize(x, dim=-1).to(torch.bfloat16)
-        lens[c0:c1] = torch.randint(32, Ld + 1, (c1 - c0,), generator=g, device=dev)
-    dm = torch.arange(Ld, device=dev)[None, :] < lens[:, None]
-    g.manual_seed(99)
-    Q = torch.nn.functional.normalize(torch.randn((1024, 32, d), generator=g, device=dev), dim=-1).to(torch.bfloat16)
-    valid_tokens = torch.tensor([float(lens.sum())], device=dev, dtype=torch.float64)
+    codes, res, lens = plaid_corpus(lo, hi, dev)
+    T = int(codes.numel())
+    cu = F.pad(lens.cumsum(0), (1, 0)).int()
+    cent, bw = plaid_tables(dev)
+    Q = retrieve_queries(1024, dev)
+    lens_host = lens.cpu()
+    tok = torch.tensor([float(T)], device=dev, dtype=torch.float64)
     if world > 1:
-        dist.all_reduce(valid_tokens)
+        dist.all_reduce(tok)
+    n_tok = float(tok.item())
 
     def run():
-        return sharded.retrieve_sharded(Q, D, 100, d_mask=dm, doc_offset=lo, n_docs_total=n_docs, normalize=False, chunk=chunk)
+        return sharded.retrieve_plaid_sharded(Q, codes, res, cu, cent, bw, 2, 100, doc_offset=lo, n_docs_total=n_docs, chunk=16 * CHUNK,
+                                              doc_lengths_host=lens_host)
 
-    run()
+    out_res = run()
     if world > 1:
         dist.barrier()
     torch.cuda.synchronize()
-    reps = 2
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(reps):
-        s, i = run()
-    e1.record()
-    torch.cuda.synchronize()
-    t = torch.tensor([e0.elapsed_time(e1) / reps], device=dev, dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms = float(t.item())
-    flops = 2.0 * d * 1024 * 32 * float(valid_tokens.item())
-    return {"metric": "retrieve queries/s", "value": 1024 / (ms * 1e-3), "unit": "queries/s", "ms_per_batch": ms,
-            "n_docs": n_docs, "queries": 1024, "top_k": 100, "chunk": chunk, "scaling": "strong",
-            "tflops_valid": flops / (ms * 1e-3) / 1e12, "best_index_q0": int(i[0, 0])}
+    ms_min, ms_med, out_res = _timed(run, dev, 3, world)
+    flops = 2.0 * DIM * 1024 * 32 * n_tok
+    out = {"metric": "PLAID retrieve queries/s", "value": 1024 / (ms_med * 1e-3), "unit": "queries/s", "ms_per_batch": ms_med,
+           "ms_per_batch_min": ms_min, "repetitions": 3, "n_docs": n_docs, "queries": 1024, "top_k": 100, "nbits": 2, "scaling": "strong",
+           "tflops_valid": flops / (ms_med * 1e-3) / 1e12,
+           "roofline": roofline("tensor", flops / world, ms_med * 1e-3, kernel="plaid_decompress16_kernel + fwd_tc_kernel (fused top-k)",
+                                note="per GPU; 128 query-tile groups share every decoded token, so the tensor pipe bounds it")}
+    if verify and world == 1:
+        from oracle import maxsim_oracle as O
+
+        Qh = Q.float().cpu().numpy()
+        cu_h = F.pad(lens_host.cumsum(0), (1, 0)).numpy()
+        cent_h, bw_h = cent.float().cpu().numpy(), bw.cpu().numpy()
+
+        def score_docs(q_rows, ids):
+            cs, rs, ls = [], [], []
+            for j in ids:
+                a, b = int(cu_h[j]), int(cu_h[j + 1])
+                cs.append(codes[a:b])
+                rs.append(res[a:b])
+                ls.append(b - a)
+            cc, rr = torch.cat(cs).cpu().numpy(), torch.cat(rs).cpu().numpy()
+            c2 = np.concatenate([[0], np.cumsum(ls)])
+            emb = torch.from_numpy(O.plaid_decompress(cc, rr, cent_h, bw_h, 2)).to(torch.bfloat16).float().numpy()
+            outp = np.zeros((len(q_rows), len(ids)), np.float32)
+            for n in range(len(ids)):
+                dj = emb[c2[n]:c2[n + 1]]
+                outp[:, n] = np.einsum("isd,td->ist", Qh[q_rows], dj).max(-1).sum(-1)
+            return outp
+
+        out["verified"] = verify_topk(Q, score_docs, n_docs, out_res, n_random=1000)
+    return out
 
 
 def _time_us(fn, dev, iters=10, warm=3, graph=False):
@@ -227,9 +554,11 @@ def _time_us(fn, dev, iters=10, warm=3, graph=False):
     run = fn
     if graph:
         try:
-            gr = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(gr):
-                fn()
+            st = torch.cuda.Stream(dev)
+            with torch.cuda.stream(st):
+                gr = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(gr, stream=st):
+                    fn()
             run = gr.replay
             run()
             torch.cuda.synchronize(dev)
@@ -246,14 +575,15 @@ def _time_us(fn, dev, iters=10, warm=3, graph=False):
 
 
 def other_configs(dev):
-    """Kernel timings of the other BASELINE shapes (rank 0, one GPU): the KD layout in bf16 and e4m3
-    (HBM-bound: GB/s over the document bytes read once), the packed ColPali-shaped batch forward and
-    forward + backward (TFLOP/s on valid tokens), and the PLAID candidate score (GB/s over codes + table rows)."""
+    """Kernel timings of the other workload shapes (rank 0, one GPU), each with the roofline that bounds it: the KD
+    layout in bf16 and e4m3 (HBM: document bytes read once), the packed ColPali-shaped batch forward and forward +
+    backward (tensor: valid FLOPs), the PLAID candidate score, decode kernel and few-query rerank (HBM: compressed
+    bytes), and the per-row top-k kernel (HBM: score bytes)."""
     import torch
     import torch.nn.functional as F
 
     import late_interaction_kernels_b200 as lik
-    from late_interaction_kernels_b200 import fp8, plaid
+    from late_interaction_kernels_b200 import _ops, fp8, plaid
 
     out = {}
     g = torch.Generator(device=dev).manual_seed(7)
@@ -262,13 +592,17 @@ def other_configs(dev):
     D = F.normalize(torch.randn((64, 32, 300, 128), generator=g, device=dev), dim=-1)
     lens = torch.randint(64, 301, (64, 32), generator=g, device=dev)
     dm = torch.arange(300, device=dev)[None, None, :] < lens[..., None]
+    valid = float(lens.sum())
     qb, db = Q.bfloat16(), D.bfloat16()
     t = _time_us(lambda: lik.maxsim(qb, db, d_mask=dm), dev, graph=True)
-    out["kd_bf16_fwd"] = {"us": t, "GBps_document_bytes": db.numel() * 2 / t / 1e3, "shape": "Q[64,32,128] x D[64,32,300,128]"}
+    out["kd_bf16_fwd"] = {"us": t, "shape": "Q[64,32,128] x D[64,32,300,128]",
+                          "roofline": roofline("hbm", valid * 256 + qb.numel() * 2, t * 1e-6, kernel="fwd_tc_kernel (grouped)",
+                                               note="valid document rows + queries, read once")}
     q8, sq = fp8.quantize_fp8_per_token(Q)
     d8, sd = fp8.quantize_fp8_per_token(D)
     t = _time_us(lambda: fp8.maxsim_inference_fp8(q8, d8, scale_Q=sq, scale_D=sd, d_mask=dm), dev, graph=True)
-    out["kd_e4m3_fwd"] = {"us": t, "GBps_document_bytes": (d8.numel() + sd.numel() * 4) / t / 1e3}
+    out["kd_e4m3_fwd"] = {"us": t, "roofline": roofline("hbm", valid * (128 + 4) + q8.numel(), t * 1e-6, kernel="fwd_tc_kernel (e4m3, grouped)",
+                                                        note="valid e4m3 rows + their fp32 scales, read once")}
     del D, db, d8
     # packed: 128 queries of U[16,32] tokens x 128 documents of U[900,1030] tokens
     ql = torch.randint(16, 33, (128,), generator=g, device=dev)
@@ -279,7 +613,8 @@ def other_configs(dev):
     Dp = F.normalize(torch.randn((int(dl.sum()), 128), generator=g, device=dev), dim=-1).bfloat16()
     fl = 2.0 * 128 * float(ql.sum()) * float(dl.sum())
     t = _time_us(lambda: lik.maxsim_varlen(Qp, Dp, cq, cd, 32, 1030), dev, graph=True)
-    out["varlen_fwd"] = {"us": t, "tflops_valid": fl / t / 1e6, "shape": "128 q U[16,32] x 128 docs U[900,1030]"}
+    out["varlen_fwd"] = {"us": t, "shape": "128 q U[16,32] x 128 docs U[900,1030]",
+                         "roofline": roofline("tensor", fl, t * 1e-6, kernel="fwd_tc_kernel (packed)")}
     Qr, Dr = Qp.clone().requires_grad_(), Dp.clone().requires_grad_()
     go = torch.randn((128, 128), generator=g, device=dev)
 
@@ -288,61 +623,45 @@ def other_configs(dev):
         Dr.grad = None
         lik.maxsim_varlen(Qr, Dr, cq, cd, 32, 1030).backward(go)
 
-    t = _time_us(fb, dev)
-    out["varlen_fwd_bwd"] = {"us": t, "tflops_valid": (fl + 4.0 * 128 * float(ql.sum()) * 128) / t / 1e6}
+    t = _time_us(fb, dev, graph=True)
+    flb = fl + 4.0 * 128 * float(ql.sum()) * 128
+    out["varlen_fwd_bwd"] = {"us": t, "timed": "CUDA-graph replay of forward + backward",
+                             "roofline": roofline("tensor", flb, t * 1e-6, kernel="fwd_tc_kernel + bwd_dq16 + bwd_dd_sort4 + bwd_dd_reduce16",
+                                                  note="the 60 % target is quoted on this shape")}
     # PLAID candidate score: 65536 centroids, 8192 candidate documents of up to 300 codes
     qcs = torch.randn((65536, 32), generator=g, device=dev)
     codes = torch.randint(0, 65536, (8192, 300), generator=g, device=dev, dtype=torch.int32)
     cl = torch.randint(32, 301, (8192,), generator=g, device=dev)
     t = _time_us(lambda: plaid.plaid_approx_score(qcs, codes, cl), dev, graph=True)
-    out["plaid_approx"] = {"us": t, "GBps_codes_and_rows": float(cl.sum()) * (4 + 32 * 4) / t / 1e3, "shape": "8192 docs x <=300 codes, 32 query tokens"}
+    out["plaid_approx"] = {"us": t, "shape": "8192 docs x <=300 codes, 32 query tokens",
+                           "roofline": roofline("hbm", float(cl.sum()) * 4, t * 1e-6, kernel="plaid_approx_kernel",
+                                                note="code bytes only: the 8.4 MB score table stays in L2, its rows are not HBM traffic")}
+    # PLAID: decode kernel alone, and the few-query rerank (the reference's published PLAID shape: one query x 10k / 25k docs)
+    cent, bw = plaid_tables(dev)
+    for nd in (10_000, 25_000):
+        pc, pr, pl_ = plaid_corpus(0, nd, dev)
+        pcu = F.pad(pl_.cumsum(0), (1, 0)).int()
+        T = int(pc.numel())
+        if nd == 25_000:
+            ix, keep = _ops.plaid_index(pc, pr, cent, bw, 2, 128)
+            t = _time_us(lambda: _ops.plaid_decompress(ix, 0, T, True, torch.bfloat16, dev), dev)
+            out["plaid_decompress"] = {"us": t, "tokens": T,
+                                       "roofline": roofline("hbm", T * (36.0 + 256.0), t * 1e-6, kernel="plaid_decompress16_kernel",
+                                                            note="4 B code + 32 B residual in, 256 B bf16 row out per token")}
+        for nq in (1, 8, 32):
+            Qq = retrieve_queries(nq, dev)
+            t = _time_us(lambda: plaid.retrieve_residual_varlen(Qq, pc, pr, pcu, cent, bw, 2, 10), dev, iters=5)
+            out[f"plaid_top10_{nq}q_{nd // 1000}k_docs"] = {
+                "us": t, "tokens": T,
+                "roofline": roofline("hbm", T * 36.0, t * 1e-6, kernel="fwd_tc_kernel (PLAID decode in the producer warps, fused top-k)",
+                                     note="compressed bytes (36 B per token) read once; includes the merge kernel and the query norms")}
+    # per-row top-k kernel on a score matrix
+    sc = torch.randn((1024, 4096), generator=g, device=dev)
+    t = _time_us(lambda: _ops.topk_rows(sc, 100), dev, graph=True)
+    out["topk_rows"] = {"us": t, "shape": "[1024, 4096] fp32 -> top-100",
+                        "roofline": roofline("hbm", sc.numel() * 4.0, t * 1e-6, kernel="topk_kernel",
+                                             note="one read of the scores; the kernel is bound by its shared-memory sorts")}
     return out
-
-
-def plaid_retrieve_bench(n_docs, world, rank, dev):
-    """Sharded top-k over a PLAID index (2-bit residuals, d=128, 65536 fp16 centroids): the shard's
-    codes and residual bytes are decompressed chunk by chunk, scored and merged; 1024 queries, top-100."""
-    import torch
-    import torch.distributed as dist
-    import torch.nn.functional as F
-
-    from late_interaction_kernels_b200 import sharded
-
-    lo, hi = sharded.shard_bounds(n_docs, world, rank)
-    g = torch.Generator(device=dev).manual_seed(4321 + rank)
-    lens = torch.randint(32, 301, (hi - lo,), generator=g, device=dev)
-    T = int(lens.sum())
-    codes = torch.randint(0, 65536, (T,), generator=g, device=dev, dtype=torch.int32)
-    res = torch.randint(0, 256, (T, 32), generator=g, device=dev, dtype=torch.uint8)
-    cu = F.pad(lens.cumsum(0), (1, 0)).int()
-    g.manual_seed(5)
-    cent = F.normalize(torch.randn((65536, 128), generator=g, device=dev), dim=-1).half()
-    bw = torch.linspace(-0.1, 0.1, 4, device=dev)
-    Q = F.normalize(torch.randn((1024, 32, 128), generator=g, device=dev), dim=-1).bfloat16()
-    tok = torch.tensor([float(T)], device=dev, dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(tok)
-
-    def run():
-        return sharded.retrieve_plaid_sharded(Q, codes, res, cu, cent, bw, 2, 100, doc_offset=lo, n_docs_total=n_docs, chunk=4096)
-
-    run()
-    if world > 1:
-        dist.barrier()
-    torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    s, i = run()
-    e1.record()
-    torch.cuda.synchronize()
-    t = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms = float(t.item())
-    n_tok = float(tok.item())
-    return {"metric": "PLAID retrieve queries/s", "value": 1024 / (ms * 1e-3), "unit": "queries/s", "ms_per_batch": ms, "n_docs": n_docs,
-            "queries": 1024, "top_k": 100, "nbits": 2, "scaling": "strong", "tflops_valid": 2.0 * 128 * 1024 * 32 * n_tok / (ms * 1e-3) / 1e12,
-            "compressed_GBps": n_tok * 36 / (ms * 1e-3) / 1e9}
 
 
 def main():
@@ -354,8 +673,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--retrieve-docs", type=int, default=1_000_000,
                     help="corpus size of the sharded top-k retrieve reported under extra.retrieve (0 = skip)")
-    ap.add_argument("--only", default=None, choices=["fwd", "fwd_infer", "bwd", "step"],
-                    help="profiling aid: launch only this part of the step, --steps times, and print its mean time")
+    ap.add_argument("--only", default=None, choices=["fwd", "fwd_infer", "bwd", "step", "retrieve", "plaid", "topk_rows", "decompress"],
+                    help="profiling aid: launch only this part, --steps times, and print its mean time")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -387,7 +706,7 @@ def main():
         # keep stdout for the one JSON line: NCCL's own log lines (version banner, warnings) go to stderr
         os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
         dist.init_process_group("nccl", device_id=dev)
-    _lib.load()
+    lib = _lib.load()
 
     Q, D, dm, lens, g = make_inputs()
     fwd_flops, bwd_flops = flops_of(lens)
@@ -412,16 +731,37 @@ def main():
         torch.cuda.synchronize()
 
     if args.only:
+        from late_interaction_kernels_b200 import plaid as plaid_mod
         from late_interaction_kernels_b200.backward import maxsim_backward_lowmem
 
         qs, ds = _ops.padded_spec(dQ), _ops.padded_spec(dD, dM)
-        _, am = _ops.forward(qs, ds, save_argmax=True)
-        part = {
-            "fwd": lambda: _ops.forward(qs, ds, save_argmax=True),
-            "fwd_infer": lambda: _ops.forward(qs, ds),
-            "bwd": lambda: maxsim_backward_lowmem(dG, dQ, dD, am),
-            "step": step,
-        }[args.only]
+        if args.only in ("fwd", "fwd_infer", "bwd", "step"):
+            _, am = _ops.forward(qs, ds, save_argmax=True)
+            part = {
+                "fwd": lambda: _ops.forward(qs, ds, save_argmax=True),
+                "fwd_infer": lambda: _ops.forward(qs, ds),
+                "bwd": lambda: maxsim_backward_lowmem(dG, dQ, dD, am),
+                "step": step,
+            }[args.only]
+        elif args.only == "retrieve":  # one 4096-document chunk of the corpus, 1024 queries, fused top-k
+            Dc, lc = dense_corpus(0, CHUNK, dev)
+            mc = torch.arange(300, device=dev)[None, :] < lc[:, None]
+            Qc = retrieve_queries(1024, dev)
+            part = lambda: lik.retrieve(Qc, Dc, 100, d_mask=mc, normalize=False)  # noqa: E731
+        elif args.only == "plaid":  # 8 queries x 25k compressed documents: decode inside the scoring kernel, fused top-k
+            pc, pr, pl_ = plaid_corpus(0, 25_000, dev)
+            pcu = torch.nn.functional.pad(pl_.cumsum(0), (1, 0)).int()
+            cent, bw = plaid_tables(dev)
+            Qc = retrieve_queries(8, dev)
+            part = lambda: plaid_mod.retrieve_residual_varlen(Qc, pc, pr, pcu, cent, bw, 2, 10)  # noqa: E731
+        elif args.only == "decompress":
+            pc, pr, pl_ = plaid_corpus(0, 25_000, dev)
+            cent, bw = plaid_tables(dev)
+            ix, keep = _ops.plaid_index(pc, pr, cent, bw, 2, 128)
+            part = lambda: _ops.plaid_decompress(ix, 0, int(pc.numel()), True, torch.bfloat16, dev)  # noqa: E731
+        else:
+            sc = torch.randn((1024, 4096), device=dev)
+            part = lambda: _ops.topk_rows(sc, 100)  # noqa: E731
         for _ in range(args.warmup):
             part()
         torch.cuda.synchronize()
@@ -434,17 +774,21 @@ def main():
         emit({"only": args.only, "ms": a.elapsed_time(b) / args.steps, "steps": args.steps})
         return
 
+    parity = assert_step_parity(lik, dQ, dD, dM, dG, Q, D, dm, g) if rank == 0 else None
+
     for _ in range(args.warmup):
         step()
     barrier()
     ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
     with ClockSampler(local_rank) as clocks:
         barrier()
+        n_launch0 = lib.lik_launch_count()
         for a, b in ev:
             flush.zero_()
             a.record()
             step()
             b.record()
+        n_launch = lib.lik_launch_count() - n_launch0
         barrier()
     total_ms = sum(a.elapsed_time(b) for a, b in ev)
     lik.check_device_status(dev)
@@ -514,25 +858,32 @@ def main():
     h2d = hQ.numel() * 2 + hD.numel() * 2 + hM.numel() + hG.numel() * 4
     d2h = hS.numel() * 4 + hGQ.numel() * 2 + hGD.numel() * 2
 
-    # ---- roofline of the dominant kernel (the tcgen05 forward with argmax), timed alone ----
+    # ---- roofline of the dominant kernel (the tcgen05 forward with argmax), timed alone; and of the backward ----
     qs, ds = _ops.padded_spec(dQ), _ops.padded_spec(dD, dM)
-    for _ in range(3):
-        _ops.forward(qs, ds, save_argmax=True)
-    fev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(10)]
-    for a, b in fev:
-        flush.zero_()
-        a.record()
-        _ops.forward(qs, ds, save_argmax=True)
-        b.record()
-    torch.cuda.synchronize()
-    fwd_ms = float(np.mean([a.elapsed_time(b) for a, b in fev]))
-    peak_tf, _, which = measured_peaks()
-    achieved = fwd_flops / (fwd_ms * 1e-3) / 1e12
-    roofline = {"bound": "tensor", "achieved": achieved, "peak": peak_tf, "unit": "TFLOP/s", "frac": achieved / peak_tf,
-                # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel on this workload, from the
-                # ncu capture summarised in profiles/fwd_tc_kernel_argmax_c2.txt (31.55 MB + 4.02 MB)
-                "traffic": 35.57e6, "traffic_unit": "bytes per launch",
-                "kernel": "fwd_tc_kernel (bf16, argmax, masked)", "kernel_ms": fwd_ms, "peak_source": which}
+
+    def alone(fn, n=10):
+        for _ in range(3):
+            fn()
+        fev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(n)]
+        for a, b in fev:
+            flush.zero_()
+            a.record()
+            fn()
+            b.record()
+        torch.cuda.synchronize()
+        return float(np.mean([a.elapsed_time(b) for a, b in fev]))
+
+    fwd_ms = alone(lambda: _ops.forward(qs, ds, save_argmax=True))
+    infer_ms = alone(lambda: _ops.forward(qs, ds))
+    _, am = _ops.forward(qs, ds, save_argmax=True)
+    bwd_ms = alone(lambda: _ops.backward(qs, ds, dG, am))
+    rows_valid = float(lens.sum())
+    fwd_bytes = dQ.numel() * 2 + rows_valid * DIM * 2 + dM.numel() + NQ * ND * 4 + NQ * ND * LQ * 4
+    bwd_bytes = dQ.numel() * 2 + rows_valid * DIM * 2 + NQ * ND * LQ * 4 + NQ * ND * 4 + dQ.numel() * 2 + dD.numel() * 2
+    main_roof = roofline("tensor", fwd_flops, fwd_ms * 1e-3, kernel="fwd_tc_kernel (bf16, argmax, masked)",
+                         traffic=profiled_traffic("fwd_tc_kernel_argmax_inbatch"))
+    main_roof["traffic_unit"] = "bytes per launch (ncu dram__bytes_read.sum + dram__bytes_write.sum; null when no capture is committed)"
+    main_roof["algorithmic_bytes"] = fwd_bytes
 
     line = {
         "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
@@ -541,20 +892,30 @@ def main():
         "config": {"workload": WORKLOAD, "parallelism": f"replicas x{world}", "l2": "flushed between steps (256 MB write)",
                    "fwd_flops_per_step": fwd_flops, "bwd_flops_per_step": bwd_flops},
         "e2e": {"value": e2e_val, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
-        # per step: mask_lens + fwd_tc (forward), bwd_dq_fast + bwd_dd_sort + bwd_dd_reduce (backward)
-        "gpu_launches": 5 * args.steps,
-        "roofline": roofline,
+        # kernels of this library launched inside the timed region (counted by the library, lik_launch_count)
+        "gpu_launches": int(n_launch),
+        "roofline": main_roof,
+        "parity_before_timing": parity,
         "clocks": clocks.summary(),
+        "extra": {
+            "step_kernels": {
+                "forward_no_argmax": roofline("tensor", fwd_flops, infer_ms * 1e-3, kernel="fwd_tc_kernel (bf16, masked)"),
+                "backward": roofline("hbm", bwd_bytes, bwd_ms * 1e-3, kernel="bwd_dq16 + bwd_dd_sort4 + bwd_dd_reduce16",
+                                     note="algorithmic bytes: Q, valid D rows, winners, upstream gradient in; both gradients out.  "
+                                          "The kernels gather one 256-byte row per (pair, query token) out of L2, 34x these bytes"),
+            },
+        },
     }
     if args.retrieve_docs > 0:
-        del Qr, Dr, flush
+        del Qr, Dr, flush, sets
         torch.cuda.empty_cache()
-        line["extra"] = {"retrieve": retrieve_bench(args.retrieve_docs, world, rank, dev)}
+        line["extra"]["retrieve"] = retrieve_bench(args.retrieve_docs, world, rank, dev, verify=rank == 0)
         torch.cuda.empty_cache()
-        line["extra"]["plaid_retrieve"] = plaid_retrieve_bench(args.retrieve_docs, world, rank, dev)
+        line["extra"]["plaid_retrieve"] = plaid_retrieve_bench(args.retrieve_docs, world, rank, dev, verify=rank == 0)
         torch.cuda.empty_cache()
         if world == 1:
             line["extra"]["other_configs"] = other_configs(dev)
+    lik.check_device_status(dev)
     if rank == 0:
         if not args.no_cpu_baseline and world == 1:
             sample_q = 16
@@ -566,7 +927,8 @@ def main():
                 reps += 1
             dt = time.perf_counter() - t0
             line["cpu_baseline"] = {"value": (cf + cb) * reps / dt / 1e12, "unit": "TFLOP/s", "cores": os.cpu_count() or 1,
-                                    "kind": "port", "sample": f"{reps} x ({sample_q} queries x {ND} docs fwd+bwd), numpy oracle, all host threads"}
+                                    "kind": "port", "sample": f"{reps} x ({sample_q} queries x {ND} docs fwd+bwd), numpy oracle, all host threads",
+                                    "other_workloads": cpu_other_workloads()}
         emit(line)
     if world > 1:
         dist.destroy_process_group()

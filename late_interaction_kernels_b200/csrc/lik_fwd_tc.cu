@@ -316,7 +316,6 @@ struct TcParams {
 };
 
 constexpr int PLAID_WARPS = 3;  // warps 0, 18 and 19 decode compressed tokens in the PLAID kernels
-constexpr int PLAID_UNROLL = 4; // tokens in flight per half-warp
 
 struct SharedCtl {
   unsigned long long q_full, q_empty;
@@ -324,8 +323,10 @@ struct SharedCtl {
   unsigned long long acc_full[2], acc_empty[2];
   int grp_abort[2];             // set by a group's first warp when its bounded wait gave up
   uint32_t stage_info[8];
-  int4 unit_info[UNIT_RING];    // per work unit: x = document length | LEN_FLAG_MASKED, y = its first row, z = query (LIST)
+  int4 unit_info[UNIT_RING];    // per work unit: x = document length | LEN_FLAG_MASKED, y = its first row, z = tile group, w = document
   volatile int units_posted;    // units published in unit_info so far
+  volatile int units_total;     // all units of this CTA once the producer has walked them (INT_MAX until then)
+  int grp_done[2];              // set by a group's first warp when the stream has ended
   uint32_t tmem_base;
   volatile int abort_flag;
   int seg_off[2][TILE_M], seg_len[2][TILE_M], seg_q[2][TILE_M];
@@ -365,20 +366,22 @@ __device__ __forceinline__ bool wait_bar(unsigned long long* bar, uint32_t parit
   return wait_bar_slow(b, parity, ctl, status);
 }
 // Bounded wait until the producer has published unit `uc` of this CTA in the unit ring.
-__device__ __noinline__ bool wait_posted_slow(SharedCtl* ctl, int uc, int* status) {
+// Returns 1 when the unit is there, 2 when the stream has ended before it, 0 when the CTA is aborting.
+__device__ __noinline__ int wait_posted_slow(SharedCtl* ctl, int uc, int* status) {
   const long long t0 = clock64();
   while (true) {
-    if (ctl->units_posted > uc) return true;
-    if (ctl->abort_flag) return false;
+    if (ctl->units_posted > uc) return 1;
+    if (ctl->units_total <= uc) return 2;
+    if (ctl->abort_flag) return 0;
     if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
       ctl->abort_flag = 1;
       if (status) atomicOr(status, LIK_DEV_WAIT_TIMEOUT);
-      return false;
+      return 0;
     }
   }
 }
-__device__ __forceinline__ bool wait_posted(SharedCtl* ctl, int uc, int* status) {
-  if (ctl->units_posted > uc) return true;
+__device__ __forceinline__ int wait_posted(SharedCtl* ctl, int uc, int* status) {
+  if (ctl->units_posted > uc) return 1;
   return wait_posted_slow(ctl, uc, status);
 }
 
@@ -631,9 +634,11 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
       mbar_init(smem_u32(&ctl->acc_full[a]), 1);
       mbar_init(smem_u32(&ctl->acc_empty[a]), GROUP_WARPS);
       ctl->grp_abort[a] = 0;
+      ctl->grp_done[a] = 0;
     }
     ctl->abort_flag = 0;
     ctl->units_posted = 0;
+    ctl->units_total = 0x7fffffff;
     fence_barrier_init();
     prefetch_tmap(&q_map);
     if (!PLAID)
@@ -680,6 +685,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
       while (have && ok) {
         const int grp = list ? raw_cur.q : cur.grp;
         const int next_grp = have_nxt ? (list ? raw_nxt.q : nxt.grp) : -1;
+        const int doc = cur.doc;
         long long drow0;
         int dlen;
         bool dmasked;
@@ -722,7 +728,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
         // publish the unit for the epilogue groups, then its stages; an empty document still sends one
         // (empty) stage so that every unit passes through the same hand-shakes
         if (elect) {
-          ctl->unit_info[uc & (UNIT_RING - 1)] = make_int4(dlen | (dmasked ? LEN_FLAG_MASKED : 0), (int)drow0, grp, 0);
+          ctl->unit_info[uc & (UNIT_RING - 1)] = make_int4(dlen | (dmasked ? LEN_FLAG_MASKED : 0), (int)drow0, grp, doc);
           __threadfence_block();
           ctl->units_posted = (int)uc + 1;
         }
@@ -739,43 +745,21 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
             ctl->stage_info[st] = info;
           }
           if (PLAID) {
-            // tokens of the stage go round-robin to the six half-warps of the three decoder warps
+            // the stage's tokens in six equal runs, one per half-warp of the three decoder warps
             const int hl = lane & 15;
             const int hw6 = pw * 2 + (lane >> 4);
-            const bool lane_on = hl * 8 < P.plaid.dim;
+            const int per = (ncols + 2 * PLAID_WARPS - 1) / (2 * PLAID_WARPS);
+            const int t_lo = min(hw6 * per, ncols), n_run = min(per, ncols - t_lo);
             unsigned char* stage = d_smem + (size_t)st * d_stage_bytes + (hl >> 3) * (TILE_N * SLAB_BYTES_ROW);
-            for (int tb = 0; tb < ncols; tb += 2 * PLAID_WARPS * PLAID_UNROLL) {  // same trip count on every lane
-              const int t0 = tb + hw6;
-              int code[PLAID_UNROLL];
-#pragma unroll
-              for (int u = 0; u < PLAID_UNROLL; ++u) {
-                const int t = t0 + u * 2 * PLAID_WARPS;
-                code[u] = t < ncols ? plaid_code(P.plaid, drow0 + c0 + t, P.status) : 0;
-              }
-              PlaidRaw r[PLAID_UNROLL];
-#pragma unroll
-              for (int u = 0; u < PLAID_UNROLL; ++u) {
-                const int t = t0 + u * 2 * PLAID_WARPS;
-                if (t < ncols && lane_on) r[u] = plaid_load(P.plaid, drow0 + c0 + t, code[u], hl);
-                else r[u] = PlaidRaw{make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), 0ull};
-              }
-#pragma unroll
-              for (int u = 0; u < PLAID_UNROLL; ++u) {
-                const int t = t0 + u * 2 * PLAID_WARPS;
-                // the shuffles of the norm need the whole half-warp: a token past the end is computed and dropped
-                float e[8];
-                plaid_features(P.plaid, r[u], ctl->plaid_bw, e);
-                if (!lane_on) {
-#pragma unroll
-                  for (int i = 0; i < 8; ++i) e[i] = 0.f;
-                }
-                const float inv = plaid_inv_norm(P.plaid, e);
-#pragma unroll
-                for (int i = 0; i < 8; ++i) e[i] *= inv;
-                if (t < ncols && lane_on)
-                  *reinterpret_cast<uint4*>(stage + t * SLAB_BYTES_ROW + (((hl & 7) ^ (t & 7)) << 4)) = plaid_pack16(e, P.plaid_f16 != 0);
-              }
-            }
+            const bool f16 = P.plaid_f16 != 0;
+            auto sink = [&](int t, const float (&e)[8]) {
+              const int row = t_lo + t;
+              *reinterpret_cast<uint4*>(stage + row * SLAB_BYTES_ROW + (((hl & 7) ^ (row & 7)) << 4)) = plaid_pack16(e, f16);
+            };
+            if (P.plaid.centroid_dtype == LIK_F32)
+              plaid_decode_range<true, 4>(P.plaid, ctl->plaid_bw, drow0 + c0 + t_lo, n_run, per, lane, hl * 8 < P.plaid.dim, P.status, sink);
+            else
+              plaid_decode_range<false, 8>(P.plaid, ctl->plaid_bw, drow0 + c0 + t_lo, n_run, per, lane, hl * 8 < P.plaid.dim, P.status, sink);
             fence_proxy_async();
             __syncwarp();
             if (lane == 0) mbar_arrive(full);
@@ -796,6 +780,11 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
           c0 += TILE_N;
         } while (c0 < dlen);
         ++uc;
+      }
+      if (ok && elect) {
+        // tell the epilogue groups how many units there were
+        __threadfence_block();
+        ctl->units_total = (int)uc;
       }
       if (ok) {
         // tell the issuer that the stream has ended
@@ -943,11 +932,10 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
     const bool leader = (e & 7) == 0;
 #define LIK_GRP_SYNC() asm volatile("bar.sync %0, %1;" ::"r"(1 + wg), "r"(2 * EPI_THREADS) : "memory")
 #define LIK_SUB_SYNC() asm volatile("bar.sync %0, %1;" ::"r"(3 + wg), "r"(EPI_THREADS) : "memory")
-#define LIK_GROUP_WAIT_ACC(also_posted)                                              \
+#define LIK_GROUP_WAIT_ACC()                                                         \
   do {                                                                               \
     if (leader) {                                                                    \
-      bool ok_ = wait_bar(&ctl->acc_full[wg], n_acc & 1, ctl, P.status);             \
-      if (ok_ && (also_posted)) ok_ = wait_posted(ctl, uc, P.status);                \
+      const bool ok_ = wait_bar(&ctl->acc_full[wg], n_acc & 1, ctl, P.status);       \
       if (!ok_ && lane == 0) ctl->grp_abort[wg] = 1;                                 \
     }                                                                                \
     LIK_GRP_SYNC();                                                                  \
@@ -990,25 +978,30 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
     }                                                                                                  \
   } while (0)
 
-    UnitIter it;
-    bool have_unit = iter_begin(P, n_groups, it);
     const bool cross = P.pairing == LIK_PAIR_CROSS;
-    for (; have_unit && ok; ++uc, have_unit = iter_next(P, n_groups, it)) {
-      int grp = it.grp;
-      const int doc = it.doc;
-      bool waited = false;
-      if (list) {
-        // the query of a pair is only known from the unit ring
-        if (leader) {
-          const bool ok_ = wait_posted(ctl, uc, P.status);
-          if (!ok_ && lane == 0) ctl->grp_abort[wg] = 1;
+    for (;; ++uc) {
+      // with one resident tile the two groups take alternate units
+      if (P.mt == 1 && (uc & 1) != wg) continue;
+      // The unit (tile group, document, length, first row) comes from the producer's ring.  The group's first warp
+      // waits for its publication and - in kernels without per-column multipliers, which have nothing to prepare
+      // while the MMAs run - for the unit's first accumulator, when this group has a tile in the unit's tile group.
+      if (leader) {
+        int st_ = wait_posted(ctl, uc, P.status);
+        if (st_ == 1 && !SCALED) {
+          const int g_ = ctl->unit_info[uc & (UNIT_RING - 1)].z;
+          if (g_ * P.mt + (P.mt == 2 ? wg : 0) < n_tiles && !wait_bar(&ctl->acc_full[wg], n_acc & 1, ctl, P.status)) st_ = 0;
         }
-        LIK_GRP_SYNC();
-        ok = ctl->grp_abort[wg] == 0;
-        if (!ok) break;
-        grp = ctl->unit_info[uc & (UNIT_RING - 1)].z;
-        waited = true;
+        if (lane == 0) {
+          if (st_ == 0) ctl->grp_abort[wg] = 1;
+          if (st_ == 2) ctl->grp_done[wg] = 1;
+        }
       }
+      LIK_GRP_SYNC();
+      ok = ctl->grp_abort[wg] == 0;
+      if (!ok || ctl->grp_done[wg]) break;
+      const int4 uinfo = ctl->unit_info[uc & (UNIT_RING - 1)];
+      const int grp = uinfo.z;
+      const int doc = uinfo.w;
       if (grp != cur_grp) {
         cur_grp = grp;
         // (re)build the segment table of this group's tile `wg` (mt == 2) or tile 0 (mt == 1: both groups)
@@ -1091,29 +1084,8 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
           }
         }
       }
-      // with two resident tiles each group handles its own tile for every document; with one tile the
-      // groups alternate documents
-      const bool mine = P.mt == 2 ? have_tile : ((uc & 1) == wg);
-      if (!mine) continue;
-
-      // Unit data (length, first row) comes from the producer's ring.  Kernels with per-column
-      // multipliers wait for the publication alone (it precedes the unit's loads) so that they can stage
-      // the column arrays while the MMAs run; the others take it with their first accumulator wait.
-      if (SCALED || waited) {
-        if (!waited) {
-          if (leader) {
-            const bool ok_ = wait_posted(ctl, uc, P.status);
-            if (!ok_ && lane == 0) ctl->grp_abort[wg] = 1;
-          }
-          LIK_GRP_SYNC();
-          ok = ctl->grp_abort[wg] == 0;
-        }
-        if (ok && !SCALED) LIK_GROUP_WAIT_ACC(false);
-      } else {
-        LIK_GROUP_WAIT_ACC(true);
-      }
-      if (!ok) break;
-      const int4 uinfo = ctl->unit_info[uc & (UNIT_RING - 1)];
+      // a tile group with an odd tile out: the second epilogue group has nothing in it
+      if (!have_tile) continue;
       const int dlen = uinfo.x & ~LEN_FLAG_MASKED;
       const long long drow0 = uinfo.y;
       const bool holes = (uinfo.x & LEN_FLAG_MASKED) != 0;  // the document's mask is not a plain prefix
@@ -1143,7 +1115,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
   } while (0)
         if (SCALED) LIK_STAGE_COLUMNS();  // before the accumulator wait: overlaps the MMAs
         if (SCALED || c0 > 0) {
-          LIK_GROUP_WAIT_ACC(false);
+          LIK_GROUP_WAIT_ACC();
           if (!ok) break;
         }
         ++n_acc;

@@ -85,59 +85,33 @@ __global__ void __launch_bounds__(256) plaid_decompress_kernel(PlaidView v, long
   }
 }
 
-// Half-warp per token, the arithmetic of lik_plaid_row.cuh (the scoring kernel's producer warps decode
+// Half-warp per run of tokens, the arithmetic of lik_plaid_row.cuh (the scoring kernel's producer warps decode
 // tokens with the same functions, so rows written here and tiles decoded there hold the same bits):
 // 16-byte centroid loads, one load for a lane's eight bucket codes, 16-byte stores.
-constexpr int PD_UNROLL = 4;  // tokens in flight per half-warp
+constexpr int PD_RUN = 64;  // consecutive tokens per half-warp
 
-template <typename O>
+template <typename O, bool CF32>
 __global__ void __launch_bounds__(256) plaid_decompress16_kernel(PlaidSrc S, long long tok0, long long count, O* __restrict__ out,
                                                                int* status) {
   __shared__ float bw[256];
   for (int b = threadIdx.x; b < (1 << S.nbits); b += blockDim.x) bw[b] = S.bucket_weights[b];
   __syncthreads();
-  const int hl = threadIdx.x & 15;
-  const long long hw = (long long)blockIdx.x * 16 + (threadIdx.x >> 4);  // half-warp number
-  const long long n_hw = (long long)gridDim.x * 16;
-  const bool lane_on = hl * 8 < S.dim;
-  // every thread runs the same number of rounds (the norm's shuffles are warp-wide)
-  for (long long base = 0; base < count; base += n_hw * PD_UNROLL) {
-    int code[PD_UNROLL];
-#pragma unroll
-    for (int u = 0; u < PD_UNROLL; ++u) {
-      const long long w = base + u * n_hw + hw;
-      code[u] = w < count ? plaid_code(S, tok0 + w, status) : 0;
+  const int lane = threadIdx.x & 31, hl = lane & 15;
+  const long long first = ((long long)blockIdx.x * 16 + (threadIdx.x >> 4)) * PD_RUN;  // first token of this half-warp's run
+  long long left = count - first;
+  const int n = left <= 0 ? 0 : (left < PD_RUN ? (int)left : PD_RUN);
+  O* dst = out + first * S.dim + hl * 8;
+  const int dim = S.dim;
+  auto sink = [&](int t, const float (&e)[8]) {
+    O* p = dst + (long long)t * dim;
+    if (sizeof(O) == 4) {
+      reinterpret_cast<float4*>(p)[0] = make_float4(e[0], e[1], e[2], e[3]);
+      reinterpret_cast<float4*>(p)[1] = make_float4(e[4], e[5], e[6], e[7]);
+    } else {
+      *reinterpret_cast<uint4*>(p) = plaid_pack16(e, dtype_of<O>::value == LIK_F16);
     }
-    PlaidRaw r[PD_UNROLL];
-#pragma unroll
-    for (int u = 0; u < PD_UNROLL; ++u) {
-      const long long w = base + u * n_hw + hw;
-      if (w < count && lane_on) r[u] = plaid_load(S, tok0 + w, code[u], hl);
-      else r[u] = PlaidRaw{make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), 0ull};
-    }
-#pragma unroll
-    for (int u = 0; u < PD_UNROLL; ++u) {
-      const long long w = base + u * n_hw + hw;
-      float e[8];
-      plaid_features(S, r[u], bw, e);
-      if (!lane_on) {
-#pragma unroll
-        for (int i = 0; i < 8; ++i) e[i] = 0.f;
-      }
-      const float inv = plaid_inv_norm(S, e);
-#pragma unroll
-      for (int i = 0; i < 8; ++i) e[i] *= inv;
-      if (w < count && lane_on) {
-        O* dst = out + w * S.dim + hl * 8;
-        if (sizeof(O) == 4) {
-          reinterpret_cast<float4*>(dst)[0] = make_float4(e[0], e[1], e[2], e[3]);
-          reinterpret_cast<float4*>(dst)[1] = make_float4(e[4], e[5], e[6], e[7]);
-        } else {
-          *reinterpret_cast<uint4*>(dst) = plaid_pack16(e, dtype_of<O>::value == LIK_F16);
-        }
-      }
-    }
-  }
+  };
+  plaid_decode_range<CF32, CF32 ? 4 : 8>(S, bw, tok0 + first, n, PD_RUN, lane, hl * 8 < dim, status, sink);
 }
 
 // Approximate score: one warp per document, lane = query token (chunks of 32).
@@ -267,16 +241,22 @@ extern "C" int lik_plaid_decompress(const lik_plaid_index* index, int64_t token_
     PlaidSrc S{index->codes, index->residuals, index->centroids, index->bucket_weights, index->centroid_dtype, index->n_centroids,
                index->nbits, v.packed_dim, index->dim, normalize ? 1 : 0};
     if (plaid_row16_ok(S) && ((uintptr_t)out % 16) == 0 && (out_dtype == LIK_F32 || out_dtype == LIK_F16 || out_dtype == LIK_BF16)) {
-      // enough half-warps to fill the machine, PD_UNROLL tokens in flight each
-      long long blocks = ceil_div(token_count, 16 * PD_UNROLL);
-      const long long cap = (long long)sm_count() * 16;
-      if (blocks > cap) blocks = cap;
+      const unsigned blocks = (unsigned)ceil_div(token_count, 16 * PD_RUN);
+      const bool cf32 = index->centroid_dtype == LIK_F32;
+#define LIK_DEC16(O)                                                                                                  \
+  do {                                                                                                                \
+    if (cf32)                                                                                                         \
+      plaid_decompress16_kernel<O, true><<<blocks, 256, 0, st>>>(S, token_begin, token_count, (O*)out, status), ::lik::count_launch(); \
+    else                                                                                                              \
+      plaid_decompress16_kernel<O, false><<<blocks, 256, 0, st>>>(S, token_begin, token_count, (O*)out, status), ::lik::count_launch(); \
+  } while (0)
       if (out_dtype == LIK_F32)
-        plaid_decompress16_kernel<float><<<(unsigned)blocks, 256, 0, st>>>(S, token_begin, token_count, (float*)out, status), ::lik::count_launch();
+        LIK_DEC16(float);
       else if (out_dtype == LIK_F16)
-        plaid_decompress16_kernel<__half><<<(unsigned)blocks, 256, 0, st>>>(S, token_begin, token_count, (__half*)out, status), ::lik::count_launch();
+        LIK_DEC16(__half);
       else
-        plaid_decompress16_kernel<__nv_bfloat16><<<(unsigned)blocks, 256, 0, st>>>(S, token_begin, token_count, (__nv_bfloat16*)out, status), ::lik::count_launch();
+        LIK_DEC16(__nv_bfloat16);
+#undef LIK_DEC16
       LIK_CUDA_OK(cudaGetLastError());
       return LIK_OK;
     }

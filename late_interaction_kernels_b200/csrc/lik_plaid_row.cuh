@@ -28,9 +28,15 @@ struct PlaidSrc {
 };
 
 // raw loads of one token slice: issued for several tokens before any of them is used
+template <bool CF32>
 struct PlaidRaw {
-  uint4 c0, c1;             // centroid slice (c1 only for fp32 centroids)
+  uint4 c0;                 // centroid slice: eight 16-bit values, or the first four fp32 values
   unsigned long long w;     // the lane's eight bucket codes
+};
+template <>
+struct PlaidRaw<true> {
+  uint4 c0, c1;             // eight fp32 centroid values
+  unsigned long long w;
 };
 
 __device__ __forceinline__ int plaid_code(const PlaidSrc& S, long long tok, int* status) {
@@ -42,11 +48,15 @@ __device__ __forceinline__ int plaid_code(const PlaidSrc& S, long long tok, int*
   return c;
 }
 
-__device__ __forceinline__ PlaidRaw plaid_load(const PlaidSrc& S, long long tok, int code, int hl) {
-  PlaidRaw r;
-  r.c1 = make_uint4(0, 0, 0, 0);
+template <bool CF32>
+__device__ __forceinline__ PlaidRaw<CF32> plaid_load(const PlaidSrc& S, long long tok, int code, int hl, bool on) {
+  PlaidRaw<CF32> r;
+  r.c0 = make_uint4(0, 0, 0, 0);
+  r.w = 0ull;
+  if constexpr (CF32) r.c1 = make_uint4(0, 0, 0, 0);
+  if (!on) return r;
   const long long off = (long long)code * S.dim + hl * 8;
-  if (S.centroid_dtype == LIK_F32) {
+  if constexpr (CF32) {
     const uint4* p = reinterpret_cast<const uint4*>(static_cast<const float*>(S.centroids) + off);
     r.c0 = __ldg(p);
     r.c1 = __ldg(p + 1);
@@ -64,9 +74,10 @@ __device__ __forceinline__ PlaidRaw plaid_load(const PlaidSrc& S, long long tok,
 }
 
 // e[i] = centroid + bucket weight for the lane's eight features; bw points at the table in shared memory
-__device__ __forceinline__ void plaid_features(const PlaidSrc& S, const PlaidRaw& r, const float* bw, float (&e)[8]) {
+template <bool CF32>
+__device__ __forceinline__ void plaid_features(const PlaidSrc& S, const PlaidRaw<CF32>& r, const float* bw, float (&e)[8]) {
   float c[8];
-  if (S.centroid_dtype == LIK_F32) {
+  if constexpr (CF32) {
     c[0] = __uint_as_float(r.c0.x); c[1] = __uint_as_float(r.c0.y); c[2] = __uint_as_float(r.c0.z); c[3] = __uint_as_float(r.c0.w);
     c[4] = __uint_as_float(r.c1.x); c[5] = __uint_as_float(r.c1.y); c[6] = __uint_as_float(r.c1.z); c[7] = __uint_as_float(r.c1.w);
   } else if (S.centroid_dtype == LIK_BF16) {
@@ -94,6 +105,46 @@ __device__ __forceinline__ float plaid_inv_norm(const PlaidSrc& S, const float (
 #pragma unroll
   for (int o = 8; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
   return 1.f / fmaxf(sqrtf(ss), 1e-12f);
+}
+
+// A half-warp decodes the `n` consecutive tokens [tok0, tok0 + n) and hands the lane's eight finished values of
+// token t (0-based) to sink(t, values).  The centroid codes are read 16 at a time (one per lane, a chunk ahead of
+// their use) and passed around with shuffles; U row loads are in flight per half-warp.  Both half-warps of a warp
+// must call this with the same n_uniform >= n (the shuffles are warp-wide): tokens past n are computed on zeros and
+// dropped.  `lane` is the lane in the warp, `lane_on` whether the lane's features exist (8 * (lane & 15) < dim).
+template <bool CF32, int U, typename Sink>
+__device__ __forceinline__ void plaid_decode_range(const PlaidSrc& S, const float* bw, long long tok0, int n, int n_uniform, int lane,
+                                                   bool lane_on, int* status, Sink sink) {
+  const int hl = lane & 15;
+  int code_next = hl < n ? plaid_code(S, tok0 + hl, status) : 0;
+  for (int c0 = 0; c0 < n_uniform; c0 += 16) {
+    const int code_cur = code_next;
+    code_next = c0 + 16 + hl < n ? plaid_code(S, tok0 + c0 + 16 + hl, status) : 0;
+#pragma unroll 1
+    for (int b = 0; b < 16; b += U) {
+      PlaidRaw<CF32> r[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int t = c0 + b + u;
+        const int code = __shfl_sync(0xffffffffu, code_cur, (lane & 16) | (b + u));
+        r[u] = plaid_load<CF32>(S, tok0 + t, code, hl, t < n && lane_on);
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int t = c0 + b + u;
+        float e[8];
+        plaid_features<CF32>(S, r[u], bw, e);
+        if (!lane_on) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) e[i] = 0.f;
+        }
+        const float inv = plaid_inv_norm(S, e);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) e[i] *= inv;
+        if (t < n && lane_on) sink(t, e);
+      }
+    }
+  }
 }
 
 // eight fp32 values -> eight 16-bit operand values (bf16 or fp16), round to nearest even

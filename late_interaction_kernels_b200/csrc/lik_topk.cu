@@ -176,57 +176,83 @@ struct SlotParams {
   long long* out_index;
 };
 
-__global__ void __launch_bounds__(256) topk_slots_kernel(SlotParams P) {
-  extern __shared__ unsigned char raw[];
-  long long* top_i = reinterpret_cast<long long*>(raw);
-  long long* blk_i = top_i + P.KP;
-  float* top_k = reinterpret_cast<float*>(blk_i + P.KP);
-  float* blk_k = top_k + P.KP;
-  const int tid = threadIdx.x, nt = blockDim.x;
+constexpr int SLOT_W = 256;  // merge width: the capacity of a candidate list, and the block size
+
+// The kept list (SLOT_W entries, best first; the first k are the answer so far) absorbs the pending block.
+__device__ void slots_flush(float* top_k, long long* top_i, float* blk_k, long long* blk_i, int n_pend, int tid) {
+  if (tid >= n_pend) {
+    blk_k[tid] = -INFINITY;
+    blk_i[tid] = kPadIdx;
+  }
+  bitonic_sort(blk_k, blk_i, SLOT_W, tid, SLOT_W);
+  {
+    Cand a{top_k[tid], top_i[tid]}, c{blk_k[SLOT_W - 1 - tid], blk_i[SLOT_W - 1 - tid]};
+    if (before(c, a)) {
+      top_k[tid] = c.key;
+      top_i[tid] = c.idx;
+    }
+  }
+  bitonic_merge(top_k, top_i, SLOT_W, tid, SLOT_W);
+}
+
+// One CTA of SLOT_W threads per query.  Every list of the query is read once (one entry per thread); only
+// entries that beat the current k-th best are collected, and the collected block is sorted and merged when it
+// would overflow.  After the first list few entries survive the filter, so the sorts are rare.
+__global__ void __launch_bounds__(SLOT_W) topk_slots_kernel(SlotParams P) {
+  __shared__ long long top_i[SLOT_W], blk_i[SLOT_W];
+  __shared__ float top_k[SLOT_W], blk_k[SLOT_W];
+  __shared__ int n_pend_s;
+  const int tid = threadIdx.x, lane = tid & 31;
   const long long q = blockIdx.x;
   const int tile = (int)(q / P.qpt), et = (int)(q - (long long)tile * P.qpt);
   const int g = tile / P.mt, m = tile - g * P.mt;
   const int n_sub = P.mt == 2 ? 1 : 2;
-  for (int t = tid; t < P.KP; t += nt) {
-    top_k[t] = -INFINITY;
-    top_i[t] = kPadIdx;
-  }
+  top_k[tid] = -INFINITY;
+  top_i[tid] = kPadIdx;
+  if (tid == 0) n_pend_s = 0;
   __syncthreads();
   for (int c = 0; c < P.n_ctas; ++c) {
     const long long g_lo = (long long)P.n_groups * c / P.n_ctas, g_hi = (long long)P.n_groups * (c + 1) / P.n_ctas;
     if (g < g_lo || g > g_hi) continue;
     for (int sub = 0; sub < n_sub; ++sub) {
-    const long long list = (long long)(c + g) * (2 * P.qpt) + (P.mt == 2 ? m : sub) * P.qpt + et;
-    int cnt = P.hdr[list].x;
-    if (cnt > P.cap) cnt = P.cap;
-    for (int b0 = 0; b0 < cnt; b0 += P.KP) {
-      for (int t = tid; t < P.KP; t += nt) {
-        float key = -INFINITY;
-        long long id = kPadIdx;
-        if (b0 + t < cnt) {
-          key = P.keys[list * P.cap + b0 + t];
-          id = P.idx[list * P.cap + b0 + t];
-        }
-        blk_k[t] = key;
-        blk_i[t] = id;
+      const long long list = (long long)(c + g) * (2 * P.qpt) + (P.mt == 2 ? m : sub) * P.qpt + et;
+      int cnt = P.hdr[list].x;
+      if (cnt > P.cap) cnt = P.cap;
+      if (cnt <= 0) continue;
+      int n_pend = n_pend_s;
+      if (n_pend + cnt > SLOT_W) {  // the pending block could overflow: absorb it first
+        __syncthreads();
+        slots_flush(top_k, top_i, blk_k, blk_i, n_pend, tid);
+        if (tid == 0) n_pend_s = 0;
+        __syncthreads();
+        n_pend = 0;
       }
-      bitonic_sort(blk_k, blk_i, P.KP, tid, nt);
-      for (int t = tid; t < P.KP; t += nt) {
-        Cand a{top_k[t], top_i[t]}, cnd{blk_k[P.KP - 1 - t], blk_i[P.KP - 1 - t]};
-        if (before(cnd, a)) {
-          top_k[t] = cnd.key;
-          top_i[t] = cnd.idx;
-        }
+      Cand mine{-INFINITY, kPadIdx};
+      if (tid < cnt) mine = Cand{P.keys[list * P.cap + tid], (long long)P.idx[list * P.cap + tid]};
+      const Cand kth{top_k[P.k - 1], top_i[P.k - 1]};
+      const bool pass = tid < cnt && before(mine, kth);
+      const unsigned mask = __ballot_sync(0xffffffffu, pass);
+      int base = 0;
+      if (lane == 0 && mask) base = atomicAdd(&n_pend_s, __popc(mask));
+      base = __shfl_sync(0xffffffffu, base, 0);
+      if (pass) {
+        const int pos = base + __popc(mask & ((1u << lane) - 1u));
+        blk_k[pos] = mine.key;
+        blk_i[pos] = mine.idx;
       }
-      bitonic_merge(top_k, top_i, P.KP, tid, nt);
-    }
+      __syncthreads();
     }
   }
+  {
+    const int n_pend = n_pend_s;
+    __syncthreads();
+    if (n_pend > 0) slots_flush(top_k, top_i, blk_k, blk_i, n_pend, tid);
+  }
   const float sgn = P.largest ? 1.f : -1.f;
-  for (int t = tid; t < P.k; t += nt) {
-    const bool pad = top_i[t] == kPadIdx;
-    P.out_scores[q * P.k + t] = pad ? -sgn * INFINITY : sgn * top_k[t];
-    P.out_index[q * P.k + t] = pad ? -1 : top_i[t] + P.index_offset;
+  if (tid < P.k) {
+    const bool pad = top_i[tid] == kPadIdx;
+    P.out_scores[q * P.k + tid] = pad ? -sgn * INFINITY : sgn * top_k[tid];
+    P.out_index[q * P.k + tid] = pad ? -1 : top_i[tid] + P.index_offset;
   }
 }
 
@@ -234,10 +260,12 @@ int launch_topk_slots(const float* keys, const int* idx, const int2* hdr, int ca
                       long long n_q, int k, int largest, long long index_offset, float* out_scores, long long* out_index,
                       cudaStream_t st) {
   if (n_q <= 0 || k <= 0) return LIK_OK;
+  if (cap > SLOT_W || k > SLOT_W) {
+    set_error("candidate lists of %d entries / k = %d exceed the merge width %d", cap, k, SLOT_W);
+    return LIK_ERR_UNSUPPORTED;
+  }
   SlotParams P{keys, idx, hdr, cap, n_ctas, n_groups, mt, qpt, n_q, index_offset, k, 2, largest, out_scores, out_index};
-  while (P.KP < k) P.KP <<= 1;
-  const size_t smem = (size_t)P.KP * 2 * (sizeof(long long) + sizeof(float));
-  topk_slots_kernel<<<(unsigned)n_q, 256, smem, st>>>(P), ::lik::count_launch();
+  topk_slots_kernel<<<(unsigned)n_q, SLOT_W, 0, st>>>(P), ::lik::count_launch();
   LIK_CUDA_OK(cudaGetLastError());
   return LIK_OK;
 }

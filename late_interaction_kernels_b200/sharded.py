@@ -111,10 +111,11 @@ def retrieve_sharded(Q, D_local, top_k, q_mask=None, d_mask=None, *, doc_offset:
 
 def retrieve_plaid_sharded(Q, codes_local, residuals_local, cu_local, centroids, bucket_weights, nbits, top_k, *,
                            doc_offset: int, n_docs_total: int, normalize: bool = True, chunk: int = 4096,
-                           largest: bool = True, group=None):
+                           largest: bool = True, group=None, doc_lengths_host=None):
     """Sharded top-k over a PLAID index: every rank holds the codes / residuals / offsets of its own
     contiguous document range (``cu_local`` re-based to start at 0) and the replicated centroids and bucket
-    weights; local fused decompress + score + top-k, one all-gather, one merge."""
+    weights; local fused decompress + score + top-k, one all-gather, one merge.  ``doc_lengths_host`` (CPU int64
+    lengths of the local documents) saves the device->host copy of the offsets when the corpus is scored in pieces."""
     from .plaid import retrieve_residual_varlen
 
     q2 = Q.dim() == 2
@@ -125,7 +126,8 @@ def retrieve_plaid_sharded(Q, codes_local, residuals_local, cu_local, centroids,
     nd_local = cu_local.numel() - 1
     if nd_local > 0:
         s, i = retrieve_residual_varlen(Q, codes_local, residuals_local, cu_local, centroids, bucket_weights, nbits,
-                                        min(k, nd_local), normalize=normalize, chunk=chunk, largest=largest)
+                                        min(k, nd_local), normalize=normalize, chunk=chunk, largest=largest,
+                                        doc_lengths_host=doc_lengths_host)
         i = i + doc_offset
     else:
         s = torch.empty((Q.shape[0], 0), dtype=torch.float32, device=Q.device)

@@ -149,7 +149,14 @@ def test_plaid_padded_training_path_in_kernel(monkeypatch):
     assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
     want = O.maxsim_residual(f32(dev(Q, torch.bfloat16)), codes, res, lens, cent, bw, nbits)
     assert O.rel_err(f32(outs[0][0]), want) < 3e-2
-    wq = O.residual_grad_q(f32(g), f32(dev(Q, torch.bfloat16)), codes, res, lens, cent, bw, nbits)
+    # The gradient of a max jumps when a near-tie flips, and the operands here are rounded to bf16 while the oracle
+    # decodes in fp32: so the winners are taken from the kernel (the scores above pin them within tolerance) and the
+    # oracle supplies the gradient arithmetic for those winners, including the query-side normalise Jacobian.
+    Qb = dev(Q, torch.bfloat16)
+    _, am, _ = plaid._maxsim_residual_forward(Qb, *args, True, True)
+    emb = O.plaid_decompress(codes, res, cent, bw, nbits, normalize=True)
+    g_hat, _ = O.backward_from_argmax(f32(g), O.l2_normalize(f32(Qb)), emb, am.cpu().numpy())
+    wq = O.normalize_jacobian(g_hat, f32(Qb))
     assert O.rel_err(f32(outs[0][1]), wq) < 3e-2
 
 
