@@ -51,7 +51,8 @@ enum lik_dev_status {
   LIK_DEV_ARGMAX_STRIDE = 2,/* a query has more tokens than argmax_stride */
   LIK_DEV_WAIT_TIMEOUT = 4, /* a bounded mbarrier wait expired inside the tensor-core kernel */
   LIK_DEV_CODE_RANGE = 8,   /* PLAID centroid code outside [0, n_centroids) (read as centroid 0) */
-  LIK_DEV_LEN_RANGE = 16    /* a length exceeds the padded extent (clamped) */
+  LIK_DEV_LEN_RANGE = 16,   /* a length exceeds the padded extent (clamped) */
+  LIK_DEV_INTERNAL = 32     /* a kernel's own consistency check failed (the access was skipped) */
 };
 
 enum lik_normalize { LIK_NORM_NONE = 0, LIK_NORM_Q = 1, LIK_NORM_D = 2, LIK_NORM_BOTH = 3, LIK_NORM_ROUNDED = 4 };
@@ -301,6 +302,12 @@ int lik_plaid_fwd(const lik_fwd_args* args, const lik_plaid_index* index, const 
 /* out[r] = 1 / max(||x_r||, eps) for every row; the fused-normalise kernels take these. */
 int lik_row_inv_norm(const void* data, int32_t dtype, int64_t n_rows, int32_t dim, int64_t row_stride, float eps,
                      float* out, lik_stream_t stream);
+/* Self-test of the bounded waits: every wait inside the tensor-core kernel (on a TMA stage, an accumulator, the unit
+ * ring) gives up after a cycle limit, raises LIK_DEV_WAIT_TIMEOUT, lets the CTA drain and return.  This launches one
+ * thread that runs that same wait on a barrier nothing arrives at, with limit_cycles (at most 2e8, a tenth of a
+ * second) as its limit.  result (device, int32[3]) = {what the wait returned (0 = gave up), the CTA's abort flag,
+ * cycles spent}.  Nothing faults, traps or hangs.  (No counterpart in the reference, whose length checks trap.) */
+int lik_selftest_wait_timeout(int64_t limit_cycles, int32_t* status, int32_t* result, lik_stream_t stream);
 const char* lik_last_error(void);
 /* kernels this library has launched in this process so far (all threads, all devices) */
 uint64_t lik_launch_count(void);

@@ -30,6 +30,7 @@ DEV_STATUS_TEXT = {
     4: "a bounded wait expired inside the tensor-core kernel",
     8: "a PLAID centroid code is outside [0, n_centroids)",
     16: "a sequence length exceeds the padded extent",
+    32: "an internal consistency check of a kernel failed",
 }
 
 _DTYPES = {torch.float32: LIK_F32, torch.float16: LIK_F16, torch.bfloat16: LIK_BF16}
@@ -116,6 +117,8 @@ def _declare(lib):
     lib.lik_plaid_fwd_workspace.restype = sz
     lib.lik_plaid_fwd.argtypes = [C.POINTER(FwdArgs), C.POINTER(PlaidIndex), C.POINTER(TopkSpec), vp]
     lib.lik_plaid_fwd.restype = i32
+    lib.lik_selftest_wait_timeout.argtypes = [i64, vp, vp, vp]
+    lib.lik_selftest_wait_timeout.restype = i32
     lib.lik_launch_count.argtypes = []
     lib.lik_launch_count.restype = C.c_uint64
     lib.lik_topk_rows.argtypes = [vp, i64, i64, i64, i32, i32, i64, i32, vp, vp, vp]
@@ -139,7 +142,7 @@ def _declare(lib):
 EXPORTED_SYMBOLS = (
     "lik_maxsim_fwd_workspace", "lik_maxsim_fwd", "lik_maxsim_fwd_static", "lik_maxsim_bwd_workspace", "lik_maxsim_bwd", "lik_topk_rows",
     "lik_maxsim_fwd_topk_supported", "lik_maxsim_fwd_topk_workspace", "lik_maxsim_fwd_topk",
-    "lik_plaid_fwd_supported", "lik_plaid_fwd_workspace", "lik_plaid_fwd", "lik_launch_count",
+    "lik_plaid_fwd_supported", "lik_plaid_fwd_workspace", "lik_plaid_fwd", "lik_launch_count", "lik_selftest_wait_timeout",
     "lik_topk_merge", "lik_plaid_decompress", "lik_plaid_approx", "lik_plaid_bwd_dq", "lik_row_inv_norm",
     "lik_last_error", "lik_version", "lik_device_supported",
 )

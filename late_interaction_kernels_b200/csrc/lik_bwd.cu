@@ -11,6 +11,7 @@
 #include <mutex>
 
 #include "lik_common.cuh"
+#include "lik_sort.cuh"
 
 namespace lik {
 
@@ -29,19 +30,66 @@ struct BwdParams {
   float* gq32;  // atomic path accumulators
   float* gd32;
   int* status;
+  // pair lists, deterministic path: the pairs grouped by query and by document (stable sorts of the pair index)
+  const int* perm_q;   // [n_pairs] pair indices ordered by query, ties in list order
+  const int* start_q;  // [n_q + 1] run of query i in perm_q
+  const int* perm_d;   // [n_pairs] pair indices ordered by document
+  const int* start_d;  // [n_d + 1]
 };
 
-// slots of query i are contiguous for CROSS and GROUPED pairing
-__device__ __forceinline__ void query_slots(const PairMap& pm, int i, long long& p0, int& count, int& j0) {
+// The scores of query i: `count` of them, numbered p0 .. p0 + count - 1 (CROSS, GROUPED: score slots; LIST:
+// positions in perm_q).
+__device__ __forceinline__ void query_slots(const BwdParams& P, int i, long long& p0, int& count, int& j0) {
+  const PairMap& pm = P.pm;
   if (pm.pairing == LIK_PAIR_CROSS) {
     p0 = (long long)i * pm.n_d;
     count = pm.n_d;
     j0 = 0;
-  } else {
+  } else if (pm.pairing == LIK_PAIR_GROUPED) {
     p0 = (long long)i * pm.group;
     count = pm.group;
     j0 = i * pm.group;
+  } else {
+    p0 = P.start_q[i];
+    count = P.start_q[i + 1] - (int)p0;
+    j0 = 0;
   }
+}
+// score slot and document of the jj-th score of a query
+__device__ __forceinline__ void nth_score(const BwdParams& P, long long p0, int j0, int jj, long long& slot, int& j) {
+  if (P.pm.pairing == LIK_PAIR_LIST) {
+    slot = P.perm_q[p0 + jj];
+    j = P.pm.pair_d[slot];
+  } else {
+    slot = p0 + jj;
+    j = j0 + jj;
+  }
+}
+// The scores of document j: n_qr of them; the ii-th one is score slot doc_slot(ii) of query doc_query(ii, slot).
+struct DocScores {
+  int n_qr, i_begin;
+  long long first;  // LIST: run of the document in perm_d
+};
+__device__ __forceinline__ DocScores doc_scores(const BwdParams& P, int j) {
+  DocScores d{0, 0, 0};
+  if (P.pm.pairing == LIK_PAIR_CROSS) {
+    d.n_qr = P.pm.n_q;
+  } else if (P.pm.pairing == LIK_PAIR_GROUPED) {
+    d.n_qr = 1;
+    d.i_begin = j / P.pm.group;
+  } else {
+    d.first = P.start_d[j];
+    d.n_qr = P.start_d[j + 1] - (int)d.first;
+  }
+  return d;
+}
+__device__ __forceinline__ long long doc_slot(const BwdParams& P, const DocScores& d, int j, int ii) {
+  if (P.pm.pairing == LIK_PAIR_CROSS) return (long long)(d.i_begin + ii) * P.pm.n_d + j;
+  if (P.pm.pairing == LIK_PAIR_GROUPED) return j;
+  return __ldg(P.perm_d + d.first + ii);
+}
+__device__ __forceinline__ int doc_query(const BwdParams& P, const DocScores& d, int ii, long long slot) {
+  return P.pm.pairing == LIK_PAIR_LIST ? __ldg(P.pm.pair_q + slot) : d.i_begin + ii;
 }
 
 template <typename G>
@@ -73,17 +121,20 @@ __global__ void __launch_bounds__(256) bwd_dq_kernel(BwdParams P) {
   if (active) {
     long long p0;
     int count, j0;
-    query_slots(P.pm, i, p0, count, j0);
+    query_slots(P, i, p0, count, j0);
     const T* __restrict__ Dg = (const T*)P.d.data;
     for (int jj = 0; jj < count; ++jj) {
-      const int t = P.argmax[(p0 + jj) * P.argmax_stride + s];
+      long long slot;
+      int j;
+      nth_score(P, p0, j0, jj, slot, j);
+      const int t = P.argmax[slot * P.argmax_stride + s];
       if (t < 0) continue;
       long long drow0;
       int dlen;
-      seq_bounds(P.d, j0 + jj, drow0, dlen, nullptr);
+      seq_bounds(P.d, j, drow0, dlen, nullptr);
       if (t >= dlen) continue;
       const long long drow = drow0 + t;
-      float f = P.g[p0 + jj] * row_factor(P.d, drow);
+      float f = P.g[slot] * row_factor(P.d, drow);
       const T* src = Dg + drow * P.d.row_stride;
 #pragma unroll
       for (int c = 0; c < CMAX; ++c) {
@@ -416,7 +467,7 @@ __global__ void __launch_bounds__(256) bwd_dq_fast_kernel(BwdParams P) {
     for (int e = 0; e < 4; ++e) acc[c][e] = 0.f;
   long long p0;
   int count, j0;
-  query_slots(P.pm, i, p0, count, j0);
+  query_slots(P, i, p0, count, j0);
   const int lq = P.argmax_stride;
   const long long pitch = P.d.row_stride;
   const T* __restrict__ Dlane = (const T*)P.d.data + lane * 4;
@@ -431,14 +482,17 @@ __global__ void __launch_bounds__(256) bwd_dq_fast_kernel(BwdParams P) {
       const int jj = tid >> 3, r = tid & 7;
       int2 e = make_int2(-1, 0);
       if (jb + jj < count && s0 + r < lq) {
-        const int t = P.argmax[(p0 + jb + jj) * lq + s0 + r];
+        long long slot;
+        int j;
+        nth_score(P, p0, j0, jb + jj, slot, j);
+        const int t = P.argmax[slot * lq + s0 + r];
         if (t >= 0) {
           long long r0;
           int dl;
-          seq_bounds(P.d, j0 + jb + jj, r0, dl, nullptr);
+          seq_bounds(P.d, j, r0, dl, nullptr);
           const long long drow = r0 + t;
           if (t < dl && drow < P.d.n_rows) {  // a saved winner outside its document contributes nothing
-            float f = P.g[p0 + jb + jj];
+            float f = P.g[slot];
             if (d_factor) f *= row_factor(P.d, drow);
             e = make_int2((int)drow, __float_as_int(f));
           }
@@ -623,7 +677,7 @@ __global__ void __launch_bounds__(256) bwd_dq16_kernel(BwdParams P) {
     for (int e = 0; e < N; ++e) acc[c][e] = 0.f;
   long long p0;
   int count, j0;
-  query_slots(P.pm, i, p0, count, j0);
+  query_slots(P, i, p0, count, j0);
   const int lq = P.argmax_stride;
   const long long pitch = P.d.row_stride;
   const T* __restrict__ Dlane = (const T*)P.d.data + hl * N;
@@ -639,14 +693,17 @@ __global__ void __launch_bounds__(256) bwd_dq16_kernel(BwdParams P) {
       const int jj = x >> 4, r = x & 15;
       int2 e = make_int2(-1, 0);
       if (jb + jj < count && s0 + r < lq) {
-        const int t = P.argmax[(p0 + jb + jj) * lq + s0 + r];
+        long long slot;
+        int j;
+        nth_score(P, p0, j0, jb + jj, slot, j);
+        const int t = P.argmax[slot * lq + s0 + r];
         if (t >= 0) {
           long long r0;
           int dl;
-          seq_bounds(P.d, j0 + jb + jj, r0, dl, nullptr);
+          seq_bounds(P.d, j, r0, dl, nullptr);
           const long long drow = r0 + t;
           if (t < dl && drow < P.d.n_rows) {  // a saved winner outside its document contributes nothing
-            float f = P.g[p0 + jb + jj];
+            float f = P.g[slot];
             if (d_factor) f *= row_factor(P.d, drow);
             e = make_int2((int)drow, __float_as_int(f));
           }
@@ -731,29 +788,21 @@ __global__ void __launch_bounds__(DDS_WARPS * 32) bwd_dd_sort_kernel(BwdParams P
     if (tid == 0 && P.status) atomicOr(P.status, LIK_DEV_LEN_RANGE);
     return;
   }
-  int i_begin, i_end;
-  if (P.pm.pairing == LIK_PAIR_CROSS) {
-    i_begin = 0;
-    i_end = P.pm.n_q;
-  } else {
-    i_begin = j / P.pm.group;
-    i_end = i_begin + 1;
-  }
+  const DocScores ds = doc_scores(P, j);
+  const bool list = P.pm.pairing == LIK_PAIR_LIST;
   const int lq = P.argmax_stride;
-  const int n_ent = (i_end - i_begin) * lq;
-  const long long base = (long long)j * n_ent;  // every document has the same number of entries
+  const int n_ent = ds.n_qr * lq;
+  const long long base = list ? ds.first * lq : (long long)j * n_ent;  // first entry of the document's slice of the list
   int* hist = dds_raw;                          // [DDS_WARPS][ld_pad]
   int* tok_off = hist + DDS_WARPS * ld_pad;     // [ld_pad + 1]
-  float* gcol = reinterpret_cast<float*>(tok_off + ld_pad + 1);  // [i_end - i_begin]
+  float* gcol = reinterpret_cast<float*>(tok_off + ld_pad + 1);  // [n_qr] (not for pair lists)
 
   for (int x = tid; x < DDS_WARPS * ld_pad; x += blockDim.x) hist[x] = 0;
-  for (int x = tid; x < i_end - i_begin; x += blockDim.x) {
-    const long long p = P.pm.pairing == LIK_PAIR_CROSS ? (long long)(i_begin + x) * P.pm.n_d + j : (long long)j;
-    gcol[x] = P.g[p];
-  }
+  if (!list)
+    for (int x = tid; x < ds.n_qr; x += blockDim.x) gcol[x] = P.g[doc_slot(P, ds, j, x)];
   __syncthreads();
 
-  // entry e = (i - i_begin) * lq + s ; slice of this warp (multiple of 32 so rounds stay aligned)
+  // entry e = ii * lq + s ; slice of this warp (multiple of 32 so rounds stay aligned)
   const int per_warp = ((n_ent + DDS_WARPS - 1) / DDS_WARPS + 31) & ~31;
   const int e_lo = warp * per_warp, e_hi = min(n_ent, e_lo + per_warp);
 
@@ -761,18 +810,19 @@ __global__ void __launch_bounds__(DDS_WARPS * 32) bwd_dd_sort_kernel(BwdParams P
   auto raw_winner = [&](int e) -> int {
     if (e >= e_hi) return -1;
     const int ii = e / lq, s = e - ii * lq;
-    const long long p = P.pm.pairing == LIK_PAIR_CROSS ? (long long)(i_begin + ii) * P.pm.n_d + j : (long long)j;
-    return __ldg(P.argmax + p * lq + s);
+    return __ldg(P.argmax + doc_slot(P, ds, j, ii) * lq + s);
   };
   // validate a raw winner: -1 when the entry contributes nothing
-  auto checked = [&](int e, int t, int& qrow_out) -> int {
+  auto checked = [&](int e, int t, int& qrow_out, float& g_out) -> int {
     if (t < 0 || t >= dlen) return -1;
     const int ii = e / lq, s = e - ii * lq;
+    const long long slot = doc_slot(P, ds, j, ii);
     long long qrow0;
     int qlen;
-    seq_bounds(P.q, i_begin + ii, qrow0, qlen, nullptr);
+    seq_bounds(P.q, doc_query(P, ds, ii, slot), qrow0, qlen, nullptr);
     if (s >= qlen || !row_valid(P.q, qrow0 + s)) return -1;
     qrow_out = (int)(qrow0 + s);
+    g_out = list ? P.g[slot] : gcol[ii];
     return t;
   };
 
@@ -783,7 +833,8 @@ __global__ void __launch_bounds__(DDS_WARPS * 32) bwd_dd_sort_kernel(BwdParams P
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
       int qr;
-      const int t = checked(e + 32 * u, t4[u], qr);
+      float gg;
+      const int t = checked(e + 32 * u, t4[u], qr, gg);
       if (t >= 0) atomicAdd(&hist[warp * ld_pad + t], 1);
     }
   }
@@ -822,15 +873,15 @@ __global__ void __launch_bounds__(DDS_WARPS * 32) bwd_dd_sort_kernel(BwdParams P
   for (int eb = e_lo; eb < e_hi; eb += 32) {
     const int e = eb + lane;
     int qrow = 0;
+    float gg = 0.f;
     const int t_raw = t_next;
     t_next = raw_winner(e + 32);  // in flight while this round is placed
-    const int t = e < e_hi ? checked(e, t_raw, qrow) : -1;
+    const int t = e < e_hi ? checked(e, t_raw, qrow, gg) : -1;
     const unsigned peers = __match_any_sync(0xffffffffu, t);
     if (t >= 0) {
       const int rank = __popc(peers & ((1u << lane) - 1u));
       const int pos = hist[warp * ld_pad + t] + rank;
-      const float w = gcol[e / lq] * row_factor(P.q, qrow);
-      O.pairs[base + pos] = make_int2(qrow, __float_as_int(w));
+      O.pairs[base + pos] = make_int2(qrow, __float_as_int(gg * row_factor(P.q, qrow)));
     }
     __syncwarp();
     if (t >= 0 && (peers & ((1u << lane) - 1u)) == 0) hist[warp * ld_pad + t] += __popc(peers);
@@ -932,28 +983,20 @@ __global__ void __launch_bounds__(DDS_WARPS * 32) bwd_dd_sort4_kernel(BwdParams 
     if (tid == 0 && P.status) atomicOr(P.status, LIK_DEV_LEN_RANGE);
     return;
   }
-  int i_begin, i_end;
-  if (P.pm.pairing == LIK_PAIR_CROSS) {
-    i_begin = 0;
-    i_end = P.pm.n_q;
-  } else {
-    i_begin = j / P.pm.group;
-    i_end = i_begin + 1;
-  }
+  const DocScores ds = doc_scores(P, j);
+  const bool list = P.pm.pairing == LIK_PAIR_LIST;
   const int lq = P.argmax_stride;          // multiple of 4
-  const int qpr = lq >> 2;                 // 16-byte groups per (query, document) slot
-  const int n_quad = (i_end - i_begin) * qpr;
+  const int qpr = lq >> 2;                 // 16-byte groups per score slot
+  const int n_quad = ds.n_qr * qpr;
   const int n_ent = n_quad * 4;
-  const long long base = (long long)j * n_ent;
+  const long long base = list ? ds.first * lq : (long long)j * n_ent;
   int* hist = dds_raw;                          // [DDS_WARPS][ld_pad]
   int* tok_off = hist + DDS_WARPS * ld_pad;     // [ld_pad + 1] (kept for the layout shared with the scalar kernel)
-  float* gcol = reinterpret_cast<float*>(tok_off + ld_pad + 1);  // [i_end - i_begin]
+  float* gcol = reinterpret_cast<float*>(tok_off + ld_pad + 1);  // [n_qr] (not for pair lists)
 
   for (int x = tid; x < DDS_WARPS * ld_pad; x += blockDim.x) hist[x] = 0;
-  for (int x = tid; x < i_end - i_begin; x += blockDim.x) {
-    const long long p = P.pm.pairing == LIK_PAIR_CROSS ? (long long)(i_begin + x) * P.pm.n_d + j : (long long)j;
-    gcol[x] = P.g[p];
-  }
+  if (!list)
+    for (int x = tid; x < ds.n_qr; x += blockDim.x) gcol[x] = P.g[doc_slot(P, ds, j, x)];
   __syncthreads();
 
   // slice of this warp in 16-byte groups, a multiple of 32 * DDS_LOADS so that rounds stay whole
@@ -965,16 +1008,13 @@ __global__ void __launch_bounds__(DDS_WARPS * 32) bwd_dd_sort4_kernel(BwdParams 
   auto load_quad = [&](int m) -> int4 {
     if (m >= m_hi) return none;
     const int ii = m / qpr, sq = m - ii * qpr;
-    const long long p = P.pm.pairing == LIK_PAIR_CROSS ? (long long)(i_begin + ii) * P.pm.n_d + j : (long long)j;
-    return __ldg(reinterpret_cast<const int4*>(P.argmax + p * lq) + sq);
+    return __ldg(reinterpret_cast<const int4*>(P.argmax + doc_slot(P, ds, j, ii) * lq) + sq);
   };
-  // query row of entry (ii, s) or -1 when that query token takes no part
-  auto query_row = [&](int ii, int s) -> int {
-    long long qrow0;
-    int qlen;
-    seq_bounds(P.q, i_begin + ii, qrow0, qlen, nullptr);
-    if (s >= qlen || !row_valid(P.q, qrow0 + s)) return -1;
-    return (int)(qrow0 + s);
+  // first query row and length of the query of score ii (and its upstream gradient)
+  auto query_of = [&](int ii, long long& qrow0, int& qlen, float& gg) {
+    const long long slot = doc_slot(P, ds, j, ii);
+    seq_bounds(P.q, doc_query(P, ds, ii, slot), qrow0, qlen, nullptr);
+    gg = list ? P.g[slot] : gcol[ii];
   };
 
   // ---- pass 1: per-warp histogram of the winners per token ----
@@ -987,17 +1027,20 @@ __global__ void __launch_bounds__(DDS_WARPS * 32) bwd_dd_sort4_kernel(BwdParams 
       const int m = mb + u * 32 + lane;
       if (m >= m_hi) continue;
       const int ii = m / qpr, s4 = (m - ii * qpr) * 4;
+      long long qrow0;
+      int qlen;
+      float gg;
+      query_of(ii, qrow0, qlen, gg);
       const int t4[4] = {w[u].x, w[u].y, w[u].z, w[u].w};
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
         const int t = t4[k];
-        if (t >= 0 && t < dlen && query_row(ii, s4 + k) >= 0) atomicAdd(&hist[warp * ld_pad + t], 1);
+        if (t >= 0 && t < dlen && s4 + k < qlen && row_valid(P.q, qrow0 + s4 + k)) atomicAdd(&hist[warp * ld_pad + t], 1);
       }
     }
   }
   __syncthreads();
-  // ---- offsets: warp w takes tokens w*32 .. in steps of DDS_WARPS*32; a running total per 32 tokens is
-  // needed first, so warp 0 scans the per-token totals and the other warps wait ----
+  // ---- offsets: warp 0 scans the per-token totals ----
   if (warp == 0) {
     int running = 0;
     for (int tb = 0; tb < dlen; tb += 32) {
@@ -1036,14 +1079,16 @@ __global__ void __launch_bounds__(DDS_WARPS * 32) bwd_dd_sort4_kernel(BwdParams 
       const int m = mb + u * 32 + lane;
       const bool in = m < m_hi;
       const int ii = in ? m / qpr : 0, s4 = in ? (m - ii * qpr) * 4 : 0;
-      const float gi = in ? gcol[ii] : 0.f;
+      long long qrow0 = 0;
+      int qlen = 0;
+      float gi = 0.f;
+      if (in) query_of(ii, qrow0, qlen, gi);
       const int t4[4] = {w[u].x, w[u].y, w[u].z, w[u].w};
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
         int t = t4[k];
-        int qrow = -1;
-        if (in && t >= 0 && t < dlen) qrow = query_row(ii, s4 + k);
-        if (qrow < 0) t = -1;
+        const int qrow = (int)(qrow0 + s4 + k);
+        if (!(in && t >= 0 && t < dlen && s4 + k < qlen && row_valid(P.q, qrow))) t = -1;
         const unsigned peers = __match_any_sync(0xffffffffu, t);
         if (t >= 0) {
           const int rank = __popc(peers & ((1u << lane) - 1u));
@@ -1197,11 +1242,30 @@ __global__ void __launch_bounds__(256) bwd_finalize_kernel(const float* __restri
 int launch_row_inv_norm(const void* data, int dtype, long long n_rows, int dim, long long stride, float eps, float* out,
                         cudaStream_t st);
 
+// Sort keys of a pair list: the query and the document of every pair (a pair with an index out of range gets the key
+// one past the last sequence on both sides, so it sorts behind every run and no gradient kernel visits it), and the
+// pair index as the value that travels with them.
+__global__ void pair_keys_kernel(const int* __restrict__ pair_q, const int* __restrict__ pair_d, long long n, int n_q, int n_d,
+                                 unsigned* __restrict__ kq, unsigned* __restrict__ kd, unsigned* __restrict__ vq,
+                                 unsigned* __restrict__ vd, int* status) {
+  const long long p = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (p >= n) return;
+  const int i = pair_q[p], j = pair_d[p];
+  const bool ok = i >= 0 && i < n_q && j >= 0 && j < n_d;
+  if (!ok && status) atomicOr(status, LIK_DEV_PAIR_RANGE);
+  kq[p] = ok ? (unsigned)i : (unsigned)n_q;
+  kd[p] = ok ? (unsigned)j : (unsigned)n_d;
+  vq[p] = (unsigned)p;
+  vd[p] = (unsigned)p;
+}
+
 namespace {
 
 struct BwdPlan {
   size_t qn_off, dn_off, gq32_off, gd32_off, pairs_off, begin_off, cnt_off, total;
+  size_t kq_off, kd_off, pq_off, pd_off, sq_off, sd_off, sort_off;  // pair lists grouped by query / by document
   bool fast, sorted;
+  bool list_sorted;  // pair list on the deterministic kernels
   bool row16;  // 16-byte gathers: rows 16-byte aligned, width a multiple of 16 bytes, at most 1024 bytes
   int ld_pad;
   size_t sort_smem;
@@ -1238,11 +1302,29 @@ BwdPlan plan_bwd(const lik_bwd_args& a) {
     pl.dn_off = take((size_t)a.d.n_rows * 4);
   }
   const bool list = a.pairing == LIK_PAIR_LIST;
-  if (a.grad_q && list) pl.gq32_off = take((size_t)a.q.n_rows * a.dim * 4);
-  if (a.grad_d && (list || !a.deterministic)) pl.gd32_off = take((size_t)a.d.n_rows * a.dim * 4);
-  if (a.grad_d && !list && a.deterministic && pl.fast && a.d.n_seq > 0 && a.d.max_len > 0 && a.d.n_rows < (1ll << 31) &&
+  pl.kq_off = pl.kd_off = pl.pq_off = pl.pd_off = pl.sq_off = pl.sd_off = pl.sort_off = (size_t)-1;
+  // a pair list goes through the same deterministic kernels once its pairs are grouped by query and by document
+  pl.list_sorted = list && a.deterministic && pl.fast && a.n_pairs > 0 && a.n_pairs < (1ll << 31) && a.d.max_len > 0 &&
+                   a.q.max_len > 0 && a.q.n_seq > 0 && a.d.n_seq > 0;
+  if (pl.list_sorted) {
+    const size_t ws_sort = ((size_t)DDS_WARPS * (a.d.max_len + 1) + a.d.max_len + 2) * 4;
+    if (ws_sort > 200 * 1024) pl.list_sorted = false;
+  }
+  if (pl.list_sorted) {
+    pl.kq_off = take((size_t)a.n_pairs * 4);
+    pl.kd_off = take((size_t)a.n_pairs * 4);
+    pl.pq_off = take((size_t)a.n_pairs * 4);
+    pl.pd_off = take((size_t)a.n_pairs * 4);
+    pl.sq_off = take((size_t)(a.q.n_seq + 1) * 4);
+    pl.sd_off = take((size_t)(a.d.n_seq + 1) * 4);
+    pl.sort_off = take(sort_pairs_scratch(a.n_pairs));
+  }
+  const bool scatter = list && !pl.list_sorted;
+  if (a.grad_q && scatter) pl.gq32_off = take((size_t)a.q.n_rows * a.dim * 4);
+  if (a.grad_d && (scatter || !a.deterministic)) pl.gd32_off = take((size_t)a.d.n_rows * a.dim * 4);
+  if (a.grad_d && !scatter && a.deterministic && pl.fast && a.d.n_seq > 0 && a.d.max_len > 0 && a.d.n_rows < (1ll << 31) &&
       a.q.n_rows < (1ll << 31)) {
-    const long long n_qrange = a.pairing == LIK_PAIR_CROSS ? a.q.n_seq : 1;
+    const long long n_qrange = a.pairing == LIK_PAIR_CROSS ? a.q.n_seq : (list ? 0 : 1);
     pl.ld_pad = a.d.max_len + 1;
     pl.sort_smem = ((size_t)DDS_WARPS * pl.ld_pad + pl.ld_pad + 1 + (size_t)n_qrange) * 4;
     if (pl.sort_smem <= 200 * 1024) {
@@ -1285,7 +1367,29 @@ ForkJoin* fork_join_locked() {
 
 template <typename T, typename G>
 int run_bwd(const lik_bwd_args& a, BwdParams& P, const BwdPlan& pl, cudaStream_t st_main) {
-  const bool list = a.pairing == LIK_PAIR_LIST;
+  const bool list = a.pairing == LIK_PAIR_LIST && !pl.list_sorted;  // pair list on the atomic path
+  if (pl.list_sorted) {
+    // group the pairs by query and by document: two stable sorts of the pair index
+    char* w = (char*)a.workspace;
+    unsigned *kq = (unsigned*)(w + pl.kq_off), *kd = (unsigned*)(w + pl.kd_off);
+    unsigned *pq = (unsigned*)(w + pl.pq_off), *pd = (unsigned*)(w + pl.pd_off);
+    pair_keys_kernel<<<(unsigned)ceil_div(a.n_pairs, 256), 256, 0, st_main>>>(a.pair_q, a.pair_d, a.n_pairs, a.q.n_seq, a.d.n_seq, kq, kd,
+                                                                            pq, pd, a.status), ::lik::count_launch();
+    LIK_CUDA_OK(cudaGetLastError());
+    auto bits = [](int n) { int b = 1; while ((1ll << b) <= n) ++b; return b; };
+    int rc = stable_sort_pairs(kq, pq, a.n_pairs, bits(a.q.n_seq), w + pl.sort_off, st_main);
+    if (rc) return rc;
+    rc = stable_sort_pairs(kd, pd, a.n_pairs, bits(a.d.n_seq), w + pl.sort_off, st_main);
+    if (rc) return rc;
+    rc = run_starts(kq, a.n_pairs, a.q.n_seq, (int*)(w + pl.sq_off), st_main);
+    if (rc) return rc;
+    rc = run_starts(kd, a.n_pairs, a.d.n_seq, (int*)(w + pl.sd_off), st_main);
+    if (rc) return rc;
+    P.perm_q = (const int*)pq;
+    P.perm_d = (const int*)pd;
+    P.start_q = (const int*)(w + pl.sq_off);
+    P.start_d = (const int*)(w + pl.sd_off);
+  }
   // fork only when both gradients run the gather kernels and the problem is large enough to matter
   const bool want_fork = a.grad_q && a.grad_d && !list && a.deterministic && pl.fast && pl.sorted &&
                          P.pm.n_scores * (long long)a.argmax_stride >= (1ll << 20);
@@ -1476,6 +1580,7 @@ extern "C" int lik_maxsim_bwd(const lik_bwd_args* a, lik_stream_t stream) {
   P.grad_d = a->grad_d;
   P.gq32 = P.gd32 = nullptr;
   P.status = a->status;
+  P.perm_q = P.start_q = P.perm_d = P.start_d = nullptr;
   switch (a->dtype) {
     case LIK_F32:
       return run_bwd_g<float>(*a, P, pl, st);

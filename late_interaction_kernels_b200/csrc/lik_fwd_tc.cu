@@ -44,7 +44,7 @@ constexpr int MAX_SLABS = 2;
 constexpr int NUM_THREADS = 640;
 constexpr int EPI_THREADS = 128;     // threads per half of an epilogue group (one per accumulator row)
 constexpr int GROUP_WARPS = 8;
-constexpr long long WAIT_LIMIT_CYCLES = 4000000000ll;  // about 2 s per wait at 2 GHz
+constexpr long long WAIT_LIMIT_CYCLES = 4000000000ll;  // default limit of a wait: about 2 s at 2 GHz
 constexpr int LEN_FLAG_MASKED = 1 << 30;
 constexpr uint32_t TRY_WAIT_HINT_NS = 20000;  // how long one try_wait may keep the thread suspended
 constexpr int UNIT_RING = 8;                  // slots of the producer -> epilogue unit ring
@@ -280,6 +280,7 @@ struct TopkOut {
   int qpg;          // lists per slot: two query tiles' worth
   int largest;
   int doc_base;     // added to the document index stored with a candidate
+  int n_lists;      // lists allocated (the kernel checks every list number against it)
 };
 
 // One row of the pair-list table (LIK_PAIR_LIST): written by list_units_kernel, read by the producer.
@@ -329,6 +330,7 @@ struct SharedCtl {
   int grp_done[2];              // set by a group's first warp when the stream has ended
   uint32_t tmem_base;
   volatile int abort_flag;
+  long long wait_limit;         // cycles after which a wait gives up
   int seg_off[2][TILE_M], seg_len[2][TILE_M], seg_q[2][TILE_M];
   short row_seg[2][TILE_M];
   int n_seg[2];
@@ -353,7 +355,7 @@ __device__ __noinline__ bool wait_bar_slow(uint32_t b, uint32_t parity, SharedCt
   while (true) {
     if (mbar_try_wait(b, parity)) return true;
     if (ctl->abort_flag) return false;
-    if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
+    if (clock64() - t0 > ctl->wait_limit) {
       ctl->abort_flag = 1;
       if (status) atomicOr(status, LIK_DEV_WAIT_TIMEOUT);
       return false;
@@ -373,7 +375,7 @@ __device__ __noinline__ int wait_posted_slow(SharedCtl* ctl, int uc, int* status
     if (ctl->units_posted > uc) return 1;
     if (ctl->units_total <= uc) return 2;
     if (ctl->abort_flag) return 0;
-    if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
+    if (clock64() - t0 > ctl->wait_limit) {
       ctl->abort_flag = 1;
       if (status) atomicOr(status, LIK_DEV_WAIT_TIMEOUT);
       return 0;
@@ -637,6 +639,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
       ctl->grp_done[a] = 0;
     }
     ctl->abort_flag = 0;
+    ctl->wait_limit = WAIT_LIMIT_CYCLES;
     ctl->units_posted = 0;
     ctl->units_total = 0x7fffffff;
     fence_barrier_init();
@@ -959,6 +962,10 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
       const unsigned ukey_ = ordered_key(key_);                                                        \
       if (ukey_ > ctl->seg_thr[wg][sg_]) {                                                             \
         int cnt_ = ctl->seg_cnt[wg][sg_];                                                              \
+        if ((unsigned)cnt_ >= (unsigned)TOPK_CAP || (unsigned)ctl->seg_list[wg][sg_] >= (unsigned)P.topk.n_lists) {  \
+          if (lane == 0 && P.status) atomicOr(P.status, LIK_DEV_INTERNAL);                             \
+          break;                                                                                       \
+        }                                                                                              \
         float* keys_ = P.topk.cand_key + (long long)ctl->seg_list[wg][sg_] * TOPK_CAP;                 \
         int* idx_ = P.topk.cand_idx + (long long)ctl->seg_list[wg][sg_] * TOPK_CAP;                    \
         if (lane == 0) {                                                                               \
@@ -1002,6 +1009,10 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
       const int4 uinfo = ctl->unit_info[uc & (UNIT_RING - 1)];
       const int grp = uinfo.z;
       const int doc = uinfo.w;
+      if ((unsigned)grp >= (unsigned)(list ? P.n_q : n_groups)) {  // cannot happen; never index with it if it does
+        if (lane == 0 && P.status) atomicOr(P.status, LIK_DEV_INTERNAL);
+        break;
+      }
       if (grp != cur_grp) {
         cur_grp = grp;
         // (re)build the segment table of this group's tile `wg` (mt == 2) or tile 0 (mt == 1: both groups)
@@ -1052,6 +1063,10 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
             // the candidate list of (this CTA, this group, this query)
             // (with one resident tile the two epilogue groups take alternate documents: a list each)
             my_list = ((int)blockIdx.x + grp) * P.topk.qpg + (P.mt == 2 ? m : wg) * P.q_per_tile + et;
+            if ((unsigned)my_list >= (unsigned)P.topk.n_lists) {
+              if (P.status) atomicOr(P.status, LIK_DEV_INTERNAL);
+              my_list = 0;
+            }
             const int2 hd = P.topk.hdr[my_list];
             ctl->seg_list[wg][et] = my_list;
             ctl->seg_cnt[wg][et] = hd.x;
@@ -1243,6 +1258,29 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// The bounded wait of the kernel above, alone: one thread waits on a barrier that nothing ever arrives at, with a
+// limit the caller chooses.  It must give up after that many cycles, raise LIK_DEV_WAIT_TIMEOUT in the status word,
+// set the abort flag and return - the path every role of the scoring kernel takes when a hand-shake never comes.
+// result[0] = what the wait returned (0 = gave up), result[1] = the abort flag, result[2] = cycles spent.
+__global__ void wait_probe_kernel(long long limit, int* status, int* result) {
+  __shared__ SharedCtl ctl;
+  if (threadIdx.x == 0) {
+    mbar_init(smem_u32(&ctl.q_full), 1);
+    ctl.abort_flag = 0;
+    ctl.wait_limit = limit;
+    fence_barrier_init();
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const long long t0 = clock64();
+    const bool got = wait_bar(&ctl.q_full, 0, &ctl, status);
+    const long long dt = clock64() - t0;
+    result[0] = got ? 1 : 0;
+    result[1] = ctl.abort_flag;
+    result[2] = dt > 0x7fffffffll ? 0x7fffffff : (int)dt;
   }
 }
 
@@ -1534,9 +1572,9 @@ TcWs tc_ws_layout(const TcPlan& pl, const lik_fwd_args& a, const TcExtra& x) {
 
 size_t fwd_tc_workspace(const lik_fwd_args& a, const TcExtra& x) { return tc_ws_layout(plan_tc(a, x), a, x).total; }
 
-int launch_topk_slots(const float* keys, const int* idx, const int2* hdr, int cap, int n_ctas, int n_groups, int mt, int qpt,
-                      long long n_q, int k, int largest, long long index_offset, float* out_scores, long long* out_index,
-                      cudaStream_t st);
+int launch_topk_slots(const float* keys, const int* idx, const int2* hdr, long long n_lists, int cap, int n_ctas, int n_groups,
+                      int mt, int qpt, long long n_q, int k, int largest, long long index_offset, float* out_scores,
+                      long long* out_index, cudaStream_t st);
 
 int launch_fwd_tc(const lik_fwd_args& a, const float* qn, const float* dn, void* ws, size_t ws_bytes, cudaStream_t st,
                   const TcExtra& x) {
@@ -1624,6 +1662,7 @@ int launch_fwd_tc(const lik_fwd_args& a, const float* qn, const float* dn, void*
     P.topk.qpg = 2 * pl.q_per_tile;
     P.topk.largest = x.topk_largest;
     P.topk.doc_base = x.topk_doc_base;
+    P.topk.n_lists = (int)w.n_lists;
     if (!(x.topk_flags & LIK_TOPK_CONTINUE))
       LIK_CUDA_OK(cudaMemsetAsync(P.topk.hdr, 0, (size_t)w.n_lists * sizeof(int2), st));  // empty lists, no threshold
   }
@@ -1663,7 +1702,7 @@ int launch_fwd_tc(const lik_fwd_args& a, const float* qn, const float* dn, void*
     LIK_CUDA_OK(cudaGetLastError());
   }
   if (x.topk_k > 0 && !(x.topk_flags & LIK_TOPK_PARTIAL)) {
-    rc = launch_topk_slots(P.topk.cand_key, P.topk.cand_idx, P.topk.hdr, TOPK_CAP, pl.grid, pl.n_groups, pl.mt, pl.q_per_tile,
+    rc = launch_topk_slots(P.topk.cand_key, P.topk.cand_idx, P.topk.hdr, w.n_lists, TOPK_CAP, pl.grid, pl.n_groups, pl.mt, pl.q_per_tile,
                            a.q.n_seq, x.topk_k, x.topk_largest, x.topk_index_offset, x.topk_scores, (long long*)x.topk_index, st);
     if (rc) return rc;
   }
@@ -1671,3 +1710,12 @@ int launch_fwd_tc(const lik_fwd_args& a, const float* qn, const float* dn, void*
 }
 
 }  // namespace lik
+
+extern "C" int lik_selftest_wait_timeout(int64_t limit_cycles, int32_t* status, int32_t* result, lik_stream_t stream) {
+  using namespace lik;
+  LIK_REQUIRE(result != nullptr, "result is NULL");
+  LIK_REQUIRE(limit_cycles > 0 && limit_cycles <= 200000000ll, "limit_cycles outside (0, 2e8]");
+  wait_probe_kernel<<<1, 32, 0, (cudaStream_t)stream>>>((long long)limit_cycles, status, result), ::lik::count_launch();
+  LIK_CUDA_OK(cudaGetLastError());
+  return LIK_OK;
+}

@@ -170,7 +170,7 @@ struct SlotParams {
   const int* idx;
   const int2* hdr;
   int cap, n_ctas, n_groups, mt, qpt;
-  long long n_q, index_offset;
+  long long n_q, index_offset, n_lists;
   int k, KP, largest;
   float* out_scores;
   long long* out_index;
@@ -216,12 +216,13 @@ __global__ void __launch_bounds__(SLOT_W) topk_slots_kernel(SlotParams P) {
     if (g < g_lo || g > g_hi) continue;
     for (int sub = 0; sub < n_sub; ++sub) {
       const long long list = (long long)(c + g) * (2 * P.qpt) + (P.mt == 2 ? m : sub) * P.qpt + et;
+      if (list >= P.n_lists) continue;
       int cnt = P.hdr[list].x;
       if (cnt > P.cap) cnt = P.cap;
       if (cnt <= 0) continue;
       int n_pend = n_pend_s;
+      __syncthreads();  // every thread has read the count before this list's survivors are added to it
       if (n_pend + cnt > SLOT_W) {  // the pending block could overflow: absorb it first
-        __syncthreads();
         slots_flush(top_k, top_i, blk_k, blk_i, n_pend, tid);
         if (tid == 0) n_pend_s = 0;
         __syncthreads();
@@ -256,15 +257,15 @@ __global__ void __launch_bounds__(SLOT_W) topk_slots_kernel(SlotParams P) {
   }
 }
 
-int launch_topk_slots(const float* keys, const int* idx, const int2* hdr, int cap, int n_ctas, int n_groups, int mt, int qpt,
-                      long long n_q, int k, int largest, long long index_offset, float* out_scores, long long* out_index,
-                      cudaStream_t st) {
+int launch_topk_slots(const float* keys, const int* idx, const int2* hdr, long long n_lists, int cap, int n_ctas, int n_groups,
+                      int mt, int qpt, long long n_q, int k, int largest, long long index_offset, float* out_scores,
+                      long long* out_index, cudaStream_t st) {
   if (n_q <= 0 || k <= 0) return LIK_OK;
   if (cap > SLOT_W || k > SLOT_W) {
     set_error("candidate lists of %d entries / k = %d exceed the merge width %d", cap, k, SLOT_W);
     return LIK_ERR_UNSUPPORTED;
   }
-  SlotParams P{keys, idx, hdr, cap, n_ctas, n_groups, mt, qpt, n_q, index_offset, k, 2, largest, out_scores, out_index};
+  SlotParams P{keys, idx, hdr, cap, n_ctas, n_groups, mt, qpt, n_q, index_offset, n_lists, k, 2, largest, out_scores, out_index};
   topk_slots_kernel<<<(unsigned)n_q, SLOT_W, 0, st>>>(P), ::lik::count_launch();
   LIK_CUDA_OK(cudaGetLastError());
   return LIK_OK;

@@ -1,5 +1,10 @@
 """Arbitrary ``(query, document)`` pair lists on packed batches: ``score_pairs_packed``
-(reference: score_pairs.py:281-511)."""
+(reference: score_pairs.py:281-511).
+
+The forward runs on the tensor-core kernel (one pair per work unit; consecutive pairs of the same query share the
+resident query tile).  The backward groups the pairs by query and by document with two stable device sorts and then
+uses the same destination-owned kernels as the other layouts, so the gradients are bitwise reproducible (the
+reference scatters both with fp32 atomics, score_pairs.py:148-273)."""
 
 from __future__ import annotations
 
@@ -40,7 +45,7 @@ class _MaxSimScorePairsFn(torch.autograd.Function):
         q = _ops.packed_spec(Q.to(dt), cu_q, ctx.max_q)
         d = _ops.packed_spec(D.to(dt), cu_d, ctx.max_d)
         gq, gd = _ops.backward(
-            q, d, grad_out, argmax, pairing=_lib.PAIR_LIST, pair_q=pair_q, pair_d=pair_d, deterministic=False,
+            q, d, grad_out, argmax, pairing=_lib.PAIR_LIST, pair_q=pair_q, pair_d=pair_d, deterministic=True,
             grad_dtype=dt, need_q=ctx.needs_input_grad[0], need_d=ctx.needs_input_grad[1],
         )
         gq = None if gq is None else gq.to(Q.dtype)

@@ -264,3 +264,26 @@ def test_backward_with_forked_stream_is_graph_capturable():
     gr.replay()
     torch.cuda.synchronize()
     assert torch.equal(gq, eq) and torch.equal(gd, ed)
+
+
+def test_a_bounded_wait_that_runs_out_reports_and_returns():
+    """Failure detection without a fault: the wait the tensor-core kernel's roles use, on a barrier nothing arrives
+    at, must give up after its cycle limit, raise the time-out bit in the status word and let the kernel return."""
+    import late_interaction_kernels_b200 as lik
+    from late_interaction_kernels_b200 import _lib, _ops
+
+    lib = _lib.load()
+    status = _ops.status_word("cuda")
+    lik.check_device_status()
+    res = torch.full((3,), -1, dtype=torch.int32, device="cuda")
+    limit = 2_000_000  # about a millisecond
+    _lib.check(lib.lik_selftest_wait_timeout(limit, status.data_ptr(), res.data_ptr(), _lib.stream_ptr(res.device)), "selftest")
+    torch.cuda.synchronize()
+    got, aborted, cycles = res.tolist()
+    assert got == 0 and aborted == 1
+    assert limit <= cycles < 50 * limit
+    with pytest.raises(RuntimeError, match="bounded wait expired"):
+        lik.check_device_status()
+    lik.check_device_status()  # the word was reset; the context is healthy
+    assert float(lik.maxsim(torch.ones(1, 2, 16, device="cuda").bfloat16(), torch.ones(1, 3, 16, device="cuda").bfloat16())) == 32.0
+    assert lib.lik_selftest_wait_timeout(10**10, None, res.data_ptr(), None) == -1

@@ -215,6 +215,20 @@ def test_pair_list_on_tensor_cores():
     (score_pairs_packed(Qt, Dt, dev(cu_q), dev(cu_d), dev(pq), dev(pd)) * dev(g)).sum().backward()
     wq, wd = O.pair_list_grads(g, f32(Qb), f32(Db), cu_q, cu_d, pq, pd)
     assert O.rel_err(f32(Qt.grad), wq) < 2e-2 and O.rel_err(f32(Dt.grad), wd) < 2e-2
+    # the backward is destination-owned for pair lists too: the same bits every time, and nothing from atomics
+    from late_interaction_kernels_b200 import _lib as L_
+
+    n0 = L_.load().lik_launch_count()
+    for _ in range(3):
+        Q2, D2 = Qb.clone().requires_grad_(), Db.clone().requires_grad_()
+        (score_pairs_packed(Q2, D2, dev(cu_q), dev(cu_d), dev(pq), dev(pd)) * dev(g)).sum().backward()
+        assert torch.equal(Q2.grad, Qt.grad) and torch.equal(D2.grad, Dt.grad)
+    assert L_.load().lik_launch_count() > n0
+    # fp32 inputs (the exact FMA forward) go through the same grouped backward
+    Qf, Df = dev(Q).requires_grad_(), dev(D).requires_grad_()
+    (score_pairs_packed(Qf, Df, dev(cu_q), dev(cu_d), dev(pq), dev(pd)) * dev(g)).sum().backward()
+    wq32, wd32 = O.pair_list_grads(g, Q, D, cu_q, cu_d, pq, pd)
+    assert O.rel_err(f32(Qf.grad), wq32) < 1e-5 and O.rel_err(f32(Df.grad), wd32) < 1e-5
     # an index outside the batch scores 0 and is reported
     bad = pq.copy()
     bad[5] = 99
