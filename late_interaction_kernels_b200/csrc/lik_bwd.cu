@@ -654,7 +654,7 @@ __device__ __forceinline__ void store_row16(G* out, const float (&acc)[CH][Vec16
 constexpr int DQ16_TOK = 16;  // query tokens per CTA (one per half-warp)
 
 template <typename T, typename G, int CH>
-__global__ void __launch_bounds__(256) bwd_dq16_kernel(BwdParams P) {
+__global__ void __launch_bounds__(256, CH == 1 ? 8 : 1) bwd_dq16_kernel(BwdParams P) {
   constexpr int N = Vec16<T>::N;
   constexpr int U = 8 / CH;  // rows in flight per half-warp
   __shared__ int2 s_e[DQ_JC][DQ16_TOK];
@@ -790,6 +790,7 @@ __global__ void __launch_bounds__(DDS_WARPS * 32) bwd_dd_sort_kernel(BwdParams P
   }
   const DocScores ds = doc_scores(P, j);
   const bool list = P.pm.pairing == LIK_PAIR_LIST;
+  const int t_bits = 32 - __clz(ld_pad);  // winners are below ld_pad
   const int lq = P.argmax_stride;
   const int n_ent = ds.n_qr * lq;
   const long long base = list ? ds.first * lq : (long long)j * n_ent;  // first entry of the document's slice of the list
@@ -877,7 +878,7 @@ __global__ void __launch_bounds__(DDS_WARPS * 32) bwd_dd_sort_kernel(BwdParams P
     const int t_raw = t_next;
     t_next = raw_winner(e + 32);  // in flight while this round is placed
     const int t = e < e_hi ? checked(e, t_raw, qrow, gg) : -1;
-    const unsigned peers = __match_any_sync(0xffffffffu, t);
+    const unsigned peers = warp_peers(t, t_bits);
     if (t >= 0) {
       const int rank = __popc(peers & ((1u << lane) - 1u));
       const int pos = hist[warp * ld_pad + t] + rank;
@@ -985,6 +986,7 @@ __global__ void __launch_bounds__(DDS_WARPS * 32) bwd_dd_sort4_kernel(BwdParams 
   }
   const DocScores ds = doc_scores(P, j);
   const bool list = P.pm.pairing == LIK_PAIR_LIST;
+  const int t_bits = 32 - __clz(ld_pad);  // winners are below ld_pad
   const int lq = P.argmax_stride;          // multiple of 4
   const int qpr = lq >> 2;                 // 16-byte groups per score slot
   const int n_quad = ds.n_qr * qpr;
@@ -1089,7 +1091,7 @@ __global__ void __launch_bounds__(DDS_WARPS * 32) bwd_dd_sort4_kernel(BwdParams 
         int t = t4[k];
         const int qrow = (int)(qrow0 + s4 + k);
         if (!(in && t >= 0 && t < dlen && s4 + k < qlen && row_valid(P.q, qrow))) t = -1;
-        const unsigned peers = __match_any_sync(0xffffffffu, t);
+        const unsigned peers = warp_peers(t, t_bits);
         if (t >= 0) {
           const int rank = __popc(peers & ((1u << lane) - 1u));
           const int pos = hist[warp * ld_pad + t] + rank;

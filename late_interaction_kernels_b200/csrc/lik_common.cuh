@@ -199,6 +199,19 @@ inline long long n_scores_of(int pairing, int n_q, int n_d, long long n_pairs) {
   return n_pairs;
 }
 
+// Lanes of the warp whose value equals this lane's, for values in [0, 2^nbits); lanes with a negative value are in
+// nobody's set (their own result is meaningless).  One ballot per bit: the cost does not depend on how many
+// different values the warp holds, unlike match.any, which on this GPU slows down with every distinct value.
+__device__ __forceinline__ unsigned warp_peers(int v, int nbits) {
+  unsigned peers = __ballot_sync(0xffffffffu, v >= 0);
+  for (int b = 0; b < nbits; ++b) {
+    const bool bit = (v >> b) & 1;
+    const unsigned m = __ballot_sync(0xffffffffu, bit);
+    peers &= bit ? m : ~m;
+  }
+  return peers;
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

@@ -4,7 +4,7 @@
 // (2) exclusive scan of the histograms in (digit, block) order, which gives every block the first output
 // position of each digit, (3) scatter: inside a block every warp owns a contiguous slice, counts its digits,
 // the block turns the counts into per-(warp, digit) start positions (digit-major, then warp), and the warp
-// places its elements slice order, ranking equal digits of one 32-element round with match_any.  Every step
+// places its elements in slice order, ranking equal digits of one 32-element round with eight ballots.  Every step
 // keeps the input order of equal keys, so the sort is stable and its result does not depend on timing.
 #include "lik_sort.cuh"
 
@@ -92,8 +92,8 @@ __global__ void __launch_bounds__(RS_WARPS * 32) rs_scatter_kernel(const unsigne
     const bool in = e < n;
     const unsigned k = in ? keys_in[e] : 0u;
     const unsigned v = in ? vals_in[e] : 0u;
-    const unsigned d = in ? ((k >> shift) & 255u) : (256u + (unsigned)lane);  // lanes past the end match nobody
-    const unsigned peers = __match_any_sync(0xffffffffu, d);
+    const int d = in ? (int)((k >> shift) & 255u) : -1;  // lanes past the end match nobody
+    const unsigned peers = warp_peers(d, 8);
     if (in) {
       const unsigned pos = cnt[warp][d] + (unsigned)__popc(peers & ((1u << lane) - 1u));
       keys_out[pos] = k;

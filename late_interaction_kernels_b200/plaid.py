@@ -15,11 +15,14 @@ from . import _lib, _ops
 
 # decompressed tokens held at once (rows of `dim` operand-dtype values)
 _DECOMPRESS_TOKENS = 1 << 22
-# Up to this many query-tile groups (a group = 256 query-token rows = eight 32-token queries) the index is decoded
-# inside the scoring kernel (``lik_plaid_fwd``): every group decodes the tokens it scores, which beats writing
-# and re-reading operand rows while few groups share them.  Beyond it the tokens are decoded once per call
-# (``lik_plaid_decompress``) and scored by every group.  Both ways produce the same bits.
-_FUSED_DECODE_MAX_GROUPS = 4
+# The index can also be decoded INSIDE the scoring kernel (``lik_plaid_fwd``: the kernel's producer warps gather,
+# unpack, normalise and write the operand tiles, so no operand row ever exists in memory).  Every query-tile group
+# (256 query-token rows = eight 32-token queries) then decodes the tokens it scores, with three decoder warps per SM.
+# Measured on B200 that is slower than decoding once per call with the whole machine (``lik_plaid_decompress``, about
+# half the HBM copy rate) and scoring the rows, even for a single query (4.0 ms against 0.64 ms for 25 000 documents),
+# so by default no problem takes it: this is the largest number of tile groups for which it is used.  Both ways
+# produce the same bits.
+_FUSED_DECODE_MAX_GROUPS = 0
 
 
 def _tile_groups(Nq: int, Lq: int) -> int:
@@ -250,7 +253,7 @@ def retrieve_residual_varlen(Q, codes_flat, residuals_flat, cu_seqlens_d, centro
                              normalize=True, chunk=4096, largest=True, doc_lengths_host=None):
     """Top-``top_k`` documents per query straight from a ragged PLAID index, never materialising
     ``[Nq, Nd]``: documents are decompressed ``chunk`` at a time into operand rows, scored, and merged
-    into a running ``[Nq, k]`` list (score desc, index asc).  This is the build's fused form of "call
+    into a running ``[Nq, k]`` list (score desc, index asc).  This is the fused form of "call
     ``maxsim_residual_varlen`` then ``torch.topk``" (docs/benchmarks.md:191-206 of the reference).
 
     ``cu_seqlens_d`` is read on the host once to place chunk boundaries (pass ``doc_lengths_host``, a CPU
@@ -303,7 +306,9 @@ def retrieve_residual_varlen(Q, codes_flat, residuals_flat, cu_seqlens_d, centro
         # many queries: every token is decoded once (in pieces of `chunk` documents, sized so that a piece's operand
         # rows stay small) and the scoring kernel carries its candidate lists from piece to piece
         state = _ops.TopkState() if k <= _lib.TOPK_FUSED_MAX else None
-        pieces = [(j0, min(Nd, j0 + chunk)) for j0 in range(0, Nd, chunk)]
+        # a piece holds at least `chunk` documents and as many more as keep its operand rows within the budget
+        per_piece = max(int(chunk), int(_DECOMPRESS_TOKENS * Nd // max(int(cu_host[Nd]), 1)), 1)
+        pieces = [(j0, min(Nd, j0 + per_piece)) for j0 in range(0, Nd, per_piece)]
         for n, (j0, j1) in enumerate(pieces):
             t0, t1 = int(cu_host[j0]), int(cu_host[j1])
             emb = _ops.plaid_decompress(ix, t0, t1 - t0, normalize, odt, dev)

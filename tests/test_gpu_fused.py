@@ -165,7 +165,10 @@ def test_plaid_retrieve_in_one_kernel_and_in_pieces(monkeypatch):
 
     codes, res, cu, cent, bw = _plaid_ragged(11, 3000, 128, 2, 1024, 60)
     rng = np.random.default_rng(4)
-    for nq in (2, 40):  # one tile group (decoded in the kernel) / five groups (decoded once, lists carried over pieces)
+    # (queries, decode inside the scoring kernel?, token budget of a piece of decoded rows)
+    for nq, in_kernel, budget in ((2, True, 1 << 22), (2, False, 1 << 22), (40, False, 20_000), (40, False, 1 << 22)):
+        monkeypatch.setattr(plaid, "_FUSED_DECODE_MAX_GROUPS", (1 << 30) if in_kernel else 0)
+        monkeypatch.setattr(plaid, "_DECOMPRESS_TOKENS", budget)
         Q = dev(rng.standard_normal((nq, 32, 128)).astype(np.float32), torch.bfloat16)
         args = (Q, dev(codes), dev(res), dev(cu), dev(cent), dev(bw), 2)
         full = plaid.maxsim_residual_varlen(*args)
@@ -173,12 +176,14 @@ def test_plaid_retrieve_in_one_kernel_and_in_pieces(monkeypatch):
         n0 = _lib.load().lik_launch_count()
         s, i = plaid.retrieve_residual_varlen(*args, 100, chunk=700)
         used = _lib.load().lik_launch_count() - n0
-        assert torch.equal(i, wi) and torch.equal(s, ws), nq
-        if nq == 2:
-            assert used <= 4, f"decode + score + top-k in one kernel (saw {used} launches)"
+        assert torch.equal(i, wi) and torch.equal(s, ws), (nq, in_kernel, budget)
+        if in_kernel:
+            assert used <= 3, f"query norms, decode + score + top-k in one kernel, merge (saw {used} launches)"
+        elif budget == 20_000:
+            assert used >= 4 * 3, "several pieces, each decoded and scored into the same candidate lists"
         s, i = plaid.retrieve_residual_varlen(*args, 100, chunk=700, largest=False)
         ws2, wi2 = _stable_topk(full, 100, largest=False)
-        assert torch.equal(i, wi2) and torch.equal(s, ws2), nq
+        assert torch.equal(i, wi2) and torch.equal(s, ws2), (nq, in_kernel, budget)
 
 
 # ----------------------------------------------------------------------------- pair lists on the tensor cores
