@@ -654,7 +654,7 @@ __device__ __forceinline__ void store_row16(G* out, const float (&acc)[CH][Vec16
 constexpr int DQ16_TOK = 16;  // query tokens per CTA (one per half-warp)
 
 template <typename T, typename G, int CH>
-__global__ void __launch_bounds__(256, CH == 1 ? 8 : 1) bwd_dq16_kernel(BwdParams P) {
+__global__ void __launch_bounds__(256) bwd_dq16_kernel(BwdParams P) {
   constexpr int N = Vec16<T>::N;
   constexpr int U = 8 / CH;  // rows in flight per half-warp
   __shared__ int2 s_e[DQ_JC][DQ16_TOK];
@@ -764,7 +764,7 @@ __global__ void __launch_bounds__(256, CH == 1 ? 8 : 1) bwd_dq16_kernel(BwdParam
 // bwd_dd_reduce_kernel, one warp per document token: reads its list (coalesced), gathers the query
 // rows with independent vector loads, accumulates in list order and stores the row once.
 // ---------------------------------------------------------------------------------
-constexpr int DDS_WARPS = 16;
+constexpr int DDS_WARPS = 16;  // most warps a sort CTA uses
 #ifndef LIK_DD_UNROLL
 #define LIK_DD_UNROLL 8
 #endif
@@ -777,6 +777,7 @@ struct DdSortOut {
 };
 
 __global__ void __launch_bounds__(DDS_WARPS * 32) bwd_dd_sort_kernel(BwdParams P, DdSortOut O, int ld_pad) {
+  const int n_warps = blockDim.x >> 5;  // the launcher sizes the CTA to the entries per document
   extern __shared__ int dds_raw[];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int j = blockIdx.x;
@@ -794,17 +795,17 @@ __global__ void __launch_bounds__(DDS_WARPS * 32) bwd_dd_sort_kernel(BwdParams P
   const int lq = P.argmax_stride;
   const int n_ent = ds.n_qr * lq;
   const long long base = list ? ds.first * lq : (long long)j * n_ent;  // first entry of the document's slice of the list
-  int* hist = dds_raw;                          // [DDS_WARPS][ld_pad]
-  int* tok_off = hist + DDS_WARPS * ld_pad;     // [ld_pad + 1]
+  int* hist = dds_raw;                          // [n_warps][ld_pad]
+  int* tok_off = hist + n_warps * ld_pad;     // [ld_pad + 1]
   float* gcol = reinterpret_cast<float*>(tok_off + ld_pad + 1);  // [n_qr] (not for pair lists)
 
-  for (int x = tid; x < DDS_WARPS * ld_pad; x += blockDim.x) hist[x] = 0;
+  for (int x = tid; x < n_warps * ld_pad; x += blockDim.x) hist[x] = 0;
   if (!list)
     for (int x = tid; x < ds.n_qr; x += blockDim.x) gcol[x] = P.g[doc_slot(P, ds, j, x)];
   __syncthreads();
 
   // entry e = ii * lq + s ; slice of this warp (multiple of 32 so rounds stay aligned)
-  const int per_warp = ((n_ent + DDS_WARPS - 1) / DDS_WARPS + 31) & ~31;
+  const int per_warp = ((n_ent + n_warps - 1) / n_warps + 31) & ~31;
   const int e_lo = warp * per_warp, e_hi = min(n_ent, e_lo + per_warp);
 
   // raw saved winner of entry e (no validation): a plain load that can be issued ahead of its use
@@ -847,7 +848,7 @@ __global__ void __launch_bounds__(DDS_WARPS * 32) bwd_dd_sort_kernel(BwdParams P
       const int t = tb + lane;
       int tot = 0;
       if (t < dlen)
-        for (int w = 0; w < DDS_WARPS; ++w) tot += hist[w * ld_pad + t];
+        for (int w = 0; w < n_warps; ++w) tot += hist[w * ld_pad + t];
       int incl = tot;
 #pragma unroll
       for (int o = 1; o < 32; o <<= 1) {
@@ -859,7 +860,7 @@ __global__ void __launch_bounds__(DDS_WARPS * 32) bwd_dd_sort_kernel(BwdParams P
         O.tok_begin[drow0 + t] = base + excl;
         O.tok_cnt[drow0 + t] = tot;
         int b = excl;
-        for (int w = 0; w < DDS_WARPS; ++w) {
+        for (int w = 0; w < n_warps; ++w) {
           const int c = hist[w * ld_pad + t];
           hist[w * ld_pad + t] = b;
           b += c;
@@ -973,6 +974,7 @@ __global__ void __launch_bounds__(256) bwd_dd_reduce_kernel(BwdParams P, DdSortO
 constexpr int DDS_LOADS = 8;  // 16-byte loads in flight per lane
 
 __global__ void __launch_bounds__(DDS_WARPS * 32) bwd_dd_sort4_kernel(BwdParams P, DdSortOut O, int ld_pad) {
+  const int n_warps = blockDim.x >> 5;  // the launcher sizes the CTA to the entries per document
   extern __shared__ int dds_raw[];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int j = blockIdx.x;
@@ -992,18 +994,18 @@ __global__ void __launch_bounds__(DDS_WARPS * 32) bwd_dd_sort4_kernel(BwdParams 
   const int n_quad = ds.n_qr * qpr;
   const int n_ent = n_quad * 4;
   const long long base = list ? ds.first * lq : (long long)j * n_ent;
-  int* hist = dds_raw;                          // [DDS_WARPS][ld_pad]
-  int* tok_off = hist + DDS_WARPS * ld_pad;     // [ld_pad + 1] (kept for the layout shared with the scalar kernel)
+  int* hist = dds_raw;                          // [n_warps][ld_pad]
+  int* tok_off = hist + n_warps * ld_pad;     // [ld_pad + 1] (kept for the layout shared with the scalar kernel)
   float* gcol = reinterpret_cast<float*>(tok_off + ld_pad + 1);  // [n_qr] (not for pair lists)
 
-  for (int x = tid; x < DDS_WARPS * ld_pad; x += blockDim.x) hist[x] = 0;
+  for (int x = tid; x < n_warps * ld_pad; x += blockDim.x) hist[x] = 0;
   if (!list)
     for (int x = tid; x < ds.n_qr; x += blockDim.x) gcol[x] = P.g[doc_slot(P, ds, j, x)];
   __syncthreads();
 
   // slice of this warp in 16-byte groups, a multiple of 32 * DDS_LOADS so that rounds stay whole
   const int round_quads = 32 * DDS_LOADS;
-  const int per_warp = (((n_quad + DDS_WARPS - 1) / DDS_WARPS + round_quads - 1) / round_quads) * round_quads;
+  const int per_warp = (((n_quad + n_warps - 1) / n_warps + round_quads - 1) / round_quads) * round_quads;
   const int m_lo = warp * per_warp, m_hi = min(n_quad, m_lo + per_warp);
   const int4 none = make_int4(-1, -1, -1, -1);
 
@@ -1049,7 +1051,7 @@ __global__ void __launch_bounds__(DDS_WARPS * 32) bwd_dd_sort4_kernel(BwdParams 
       const int t = tb + lane;
       int tot = 0;
       if (t < dlen)
-        for (int w = 0; w < DDS_WARPS; ++w) tot += hist[w * ld_pad + t];
+        for (int w = 0; w < n_warps; ++w) tot += hist[w * ld_pad + t];
       int incl = tot;
 #pragma unroll
       for (int o = 1; o < 32; o <<= 1) {
@@ -1061,7 +1063,7 @@ __global__ void __launch_bounds__(DDS_WARPS * 32) bwd_dd_sort4_kernel(BwdParams 
         O.tok_begin[drow0 + t] = base + excl;
         O.tok_cnt[drow0 + t] = tot;
         int b = excl;
-        for (int w = 0; w < DDS_WARPS; ++w) {
+        for (int w = 0; w < n_warps; ++w) {
           const int c = hist[w * ld_pad + t];
           hist[w * ld_pad + t] = b;
           b += c;
@@ -1268,6 +1270,7 @@ struct BwdPlan {
   size_t kq_off, kd_off, pq_off, pd_off, sq_off, sd_off, sort_off;  // pair lists grouped by query / by document
   bool fast, sorted;
   bool list_sorted;  // pair list on the deterministic kernels
+  int sort_warps;    // warps per CTA of the winner sort: about 2048 entries of a document per warp
   bool row16;  // 16-byte gathers: rows 16-byte aligned, width a multiple of 16 bytes, at most 1024 bytes
   int ld_pad;
   size_t sort_smem;
@@ -1309,7 +1312,7 @@ BwdPlan plan_bwd(const lik_bwd_args& a) {
   pl.list_sorted = list && a.deterministic && pl.fast && a.n_pairs > 0 && a.n_pairs < (1ll << 31) && a.d.max_len > 0 &&
                    a.q.max_len > 0 && a.q.n_seq > 0 && a.d.n_seq > 0;
   if (pl.list_sorted) {
-    const size_t ws_sort = ((size_t)DDS_WARPS * (a.d.max_len + 1) + a.d.max_len + 2) * 4;
+    const size_t ws_sort = ((size_t)(a.d.max_len + 1) + a.d.max_len + 2) * 4;  // with one warp per CTA
     if (ws_sort > 200 * 1024) pl.list_sorted = false;
   }
   if (pl.list_sorted) {
@@ -1328,7 +1331,15 @@ BwdPlan plan_bwd(const lik_bwd_args& a) {
       a.q.n_rows < (1ll << 31)) {
     const long long n_qrange = a.pairing == LIK_PAIR_CROSS ? a.q.n_seq : (list ? 0 : 1);
     pl.ld_pad = a.d.max_len + 1;
-    pl.sort_smem = ((size_t)DDS_WARPS * pl.ld_pad + pl.ld_pad + 1 + (size_t)n_qrange) * 4;
+    // entries (query token, winner) per document: every document has the same number, except in a pair list (average)
+    const long long ent = a.pairing == LIK_PAIR_CROSS ? (long long)a.q.n_seq * a.argmax_stride
+                          : a.pairing == LIK_PAIR_GROUPED ? (long long)a.argmax_stride
+                                                          : ceil_div(a.n_pairs, a.d.n_seq) * a.argmax_stride;
+    long long nw = ceil_div(ent, 2048);
+    pl.sort_warps = (int)(nw < 1 ? 1 : (nw > DDS_WARPS ? DDS_WARPS : nw));
+    auto smem_for = [&](int w) { return ((size_t)w * pl.ld_pad + pl.ld_pad + 1 + (size_t)n_qrange) * 4; };
+    while (pl.sort_warps > 1 && smem_for(pl.sort_warps) > 200 * 1024) pl.sort_warps >>= 1;  // long documents: fewer histograms
+    pl.sort_smem = smem_for(pl.sort_warps);
     if (pl.sort_smem <= 200 * 1024) {
       pl.sorted = true;
       const long long n_ent = n_scores_of(a.pairing, a.q.n_seq, a.d.n_seq, a.n_pairs) * (long long)a.argmax_stride;
@@ -1458,10 +1469,10 @@ int run_bwd(const lik_bwd_args& a, BwdParams& P, const BwdPlan& pl, cudaStream_t
       const bool quads = a.argmax_stride % 4 == 0 && ((uintptr_t)a.argmax % 16) == 0;
       if (quads) {
         LIK_CUDA_OK(cudaFuncSetAttribute(bwd_dd_sort4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.sort_smem));
-        bwd_dd_sort4_kernel<<<(unsigned)a.d.n_seq, DDS_WARPS * 32, pl.sort_smem, st>>>(P, O, pl.ld_pad), ::lik::count_launch();
+        bwd_dd_sort4_kernel<<<(unsigned)a.d.n_seq, pl.sort_warps * 32, pl.sort_smem, st>>>(P, O, pl.ld_pad), ::lik::count_launch();
       } else {
         LIK_CUDA_OK(cudaFuncSetAttribute(bwd_dd_sort_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.sort_smem));
-        bwd_dd_sort_kernel<<<(unsigned)a.d.n_seq, DDS_WARPS * 32, pl.sort_smem, st>>>(P, O, pl.ld_pad), ::lik::count_launch();
+        bwd_dd_sort_kernel<<<(unsigned)a.d.n_seq, pl.sort_warps * 32, pl.sort_smem, st>>>(P, O, pl.ld_pad), ::lik::count_launch();
       }
       LIK_CUDA_OK(cudaGetLastError());
       if (pl.row16) {

@@ -21,6 +21,7 @@
 // sets a shared abort flag, drains its TMA copies, frees TMEM and returns.
 #include <cuda.h>
 
+#include <cstdlib>
 #include <cstring>
 
 #include "lik_common.cuh"
@@ -428,7 +429,7 @@ __device__ __forceinline__ TileInfo tile_info(const TcParams& P, int tile) {
 struct UnitIter {
   int sb;               // super-block
   int doc_lo, doc_hi;   // its documents
-  long long u, u_end;   // position and end of this CTA's share of the super-block
+  int left;             // units of this CTA's share of the super-block still to come, this one included
   int grp, doc, in_grp;
 };
 
@@ -445,20 +446,20 @@ __device__ __forceinline__ bool iter_enter(const TcParams& P, int n_groups, Unit
       it.doc_hi = P.n_d;
       units = P.n_flat;
     }
-    it.u = units * c / G;
-    it.u_end = units * (c + 1) / G;
-    if (it.u < it.u_end) {
+    const long long u = units * c / G, u_end = units * (c + 1) / G;
+    if (u < u_end) {
+      it.left = (int)(u_end - u);
       if (P.pairing == LIK_PAIR_CROSS) {
         const int nd_b = it.doc_hi - it.doc_lo;
-        it.grp = (int)(it.u / nd_b);
-        it.doc = it.doc_lo + (int)(it.u - (long long)it.grp * nd_b);
+        it.grp = (int)(u / nd_b);
+        it.doc = it.doc_lo + (int)(u - (long long)it.grp * nd_b);
         it.in_grp = 0;
       } else if (P.pairing == LIK_PAIR_GROUPED) {
-        it.doc = (int)it.u;
+        it.doc = (int)u;
         it.grp = it.doc / P.group;
         it.in_grp = it.doc - it.grp * P.group;
       } else {
-        it.doc = (int)it.u;
+        it.doc = (int)u;
         it.grp = -1;  // comes from the table
         it.in_grp = 0;
       }
@@ -473,7 +474,7 @@ __device__ __forceinline__ bool iter_begin(const TcParams& P, int n_groups, Unit
   return iter_enter(P, n_groups, it);
 }
 __device__ __forceinline__ bool iter_next(const TcParams& P, int n_groups, UnitIter& it) {
-  if (++it.u < it.u_end) {
+  if (--it.left > 0) {
     ++it.doc;
     if (P.pairing == LIK_PAIR_CROSS) {
       if (it.doc == it.doc_hi) {
@@ -496,25 +497,24 @@ __device__ __forceinline__ bool iter_next(const TcParams& P, int n_groups, UnitI
 struct UnitRaw {
   int a, b, q;
 };
-__device__ __forceinline__ UnitRaw unit_fetch(const TcParams& P, const UnitIter& it) {
+__device__ __forceinline__ UnitRaw unit_fetch(const TcParams& P, int doc) {
   UnitRaw r{0, 0, 0};
   if (P.pairing == LIK_PAIR_LIST) {
-    const int4 t = __ldg(P.list_tab + it.doc);
+    const int4 t = __ldg(P.list_tab + doc);
     r.q = t.x;
     r.a = t.y;
     r.b = t.z;
   } else if (P.d.cu) {
-    r.a = P.d.cu[it.doc];
-    r.b = P.d.cu[it.doc + 1];
+    r.a = P.d.cu[doc];
+    r.b = P.d.cu[doc + 1];
   } else if (P.d.lens) {
-    r.a = P.d.lens[it.doc];
+    r.a = P.d.lens[doc];
   }
   return r;
 }
 // First row and column count of the fetched document; `masked` tells whether its mask has holes.
 // Lengths come from the caller-validated views, clamped to the padded extent.
-__device__ __forceinline__ void unit_resolve(const TcParams& P, const UnitIter& it, const UnitRaw& r, long long& row0, int& len,
-                                             bool& masked) {
+__device__ __forceinline__ void unit_resolve(const TcParams& P, int doc, const UnitRaw& r, long long& row0, int& len, bool& masked) {
   masked = false;
   if (P.pairing == LIK_PAIR_LIST) {
     row0 = r.a;
@@ -525,7 +525,7 @@ __device__ __forceinline__ void unit_resolve(const TcParams& P, const UnitIter& 
     len = b > a ? b - a : 0;
     if ((long long)a + len > P.d.n_rows) len = P.d.n_rows > a ? (int)(P.d.n_rows - a) : 0;
   } else {
-    row0 = (long long)it.doc * P.d.seq_stride;
+    row0 = (long long)doc * P.d.seq_stride;
     len = P.d.max_len;
     if (P.d.lens) {
       int l = r.a;
@@ -675,31 +675,30 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
       const int x_per_slab = SLAB_BYTES_ROW / P.elt_bytes;
       bool ok = true;
       int tiles_here = 0;
-      UnitIter cur, nxt;
-      bool have = iter_begin(P, n_groups, cur);
-      UnitRaw raw_cur{0, 0, 0}, raw_nxt{0, 0, 0};
-      bool have_nxt = false;
+      // the iterator stands one unit ahead: that unit's length words are in flight while this one is produced
+      UnitIter it;
+      bool have = iter_begin(P, n_groups, it);
+      int nx_grp = 0, nx_doc = 0;
+      UnitRaw nx_raw{0, 0, 0};
       if (have) {
-        raw_cur = unit_fetch(P, cur);
-        nxt = cur;
-        have_nxt = iter_next(P, n_groups, nxt);
-        if (have_nxt) raw_nxt = unit_fetch(P, nxt);
+        nx_grp = it.grp;
+        nx_doc = it.doc;
+        nx_raw = unit_fetch(P, nx_doc);
       }
       while (have && ok) {
-        const int grp = list ? raw_cur.q : cur.grp;
-        const int next_grp = have_nxt ? (list ? raw_nxt.q : nxt.grp) : -1;
-        const int doc = cur.doc;
+        const int doc = nx_doc;
+        const int grp = list ? nx_raw.q : nx_grp;
         long long drow0;
         int dlen;
         bool dmasked;
-        unit_resolve(P, cur, raw_cur, drow0, dlen, dmasked);
-        // step the look-ahead now so that the next unit's length words are in flight during this unit
-        cur = nxt;
-        raw_cur = raw_nxt;
-        have = have_nxt;
+        unit_resolve(P, doc, nx_raw, drow0, dlen, dmasked);
+        have = iter_next(P, n_groups, it);
+        int next_grp = -1;
         if (have) {
-          have_nxt = iter_next(P, n_groups, nxt);
-          if (have_nxt) raw_nxt = unit_fetch(P, nxt);
+          nx_grp = it.grp;
+          nx_doc = it.doc;
+          nx_raw = unit_fetch(P, nx_doc);
+          next_grp = list ? nx_raw.q : nx_grp;
         }
         const bool last_unit_of_grp = next_grp != grp;
         uint32_t first = 0;
@@ -986,6 +985,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
   } while (0)
 
     const bool cross = P.pairing == LIK_PAIR_CROSS;
+    const bool every_group_full = P.mt == 1 || (n_tiles & 1) == 0;
     for (;; ++uc) {
       // with one resident tile the two groups take alternate units
       if (P.mt == 1 && (uc & 1) != wg) continue;
@@ -995,8 +995,9 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
       if (leader) {
         int st_ = wait_posted(ctl, uc, P.status);
         if (st_ == 1 && !SCALED) {
-          const int g_ = ctl->unit_info[uc & (UNIT_RING - 1)].z;
-          if (g_ * P.mt + (P.mt == 2 ? wg : 0) < n_tiles && !wait_bar(&ctl->acc_full[wg], n_acc & 1, ctl, P.status)) st_ = 0;
+          // (only the last tile group can lack this group's tile, and only when the tile count is odd)
+          const bool mine_ = every_group_full || ctl->unit_info[uc & (UNIT_RING - 1)].z * P.mt + wg < n_tiles;
+          if (mine_ && !wait_bar(&ctl->acc_full[wg], n_acc & 1, ctl, P.status)) st_ = 0;
         }
         if (lane == 0) {
           if (st_ == 0) ctl->grp_abort[wg] = 1;
@@ -1421,7 +1422,16 @@ int make_map(CUtensorMap* map, const lik_seqs& s, int dtype, int dim, int box_ro
 }
 
 constexpr size_t SB_WINDOW_BYTES = 48u << 20;   // documents of one super-block: stays in L2 while every group passes
-constexpr size_t SB_MIN_BYTES = 96u << 20;      // smaller document sets are walked as one block
+// LIK_SB_WINDOW_MB overrides the window (a tuning knob; document sets below twice the window are walked as one block)
+static size_t sb_window_bytes() {
+  static size_t v = 0;
+  if (!v) {
+    const char* e = getenv("LIK_SB_WINDOW_MB");
+    const long mb = e ? atol(e) : 0;
+    v = mb > 0 ? (size_t)mb << 20 : SB_WINDOW_BYTES;
+  }
+  return v;
+}
 
 struct TcPlan {
   bool pack_tiles;  // ragged queries packed greedily into tiles by pack_query_tiles_kernel
@@ -1467,9 +1477,9 @@ TcPlan plan_tc(const lik_fwd_args& a, const TcExtra& x) {
     // large document sets are walked in L2-sized super-blocks (several tile groups read every document)
     const size_t row_bytes = x.plaid ? (size_t)(4 + x.plaid->packed_dim) : (size_t)a.dim * eb;
     const size_t d_bytes = (size_t)a.d.n_rows * row_bytes;
-    if (a.d.n_seq > 0 && pl.n_groups > 1 && d_bytes > SB_MIN_BYTES) {
+    if (a.d.n_seq > 0 && pl.n_groups > 1 && d_bytes > 2 * sb_window_bytes()) {
       const size_t per_doc = d_bytes / (size_t)a.d.n_seq + 1;
-      long long sb = (long long)(SB_WINDOW_BYTES / per_doc);
+      long long sb = (long long)(sb_window_bytes() / per_doc);
       if (sb < 64) sb = 64;
       if (sb < a.d.n_seq) {
         pl.sb_docs = (int)sb;

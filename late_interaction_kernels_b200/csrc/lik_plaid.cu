@@ -114,7 +114,9 @@ __global__ void __launch_bounds__(256) plaid_decompress16_kernel(PlaidSrc S, lon
   plaid_decode_range<CF32, CF32 ? 4 : 8>(S, bw, tok0 + first, n, PD_RUN, lane, hl * 8 < dim, status, sink);
 }
 
-// Approximate score: one warp per document, lane = query token (chunks of 32).
+// Approximate score: one warp per document, lane = query token (chunks of 32).  The document's codes are read 32
+// at a time (one per lane, coalesced) and handed round with shuffles; the score-table rows of eight tokens are in
+// flight at once (the table, n_centroids x lq floats, is an L2 resident gather target).
 __global__ void __launch_bounds__(256) plaid_approx_kernel(const float* __restrict__ qcs, int n_centroids, int lq,
                                                          const int* __restrict__ codes, long long n_docs, int max_ld,
                                                          const long long* __restrict__ lens, float* __restrict__ out) {
@@ -123,14 +125,27 @@ __global__ void __launch_bounds__(256) plaid_approx_kernel(const float* __restri
   if (b >= n_docs) return;
   long long len = lens[b];
   if (len > max_ld) len = max_ld;
+  const int* __restrict__ doc = codes + b * max_ld;
   float total = 0.f;
   for (int s0 = 0; s0 < lq; s0 += 32) {
     const int s = s0 + lane;
+    const float* __restrict__ col = qcs + (s < lq ? s : 0);
     float m = -INFINITY;
-    for (int t = 0; t < len; ++t) {
-      int c = codes[b * max_ld + t];
+    for (int t0 = 0; t0 < len; t0 += 32) {
+      int c = t0 + lane < len ? __ldg(doc + t0 + lane) : 0;
       if (c < 0 || c >= n_centroids) c = 0;  // out-of-range codes read centroid 0
-      if (s < lq) m = fmaxf(m, qcs[(long long)c * lq + s]);
+      const int n = (int)min((long long)32, len - t0);
+#pragma unroll 1
+      for (int u0 = 0; u0 < n; u0 += 8) {
+        float v[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const int cu = __shfl_sync(0xffffffffu, c, (u0 + u) & 31);
+          v[u] = u0 + u < n ? __ldg(col + (long long)cu * lq) : -INFINITY;
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) m = fmaxf(m, v[u]);
+      }
     }
     total += warp_sum((s < lq && m != -INFINITY) ? m : 0.f);
   }

@@ -518,6 +518,61 @@ def residual_grad_q(grad_scores, Q, codes, residuals, doc_lengths, centroids, bu
 
 
 # --------------------------------------------------------------------------- #
+# PLAID candidate generation (PARITY UNPINNED: the reference ships the scoring #
+# kernels only; these stages live in fast-plaid, which is not in the reference #
+# tree.  Restated from the published algorithm, Santhanam et al. 2022, and     #
+# anchored on the reference's own reader of the index files,                   #
+# benchmarks/plaid/bench_fastplaid_e2e.py:76-140.)                             #
+# --------------------------------------------------------------------------- #
+def plaid_ivf(codes_flat, cu_d, n_centroids):
+    """Inverted file: for every centroid the ascending documents with a token on it -> (docs, offsets)."""
+    cu_d = np.asarray(cu_d).astype(np.int64)
+    nd = len(cu_d) - 1
+    tok_doc = np.repeat(np.arange(nd), cu_d[1:] - cu_d[:-1])
+    codes = np.clip(np.asarray(codes_flat).astype(np.int64), 0, n_centroids - 1)
+    key = np.unique(codes * max(nd, 1) + tok_doc)
+    cent = key // max(nd, 1)
+    offsets = np.zeros(n_centroids + 1, np.int64)
+    offsets[1:] = np.cumsum(np.bincount(cent, minlength=n_centroids))
+    return (key - cent * max(nd, 1)).astype(np.int32), offsets
+
+
+def plaid_search(Q, codes_flat, residuals_flat, cu_d, centroids, bucket_weights, nbits, top_k, *, nprobe=4, ndocs=4096,
+                 normalize=True, qcs=None):
+    """Three-stage PLAID search of one query [Lq, d]: probe the nprobe best centroids per query token, score the
+    candidates approximately from their codes, rerank the ndocs best exactly.  Ties go to the lower index at every
+    selection.  ``qcs`` ([n_centroids, Lq]) may be passed in so that a test feeds both sides the same centroid scores.
+    Returns (scores [k], document ids [k])."""
+    Q = _f(Q, np.float32)
+    cent = _f(centroids, np.float32)
+    cu_d = np.asarray(cu_d).astype(np.int64)
+    lens = cu_d[1:] - cu_d[:-1]
+    Qn = l2_normalize(Q) if normalize else Q
+    if qcs is None:
+        qcs = cent @ Qn.T
+    ivf_docs, ivf_off = plaid_ivf(codes_flat, cu_d, cent.shape[0])
+    probe = min(nprobe, cent.shape[0])
+    cid = np.unique(topk_rows(np.asarray(qcs).T, probe)[1])
+    cand = np.unique(np.concatenate([ivf_docs[ivf_off[c]:ivf_off[c + 1]] for c in cid]).astype(np.int64)) if len(cid) else np.zeros(0, np.int64)
+    if cand.size == 0:
+        return np.zeros(0, np.float32), np.zeros(0, np.int64)
+    if cand.size > ndocs:
+        max_ld = int(lens[cand].max())
+        pad = np.zeros((cand.size, max_ld), np.int64)
+        for n, j in enumerate(cand):
+            pad[n, : lens[j]] = np.asarray(codes_flat)[cu_d[j]:cu_d[j + 1]]
+        approx = plaid_approx_score(qcs, pad, lens[cand])
+        keep = np.sort(topk_rows(approx[None], ndocs)[1][0])
+        cand = cand[keep]
+    sub_c = np.concatenate([np.asarray(codes_flat)[cu_d[j]:cu_d[j + 1]] for j in cand])
+    sub_r = np.concatenate([np.asarray(residuals_flat)[cu_d[j]:cu_d[j + 1]] for j in cand])
+    sub_cu = np.concatenate([[0], np.cumsum(lens[cand])])
+    full = maxsim_residual_varlen(Q, sub_c, sub_r, sub_cu, centroids, bucket_weights, nbits, normalize=normalize)
+    ts, ti = topk_rows(full[None], min(top_k, cand.size))
+    return ts[0].astype(np.float32), cand[ti[0]]
+
+
+# --------------------------------------------------------------------------- #
 # sharded retrieval merge (the build's own multi-GPU step; no reference twin) #
 # --------------------------------------------------------------------------- #
 def merge_topk(cand_scores, cand_idx, k, largest=True):

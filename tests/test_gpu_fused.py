@@ -243,3 +243,48 @@ def test_pair_list_on_tensor_cores():
         lik.check_device_status()
     keep = np.arange(300) != 5
     assert torch.equal(sb[dev(keep)], s[dev(keep)])
+
+
+# ----------------------------------------------------------------------------- PLAID stages in front of the scorer
+def test_plaid_search_pipeline(tmp_path):
+    """Reader -> inverted file -> probe -> approximate score -> exact rerank, against the oracle's restatement of the
+    same stages (fed the same centroid scores, so that both probe the same lists) and, with nothing pruned, against
+    the exhaustive rerank of this library."""
+    from test_plaid_index_cpu import write_fastplaid_files
+
+    from late_interaction_kernels_b200 import plaid
+    from late_interaction_kernels_b200.plaid_index import build_ivf, plaid_candidates, plaid_search, read_fastplaid_index
+
+    rng = np.random.default_rng(21)
+    nd, d, nbits, ncent = 600, 128, 2, 256
+    lens = rng.integers(1, 40, size=nd)
+    T = int(lens.sum())
+    cent = cases.unit(rng.standard_normal((ncent, d))).astype(np.float16)
+    # tokens near their centroid, as in a trained index: code = nearest centroid of a random direction
+    tok = cases.unit(rng.standard_normal((T, d))).astype(np.float32)
+    codes = (tok @ cent.astype(np.float32).T).argmax(-1).astype(np.int32)
+    res = rng.integers(0, 256, size=(T, d * nbits // 8)).astype(np.uint8)
+    bw = np.linspace(-0.05, 0.05, 4).astype(np.float32)
+    cu = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+    path = str(tmp_path / "index")
+    write_fastplaid_files(path, codes, res, lens, cent, bw, nbits, merged=True, pad_rows=7)
+    ix = build_ivf(read_fastplaid_index(path, device="cuda"))
+    Q = dev(rng.standard_normal((32, d)).astype(np.float32), torch.bfloat16)
+    # nothing pruned: identical to scoring the whole index
+    s_all, i_all = plaid_search(ix, Q, 10, nprobe=ncent, ndocs=nd)
+    ws, wi = plaid.retrieve_residual_varlen(Q, ix.codes_flat, ix.residuals_flat, ix.cu_seqlens_d, ix.centroids, ix.bucket_weights, nbits, 10)
+    assert torch.equal(i_all, wi) and torch.equal(s_all, ws)
+    # pruned: same candidates, survivors and ranking as the oracle's pipeline on the same centroid scores
+    Qn = torch.nn.functional.normalize(Q.float(), dim=-1)
+    qcs = (ix.centroids.float() @ Qn.t()).contiguous()
+    cand = plaid_candidates(ix, qcs, 3)
+    s, i = plaid_search(ix, Q, 10, nprobe=3, ndocs=50)
+    os_, oi = O.plaid_search(f32(Q), codes, res, cu, cent, bw, nbits, 10, nprobe=3, ndocs=50, qcs=f32(qcs))
+    assert 50 < cand.numel() < nd, "the probe prunes, and leaves more than ndocs for the approximate stage to cut"
+    assert set(i.tolist()) <= set(cand.tolist())
+    assert O.rel_err(f32(s), os_) < 3e-2
+    same = i.cpu().numpy() == oi
+    assert same.mean() >= 0.8 and np.all(np.abs(f32(s)[~same] - os_[~same]) < 3e-2 * np.abs(os_).max())
+    # a batch is one search per query
+    sb, ib = plaid_search(ix, torch.stack([Q, Q.flip(0)]), 10, nprobe=3, ndocs=50)
+    assert torch.equal(sb[0], s) and torch.equal(ib[0], i) and sb.shape == (2, 10)
