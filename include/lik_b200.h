@@ -156,8 +156,10 @@ int lik_maxsim_fwd_static(const lik_fwd_args* args, lik_stream_t stream);
 /* (varlen.py:389-449) and the pair-list backward (score_pairs.py:356-420).     */
 /*   grad_q[row(i,s)] = sum_p g[p] * d[row(j_p, argmax[p,s])]                   */
 /*   grad_d[row(j,t)] = sum_{p,s : argmax[p,s]=t} g[p] * q[row(i_p,s)]          */
-/* With normalize != 0 the L2-normalise Jacobian (autograd.py:213-225) is       */
-/* applied inside the kernels.  grad_q / grad_d are [n_rows, dim] contiguous.   */
+/* normalize: bit LIK_NORM_Q / LIK_NORM_D = that side was L2-normalised by the  */
+/* forward; its Jacobian (autograd.py:213-225) is applied inside the kernels     */
+/* (LIK_NORM_BOTH for maxsim(normalize=True); LIK_NORM_D alone for a projected    */
+/* document head).  grad_q / grad_d are [n_rows, dim] contiguous.                */
 /* deterministic != 0 (CROSS and GROUPED pairing): destination-owned reduction, */
 /* grads written once in grad_dtype, bitwise reproducible.  deterministic == 0: */
 /* fp32 atomics into the workspace followed by a finalise pass.                 */

@@ -143,7 +143,7 @@ __global__ void __launch_bounds__(256) bwd_dq_kernel(BwdParams P) {
       }
     }
     const float qf = P.q.scale_scalar * (P.q.scale ? P.q.scale[qrow] : 1.f);
-    if (P.normalize) {
+    if (P.normalize & LIK_NORM_Q) {
       // acc is the gradient w.r.t. q_hat = q * inv; pull it back through the normalisation
       const float inv = P.q.inv_norm[qrow];
       const T* qsrc = (const T*)P.q.data + qrow * P.q.row_stride;
@@ -294,7 +294,7 @@ __global__ void __launch_bounds__(256) bwd_dd_owned_kernel(BwdParams P) {
     if (t >= d_rows) continue;
     const long long drow = drow0 + t;
     const float df = P.d.scale_scalar * (P.d.scale ? P.d.scale[drow] : 1.f);
-    if (P.normalize) {
+    if (P.normalize & LIK_NORM_D) {
       const float inv = P.d.inv_norm[drow];
       const T* dsrc = (const T*)P.d.data + drow * P.d.row_stride;
       float dh[CMAX];
@@ -528,7 +528,7 @@ __global__ void __launch_bounds__(256) bwd_dq_fast_kernel(BwdParams P) {
   }
   if (!owns) return;
   if (active) {
-    if (P.normalize) {
+    if (P.normalize & LIK_NORM_Q) {
       normalize_jacobian_row<T, CH>(acc, (const T*)P.q.data + qrow * P.q.row_stride, P.q.inv_norm[qrow], P.dim, lane);
     } else {
       const float qf = P.q.scale_scalar * (P.q.scale ? P.q.scale[qrow] : 1.f);
@@ -737,7 +737,7 @@ __global__ void __launch_bounds__(256) bwd_dq16_kernel(BwdParams P) {
   }
   if (!owns) return;
   if (active) {
-    if (P.normalize) {
+    if (P.normalize & LIK_NORM_Q) {
       normalize_jacobian_row16<T, CH>(acc, (const T*)P.q.data + qrow * P.q.row_stride, P.q.inv_norm[qrow], P.dim, hl);
     } else {
       const float qf = P.q.scale_scalar * (P.q.scale ? P.q.scale[qrow] : 1.f);
@@ -947,7 +947,7 @@ __global__ void __launch_bounds__(256) bwd_dd_reduce_kernel(BwdParams P, DdSortO
         }
     }
   }
-  if (P.normalize) {
+  if (P.normalize & LIK_NORM_D) {
     normalize_jacobian_row<T, CH>(acc, (const T*)P.d.data + drow * P.d.row_stride, P.d.inv_norm[drow], P.dim, lane);
   } else {
     const float df = P.d.scale_scalar * (P.d.scale ? P.d.scale[drow] : 1.f);
@@ -1157,7 +1157,7 @@ __global__ void __launch_bounds__(256) bwd_dd_reduce16_kernel(BwdParams P, DdSor
         if (lane_on[c]) fma16_raw<T>(acc[c], w, load16_raw<T>(src + c * 16 * N));
     }
   }
-  if (P.normalize) {
+  if (P.normalize & LIK_NORM_D) {
     normalize_jacobian_row16<T, CH>(acc, (const T*)P.d.data + drow * P.d.row_stride, P.d.inv_norm[drow], P.dim, hl);
   } else {
     const float df = P.d.scale_scalar * (P.d.scale ? P.d.scale[drow] : 1.f);
@@ -1302,10 +1302,8 @@ BwdPlan plan_bwd(const lik_bwd_args& a) {
   pl.fast = bwd_fast_ok(a);
   pl.row16 = bwd_row16_ok(a);
   pl.sorted = false;
-  if (a.normalize) {
-    pl.qn_off = take((size_t)a.q.n_rows * 4);
-    pl.dn_off = take((size_t)a.d.n_rows * 4);
-  }
+  if (a.normalize & LIK_NORM_Q) pl.qn_off = take((size_t)a.q.n_rows * 4);
+  if (a.normalize & LIK_NORM_D) pl.dn_off = take((size_t)a.d.n_rows * 4);
   const bool list = a.pairing == LIK_PAIR_LIST;
   pl.kq_off = pl.kd_off = pl.pq_off = pl.pd_off = pl.sq_off = pl.sd_off = pl.sort_off = (size_t)-1;
   // a pair list goes through the same deterministic kernels once its pairs are grouped by query and by document
@@ -1519,11 +1517,11 @@ int run_bwd(const lik_bwd_args& a, BwdParams& P, const BwdPlan& pl, cudaStream_t
       LIK_CUDA_OK(cudaGetLastError());
     }
     if (P.gq32 && a.q.n_rows > 0) {
-      bwd_finalize_kernel<T, G><<<(unsigned)ceil_div(a.q.n_rows, 8), 256, 0, st>>>(P.gq32, P.q, a.dim, a.normalize, (G*)a.grad_q), ::lik::count_launch();
+      bwd_finalize_kernel<T, G><<<(unsigned)ceil_div(a.q.n_rows, 8), 256, 0, st>>>(P.gq32, P.q, a.dim, a.normalize & LIK_NORM_Q, (G*)a.grad_q), ::lik::count_launch();
       LIK_CUDA_OK(cudaGetLastError());
     }
     if (P.gd32 && a.d.n_rows > 0) {
-      bwd_finalize_kernel<T, G><<<(unsigned)ceil_div(a.d.n_rows, 8), 256, 0, st>>>(P.gd32, P.d, a.dim, a.normalize, (G*)a.grad_d), ::lik::count_launch();
+      bwd_finalize_kernel<T, G><<<(unsigned)ceil_div(a.d.n_rows, 8), 256, 0, st>>>(P.gd32, P.d, a.dim, a.normalize & LIK_NORM_D, (G*)a.grad_d), ::lik::count_launch();
       LIK_CUDA_OK(cudaGetLastError());
     }
   }
@@ -1568,16 +1566,17 @@ extern "C" int lik_maxsim_bwd(const lik_bwd_args* a, lik_stream_t stream) {
     return LIK_ERR_WORKSPACE;
   }
   const float *qn = nullptr, *dn = nullptr;
-  if (a->normalize) {
-    char* ws = (char*)a->workspace;
-    float* qnw = (float*)(ws + pl.qn_off);
-    float* dnw = (float*)(ws + pl.dn_off);
-    int rc = launch_row_inv_norm(a->q.data, a->dtype, a->q.n_rows, a->dim, a->q.row_stride, kBwdNormEps, qnw, st);
+  if (a->normalize & LIK_NORM_Q) {
+    float* w = (float*)((char*)a->workspace + pl.qn_off);
+    int rc = launch_row_inv_norm(a->q.data, a->dtype, a->q.n_rows, a->dim, a->q.row_stride, kBwdNormEps, w, st);
     if (rc) return rc;
-    rc = launch_row_inv_norm(a->d.data, a->dtype, a->d.n_rows, a->dim, a->d.row_stride, kBwdNormEps, dnw, st);
+    qn = w;
+  }
+  if (a->normalize & LIK_NORM_D) {
+    float* w = (float*)((char*)a->workspace + pl.dn_off);
+    int rc = launch_row_inv_norm(a->d.data, a->dtype, a->d.n_rows, a->dim, a->d.row_stride, kBwdNormEps, w, st);
     if (rc) return rc;
-    qn = qnw;
-    dn = dnw;
+    dn = w;
   }
   BwdParams P;
   P.q = make_view(a->q, qn);

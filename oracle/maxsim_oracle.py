@@ -518,6 +518,35 @@ def residual_grad_q(grad_scores, Q, codes, residuals, doc_lengths, centroids, bu
 
 
 # --------------------------------------------------------------------------- #
+# document head (reference.py:182-210)                                        #
+# --------------------------------------------------------------------------- #
+def maxsim_from_hidden(Q, H_d, W, b=None, d_mask=None, *, normalize=True):
+    """D = H_d W^T (+ b) in fp32, optional L2 norm (eps 1e-12), then MaxSim against Q (reference.py:182-210)."""
+    H = _f(H_d, np.float32)
+    D = H @ _f(W, np.float32).T
+    if b is not None:
+        D = D + _f(b, np.float32)
+    if normalize:
+        D = l2_normalize(D)
+    return maxsim(Q, D, None, d_mask)
+
+
+def from_hidden_grads(grad_scores, Q, H_d, W, b=None, d_mask=None, *, normalize=True):
+    """Gradients of maxsim_from_hidden w.r.t. (Q, H_d, W, b) in fp64: MaxSim backward onto the projected tokens,
+    the normalise Jacobian (norm clamped at 1e-12, as F.normalize differentiates), then the linear layer."""
+    Q64, H64, W64 = (np.asarray(x, dtype=np.float64) for x in (Q, H_d, W))
+    P = H64 @ W64.T + (0 if b is None else np.asarray(b, dtype=np.float64))
+    D = l2_normalize(P, 1e-12) if normalize else P
+    _, am = maxsim(Q64, D, None, d_mask, return_argmax=True)
+    gQ, gD = backward_from_argmax(grad_scores, Q64, D, am)
+    gP = normalize_jacobian(gD, P, eps=1e-12) if normalize else gD
+    gH = gP @ W64
+    gW = np.einsum("jto,jtm->om", gP, H64)
+    gb = gP.sum((0, 1))
+    return gQ, gH, gW, gb
+
+
+# --------------------------------------------------------------------------- #
 # PLAID candidate generation (PARITY UNPINNED: the reference ships the scoring #
 # kernels only; these stages live in fast-plaid, which is not in the reference #
 # tree.  Restated from the published algorithm, Santhanam et al. 2022, and     #

@@ -127,3 +127,14 @@ def retrieve_case(seed, Nq=4, Nd=37, Lq=5, Ld=9, d=16):
     D = rng.standard_normal((Nd, Ld, d)).astype(np.float32)
     dm = prefix_mask(rng.integers(1, Ld + 1, size=Nd), Ld)
     return Q, D, dm
+
+
+def from_hidden_case(seed, Nq=3, Nd=5, Lq=6, Ld=11, d_model=24, d_out=16):
+    """Document hidden states with a projection head: Q[Nq,Lq,d_out], H[Nd,Ld,d_model], W[d_out,d_model], b[d_out]."""
+    rng = np.random.default_rng(seed)
+    Q = unit(rng.standard_normal((Nq, Lq, d_out))).astype(np.float32)
+    H = rng.standard_normal((Nd, Ld, d_model)).astype(np.float32)
+    W = (rng.standard_normal((d_out, d_model)) / np.sqrt(d_model)).astype(np.float32)
+    b = (0.1 * rng.standard_normal(d_out)).astype(np.float32)
+    dm = prefix_mask(rng.integers(1, Ld + 1, size=Nd), Ld)
+    return Q, H, W, b, dm

@@ -174,6 +174,21 @@ def main():
         chk=cases.checksum(qcs, codes, lens), scores=ref.plaid_approx_score_reference(T(qcs), T(codes_ok), T(lens)).numpy()
     )
 
+    # ---- document head: projection + normalise + MaxSim (reference.py:182-210) and its autograd gradients ----
+    Q, H, W, b, dm = cases.from_hidden_case(13)
+    e = dict(chk=cases.checksum(Q, H, W, b, dm))
+    for norm in (True, False):
+        e[f"scores_norm{int(norm)}"] = ref.maxsim_from_hidden_reference(T(Q), T(H), T(W), T(b), tb(dm), normalize=norm).numpy()
+    e["scores_nobias"] = ref.maxsim_from_hidden_reference(T(Q), T(H), T(W), None, tb(dm)).numpy()
+    ts = [T(x.astype(np.float32)).requires_grad_() for x in (Q, H, W, b)]
+    s = ref.maxsim_from_hidden_reference(ts[0], ts[1], ts[2], ts[3], tb(dm))
+    # the reference promotes to fp32 inside; gradients are taken through that graph
+    g = np.random.default_rng(213).standard_normal(tuple(s.shape)).astype(np.float32)
+    (s * T(g)).sum().backward()
+    e["g"] = g
+    e["gQ"], e["gH"], e["gW"], e["gb"] = (t.grad.numpy() for t in ts)
+    out["from_hidden"] = e
+
     for name, d in out.items():
         np.savez_compressed(os.path.join(HERE, f"{name}.npz"), **{k: np.asarray(v) for k, v in d.items()})
         print(f"{name}: {sorted(d)}")

@@ -193,3 +193,15 @@ def test_merge_topk_orders_by_score_then_index():
     i = np.array([[7, 5, 2, -1, 9, -1]], np.int64)
     ms, mi = O.merge_topk(s, i, 3)
     assert mi.tolist() == [[2, 5, 9]] and ms.tolist() == [[3.0, 3.0, 2.0]]
+
+
+def test_document_head_matches_reference():
+    g = load_golden("from_hidden")
+    Q, H, W, b, dm = cases.from_hidden_case(13)
+    _chk(g, Q, H, W, b, dm)
+    assert O.rel_err(O.maxsim_from_hidden(Q, H, W, b, dm), g["scores_norm1"]) < 1e-5
+    assert O.rel_err(O.maxsim_from_hidden(Q, H, W, b, dm, normalize=False), g["scores_norm0"]) < 1e-5
+    assert O.rel_err(O.maxsim_from_hidden(Q, H, W, None, dm), g["scores_nobias"]) < 1e-5
+    gQ, gH, gW, gb = O.from_hidden_grads(g["g"], Q, H, W, b, dm)
+    for got, want in ((gQ, g["gQ"]), (gH, g["gH"]), (gW, g["gW"]), (gb, g["gb"])):
+        assert O.rel_err(got, want) < 1e-4
