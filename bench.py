@@ -751,8 +751,9 @@ def main():
                 "bwd": lambda: maxsim_backward_lowmem(dG, dQ, dD, am),
                 "step": step,
             }[args.only]
-        elif args.only == "retrieve":  # one 4096-document chunk of the corpus, 1024 queries, fused top-k
-            Dc, lc = dense_corpus(0, CHUNK, dev)
+        elif args.only == "retrieve":  # 1024 queries, fused top-k, over one 4096-document chunk (or the first --retrieve-docs documents)
+            n_only = CHUNK if args.retrieve_docs >= 1_000_000 else max(args.retrieve_docs, 1)
+            Dc, lc = dense_corpus(0, n_only, dev)
             mc = torch.arange(300, device=dev)[None, :] < lc[:, None]
             Qc = retrieve_queries(1024, dev)
             part = lambda: lik.retrieve(Qc, Dc, 100, d_mask=mc, normalize=False)  # noqa: E731

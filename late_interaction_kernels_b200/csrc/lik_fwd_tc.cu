@@ -623,7 +623,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
   const int n_tiles = P.tile_q0 ? P.tile_q0[-1] : P.n_tiles;
   const int n_groups = (n_tiles + P.mt - 1) / P.mt;
   const bool list = P.pairing == LIK_PAIR_LIST;
-  const bool topk = P.topk.cand_key != nullptr;
+  const bool topk = !ARGMAX && P.topk.cand_key != nullptr;  // the fused top-k never saves winners
 
   if (tid == 0) {
     mbar_init(smem_u32(&ctl->q_full), 1);
@@ -1549,10 +1549,13 @@ bool fwd_tc_plaid_supported(const lik_fwd_args& a, const TcExtra& x) {
   return plaid_row16_ok(*x.plaid);
 }
 
+int topk_merge_parts(int n_ctas, int n_groups);
+
 namespace {
 struct TcWs {
-  size_t partial, lens, tiles, list, hdr, keys, idx, total;
+  size_t partial, lens, tiles, list, hdr, keys, idx, merge, total;
   long long n_lists;
+  int merge_parts;  // the lists of a query are merged in this many parts first (1: in one pass)
 };
 TcWs tc_ws_layout(const TcPlan& pl, const lik_fwd_args& a, const TcExtra& x) {
   TcWs w{};
@@ -1570,6 +1573,9 @@ TcWs tc_ws_layout(const TcPlan& pl, const lik_fwd_args& a, const TcExtra& x) {
     w.hdr = take((size_t)w.n_lists * sizeof(int2));
     w.keys = take((size_t)w.n_lists * TOPK_CAP * sizeof(float));
     w.idx = take((size_t)w.n_lists * TOPK_CAP * sizeof(int));
+    // few tile groups: a query has lists from many CTAs, which are merged in parts by as many CTAs first
+    w.merge_parts = topk_merge_parts(pl.grid, pl.n_groups);
+    w.merge = take(w.merge_parts > 1 ? (size_t)w.merge_parts * a.q.n_seq * x.topk_k * (sizeof(float) + sizeof(long long)) + 8 : 0);
   }
   w.partial = take(pl.q_chunks > 1 ? (size_t)pl.n_tiles * a.d.n_seq * sizeof(float) : 0);
   w.lens = take((a.d.mask && !a.d.cu) ? (size_t)a.d.n_seq * sizeof(int) : 0);
@@ -1584,7 +1590,7 @@ size_t fwd_tc_workspace(const lik_fwd_args& a, const TcExtra& x) { return tc_ws_
 
 int launch_topk_slots(const float* keys, const int* idx, const int2* hdr, long long n_lists, int cap, int n_ctas, int n_groups,
                       int mt, int qpt, long long n_q, int k, int largest, long long index_offset, float* out_scores,
-                      long long* out_index, cudaStream_t st);
+                      long long* out_index, int parts, void* part_buf, cudaStream_t st);
 
 int launch_fwd_tc(const lik_fwd_args& a, const float* qn, const float* dn, void* ws, size_t ws_bytes, cudaStream_t st,
                   const TcExtra& x) {
@@ -1713,7 +1719,8 @@ int launch_fwd_tc(const lik_fwd_args& a, const float* qn, const float* dn, void*
   }
   if (x.topk_k > 0 && !(x.topk_flags & LIK_TOPK_PARTIAL)) {
     rc = launch_topk_slots(P.topk.cand_key, P.topk.cand_idx, P.topk.hdr, w.n_lists, TOPK_CAP, pl.grid, pl.n_groups, pl.mt, pl.q_per_tile,
-                           a.q.n_seq, x.topk_k, x.topk_largest, x.topk_index_offset, x.topk_scores, (long long*)x.topk_index, st);
+                           a.q.n_seq, x.topk_k, x.topk_largest, x.topk_index_offset, x.topk_scores, (long long*)x.topk_index,
+                           w.merge_parts, w.merge_parts > 1 ? (char*)ws + w.merge : nullptr, st);
     if (rc) return rc;
   }
   return LIK_OK;

@@ -164,7 +164,10 @@ __global__ void __launch_bounds__(256) topk_kernel(TopkParams P) {
 // only have worked on the groups [n_groups * c / n_ctas, n_groups * (c + 1) / n_ctas] (a superset of the ones
 // it really met; lists it never touched are empty).  A group is `mt` query tiles of `qpt` queries; with two
 // tiles a query has one list per slot (tile * qpt + position), with one tile it has two (the kernel's two
-// epilogue groups take alternate documents).  One CTA per query.
+// epilogue groups take alternate documents).  One CTA per (query, part): with few tile groups a query has lists
+// from many CTAs, which would make one CTA walk hundreds of lists one after the other, so the CTAs' range is cut
+// in `parts` parts merged side by side into [parts, n_q, k] lists, and the plain list merge (topk_kernel) makes
+// the answer from those.
 struct SlotParams {
   const float* keys;
   const int* idx;
@@ -174,6 +177,7 @@ struct SlotParams {
   int k, KP, largest;
   float* out_scores;
   long long* out_index;
+  int parts;  // > 1: blockIdx.y is the part, the outputs are [parts, n_q, k] and carry keys' signs undone
 };
 
 constexpr int SLOT_W = 256;  // merge width: the capacity of a candidate list, and the block size
@@ -211,7 +215,8 @@ __global__ void __launch_bounds__(SLOT_W) topk_slots_kernel(SlotParams P) {
   top_i[tid] = kPadIdx;
   if (tid == 0) n_pend_s = 0;
   __syncthreads();
-  for (int c = 0; c < P.n_ctas; ++c) {
+  const int c_lo = (int)((long long)P.n_ctas * blockIdx.y / P.parts), c_hi = (int)((long long)P.n_ctas * (blockIdx.y + 1) / P.parts);
+  for (int c = c_lo; c < c_hi; ++c) {
     const long long g_lo = (long long)P.n_groups * c / P.n_ctas, g_hi = (long long)P.n_groups * (c + 1) / P.n_ctas;
     if (g < g_lo || g > g_hi) continue;
     for (int sub = 0; sub < n_sub; ++sub) {
@@ -252,23 +257,54 @@ __global__ void __launch_bounds__(SLOT_W) topk_slots_kernel(SlotParams P) {
   const float sgn = P.largest ? 1.f : -1.f;
   if (tid < P.k) {
     const bool pad = top_i[tid] == kPadIdx;
-    P.out_scores[q * P.k + tid] = pad ? -sgn * INFINITY : sgn * top_k[tid];
-    P.out_index[q * P.k + tid] = pad ? -1 : top_i[tid] + P.index_offset;
+    const long long o = ((long long)blockIdx.y * P.n_q + q) * P.k + tid;
+    P.out_scores[o] = pad ? -sgn * INFINITY : sgn * top_k[tid];
+    P.out_index[o] = pad ? -1 : top_i[tid] + P.index_offset;
   }
+}
+
+static int launch_topk(TopkParams& P, cudaStream_t st);
+
+// In how many parts the lists of a query are merged first: a part should not walk more than about 24 CTAs' lists.
+int topk_merge_parts(int n_ctas, int n_groups) {
+  if (n_ctas <= 0 || n_groups <= 0) return 1;
+  const int ctas_per_group = n_ctas / n_groups + 2;  // CTAs whose share of the units can touch one tile group
+  if (ctas_per_group <= 32) return 1;
+  const int parts = (ctas_per_group + 15) / 16;
+  return parts > 16 ? 16 : parts;
 }
 
 int launch_topk_slots(const float* keys, const int* idx, const int2* hdr, long long n_lists, int cap, int n_ctas, int n_groups,
                       int mt, int qpt, long long n_q, int k, int largest, long long index_offset, float* out_scores,
-                      long long* out_index, cudaStream_t st) {
+                      long long* out_index, int parts, void* part_buf, cudaStream_t st) {
   if (n_q <= 0 || k <= 0) return LIK_OK;
   if (cap > SLOT_W || k > SLOT_W) {
     set_error("candidate lists of %d entries / k = %d exceed the merge width %d", cap, k, SLOT_W);
     return LIK_ERR_UNSUPPORTED;
   }
-  SlotParams P{keys, idx, hdr, cap, n_ctas, n_groups, mt, qpt, n_q, index_offset, n_lists, k, 2, largest, out_scores, out_index};
-  topk_slots_kernel<<<(unsigned)n_q, SLOT_W, 0, st>>>(P), ::lik::count_launch();
+  if (parts <= 1 || !part_buf) {
+    SlotParams P{keys, idx, hdr, cap, n_ctas, n_groups, mt, qpt, n_q, index_offset, n_lists, k, 2, largest, out_scores, out_index, 1};
+    topk_slots_kernel<<<(unsigned)n_q, SLOT_W, 0, st>>>(P), ::lik::count_launch();
+    LIK_CUDA_OK(cudaGetLastError());
+    return LIK_OK;
+  }
+  float* part_scores = (float*)part_buf;
+  long long* part_index = (long long*)((char*)part_buf + align_up((size_t)parts * n_q * k * sizeof(float), 8));
+  SlotParams P{keys, idx, hdr, cap, n_ctas, n_groups, mt, qpt, n_q, index_offset, n_lists, k, 2, largest, part_scores, part_index, parts};
+  topk_slots_kernel<<<dim3((unsigned)n_q, (unsigned)parts), SLOT_W, 0, st>>>(P), ::lik::count_launch();
   LIK_CUDA_OK(cudaGetLastError());
-  return LIK_OK;
+  TopkParams M{};
+  M.mode = 1;
+  M.cand_scores = part_scores;
+  M.cand_index = part_index;
+  M.n_lists = parts;
+  M.n_rows = n_q;
+  M.k = k;
+  M.largest = largest;
+  M.merge = 0;
+  M.out_scores = out_scores;
+  M.out_index = out_index;
+  return launch_topk(M, st);
 }
 
 static int launch_topk(TopkParams& P, cudaStream_t st) {

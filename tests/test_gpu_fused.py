@@ -178,7 +178,7 @@ def test_plaid_retrieve_in_one_kernel_and_in_pieces(monkeypatch):
         used = _lib.load().lik_launch_count() - n0
         assert torch.equal(i, wi) and torch.equal(s, ws), (nq, in_kernel, budget)
         if in_kernel:
-            assert used <= 3, f"query norms, decode + score + top-k in one kernel, merge (saw {used} launches)"
+            assert used <= 4, f"query norms, decode + score + top-k in one kernel, merge in parts + of the parts (saw {used} launches)"
         elif budget == 20_000:
             assert used >= 4 * 3, "several pieces, each decoded and scored into the same candidate lists"
         s, i = plaid.retrieve_residual_varlen(*args, 100, chunk=700, largest=False)
