@@ -307,12 +307,234 @@ int launch_topk_slots(const float* keys, const int* idx, const int2* hdr, long l
   return launch_topk(M, st);
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// Top-k of score rows by selection instead of sorting (mode 0 of TopkParams).
+//
+// One CTA of SEL_T threads per row.  The row is taken in slabs of SEL_SLAB columns that live in registers
+// (SEL_PER per thread, column = slab + j * SEL_T + thread); the k entries kept so far (the running list, or
+// the list the caller merges into) are SEL_OLD more elements per thread.  The k-th best key of all of them is
+// found by a radix select on the order-preserving 32-bit image of the float (four passes of 256 shared-memory
+// counters); entries above it are kept, and of the entries equal to it the ones with the lowest document
+// index (a second select, on the index, only when the equal entries do not all fit).  The kept k are sorted
+// once per slab that changed anything (best first, ties to the lower index) - a slab with nothing above the
+// current k-th best is dismissed after one pass over its values.
+// ---------------------------------------------------------------------------------------------
+constexpr int SEL_T = 256;
+constexpr int SEL_PER = 16;
+constexpr int SEL_SLAB = SEL_T * SEL_PER;
+constexpr int SEL_OLD = LIK_TOPK_MAX / SEL_T;
+constexpr int SEL_NE = SEL_PER + SEL_OLD;
+
+// Monotone map float -> unsigned (larger float, larger key); 0 is below every float.
+__device__ __forceinline__ unsigned sel_key(float f) {
+  const unsigned u = __float_as_uint(f);
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+
+struct SelShared {
+  int hist[256];
+  int digit, want, n_eq, count;
+};
+
+// Radix select over the elements every thread holds: key[e] (larger is better) of the elements with on[e], `nbits`
+// wide.  Returns the key of rank `want` (1 = the best) to every thread; *need_eq = how many of the elements equal to
+// it belong to the best `want`, *n_eq = how many elements equal it.  All threads of the block call it.
+template <typename K>
+__device__ K block_select(const K (&key)[SEL_NE], const bool (&on)[SEL_NE], int nbits, int want, SelShared* sh, int* need_eq, int* n_eq) {
+  const int tid = threadIdx.x, lane = tid & 31;
+  K prefix = 0;
+  for (int shift = nbits - 8; shift >= 0; shift -= 8) {
+    sh->hist[tid] = 0;
+    __syncthreads();
+#pragma unroll
+    for (int e = 0; e < SEL_NE; ++e) {
+      // bits above this digit must match what is fixed already (nothing in the first pass)
+      const bool same = shift + 8 >= nbits || (key[e] >> (shift + 8)) == (prefix >> (shift + 8));
+      if (on[e] && same) atomicAdd(&sh->hist[(int)((key[e] >> shift) & 255)], 1);
+    }
+    __syncthreads();
+    if (tid < 32) {
+      // lane l owns the bins 255 - 8 l ... 248 - 8 l (best first); find the bin in which the running count reaches `want`
+      int c[8], s = 0;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        c[i] = sh->hist[255 - 8 * lane - i];
+        s += c[i];
+      }
+      int incl = s;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int v = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += v;
+      }
+      int above = incl - s;
+      if (above < want && want <= incl) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          if (above < want && want <= above + c[i]) {
+            sh->digit = 255 - 8 * lane - i;
+            sh->want = want - above;
+            sh->n_eq = c[i];
+          }
+          above += c[i];
+        }
+      }
+    }
+    __syncthreads();
+    prefix |= (K)sh->digit << shift;
+    want = sh->want;
+  }
+  *need_eq = want;
+  *n_eq = sh->n_eq;
+  __syncthreads();  // the shared words may be rewritten by the next call
+  return prefix;
+}
+
+__global__ void __launch_bounds__(SEL_T, 3) topk_select_kernel(TopkParams P) {
+  extern __shared__ unsigned char raw[];
+  long long* top_i = reinterpret_cast<long long*>(raw);
+  float* top_k = reinterpret_cast<float*>(top_i + P.KP);
+  __shared__ SelShared sh;
+  const int tid = threadIdx.x;
+  const long long row = blockIdx.x;
+  const float sgn = P.largest ? 1.f : -1.f;
+
+  // the kept list: what the caller merges into, or empty
+  for (int t = tid; t < P.KP; t += SEL_T) {
+    float key = -INFINITY;
+    long long id = kPadIdx;
+    if (P.merge && t < P.k) {
+      const long long o = P.out_index[row * P.k + t];
+      if (o >= 0) {
+        id = o;
+        key = sgn * P.out_scores[row * P.k + t] + 0.f;
+      }
+    }
+    top_k[t] = key;
+    top_i[t] = id;
+  }
+  if (tid == 0) sh.count = 0;
+  __syncthreads();
+  bool sorted = !P.merge;  // an empty list is in order; a caller's list is taken as it comes
+  // k-th best of the kept list as a key (0: the list is not full) - a slab must beat it to matter
+  unsigned kth_key = 0;
+
+  const long long n_slabs = (P.n_cols + SEL_SLAB - 1) / SEL_SLAB;
+  for (long long sl = 0; sl < (n_slabs > 0 ? n_slabs : 1); ++sl) {
+    float f[SEL_NE];
+    unsigned u[SEL_NE];
+    bool on[SEL_NE];
+    int hit = 0;
+#pragma unroll
+    for (int j = 0; j < SEL_PER; ++j) {
+      const long long c = sl * SEL_SLAB + (long long)j * SEL_T + tid;
+      on[j] = c < P.n_cols;
+      f[j] = on[j] ? sgn * P.scores[row * P.ld + c] + 0.f : -INFINITY;
+      u[j] = on[j] ? sel_key(f[j]) : 0u;
+      if (on[j] && u[j] >= kth_key) hit = 1;  // (an equal key only matters against a higher kept index; rare, so let it through)
+    }
+    const bool last = sl + 1 >= n_slabs;
+    if (!__syncthreads_or(hit) && !(last && !sorted)) continue;
+#pragma unroll
+    for (int m = 0; m < SEL_OLD; ++m) {
+      const int t = m * SEL_T + tid;
+      on[SEL_PER + m] = t < P.k && top_i[t] != kPadIdx;
+      f[SEL_PER + m] = on[SEL_PER + m] ? top_k[t] : -INFINITY;
+      u[SEL_PER + m] = on[SEL_PER + m] ? sel_key(f[SEL_PER + m]) : 0u;
+    }
+    // kept entries carry their document index; a slab element's is its column
+    long long my_idx[SEL_OLD];
+#pragma unroll
+    for (int m = 0; m < SEL_OLD; ++m) my_idx[m] = on[SEL_PER + m] ? top_i[m * SEL_T + tid] : kPadIdx;
+    // how many real elements there are: with fewer than k, all of them are kept
+    int mine = 0;
+#pragma unroll
+    for (int e = 0; e < SEL_NE; ++e) mine += on[e] ? 1 : 0;
+    // block-wide count of the elements
+    {
+      int w = mine;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) w += __shfl_xor_sync(0xffffffffu, w, o);
+      if ((tid & 31) == 0 && w) atomicAdd(&sh.count, w);
+    }
+    __syncthreads();
+    const int n_all = sh.count;
+    __syncthreads();
+    if (tid == 0) sh.count = 0;
+    const int want = n_all < P.k ? n_all : P.k;
+    unsigned T = 0;
+    int need_eq = 0, n_eq = 0;
+    unsigned long long Ti = 0;  // ties: the kept ones have ~index >= Ti
+    bool all_ties = true;
+    if (want > 0 && n_all > P.k) {
+      T = block_select<unsigned>(u, on, 32, want, &sh, &need_eq, &n_eq);
+      if (need_eq < n_eq) {
+        // more entries equal the k-th best than fit: the lowest document indices win
+        unsigned long long ik[SEL_NE];
+        bool tie[SEL_NE];
+#pragma unroll
+        for (int e = 0; e < SEL_NE; ++e) {
+          tie[e] = on[e] && u[e] == T;
+          const long long id = e < SEL_PER ? sl * SEL_SLAB + (long long)e * SEL_T + tid + P.index_offset : my_idx[e - SEL_PER];
+          ik[e] = ~(unsigned long long)id;
+        }
+        int ne2 = 0, nn2 = 0;
+        Ti = block_select<unsigned long long>(ik, tie, 64, need_eq, &sh, &ne2, &nn2);
+        all_ties = false;
+      }
+    }
+    __syncthreads();  // everyone has read the kept list; it is rebuilt now
+    // gather the kept elements (any order), pad, sort
+    int my_pos[SEL_NE];
+#pragma unroll
+    for (int e = 0; e < SEL_NE; ++e) {
+      bool take = on[e] && (n_all <= P.k || u[e] > T);
+      if (on[e] && n_all > P.k && u[e] == T) {
+        const long long id = e < SEL_PER ? sl * SEL_SLAB + (long long)e * SEL_T + tid + P.index_offset : my_idx[e - SEL_PER];
+        take = all_ties || ~(unsigned long long)id >= Ti;
+      }
+      my_pos[e] = take ? atomicAdd(&sh.count, 1) : -1;
+    }
+    __syncthreads();
+    const int n_kept = sh.count;
+    __syncthreads();
+    if (tid == 0) sh.count = 0;
+#pragma unroll
+    for (int e = 0; e < SEL_NE; ++e) {
+      if (my_pos[e] >= 0 && my_pos[e] < P.KP) {
+        top_k[my_pos[e]] = f[e];
+        top_i[my_pos[e]] = e < SEL_PER ? sl * SEL_SLAB + (long long)e * SEL_T + tid + P.index_offset : my_idx[e - SEL_PER];
+      }
+    }
+    for (int t = n_kept + tid; t < P.KP; t += SEL_T) {
+      top_k[t] = -INFINITY;
+      top_i[t] = kPadIdx;
+    }
+    __syncthreads();
+    bitonic_sort(top_k, top_i, P.KP, tid, SEL_T);
+    sorted = true;
+    kth_key = (n_kept >= P.k) ? sel_key(top_k[P.k - 1]) : 0u;
+  }
+  for (int t = tid; t < P.k; t += SEL_T) {
+    const bool pad = top_i[t] == kPadIdx;
+    P.out_scores[row * P.k + t] = pad ? -sgn * INFINITY : sgn * top_k[t];
+    P.out_index[row * P.k + t] = pad ? -1 : top_i[t];
+  }
+}
+
 static int launch_topk(TopkParams& P, cudaStream_t st) {
   if (P.n_rows <= 0 || P.k <= 0) return LIK_OK;
   int KP = 1;
   while (KP < P.k) KP <<= 1;
   if (KP < 2) KP = 2;
   P.KP = KP;
+  if (P.mode == 0) {
+    const size_t smem = (size_t)KP * (sizeof(long long) + sizeof(float));
+    topk_select_kernel<<<(unsigned)P.n_rows, SEL_T, smem, st>>>(P), ::lik::count_launch();
+    LIK_CUDA_OK(cudaGetLastError());
+    return LIK_OK;
+  }
   size_t smem = (size_t)KP * 2 * (sizeof(long long) + sizeof(float));
   topk_kernel<<<(unsigned)P.n_rows, 256, smem, st>>>(P), ::lik::count_launch();
   LIK_CUDA_OK(cudaGetLastError());

@@ -146,13 +146,15 @@ def plaid_candidates(index: PlaidIndexData, qcs: torch.Tensor, nprobe: int) -> t
 
 
 @torch.no_grad()
-def plaid_search(index: PlaidIndexData, Q: torch.Tensor, top_k: int, *, nprobe: int = 4, ndocs: int = 4096,
+def plaid_search(index: PlaidIndexData, Q: torch.Tensor, top_k: int, *, nprobe: int = 4, ndocs: int = 1024,
                  normalize: bool = True):
     """PLAID search of one query ``[Lq, d]`` (or ``[Nq, Lq, d]``: one search per query, their candidate sets differ).
     Returns ``(scores fp32 [k], document ids int64 [k])`` (``[Nq, k]`` for a batch, padded with ``-inf`` / ``-1``
     when a query has fewer than ``k`` candidates), best first."""
     if top_k <= 0:
         raise ValueError(f"top_k must be positive, got {top_k}")
+    if not 0 < ndocs <= _lib.TOPK_MAX:
+        raise ValueError(f"ndocs must be in [1, {_lib.TOPK_MAX}] (the widest list the top-k kernels keep); got {ndocs}")
     _lib.require_cuda(Q, index.codes_flat, op="plaid_search")
     if Q.dim() == 3:
         outs = [plaid_search(index, q, top_k, nprobe=nprobe, ndocs=ndocs, normalize=normalize) for q in Q]
