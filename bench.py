@@ -87,6 +87,13 @@ def profiled_traffic(kernel_key):
         return None
 
 
+def scaled_traffic(kernel_key, units):
+    """DRAM bytes of a launch from a capture of a smaller case of the same kernel: the committed figure is per unit
+    (document, token) and traffic grows in proportion to the units."""
+    per = profiled_traffic(kernel_key)
+    return None if per is None else per * float(units)
+
+
 def roofline(bound, work, seconds, *, kernel, note=None, traffic=None, sustained=False):
     """One roofline entry: achieved = algorithmic FLOPs (bound "tensor") or bytes (bound "hbm") / time."""
     peak_tf, peak_gb, which = measured_peaks(sustained)
@@ -436,6 +443,7 @@ def retrieve_bench(n_docs, world, rank, dev, verify):
            "tflops_valid": flops / (ms_med * 1e-3) / 1e12, "launches_per_batch_per_rank": int(launches),
            "clocks": clk.summary(),
            "roofline": roofline("tensor", flops / world, ms_med * 1e-3, kernel="fwd_tc_kernel (bf16, fused top-k)", sustained=True,
+                                traffic=scaled_traffic("fwd_tc_kernel_topk_per_document", n_docs / world),
                                 note="per GPU: valid FLOPs of the shard over the batch time; one kernel runs for the whole "
                                      "batch, so the power cap sets the clock and the sustained cuBLAS figure is the peak")}
     # the default of retrieve(): fused L2 normalisation of both sides
@@ -654,6 +662,7 @@ def other_configs(dev):
             t = _time_us(lambda: _ops.plaid_decompress(ix, 0, T, True, torch.bfloat16, dev), dev)
             out["plaid_decompress"] = {"us": t, "tokens": T,
                                        "roofline": roofline("hbm", T * (36.0 + 256.0), t * 1e-6, kernel="plaid_decompress16_kernel",
+                                                            traffic=scaled_traffic("plaid_decompress16_kernel_per_token", T),
                                                             note="4 B code + 32 B residual in, 256 B bf16 row out per token")}
         for nq in (1, 8, 32):
             Qq = retrieve_queries(nq, dev)
@@ -667,8 +676,10 @@ def other_configs(dev):
     sc = torch.randn((1024, 4096), generator=g, device=dev)
     t = _time_us(lambda: _ops.topk_rows(sc, 100), dev, graph=True)
     out["topk_rows"] = {"us": t, "shape": "[1024, 4096] fp32 -> top-100",
-                        "roofline": roofline("hbm", sc.numel() * 4.0, t * 1e-6, kernel="topk_kernel",
-                                             note="one read of the scores; the kernel is bound by its shared-memory sorts")}
+                        "roofline": roofline("hbm", sc.numel() * 4.0, t * 1e-6, kernel="topk_select_kernel",
+                                             traffic=profiled_traffic("topk_select_kernel_1024x4096"),
+                                             note="one read of the scores; the kernel is bound by its radix-select passes "
+                                                  "(shared-memory counters) and the sort of the k winners")}
     return out
 
 
@@ -910,6 +921,7 @@ def main():
             "step_kernels": {
                 "forward_no_argmax": roofline("tensor", fwd_flops, infer_ms * 1e-3, kernel="fwd_tc_kernel (bf16, masked)"),
                 "backward": roofline("hbm", bwd_bytes, bwd_ms * 1e-3, kernel="bwd_dq16 + bwd_dd_sort4 + bwd_dd_reduce16",
+                                     traffic=profiled_traffic("bwd_three_kernels_inbatch"),
                                      note="algorithmic bytes: Q, valid D rows, winners, upstream gradient in; both gradients out.  "
                                           "The kernels gather one 256-byte row per (pair, query token) out of L2, 34x these bytes"),
             },
