@@ -1592,6 +1592,20 @@ int launch_topk_slots(const float* keys, const int* idx, const int2* hdr, long l
                       int mt, int qpt, long long n_q, int k, int largest, long long index_offset, float* out_scores,
                       long long* out_index, int parts, void* part_buf, cudaStream_t st);
 
+// Raise the kernel's dynamic shared memory limit once per device and size instead of on every launch (a host call
+// of a microsecond or two that small problems feel).
+template <bool F, bool A, bool X, bool PL>
+static cudaError_t allow_smem(size_t bytes) {
+  static size_t allowed[64] = {0};  // by device ordinal
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev >= 0 && dev < 64 && allowed[dev] >= bytes) return cudaSuccess;
+  e = cudaFuncSetAttribute(fwd_tc_kernel<F, A, X, PL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+  if (e == cudaSuccess && dev >= 0 && dev < 64) allowed[dev] = bytes;
+  return e;
+}
+
 int launch_fwd_tc(const lik_fwd_args& a, const float* qn, const float* dn, void* ws, size_t ws_bytes, cudaStream_t st,
                   const TcExtra& x) {
   TcPlan pl = plan_tc(a, x);
@@ -1693,8 +1707,8 @@ int launch_fwd_tc(const lik_fwd_args& a, const float* qn, const float* dn, void*
   dim3 grid((unsigned)pl.grid), block(NUM_THREADS);
 #define LIK_TC_LAUNCH(F, A, X, PL)                                                                                     \
   do {                                                                                                                 \
-    LIK_CUDA_OK(cudaFuncSetAttribute(fwd_tc_kernel<F, A, X, PL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem_bytes)); \
-    fwd_tc_kernel<F, A, X, PL><<<grid, block, pl.smem_bytes, st>>>(q_map, d_maps, P), ::lik::count_launch();                                   \
+    LIK_CUDA_OK((allow_smem<F, A, X, PL>(pl.smem_bytes)));                                                             \
+    fwd_tc_kernel<F, A, X, PL><<<grid, block, pl.smem_bytes, st>>>(q_map, d_maps, P), ::lik::count_launch();           \
   } while (0)
   if (plaid) {
     if (argmax) LIK_TC_LAUNCH(false, true, false, true);
