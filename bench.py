@@ -602,6 +602,18 @@ def other_configs(dev):
 
     out = {}
     g = torch.Generator(device=dev).manual_seed(7)
+    # the small fp32 case (the one the CPU oracle runs in full): Q[32,32,128] x D[32,180,128], fused normalisation, ragged both sides
+    Qf = torch.randn((32, 32, 128), generator=g, device=dev)
+    Df = torch.randn((32, 180, 128), generator=g, device=dev)
+    qlf = torch.randint(8, 33, (32,), generator=g, device=dev)
+    dlf = torch.randint(32, 181, (32,), generator=g, device=dev)
+    qmf = torch.arange(32, device=dev)[None, :] < qlf[:, None]
+    dmf = torch.arange(180, device=dev)[None, :] < dlf[:, None]
+    t = _time_us(lambda: lik.maxsim(Qf, Df, q_mask=qmf, d_mask=dmf, normalize=True), dev, graph=True)
+    flf = 2.0 * 128 * float(qlf.sum()) * float(dlf.sum())
+    out["inbatch_fp32_fwd_32x32"] = {"us": t, "shape": "fp32 Q[32,32,128] x D[32,180,128], normalize, q U[8,32], d U[32,180]",
+                                     "tflops_valid": flf / (t * 1e-6) / 1e12,
+                                     "note": "exact fp32-FMA kernel (fwd_generic_kernel); a launch-latency-sized problem"}
     # KD: Q[64,32,128] x D[64,32,300,128], lengths U[64,300] per candidate
     Q = F.normalize(torch.randn((64, 32, 128), generator=g, device=dev), dim=-1)
     D = F.normalize(torch.randn((64, 32, 300, 128), generator=g, device=dev), dim=-1)
