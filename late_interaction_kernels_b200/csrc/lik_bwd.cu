@@ -776,6 +776,61 @@ struct DdSortOut {
   int* tok_cnt;           // [d.n_rows] list length (zero-initialised by the launcher)
 };
 
+// Offsets of the winner sort.  In: hist[w][t] = winners of token t counted by warp w.  Out: the token's first list entry
+// and count (global), and hist[w][t] = first write position of warp w for token t.  All warps work: each takes whole
+// blocks of 32 tokens (totals, prefix inside the block), warp 0 scans the block totals, then every warp finishes
+// its blocks.  tok_off [ld_pad] and blk [ceil(ld_pad / 32) + 1] are scratch in shared memory.
+__device__ __forceinline__ void dds_offsets(int* hist, int* tok_off, int* blk, int n_warps, int ld_pad, int dlen, long long base,
+                                            long long drow0, const DdSortOut& O, int warp, int lane) {
+  const int n_blk = (dlen + 31) >> 5;
+  for (int b = warp; b < n_blk; b += n_warps) {
+    const int t = b * 32 + lane;
+    int tot = 0;
+    if (t < dlen)
+      for (int w = 0; w < n_warps; ++w) tot += hist[w * ld_pad + t];
+    int incl = tot;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int v = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += v;
+    }
+    if (t < dlen) tok_off[t] = incl - tot;
+    if (lane == 31) blk[b] = incl;
+  }
+  __syncthreads();
+  if (warp == 0) {
+    int running = 0;
+    for (int b0 = 0; b0 < n_blk; b0 += 32) {
+      const int b = b0 + lane;
+      const int tot = b < n_blk ? blk[b] : 0;
+      int incl = tot;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int v = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += v;
+      }
+      if (b < n_blk) blk[b] = running + incl - tot;
+      running += __shfl_sync(0xffffffffu, incl, 31);
+    }
+  }
+  __syncthreads();
+  for (int b = warp; b < n_blk; b += n_warps) {
+    const int t = b * 32 + lane;
+    if (t < dlen) {
+      const int excl = blk[b] + tok_off[t];
+      int pos = excl;
+      for (int w = 0; w < n_warps; ++w) {
+        const int c = hist[w * ld_pad + t];
+        hist[w * ld_pad + t] = pos;
+        pos += c;
+      }
+      O.tok_begin[drow0 + t] = base + excl;
+      O.tok_cnt[drow0 + t] = pos - excl;
+    }
+  }
+  __syncthreads();
+}
+
 __global__ void __launch_bounds__(DDS_WARPS * 32) bwd_dd_sort_kernel(BwdParams P, DdSortOut O, int ld_pad) {
   const int n_warps = blockDim.x >> 5;  // the launcher sizes the CTA to the entries per document
   extern __shared__ int dds_raw[];
@@ -797,7 +852,8 @@ __global__ void __launch_bounds__(DDS_WARPS * 32) bwd_dd_sort_kernel(BwdParams P
   const long long base = list ? ds.first * lq : (long long)j * n_ent;  // first entry of the document's slice of the list
   int* hist = dds_raw;                          // [n_warps][ld_pad]
   int* tok_off = hist + n_warps * ld_pad;     // [ld_pad + 1]
-  float* gcol = reinterpret_cast<float*>(tok_off + ld_pad + 1);  // [n_qr] (not for pair lists)
+  int* blk = tok_off + ld_pad + 1;            // [ceil(ld_pad / 32) + 1]
+  float* gcol = reinterpret_cast<float*>(blk + (ld_pad + 31) / 32 + 1);  // [n_qr] (not for pair lists)
 
   for (int x = tid; x < n_warps * ld_pad; x += blockDim.x) hist[x] = 0;
   if (!list)
@@ -842,34 +898,7 @@ __global__ void __launch_bounds__(DDS_WARPS * 32) bwd_dd_sort_kernel(BwdParams P
   }
   __syncthreads();
   // offsets: warp 0 scans the tokens; hist[w][t] becomes the first write position of warp w for token t
-  if (warp == 0) {
-    int running = 0;
-    for (int tb = 0; tb < dlen; tb += 32) {
-      const int t = tb + lane;
-      int tot = 0;
-      if (t < dlen)
-        for (int w = 0; w < n_warps; ++w) tot += hist[w * ld_pad + t];
-      int incl = tot;
-#pragma unroll
-      for (int o = 1; o < 32; o <<= 1) {
-        int v = __shfl_up_sync(0xffffffffu, incl, o);
-        if (lane >= o) incl += v;
-      }
-      const int excl = running + incl - tot;
-      if (t < dlen) {
-        O.tok_begin[drow0 + t] = base + excl;
-        O.tok_cnt[drow0 + t] = tot;
-        int b = excl;
-        for (int w = 0; w < n_warps; ++w) {
-          const int c = hist[w * ld_pad + t];
-          hist[w * ld_pad + t] = b;
-          b += c;
-        }
-      }
-      running += __shfl_sync(0xffffffffu, incl, 31);
-    }
-  }
-  __syncthreads();
+  dds_offsets(hist, tok_off, blk, n_warps, ld_pad, dlen, base, drow0, O, warp, lane);
   // stable placement
   int t_next = raw_winner(e_lo + lane);
   for (int eb = e_lo; eb < e_hi; eb += 32) {
@@ -995,17 +1024,28 @@ __global__ void __launch_bounds__(DDS_WARPS * 32) bwd_dd_sort4_kernel(BwdParams 
   const int n_ent = n_quad * 4;
   const long long base = list ? ds.first * lq : (long long)j * n_ent;
   int* hist = dds_raw;                          // [n_warps][ld_pad]
-  int* tok_off = hist + n_warps * ld_pad;     // [ld_pad + 1] (kept for the layout shared with the scalar kernel)
-  float* gcol = reinterpret_cast<float*>(tok_off + ld_pad + 1);  // [n_qr] (not for pair lists)
+  int* tok_off = hist + n_warps * ld_pad;     // [ld_pad + 1]
+  int* blk = tok_off + ld_pad + 1;            // [ceil(ld_pad / 32) + 1]
+  float* gcol = reinterpret_cast<float*>(blk + (ld_pad + 31) / 32 + 1);  // [n_qr] (not for pair lists)
+  int* q_first = reinterpret_cast<int*>(gcol + ds.n_qr);  // [n_qr] first row and length of every score's query (not for pair lists)
+  int* q_len = q_first + ds.n_qr;
 
   for (int x = tid; x < n_warps * ld_pad; x += blockDim.x) hist[x] = 0;
   if (!list)
-    for (int x = tid; x < ds.n_qr; x += blockDim.x) gcol[x] = P.g[doc_slot(P, ds, j, x)];
+    for (int x = tid; x < ds.n_qr; x += blockDim.x) {
+      const long long slot = doc_slot(P, ds, j, x);
+      gcol[x] = P.g[slot];
+      long long r0;
+      int len;
+      seq_bounds(P.q, doc_query(P, ds, x, slot), r0, len, nullptr);
+      q_first[x] = (int)r0;
+      q_len[x] = len;
+    }
   __syncthreads();
 
-  // slice of this warp in 16-byte groups, a multiple of 32 * DDS_LOADS so that rounds stay whole
+  // slice of this warp in 16-byte groups (whole warp loads); a round is DDS_LOADS loads per lane
   const int round_quads = 32 * DDS_LOADS;
-  const int per_warp = (((n_quad + n_warps - 1) / n_warps + round_quads - 1) / round_quads) * round_quads;
+  const int per_warp = ((n_quad + n_warps - 1) / n_warps + 31) & ~31;
   const int m_lo = warp * per_warp, m_hi = min(n_quad, m_lo + per_warp);
   const int4 none = make_int4(-1, -1, -1, -1);
 
@@ -1016,9 +1056,15 @@ __global__ void __launch_bounds__(DDS_WARPS * 32) bwd_dd_sort4_kernel(BwdParams 
   };
   // first query row and length of the query of score ii (and its upstream gradient)
   auto query_of = [&](int ii, long long& qrow0, int& qlen, float& gg) {
-    const long long slot = doc_slot(P, ds, j, ii);
-    seq_bounds(P.q, doc_query(P, ds, ii, slot), qrow0, qlen, nullptr);
-    gg = list ? P.g[slot] : gcol[ii];
+    if (list) {
+      const long long slot = doc_slot(P, ds, j, ii);
+      seq_bounds(P.q, doc_query(P, ds, ii, slot), qrow0, qlen, nullptr);
+      gg = P.g[slot];
+    } else {
+      qrow0 = q_first[ii];
+      qlen = q_len[ii];
+      gg = gcol[ii];
+    }
   };
 
   // ---- pass 1: per-warp histogram of the winners per token ----
@@ -1045,34 +1091,7 @@ __global__ void __launch_bounds__(DDS_WARPS * 32) bwd_dd_sort4_kernel(BwdParams 
   }
   __syncthreads();
   // ---- offsets: warp 0 scans the per-token totals ----
-  if (warp == 0) {
-    int running = 0;
-    for (int tb = 0; tb < dlen; tb += 32) {
-      const int t = tb + lane;
-      int tot = 0;
-      if (t < dlen)
-        for (int w = 0; w < n_warps; ++w) tot += hist[w * ld_pad + t];
-      int incl = tot;
-#pragma unroll
-      for (int o = 1; o < 32; o <<= 1) {
-        int v = __shfl_up_sync(0xffffffffu, incl, o);
-        if (lane >= o) incl += v;
-      }
-      const int excl = running + incl - tot;
-      if (t < dlen) {
-        O.tok_begin[drow0 + t] = base + excl;
-        O.tok_cnt[drow0 + t] = tot;
-        int b = excl;
-        for (int w = 0; w < n_warps; ++w) {
-          const int c = hist[w * ld_pad + t];
-          hist[w * ld_pad + t] = b;
-          b += c;
-        }
-      }
-      running += __shfl_sync(0xffffffffu, incl, 31);
-    }
-  }
-  __syncthreads();
+  dds_offsets(hist, tok_off, blk, n_warps, ld_pad, dlen, base, drow0, O, warp, lane);
   // ---- pass 2: placement (the winners come from L2 this time) ----
   for (int mb = m_lo; mb < m_hi; mb += round_quads) {
     int4 w[DDS_LOADS];
@@ -1270,7 +1289,7 @@ struct BwdPlan {
   size_t kq_off, kd_off, pq_off, pd_off, sq_off, sd_off, sort_off;  // pair lists grouped by query / by document
   bool fast, sorted;
   bool list_sorted;  // pair list on the deterministic kernels
-  int sort_warps;    // warps per CTA of the winner sort: about 2048 entries of a document per warp
+  int sort_warps;    // warps per CTA of the winner sort: at least 256 entries of a document per warp
   bool row16;  // 16-byte gathers: rows 16-byte aligned, width a multiple of 16 bytes, at most 1024 bytes
   int ld_pad;
   size_t sort_smem;
@@ -1333,9 +1352,11 @@ BwdPlan plan_bwd(const lik_bwd_args& a) {
     const long long ent = a.pairing == LIK_PAIR_CROSS ? (long long)a.q.n_seq * a.argmax_stride
                           : a.pairing == LIK_PAIR_GROUPED ? (long long)a.argmax_stride
                                                           : ceil_div(a.n_pairs, a.d.n_seq) * a.argmax_stride;
-    long long nw = ceil_div(ent, 2048);
+    long long nw = ceil_div(ent, 256);  // a warp per 256 entries: few, long documents still fill their CTAs
     pl.sort_warps = (int)(nw < 1 ? 1 : (nw > DDS_WARPS ? DDS_WARPS : nw));
-    auto smem_for = [&](int w) { return ((size_t)w * pl.ld_pad + pl.ld_pad + 1 + (size_t)n_qrange) * 4; };
+    auto smem_for = [&](int w) {
+      return ((size_t)w * pl.ld_pad + pl.ld_pad + 1 + (size_t)(pl.ld_pad + 31) / 32 + 1 + 3 * (size_t)n_qrange) * 4;
+    };
     while (pl.sort_warps > 1 && smem_for(pl.sort_warps) > 200 * 1024) pl.sort_warps >>= 1;  // long documents: fewer histograms
     pl.sort_smem = smem_for(pl.sort_warps);
     if (pl.sort_smem <= 200 * 1024) {
