@@ -1081,10 +1081,11 @@ __global__ void __launch_bounds__(DDS_WARPS * 32) bwd_dd_sort4_kernel(BwdParams 
       int qlen;
       float gg;
       query_of(ii, qrow0, qlen, gg);
-      const int t4[4] = {w[u].x, w[u].y, w[u].z, w[u].w};
-#pragma unroll
+      // (the four winners of a load go through one copy of the code: the kernel runs once per CTA, straight through,
+      // and its time is instruction fetch as much as anything)
+#pragma unroll 1
       for (int k = 0; k < 4; ++k) {
-        const int t = t4[k];
+        const int t = k == 0 ? w[u].x : (k == 1 ? w[u].y : (k == 2 ? w[u].z : w[u].w));
         if (t >= 0 && t < dlen && s4 + k < qlen && row_valid(P.q, qrow0 + s4 + k)) atomicAdd(&hist[warp * ld_pad + t], 1);
       }
     }
@@ -1106,10 +1107,9 @@ __global__ void __launch_bounds__(DDS_WARPS * 32) bwd_dd_sort4_kernel(BwdParams 
       int qlen = 0;
       float gi = 0.f;
       if (in) query_of(ii, qrow0, qlen, gi);
-      const int t4[4] = {w[u].x, w[u].y, w[u].z, w[u].w};
-#pragma unroll
+#pragma unroll 1
       for (int k = 0; k < 4; ++k) {
-        int t = t4[k];
+        int t = k == 0 ? w[u].x : (k == 1 ? w[u].y : (k == 2 ? w[u].z : w[u].w));
         const int qrow = (int)(qrow0 + s4 + k);
         if (!(in && t >= 0 && t < dlen && s4 + k < qlen && row_valid(P.q, qrow))) t = -1;
         const unsigned peers = warp_peers(t, t_bits);
