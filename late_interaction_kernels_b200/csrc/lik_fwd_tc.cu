@@ -1113,10 +1113,11 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
       int c0 = 0;
       do {
         const int ncols = max(0, min(TILE_N, dlen - c0));
-        // per-column arrays of this tile; the first rendezvous says the previous tile's readers are done with them
-#define LIK_STAGE_COLUMNS()                                                                               \
+        // per-column arrays of this tile.  They may be written once the previous tile's readers are done with them (a
+        // rendezvous, unless the one at the top of the unit already stands between), and read after one more rendezvous.
+#define LIK_STAGE_COLUMNS(sync_before_)                                                                   \
   do {                                                                                                    \
-    LIK_GRP_SYNC();                                                                                       \
+    if (sync_before_) LIK_GRP_SYNC();                                                                     \
     for (int c = sub * EPI_THREADS + et; c < ((ncols + 31) & ~31); c += 2 * EPI_THREADS) {                \
       float sc = 1.f, bi = -INFINITY;                                                                     \
       if (c < ncols) {                                                                                    \
@@ -1127,15 +1128,18 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
       ctl->col_scale[wg][c] = sc;                                                                         \
       ctl->col_bias[wg][c] = bi;                                                                          \
     }                                                                                                     \
-    LIK_GRP_SYNC();                                                                                       \
   } while (0)
-        if (SCALED) LIK_STAGE_COLUMNS();  // before the accumulator wait: overlaps the MMAs
+        // before the accumulator wait: overlaps the MMAs; the wait's rendezvous also publishes the columns
+        if (SCALED) LIK_STAGE_COLUMNS(c0 > 0);
         if (SCALED || c0 > 0) {
           LIK_GROUP_WAIT_ACC();
           if (!ok) break;
         }
         ++n_acc;
-        if (!SCALED && use_cols) LIK_STAGE_COLUMNS();  // a document whose mask has holes: known only now
+        if (!SCALED && use_cols) {  // a document whose mask has holes: known only now
+          LIK_STAGE_COLUMNS(true);
+          LIK_GRP_SYNC();
+        }
 #undef LIK_STAGE_COLUMNS
         tc_fence_after();
         // the accumulator goes back to the issuer as soon as this warp's last columns sit in registers
