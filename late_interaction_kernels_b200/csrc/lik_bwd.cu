@@ -592,6 +592,22 @@ __device__ __forceinline__ void fma16_raw(float (&acc)[Vec16<T>::N], float w, co
 #pragma unroll
   for (int x = 0; x < Vec16<T>::N; ++x) acc[x] = fmaf(w, v[x], acc[x]);
 }
+// bf16 rows: two features per 32-bit word, folded in with one two-wide FMA per word (fma.rn.f32x2: the same IEEE
+// operation per element as fmaf, half the FMA instructions)
+template <>
+__device__ __forceinline__ void fma16_raw<__nv_bfloat16>(float (&acc)[8], float w, const uint4& r) {
+  unsigned long long ww;
+  asm("mov.b64 %0, {%1, %1};" : "=l"(ww) : "f"(w));
+  const unsigned x[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    unsigned long long v, a;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(v) : "r"(x[i] << 16), "r"(x[i] & 0xffff0000u));
+    asm("mov.b64 %0, {%1, %2};" : "=l"(a) : "f"(acc[2 * i]), "f"(acc[2 * i + 1]));
+    asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(a) : "l"(ww), "l"(v));
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(acc[2 * i]), "=f"(acc[2 * i + 1]) : "l"(a));
+  }
+}
 __device__ __forceinline__ float half_warp_sum(float v) {
 #pragma unroll
   for (int o = 8; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
