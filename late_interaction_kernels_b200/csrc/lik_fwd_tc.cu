@@ -23,6 +23,7 @@
 
 #include <cstdlib>
 #include <cstring>
+#include <type_traits>
 
 #include "lik_common.cuh"
 #include "lik_plaid_row.cuh"
@@ -1105,12 +1106,16 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
       const int dlen = uinfo.x & ~LEN_FLAG_MASKED;
       const long long drow0 = uinfo.y;
       const bool holes = (uinfo.x & LEN_FLAG_MASKED) != 0;  // the document's mask is not a plain prefix
-      const bool use_cols = SCALED || holes;                // per-column multiplier / additive mask needed
       // where this unit's results go: CROSS / GROUPED index by document, LIST by pair (== unit)
       const long long out_col = doc;
       float run_m = -INFINITY;
       int run_i = -1;
       int c0 = 0;
+      // The tiles of the document.  The body exists twice in the kernels without per-column multipliers: documents whose
+      // mask is a plain prefix (nearly all) take the copy that has no column arrays in it, the others the general one -
+      // the common path's time goes with its code size, so the rare one stays out of it.
+      auto document_tiles = [&](auto general_) {
+      constexpr bool use_cols = SCALED || decltype(general_)::value;  // per-column multiplier / additive mask needed
       do {
         const int ncols = max(0, min(TILE_N, dlen - c0));
         // per-column arrays of this tile.  They may be written once the previous tile's readers are done with them (a
@@ -1193,6 +1198,9 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
 #undef LIK_RELEASE_ACC
         c0 += TILE_N;
       } while (c0 < dlen);
+      };
+      if (!SCALED && holes) document_tiles(std::true_type{});
+      else document_tiles(std::false_type{});
       if (!ok) break;
       // ---- end of document: half 1 hands over, half 0 merges (lower column wins a tie) ----
       float* xm = ctl->xch_m[wg][n_doc & 1];
