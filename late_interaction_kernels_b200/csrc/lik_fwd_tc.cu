@@ -1115,7 +1115,8 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
       // mask is a plain prefix (nearly all) take the copy that has no column arrays in it, the others the general one -
       // the common path's time goes with its code size, so the rare one stays out of it.
       auto document_tiles = [&](auto general_) {
-      constexpr bool use_cols = SCALED || decltype(general_)::value;  // per-column multiplier / additive mask needed
+      constexpr bool general = decltype(general_)::value;  // the document's mask has holes
+      constexpr bool use_cols = SCALED || general;          // per-column multiplier / additive mask needed
       do {
         const int ncols = max(0, min(TILE_N, dlen - c0));
         // per-column arrays of this tile.  They may be written once the previous tile's readers are done with them (a
@@ -1157,14 +1158,32 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
         // chunks of this half: cc, cc + 64, ...; only the tile's last chunk can be partial
         int cc = sub * 32;
         if (cc >= ncols) LIK_RELEASE_ACC();
-        if (use_cols) {
+        if (use_cols && general) {
+          // a mask with holes: every chunk takes multiplier and additive mask
           for (; cc < ncols; cc += 64) {
             float v[32];
             tmem_ld32_issue(lane_addr + (uint32_t)cc, v);
             tmem_ld_wait(v);
             if (cc + 64 >= ncols) LIK_RELEASE_ACC();
-            if (!holes && cc + 32 <= ncols) scale32(v, &ctl->col_scale[wg][cc]);  // whole chunk valid: multiplier only
-            else affine32(v, &ctl->col_scale[wg][cc], &ctl->col_bias[wg][cc]);    // bias is -inf past ncols and in holes
+            affine32(v, &ctl->col_scale[wg][cc], &ctl->col_bias[wg][cc]);  // bias is -inf past ncols and in holes
+            fold32<ARGMAX>(v, c0 + cc, run_m, run_i);
+          }
+        } else if (use_cols) {
+          // whole chunks are valid: multiplier only; the partial last chunk also takes the mask (-inf past ncols)
+          for (; cc + 32 <= ncols; cc += 64) {
+            float v[32];
+            tmem_ld32_issue(lane_addr + (uint32_t)cc, v);
+            tmem_ld_wait(v);
+            if (cc + 64 >= ncols) LIK_RELEASE_ACC();
+            scale32(v, &ctl->col_scale[wg][cc]);
+            fold32<ARGMAX>(v, c0 + cc, run_m, run_i);
+          }
+          if (cc < ncols) {
+            float v[32];
+            tmem_ld32_issue(lane_addr + (uint32_t)cc, v);
+            tmem_ld_wait(v);
+            LIK_RELEASE_ACC();
+            affine32(v, &ctl->col_scale[wg][cc], &ctl->col_bias[wg][cc]);
             fold32<ARGMAX>(v, c0 + cc, run_m, run_i);
           }
         } else {
@@ -1199,7 +1218,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
         c0 += TILE_N;
       } while (c0 < dlen);
       };
-      if (!SCALED && holes) document_tiles(std::true_type{});
+      if (holes) document_tiles(std::true_type{});
       else document_tiles(std::false_type{});
       if (!ok) break;
       // ---- end of document: half 1 hands over, half 0 merges (lower column wins a tie) ----
