@@ -183,10 +183,11 @@ template <bool ARGMAX>
 __device__ __forceinline__ void fold32(const float (&v)[32], int col0, float& run_m, int& run_i) {
   const float cmax = max32(v);
   if (ARGMAX) {
-    if (cmax > run_m) {
-      run_i = col0 + first_match32(v, cmax);
-      run_m = cmax;
-    }
+    // (unconditional: with 32 rows per warp some row nearly always has a new maximum, and a branch costs more than the scan)
+    const int p = first_match32(v, cmax);
+    const bool better = cmax > run_m;
+    run_i = better ? col0 + p : run_i;
+    run_m = better ? cmax : run_m;
   } else {
     run_m = fmaxf(run_m, cmax);
   }
