@@ -1206,10 +1206,10 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
             LIK_RELEASE_ACC();
             const float cmax = max32(v);
             if (ARGMAX) {
-              if (cmax > run_m) {
-                run_i = c0 + cc + tail_first_match(v, cmax, lim);
-                run_m = cmax;
-              }
+              const int p = tail_first_match(v, cmax, lim);
+              const bool better = cmax > run_m;
+              run_i = better ? c0 + cc + p : run_i;
+              run_m = better ? cmax : run_m;
             } else {
               run_m = fmaxf(run_m, cmax);
             }
@@ -1236,10 +1236,9 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
         const float m1 = xm[row];
         if (ARGMAX) {
           const int i1 = xi[row];
-          if (i1 >= 0 && (run_i < 0 || m1 > run_m || (m1 == run_m && i1 < run_i))) {
-            run_m = m1;
-            run_i = i1;
-          }
+          const bool take = (i1 >= 0) & ((run_i < 0) | (m1 > run_m) | ((m1 == run_m) & (i1 < run_i)));
+          run_m = take ? m1 : run_m;
+          run_i = take ? i1 : run_i;
         } else {
           run_m = fmaxf(run_m, m1);
         }
