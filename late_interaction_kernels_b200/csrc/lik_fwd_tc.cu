@@ -325,12 +325,11 @@ struct SharedCtl {
   unsigned long long q_full, q_empty;
   unsigned long long d_full[8], d_empty[8];
   unsigned long long acc_full[2], acc_empty[2];
-  int grp_abort[2];             // set by a group's first warp when its bounded wait gave up
+  int grp_abort[2];             // set by a group's first warp: 1 when its bounded wait gave up, 2 when the stream has ended
   uint32_t stage_info[8];
   int4 unit_info[UNIT_RING];    // per work unit: x = document length | LEN_FLAG_MASKED, y = its first row, z = tile group, w = document
   volatile int units_posted;    // units published in unit_info so far
   volatile int units_total;     // all units of this CTA once the producer has walked them (INT_MAX until then)
-  int grp_done[2];              // set by a group's first warp when the stream has ended
   uint32_t tmem_base;
   volatile int abort_flag;
   long long wait_limit;         // cycles after which a wait gives up
@@ -638,7 +637,6 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
       mbar_init(smem_u32(&ctl->acc_full[a]), 1);
       mbar_init(smem_u32(&ctl->acc_empty[a]), GROUP_WARPS);
       ctl->grp_abort[a] = 0;
-      ctl->grp_done[a] = 0;
     }
     ctl->abort_flag = 0;
     ctl->wait_limit = WAIT_LIMIT_CYCLES;
@@ -1003,25 +1001,25 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
         }
         if (lane == 0) {
           if (st_ == 0) ctl->grp_abort[wg] = 1;
-          if (st_ == 2) ctl->grp_done[wg] = 1;
+          if (st_ == 2) ctl->grp_abort[wg] = 2;
         }
       }
       LIK_GRP_SYNC();
-      ok = ctl->grp_abort[wg] == 0;
-      if (!ok || ctl->grp_done[wg]) break;
+      {
+        const int state_ = ctl->grp_abort[wg];  // 0: go on, 1: aborting, 2: no more units
+        ok = state_ != 1;
+        if (state_ != 0) break;
+      }
       const int4 uinfo = ctl->unit_info[uc & (UNIT_RING - 1)];
       const int grp = uinfo.z;
       const int doc = uinfo.w;
-      if ((unsigned)grp >= (unsigned)(list ? P.n_q : n_groups)) {  // cannot happen; never index with it if it does
-        if (lane == 0 && P.status) atomicOr(P.status, LIK_DEV_INTERNAL);
-        break;
-      }
+      // (a group number out of range cannot index anything: its tile number fails the range check below)
       if (grp != cur_grp) {
         cur_grp = grp;
         // (re)build the segment table of this group's tile `wg` (mt == 2) or tile 0 (mt == 1: both groups)
         const int m = P.mt == 2 ? wg : 0;
         tile_id = grp * P.mt + m;
-        have_tile = tile_id < n_tiles;
+        have_tile = (unsigned)tile_id < (unsigned)n_tiles;
         LIK_GRP_SYNC();  // everyone in the group is done reading the old table
         LIK_TOPK_STORE_BACK();
         TileInfo ti{};
