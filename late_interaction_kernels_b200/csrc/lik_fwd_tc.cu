@@ -325,7 +325,6 @@ struct SharedCtl {
   unsigned long long q_full, q_empty;
   unsigned long long d_full[8], d_empty[8];
   unsigned long long acc_full[2], acc_empty[2];
-  int grp_abort[2];             // set by a group's first warp: 1 when its bounded wait gave up, 2 when the stream has ended
   uint32_t stage_info[8];
   int4 unit_info[UNIT_RING];    // per work unit: x = document length | LEN_FLAG_MASKED, y = its first row, z = tile group, w = document
   volatile int units_posted;    // units published in unit_info so far
@@ -636,7 +635,6 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
     for (int a = 0; a < 2; ++a) {
       mbar_init(smem_u32(&ctl->acc_full[a]), 1);
       mbar_init(smem_u32(&ctl->acc_empty[a]), GROUP_WARPS);
-      ctl->grp_abort[a] = 0;
     }
     ctl->abort_flag = 0;
     ctl->wait_limit = WAIT_LIMIT_CYCLES;
@@ -929,19 +927,22 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
     int warp_seg = -1;        // aligned tiles: the query (segment) of this warp's rows
     // Rendezvous of the whole group / of half 0 on hardware named barriers: a waiting warp issues
     // nothing.  Nobody waits on anything else between two of them, so every warp of the group always
-    // arrives; the only bounded waits of a group (on the accumulator) are done by its first warp, which
-    // then tells the others through grp_abort whether to go on.
+    // arrives; the only bounded waits of a group (for a unit, for the accumulator) are done by its first warp,
+    // which tells the others whether to go on through the rendezvous itself: a barrier that counts the
+    // threads arriving with a true predicate (0: go on, 1: the wait gave up, 2: the stream has ended).
     const bool leader = (e & 7) == 0;
+#define LIK_GRP_SYNC_COUNT(pred_, count_out_)                                                                        \
+  asm volatile("{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %3, 0;\n\tbar.red.popc.u32 %0, %1, %2, q;\n\t}"              \
+               : "=r"(count_out_) : "r"(1 + wg), "r"(2 * EPI_THREADS), "r"((int)(pred_)) : "memory")
 #define LIK_GRP_SYNC() asm volatile("bar.sync %0, %1;" ::"r"(1 + wg), "r"(2 * EPI_THREADS) : "memory")
 #define LIK_SUB_SYNC() asm volatile("bar.sync %0, %1;" ::"r"(3 + wg), "r"(EPI_THREADS) : "memory")
 #define LIK_GROUP_WAIT_ACC()                                                         \
   do {                                                                               \
-    if (leader) {                                                                    \
-      const bool ok_ = wait_bar(&ctl->acc_full[wg], n_acc & 1, ctl, P.status);       \
-      if (!ok_ && lane == 0) ctl->grp_abort[wg] = 1;                                 \
-    }                                                                                \
-    LIK_GRP_SYNC();                                                                  \
-    ok = ctl->grp_abort[wg] == 0;                                                    \
+    bool gave_up_ = false;                                                           \
+    if (leader) gave_up_ = !wait_bar(&ctl->acc_full[wg], n_acc & 1, ctl, P.status);  \
+    int n_;                                                                          \
+    LIK_GRP_SYNC_COUNT(gave_up_ && lane == 0, n_);                                   \
+    ok = n_ == 0;                                                                    \
   } while (0)
     // top-k: write the state of the lists this thread loaded back to their headers
 #define LIK_TOPK_STORE_BACK()                                                                          \
@@ -992,21 +993,19 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
       // The unit (tile group, document, length, first row) comes from the producer's ring.  The group's first warp
       // waits for its publication and - in kernels without per-column multipliers, which have nothing to prepare
       // while the MMAs run - for the unit's first accumulator, when this group has a tile in the unit's tile group.
+      int st_ = 1;
       if (leader) {
-        int st_ = wait_posted(ctl, uc, P.status);
+        st_ = wait_posted(ctl, uc, P.status);
         if (st_ == 1 && !SCALED) {
           // (only the last tile group can lack this group's tile, and only when the tile count is odd)
           const bool mine_ = every_group_full || ctl->unit_info[uc & (UNIT_RING - 1)].z * P.mt + wg < n_tiles;
           if (mine_ && !wait_bar(&ctl->acc_full[wg], n_acc & 1, ctl, P.status)) st_ = 0;
         }
-        if (lane == 0) {
-          if (st_ == 0) ctl->grp_abort[wg] = 1;
-          if (st_ == 2) ctl->grp_abort[wg] = 2;
-        }
       }
-      LIK_GRP_SYNC();
       {
-        const int state_ = ctl->grp_abort[wg];  // 0: go on, 1: aborting, 2: no more units
+        // the first warp arrives with one true predicate when its wait gave up, with two when the stream has ended
+        int state_;
+        LIK_GRP_SYNC_COUNT((st_ == 0 && lane == 0) || (st_ == 2 && lane < 2), state_);
         ok = state_ != 1;
         if (state_ != 0) break;
       }
@@ -1279,6 +1278,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
 #undef LIK_TOPK_STORE_BACK
 #undef LIK_GROUP_WAIT_ACC
 #undef LIK_GRP_SYNC
+#undef LIK_GRP_SYNC_COUNT
 #undef LIK_SUB_SYNC
   }
 
