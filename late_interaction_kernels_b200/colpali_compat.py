@@ -3,8 +3,9 @@ kernels (reference: colpali_compat.py:97-407).
 
 Hooked: ``BaseVisualRetrieverProcessor.score_multi_vector`` (evaluation scoring) and the ``forward``
 of the five ColBERT loss heads in ``colpali_engine.loss.late_interaction_losses``.  In-batch scores
-use :func:`maxsim`; explicit negatives use :func:`maxsim_pairs` for the positives and the 4-D
-candidate-list :func:`maxsim` for the negatives.  colpali-engine >= 0.3.17 selects the backend
+use :func:`maxsim`; explicit negatives score the positive and the negatives of a query as one candidate list
+(:func:`late_interaction_kernels_b200.loss_heads.maxsim_pos_neg`: one launch where the reference uses
+:func:`maxsim_pairs` plus the 4-D :func:`maxsim`).  colpali-engine >= 0.3.17 selects the backend
 itself; there the call only emits a ``DeprecationWarning``.  Anything the kernels do not take
 (``use_smooth_max``, ``LIK_DISABLE=1``, tensors not on a B200) goes back to the original code.
 """
@@ -115,11 +116,11 @@ def _negative_scores(self, Q, pos_D, neg_D, offset):
         return None
     if neg_D.device != Q.device or neg_D.shape[-1] < 8:
         return None
-    from .autograd import maxsim, maxsim_pairs
+    from .loss_heads import maxsim_pos_neg
 
     lengths = (Q[:, :, 0] != 0).sum(dim=1)
-    pos = maxsim_pairs(Q, pos_D[offset : offset + Q.size(0)])
-    neg = maxsim(Q, neg_D)
+    # positives and negatives in one candidate list per query: one scoring launch, one backward
+    pos, neg = maxsim_pos_neg(Q, pos_D[offset : offset + Q.size(0)], neg_D)
     if self.normalize_scores:
         pos = self._apply_normalization(pos, lengths)
         neg = self._apply_normalization(neg, lengths)

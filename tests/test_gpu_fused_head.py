@@ -98,3 +98,39 @@ def test_error_messages():
         maxsim_from_hidden(tQ, tH, tW, tb[:-1])
     with pytest.raises(ValueError, match="same device"):
         maxsim_from_hidden(tQ, tH.cpu(), tW)
+
+
+# ----------------------------------------------------------------------------- positives + explicit negatives in one launch
+@pytest.mark.parametrize("lp,ln,masks", [(40, 40, False), (33, 50, False), (48, 20, True)])
+def test_pos_neg_head_equals_the_two_separate_calls(lp, ln, masks):
+    import late_interaction_kernels_b200 as lik
+    from late_interaction_kernels_b200 import _lib
+    from late_interaction_kernels_b200.loss_heads import maxsim_pos_neg
+
+    rng = np.random.default_rng(lp * 100 + ln)
+    B, K, Lq, d = 6, 3, 16, 128
+    Q = dev(cases.unit(rng.standard_normal((B, Lq, d))).astype(np.float32), torch.bfloat16)
+    P = dev(cases.unit(rng.standard_normal((B, lp, d))).astype(np.float32), torch.bfloat16)
+    N = dev(cases.unit(rng.standard_normal((B, K, ln, d))).astype(np.float32), torch.bfloat16)
+    pm = nm = None
+    if masks:
+        pm = dev(cases.prefix_mask(rng.integers(1, lp + 1, size=B), lp))
+        nm = dev(cases.prefix_mask(rng.integers(1, ln + 1, size=B * K), ln).reshape(B, K, ln))
+    leaves = [x.clone().requires_grad_(True) for x in (Q, P, N)]
+    n0 = _lib.load().lik_launch_count()
+    pos, neg = maxsim_pos_neg(*leaves, pos_mask=pm, neg_mask=nm)
+    fwd_launches = _lib.load().lik_launch_count() - n0
+    ref = [x.clone().requires_grad_(True) for x in (Q, P, N)]
+    pos_r = lik.maxsim_pairs(ref[0], ref[1], d_mask=pm)
+    neg_r = lik.maxsim(ref[0], ref[2], d_mask=nm)
+    assert torch.equal(pos, pos_r) and torch.equal(neg, neg_r)  # same kernel arithmetic on the same tokens
+    assert fwd_launches <= 2, "mask lengths + one scoring launch"
+    gp, gn = torch.randn_like(pos), torch.randn_like(neg)
+    ((pos * gp).sum() + (neg * gn).sum()).backward()
+    ((pos_r * gp).sum() + (neg_r * gn).sum()).backward()
+    for a, b in zip(leaves, ref):
+        assert O.rel_err(f32(a.grad), f32(b.grad)) < 2e-2  # grad_Q sums the two calls' bf16 results in another order
+    # and against the oracle on the positives
+    want = O.maxsim_pairs(f32(Q), f32(P), d_mask=None if pm is None else pm.cpu().numpy()) if hasattr(O, "maxsim_pairs") else None
+    if want is not None:
+        assert O.rel_err(f32(pos), want) < 2e-2
