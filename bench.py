@@ -877,7 +877,7 @@ def main():
 
     e2e_run(2)
     barrier()
-    n_e2e = max(4, min(args.steps, 10))
+    n_e2e = max(4, min(args.steps, 40))  # enough steps for the first copy-in and the last copy-out to be a small share
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     e2e_run(n_e2e)
