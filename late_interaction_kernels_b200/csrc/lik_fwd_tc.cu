@@ -10,12 +10,19 @@
 // per query (fixed order) into one score.  Scores for a (query, document) pair have exactly one
 // writer, so the forward is bitwise reproducible.
 //
-// Warp roles (640 threads): warp 0 = TMA producer; warp 1 = MMA issuer + TMEM owner; warps 2-9 =
-// epilogue group 0 (accumulator 0), warps 10-17 = epilogue group 1 (accumulator 1); warps 18-19 idle
-// (they round the block up to the register-allocation granule).  The issuer is driven by one word
-// per ring stage that the producer writes, so the unit bookkeeping stays off its critical path.  An
-// accumulator is single-buffered (two 256-column accumulators fill TMEM), so the time an epilogue
-// group holds it bounds the tensor pipe; eight warps per group halve that time.
+// Warp roles (640 threads): warp 0 = producer (TMA; the only role that walks the work units, which it publishes in
+// a small ring in shared memory); warp 1 = MMA issuer + TMEM owner, driven by one word per ring stage that the
+// producer writes; warps 2-9 = epilogue group 0 (accumulator 0), warps 10-17 = epilogue group 1 (accumulator 1);
+// warps 18-19 decode tokens beside warp 0 in the PLAID kernels and are idle otherwise (they also round the block up
+// to the register-allocation granule).  An accumulator is single-buffered (two 256-column accumulators fill TMEM).
+// What bounds the kernel is the chain of dependent steps an epilogue warp runs per (query tile, document): hand-shake,
+// three or four TMEM round trips with their folds, the hand-over between the two halves of a group, the emit.  So the
+// code on that chain is kept short and free of branches, and paths that are rare (documents whose mask has holes)
+// get their own copy of the loop instead of a test inside the common one.
+//
+// The same kernel scores into a matrix, keeps the winners for the backward, or keeps a per-query top-k (candidate
+// lists per CTA and query, merged by a second kernel); documents come from a matrix through TMA or are decoded
+// from a PLAID index by the producer warps.
 //
 // Every mbarrier wait is bounded: on expiry the CTA raises LIK_DEV_WAIT_TIMEOUT in the status word,
 // sets a shared abort flag, drains its TMA copies, frees TMEM and returns.
