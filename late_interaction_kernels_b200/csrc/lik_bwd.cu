@@ -1013,10 +1013,10 @@ __global__ void __launch_bounds__(256) bwd_dd_reduce_kernel(BwdParams P, DdSortO
 
 
 // The same sort for argmax strides that are a multiple of four: a lane reads four consecutive winners with
-// one 16-byte load and a warp keeps eight such loads in flight, so a pass over the document's winners is a
+// one 16-byte load and a warp keeps four such loads in flight (eight made the straight-line code twice as long for no gain), so a pass over the document's winners is a
 // few round trips to L2 instead of one per 32 entries.  The order inside a token's list is (warp, round,
 // load, word, lane): fixed by the data alone, hence reproducible.
-constexpr int DDS_LOADS = 8;  // 16-byte loads in flight per lane
+constexpr int DDS_LOADS = 4;  // 16-byte loads in flight per lane
 
 __global__ void __launch_bounds__(DDS_WARPS * 32) bwd_dd_sort4_kernel(BwdParams P, DdSortOut O, int ld_pad) {
   const int n_warps = blockDim.x >> 5;  // the launcher sizes the CTA to the entries per document
