@@ -299,6 +299,47 @@ size_t lik_plaid_fwd_workspace(const lik_fwd_args* args, const lik_plaid_index* 
 int lik_plaid_fwd(const lik_fwd_args* args, const lik_plaid_index* index, const lik_topk_spec* topk, lik_stream_t stream);
 
 /* ------------------------------------------------------------------------- */
+/* Document head in front of MaxSim.  Replaces the forward launcher of          */
+/* maxsim_from_hidden (fused_head.py:262-330, kernel fused_head.py:40-260):     */
+/*   scores[i, j] = MaxSim(q_i, normalize(h_j @ w^T + bias))                    */
+/* One kernel: the projection of a 128-token tile runs on the tensor cores      */
+/* into tensor memory, is rounded to the operand type (plus bias), written to   */
+/* shared memory as the operand of the scoring MMA, and scored against the      */
+/* resident queries; the projected tokens never reach device memory.  The       */
+/* inverse norms come from the rounded values and are applied in fp32 to the    */
+/* raw dot products, as lik_maxsim_fwd does with LIK_NORM_D.                    */
+/*   q: padded queries [n_seq * max_len, d_out] (no mask, no lens); at most two */
+/*      128-row tiles of whole queries.   h: padded documents [n_rows, d_model] */
+/*      (mask / lens optional).   w [d_out, d_model], bias [d_out] or NULL, all */
+/*      of `dtype` (LIK_BF16 or LIK_F16); d_out a multiple of 32 up to 128.     */
+/*   argmax (optional) [n_q * n_d, argmax_stride] as for lik_maxsim_fwd.        */
+/* lik_maxsim_hidden_fwd_supported says whether this kernel takes the problem;  */
+/* callers project with a GEMM and call lik_maxsim_fwd otherwise.               */
+/* ------------------------------------------------------------------------- */
+typedef struct lik_hidden_fwd_args {
+  lik_seqs q;          /* projected queries */
+  lik_seqs h;          /* hidden states of the document tokens */
+  const void* w;       /* [d_out, d_model] */
+  int64_t w_stride;    /* elements between rows of w */
+  const void* bias;    /* [d_out] or NULL */
+  int32_t dtype;
+  int32_t d_model;
+  int32_t d_out;
+  int32_t normalize;   /* LIK_NORM_D or LIK_NORM_NONE */
+  float* scores;       /* [q.n_seq, h.n_seq] */
+  int32_t* argmax;
+  int32_t argmax_stride;
+  int32_t reserved;
+  void* workspace;
+  size_t workspace_bytes;
+  int32_t* status;
+} lik_hidden_fwd_args;
+
+int lik_maxsim_hidden_fwd_supported(const lik_hidden_fwd_args* args);
+size_t lik_maxsim_hidden_fwd_workspace(const lik_hidden_fwd_args* args);
+int lik_maxsim_hidden_fwd(const lik_hidden_fwd_args* args, lik_stream_t stream);
+
+/* ------------------------------------------------------------------------- */
 /* Utilities                                                                    */
 /* ------------------------------------------------------------------------- */
 /* out[r] = 1 / max(||x_r||, eps) for every row; the fused-normalise kernels take these. */

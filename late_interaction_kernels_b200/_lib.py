@@ -74,6 +74,15 @@ class BwdArgs(C.Structure):
     ]
 
 
+class HiddenFwdArgs(C.Structure):
+    _fields_ = [
+        ("q", Seqs), ("h", Seqs), ("w", C.c_void_p), ("w_stride", C.c_int64), ("bias", C.c_void_p),
+        ("dtype", C.c_int32), ("d_model", C.c_int32), ("d_out", C.c_int32), ("normalize", C.c_int32),
+        ("scores", C.c_void_p), ("argmax", C.c_void_p), ("argmax_stride", C.c_int32), ("reserved", C.c_int32),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("status", C.c_void_p),
+    ]
+
+
 class TopkSpec(C.Structure):
     _fields_ = [
         ("k", C.c_int32), ("largest", C.c_int32), ("index_offset", C.c_int64), ("out_scores", C.c_void_p),
@@ -117,6 +126,12 @@ def _declare(lib):
     lib.lik_plaid_fwd_workspace.restype = sz
     lib.lik_plaid_fwd.argtypes = [C.POINTER(FwdArgs), C.POINTER(PlaidIndex), C.POINTER(TopkSpec), vp]
     lib.lik_plaid_fwd.restype = i32
+    lib.lik_maxsim_hidden_fwd_supported.argtypes = [C.POINTER(HiddenFwdArgs)]
+    lib.lik_maxsim_hidden_fwd_supported.restype = i32
+    lib.lik_maxsim_hidden_fwd_workspace.argtypes = [C.POINTER(HiddenFwdArgs)]
+    lib.lik_maxsim_hidden_fwd_workspace.restype = sz
+    lib.lik_maxsim_hidden_fwd.argtypes = [C.POINTER(HiddenFwdArgs), vp]
+    lib.lik_maxsim_hidden_fwd.restype = i32
     lib.lik_selftest_wait_timeout.argtypes = [i64, vp, vp, vp]
     lib.lik_selftest_wait_timeout.restype = i32
     lib.lik_launch_count.argtypes = []
@@ -142,6 +157,7 @@ def _declare(lib):
 EXPORTED_SYMBOLS = (
     "lik_maxsim_fwd_workspace", "lik_maxsim_fwd", "lik_maxsim_fwd_static", "lik_maxsim_bwd_workspace", "lik_maxsim_bwd", "lik_topk_rows",
     "lik_maxsim_fwd_topk_supported", "lik_maxsim_fwd_topk_workspace", "lik_maxsim_fwd_topk",
+    "lik_maxsim_hidden_fwd_supported", "lik_maxsim_hidden_fwd_workspace", "lik_maxsim_hidden_fwd",
     "lik_plaid_fwd_supported", "lik_plaid_fwd_workspace", "lik_plaid_fwd", "lik_launch_count", "lik_selftest_wait_timeout",
     "lik_topk_merge", "lik_plaid_decompress", "lik_plaid_approx", "lik_plaid_bwd_dq", "lik_row_inv_norm",
     "lik_last_error", "lik_version", "lik_device_supported",

@@ -14,7 +14,7 @@ from dataclasses import dataclass
 import torch
 
 from . import _lib
-from ._lib import BwdArgs, FwdArgs, PlaidIndex, Seqs, TopkSpec
+from ._lib import BwdArgs, FwdArgs, HiddenFwdArgs, PlaidIndex, Seqs, TopkSpec
 
 # The launchers hand raw pointers to a C library: keep torch.compile from tracing into them (it
 # breaks the graph around the call instead).
@@ -150,6 +150,40 @@ def forward(q: SeqSpec, d: SeqSpec, *, pairing=_lib.PAIR_CROSS, group=0, pair_q=
         a.workspace, a.workspace_bytes = ws.data_ptr(), nbytes
     with torch.cuda.device(dev):
         _lib.check(lib.lik_maxsim_fwd(C.byref(a), _lib.stream_ptr(dev)), "lik_maxsim_fwd")
+    return scores, argmax
+
+
+@_no_trace
+def hidden_forward(q: SeqSpec, h: SeqSpec, w: torch.Tensor, bias, *, normalize: bool, save_argmax=False):
+    """Launch ``lik_maxsim_hidden_fwd`` (projection chained into the scoring MMA).  Returns
+    (scores fp32 [n_q * n_d], argmax int32 [n_q * n_d, Lq] | None), or None when the kernel does not take the problem."""
+    lib = _lib.load()
+    dev = q.data.device
+    _lib.require_cuda(q.data, h.data, w, op="maxsim_from_hidden")
+    if not (q.data.dtype == h.data.dtype == w.dtype) or (bias is not None and bias.dtype != w.dtype):
+        return None
+    if q.data.dtype not in (torch.bfloat16, torch.float16) or w.stride(1) != 1:
+        return None
+    ns = q.n_seq * h.n_seq
+    a = HiddenFwdArgs(
+        q=q.c_struct(), h=h.c_struct(), w=w.data_ptr(), w_stride=w.stride(0), bias=_lib.ptr(bias),
+        dtype=_lib.lik_dtype(w.dtype), d_model=w.shape[1], d_out=w.shape[0],
+        normalize=_lib.NORM_D if normalize else _lib.NORM_NONE, scores=None, argmax=None, argmax_stride=q.max_len, reserved=0,
+        workspace=None, workspace_bytes=0, status=status_word(dev).data_ptr(),
+    )
+    if ns == 0 or not lib.lik_maxsim_hidden_fwd_supported(C.byref(a)):
+        return None
+    scores = torch.empty(ns, dtype=torch.float32, device=dev)
+    argmax = torch.empty((ns, q.max_len), dtype=torch.int32, device=dev) if save_argmax else None
+    a.scores = scores.data_ptr()
+    a.argmax = _lib.ptr(argmax)
+    nbytes = lib.lik_maxsim_hidden_fwd_workspace(C.byref(a))
+    ws = None
+    if nbytes:
+        ws = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+        a.workspace, a.workspace_bytes = ws.data_ptr(), nbytes
+    with torch.cuda.device(dev):
+        _lib.check(lib.lik_maxsim_hidden_fwd(C.byref(a), _lib.stream_ptr(dev)), "lik_maxsim_hidden_fwd")
     return scores, argmax
 
 

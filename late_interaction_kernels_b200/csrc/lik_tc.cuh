@@ -1,6 +1,8 @@
 // Interface between the C-ABI entry points and the tcgen05 scoring kernel (lik_fwd_tc.cu).
 #pragma once
 
+#include <cuda.h>
+
 #include "lik_common.cuh"
 #include "lik_plaid_row.cuh"
 
@@ -25,5 +27,15 @@ bool fwd_tc_plaid_supported(const lik_fwd_args& a, const TcExtra& x);
 size_t fwd_tc_workspace(const lik_fwd_args& a, const TcExtra& x);
 int launch_fwd_tc(const lik_fwd_args& a, const float* qn, const float* dn, void* ws, size_t ws_bytes, cudaStream_t st,
                   const TcExtra& x);
+
+
+// Shared with the document-head kernel (lik_head.cu).
+constexpr int LEN_FLAG_MASKED = 1 << 30;  // effective length of a document whose mask is not a plain prefix
+int make_tmap_rows(CUtensorMap* map, const void* data, int dtype, long long inner, long long n_rows, long long row_stride,
+                   int box_rows);
+bool tmap_available();
+// out[j] = (1 + index of the last valid token of padded document j) | LEN_FLAG_MASKED when the valid tokens are not a prefix
+int launch_mask_lens(const unsigned char* mask, const int* lens, int n_seq, int max_len, long long seq_stride, int* out,
+                     cudaStream_t st);
 
 }  // namespace lik

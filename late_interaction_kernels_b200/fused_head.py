@@ -5,9 +5,10 @@ with a small projection to ``d_out``.  The reference folds the projection into i
 the projected documents never exist in memory.  Here the projection is a plain GEMM (cuBLAS through
 ``torch.nn.functional.linear``) run over *pieces* of the corpus into a bounded scratch buffer, and everything after
 it is this library's kernels: the L2 normalisation is fused into the tensor-core scoring kernel (fp32 inverse norms
-applied in the epilogue), the backward is the deterministic argmax-driven pair of kernels with the normalise
-Jacobian of the document side, followed by the three GEMMs of the linear layer.  Peak extra memory is one piece of
-projected tokens (``_PIECE_TOKENS`` rows of ``d_out``), whatever the corpus size.
+applied in the epilogue).  The backward works on the winning tokens alone: they are gathered from ``H_d``, projected
+again, pushed through the deterministic argmax-driven kernels (with the normalise Jacobian of the document side) as
+short "compact" documents, and the three GEMMs of the linear layer run on those rows.  Peak extra memory of the
+forward is one piece of projected tokens (``_PIECE_TOKENS`` rows of ``d_out``), whatever the corpus size.
 
 A single kernel that chains the projection MMA into the scoring MMA through tensor memory is not built.
 """
@@ -33,11 +34,23 @@ def _project(H, W, b, dt):
     return F.linear(H.to(dt), W.to(dt), None if b is None else b.to(dt))
 
 
+# set to False to force the GEMM-in-pieces forward (tests compare the two)
+_CHAINED = True
+
+
 def _forward(Q, H_d, W, b, d_mask, normalize, save_argmax):
     Nq, Lq, d_out = Q.shape
     Nd, Ld, _ = H_d.shape
     dt = common_dtype(Q, H_d)
     q = _ops.padded_spec(Q.to(dt))
+    if _CHAINED and dt in (torch.bfloat16, torch.float16):
+        # one kernel: projection MMA -> tensor memory -> rounded operand tile in shared memory -> scoring MMA
+        h = _ops.padded_spec(H_d.to(dt), d_mask)
+        got = _ops.hidden_forward(q, h, W.to(dt).contiguous(), None if b is None else b.to(dt).contiguous(), normalize=normalize,
+                                  save_argmax=save_argmax)
+        if got is not None:
+            s, am = got
+            return s.view(Nq, Nd), (am.view(Nq, Nd, Lq) if save_argmax else None)
     scores = torch.empty((Nq, Nd), dtype=torch.float32, device=Q.device)
     argmax = torch.empty((Nq, Nd, Lq), dtype=torch.int32, device=Q.device) if save_argmax else None
     norm = _lib.NORM_D if normalize else _lib.NORM_NONE
@@ -61,37 +74,53 @@ class _MaxSimFromHiddenFn(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, grad_scores):
+        # Only winning tokens carry gradient (fused_head.py:332-456 gathers H_d at the winners too): the winners of
+        # every (query token, document) are made unique and sorted, which turns each document into a short "compact"
+        # document of at most Nq * Lq tokens.  Those rows of H_d are gathered and projected again, the deterministic
+        # backward kernels run on the compact documents (with the document-side normalise Jacobian), and the three
+        # GEMMs of the linear layer see the winner rows alone.  Cost and memory follow the winners, not the corpus;
+        # the rest of grad_H is the zero fill.
         Q, H_d, W, b, d_mask, argmax = ctx.saved_tensors
         Nq, Lq, d_out = Q.shape
         Nd, Ld, d_model = H_d.shape
+        dev = Q.device
         dt = common_dtype(Q, H_d)
-        q = _ops.padded_spec(Q.to(dt))
-        g = grad_scores.contiguous().to(torch.float32)
         need_q, need_h, need_w, need_b = ctx.needs_input_grad[:4]
-        need_d = need_h or need_w or (b is not None and need_b)
-        gQ = torch.zeros((Nq * Lq, d_out), dtype=torch.float32, device=Q.device) if need_q else None
-        gH = torch.empty_like(H_d) if need_h else None
-        gW = torch.zeros((d_out, d_model), dtype=torch.float32, device=Q.device) if need_w else None
-        gb = torch.zeros(d_out, dtype=torch.float32, device=Q.device) if (b is not None and need_b) else None
+        need_b = need_b and b is not None
+        need_d = need_h or need_w or need_b
+        g = grad_scores.contiguous().to(torch.float32)
+        sentinel = Nd * Ld  # "no winner": sorts behind every real row
+        doc = torch.arange(Nd, device=dev, dtype=torch.int64).view(1, Nd, 1)
+        has = argmax >= 0
+        rows = torch.where(has, doc * Ld + argmax.to(torch.int64), sentinel)
+        uniq, inv = torch.unique(rows.reshape(-1), return_inverse=True)  # ascending: grouped by document, sentinel last
+        cu = torch.searchsorted(uniq, torch.arange(Nd + 1, device=dev, dtype=torch.int64) * Ld).to(torch.int32)
+        n_rows = int(cu[-1])  # winner rows (the host already waited for the size of `uniq`)
+        # winner -> its position inside the compact document
+        doc_of = torch.div(uniq, Ld, rounding_mode="floor").clamp_(max=Nd - 1)
+        pos = torch.arange(uniq.numel(), device=dev, dtype=torch.int64) - cu[doc_of]
+        am_c = torch.where(has.reshape(-1), pos[inv], -1).to(torch.int32).view(Nq * Nd, Lq)
+        uniq = uniq[:n_rows]
+        gH = torch.zeros_like(H_d) if need_h else None
+        gW = torch.zeros_like(W) if need_w else None
+        gb = torch.zeros_like(b) if need_b else None
+        if n_rows == 0:
+            return (torch.zeros_like(Q) if need_q else None), gH, gW, gb, None, None
+        H_rows = H_d.reshape(Nd * Ld, d_model)[uniq]
+        P_rows = _project(H_rows, W, b, dt)
+        q = _ops.padded_spec(Q.to(dt))
+        dd = _ops.packed_spec(P_rows, cu, max(1, min(Nq * Lq, Ld)))
         norm = _lib.NORM_D if ctx.normalize else _lib.NORM_NONE
-        for j0, j1 in _pieces(Nd, Ld):
-            D = _project(H_d[j0:j1], W, b, dt)  # recomputed: the projected tokens are never kept
-            dd = _ops.padded_spec(D, None if d_mask is None else d_mask[j0:j1])
-            am = argmax[:, j0:j1].reshape(Nq * (j1 - j0), Lq)
-            gq, gd = _ops.backward(q, dd, g[:, j0:j1].contiguous(), am, normalize=norm, deterministic=True, grad_dtype=torch.float32,
-                                   need_q=need_q, need_d=need_d)
-            if need_q:
-                gQ += gq
-            if need_d:
-                gp = gd.view(j1 - j0, Ld, d_out)  # gradient w.r.t. the projected tokens before normalisation
-                if need_h:
-                    gH[j0:j1] = (gp @ W.float()).to(H_d.dtype)
-                if need_w:
-                    gW += torch.einsum("jto,jtm->om", gp, H_d[j0:j1].float())
-                if gb is not None:
-                    gb += gp.sum((0, 1))
-        return (None if gQ is None else gQ.view(Nq, Lq, d_out).to(Q.dtype), gH, None if gW is None else gW.to(W.dtype),
-                None if gb is None else gb.to(b.dtype), None, None)
+        gq, gp = _ops.backward(q, dd, g, am_c, normalize=norm, deterministic=True, grad_dtype=torch.float32,
+                               need_q=need_q, need_d=need_d)  # gp: gradient w.r.t. the projected winner rows before normalisation
+        gQ = gq.view(Nq, Lq, d_out).to(Q.dtype) if need_q else None
+        if need_h:
+            gH.view(Nd * Ld, d_model).index_copy_(0, uniq, (gp @ W.float()).to(H_d.dtype))  # unique rows: one writer each
+        if need_w:
+            gW = (gp.t() @ H_rows.float()).to(W.dtype)
+        if need_b:
+            gb = gp.sum(0).to(b.dtype)
+        return gQ, gH, gW, gb, None, None
 
 
 def maxsim_from_hidden(Q, H_d, W, b=None, d_mask=None, normalize=True):

@@ -66,6 +66,7 @@ def test_only_requested_gradients_exist(need):
 def test_bf16_documents_at_retrieval_shape_and_in_pieces(monkeypatch):
     from late_interaction_kernels_b200 import fused_head
 
+    monkeypatch.setattr(fused_head, "_CHAINED", False)  # the GEMM-in-pieces forward
     Q, H, W, b, dm = cases.from_hidden_case(21, Nq=4, Nd=300, Lq=32, Ld=96, d_model=256, d_out=128)
     tQ, tH, tW, tb, tm = dev(Q, torch.bfloat16), dev(H, torch.bfloat16), dev(W, torch.bfloat16), dev(b, torch.bfloat16), dev(dm)
     whole = fused_head.maxsim_from_hidden(tQ, tH, tW, tb, tm)
@@ -98,6 +99,96 @@ def test_error_messages():
         maxsim_from_hidden(tQ, tH, tW, tb[:-1])
     with pytest.raises(ValueError, match="same device"):
         maxsim_from_hidden(tQ, tH.cpu(), tW)
+
+
+# ----------------------------------------------------------------------------- projection chained into the scoring MMA
+def _chained_case(seed, Nq, Nd, Lq, Ld, d_model, d_out, dtype, mask):
+    Q, H, W, b, dm = cases.from_hidden_case(seed, Nq=Nq, Nd=Nd, Lq=Lq, Ld=Ld, d_model=d_model, d_out=d_out)
+    rng = np.random.default_rng(seed + 1)
+    if mask == "none":
+        dm = None
+    elif mask == "holes":
+        dm = rng.random((Nd, Ld)) < 0.7
+        dm[0] = False  # a document without a valid token
+        dm[1] = True
+    t = [dev(x, dtype) for x in (Q, H, W, b)]
+    return t, dm
+
+
+@pytest.mark.parametrize("Nq,Nd,Lq,Ld,d_model,d_out,dtype,mask,bias,normalize", [
+    (4, 40, 32, 300, 768, 128, torch.bfloat16, "prefix", True, True),    # one query tile, ragged lengths
+    (8, 33, 32, 130, 384, 96, torch.bfloat16, "holes", True, True),      # two query tiles, d_out 96, masks with holes
+    (1, 200, 32, 257, 200, 64, torch.float16, "none", False, True),      # K slab with a zero-filled tail, more documents than SMs
+    (3, 17, 40, 128, 256, 128, torch.bfloat16, "prefix", True, False),   # queries that do not fill the tile, no normalisation
+    (2, 9, 128, 1024, 768, 128, torch.bfloat16, "none", True, True),     # one query per tile, long documents
+])
+def test_chained_kernel_against_the_oracle_and_the_gemm_path(monkeypatch, Nq, Nd, Lq, Ld, d_model, d_out, dtype, mask, bias, normalize):
+    from late_interaction_kernels_b200 import _lib, fused_head
+
+    (tQ, tH, tW, tb), dm = _chained_case(Nq * 7 + Nd, Nq, Nd, Lq, Ld, d_model, d_out, dtype, mask)
+    tm = None if dm is None else dev(dm)
+    if not bias:
+        tb = None
+    n0 = _lib.load().lik_launch_count()
+    got = fused_head.maxsim_from_hidden(tQ, tH, tW, tb, tm, normalize=normalize)
+    launches = _lib.load().lik_launch_count() - n0
+    assert launches == (1 if dm is None else 2), "one kernel (plus the mask lengths)"
+    torch.cuda.synchronize()
+    from late_interaction_kernels_b200 import _ops
+    _ops.check_device_status()
+    want = O.maxsim_from_hidden(f32(tQ), f32(tH), f32(tW), None if tb is None else f32(tb), dm, normalize=normalize)
+    assert got.shape == (Nq, Nd)
+    assert O.rel_err(f32(got), want) < 2e-2
+    # the GEMM-in-pieces forward rounds the same projected values: the two agree far inside the bf16 tolerance
+    monkeypatch.setattr(fused_head, "_CHAINED", False)
+    ref = fused_head.maxsim_from_hidden(tQ, tH, tW, tb, tm, normalize=normalize)
+    assert O.rel_err(f32(got), f32(ref)) < 3e-3
+    # a second run gives the same bits
+    monkeypatch.setattr(fused_head, "_CHAINED", True)
+    assert torch.equal(got, fused_head.maxsim_from_hidden(tQ, tH, tW, tb, tm, normalize=normalize))
+
+
+def test_chained_kernel_winners_and_training_step(monkeypatch):
+    from late_interaction_kernels_b200 import fused_head
+
+    (tQ, tH, tW, tb), dm = _chained_case(5, 4, 24, 32, 200, 256, 128, torch.bfloat16, "holes")
+    tm = dev(dm)
+    s, am = fused_head._forward(tQ, tH, tW, tb, tm, True, True)
+    monkeypatch.setattr(fused_head, "_CHAINED", False)
+    s_ref, am_ref = fused_head._forward(tQ, tH, tW, tb, tm, True, True)
+    monkeypatch.setattr(fused_head, "_CHAINED", True)
+    assert (am == am_ref).float().mean().item() > 0.97  # near-ties may fall the other way between two GEMM orders
+    assert (am[:, 0] == -1).all() and (am[:, 1] >= 0).all()
+    # every winner is a valid token and reproduces its score from the projected, normalised tokens
+    P = torch.nn.functional.normalize(torch.nn.functional.linear(tH, tW, tb).float(), dim=-1)
+    idx = am.clamp(min=0).long()
+    picked = torch.gather(P.unsqueeze(0).expand(4, -1, -1, -1), 2, idx.unsqueeze(-1).expand(-1, -1, -1, P.shape[-1]))
+    sims = (picked * tQ.float().unsqueeze(1)).sum(-1) * (am >= 0)
+    assert O.rel_err(f32(sims.sum(-1)), f32(s)) < 1e-2
+    assert torch.gather(tm.unsqueeze(0).expand(4, -1, -1), 2, idx)[am >= 0].all()
+    # gradients through the chained forward: against torch autograd (fp32) on the same winners - an fp64 oracle picks
+    # other winners in near-ties, which swaps whole rows of the gradients
+    leaves = [x.clone().requires_grad_(True) for x in (tQ, tH, tW, tb)]
+    g = torch.randn(4, 24, device="cuda")
+    (fused_head.maxsim_from_hidden(*leaves, tm) * g).sum().backward()
+    rQ, rH, rW, rb = [x.detach().float().requires_grad_(True) for x in (tQ, tH, tW, tb)]
+    P = torch.nn.functional.normalize(torch.nn.functional.linear(rH, rW, rb), dim=-1)
+    picked = torch.gather(P.unsqueeze(0).expand(4, -1, -1, -1), 2, idx.unsqueeze(-1).expand(-1, -1, -1, P.shape[-1]))
+    (((picked * rQ.unsqueeze(1)).sum(-1) * (am >= 0)).sum(-1) * g).sum().backward()
+    for got, want in zip(leaves, (rQ, rH, rW, rb)):
+        assert O.rel_err(f32(got.grad), f32(want.grad)) < 2e-2
+
+
+def test_chained_kernel_declines_what_it_cannot_hold():
+    from late_interaction_kernels_b200 import _ops
+
+    Q, H, W, b, dm = cases.from_hidden_case(2, Nq=9, Nd=6, Lq=32, Ld=64, d_model=128, d_out=128)  # three query tiles
+    q = _ops.padded_spec(dev(Q, torch.bfloat16))
+    h = _ops.padded_spec(dev(H, torch.bfloat16))
+    assert _ops.hidden_forward(q, h, dev(W, torch.bfloat16), None, normalize=True) is None
+    W48 = dev(W[:48], torch.bfloat16)  # d_out not a multiple of 32
+    q48 = _ops.padded_spec(dev(Q[:2, :, :48], torch.bfloat16))
+    assert _ops.hidden_forward(q48, h, W48, None, normalize=True) is None
 
 
 # ----------------------------------------------------------------------------- positives + explicit negatives in one launch
