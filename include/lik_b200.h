@@ -339,6 +339,22 @@ int lik_maxsim_hidden_fwd_supported(const lik_hidden_fwd_args* args);
 size_t lik_maxsim_hidden_fwd_workspace(const lik_hidden_fwd_args* args);
 int lik_maxsim_hidden_fwd(const lik_hidden_fwd_args* args, lik_stream_t stream);
 
+/* Backward of the document head (fused_head.py:332-456): only winning tokens carry gradient, so the  */
+/* backward gathers them into "compact" documents, runs lik_maxsim_bwd on those and scatters the rows  */
+/* of grad_h back.                                                                                     */
+/* lik_hidden_winners: per document j, the distinct winners over all (query, query token), ascending:  */
+/*   counts[j] of them (at most `slots`, which must be >= min(n_q * lq, ld)); rows[j * slots + p] =     */
+/*   j * ld + token of compact slot p (unused slots repeat the document's first row);                   */
+/*   compact_argmax [n_q, n_d, lq] = position of each winner inside its compact document (-1: none);    */
+/*   bitmap / prefix [n_d, ceil(ld / 32)]: which tokens won, and how many winners precede each word.    */
+/* lik_hidden_scatter_rows: grad_h [n_d * ld rows of row_bytes] = the compact row of every winning     */
+/*   token (compact_rows [n_d * slots rows]), zeros elsewhere; every row is written exactly once.       */
+int lik_hidden_winners(const int32_t* argmax, int32_t n_q, int32_t n_d, int32_t lq, int32_t ld, int32_t slots,
+                       int32_t* compact_argmax, int64_t* rows, int32_t* counts, uint32_t* bitmap, int32_t* prefix,
+                       int32_t* status, lik_stream_t stream);
+int lik_hidden_scatter_rows(const void* compact_rows, int64_t row_bytes, int32_t n_d, int32_t ld, int32_t slots,
+                            const uint32_t* bitmap, const int32_t* prefix, void* grad_h, lik_stream_t stream);
+
 /* ------------------------------------------------------------------------- */
 /* Utilities                                                                    */
 /* ------------------------------------------------------------------------- */

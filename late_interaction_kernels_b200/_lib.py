@@ -132,6 +132,10 @@ def _declare(lib):
     lib.lik_maxsim_hidden_fwd_workspace.restype = sz
     lib.lik_maxsim_hidden_fwd.argtypes = [C.POINTER(HiddenFwdArgs), vp]
     lib.lik_maxsim_hidden_fwd.restype = i32
+    lib.lik_hidden_winners.argtypes = [vp, i32, i32, i32, i32, i32, vp, vp, vp, vp, vp, vp, vp]
+    lib.lik_hidden_winners.restype = i32
+    lib.lik_hidden_scatter_rows.argtypes = [vp, i64, i32, i32, i32, vp, vp, vp, vp]
+    lib.lik_hidden_scatter_rows.restype = i32
     lib.lik_selftest_wait_timeout.argtypes = [i64, vp, vp, vp]
     lib.lik_selftest_wait_timeout.restype = i32
     lib.lik_launch_count.argtypes = []
@@ -158,6 +162,7 @@ EXPORTED_SYMBOLS = (
     "lik_maxsim_fwd_workspace", "lik_maxsim_fwd", "lik_maxsim_fwd_static", "lik_maxsim_bwd_workspace", "lik_maxsim_bwd", "lik_topk_rows",
     "lik_maxsim_fwd_topk_supported", "lik_maxsim_fwd_topk_workspace", "lik_maxsim_fwd_topk",
     "lik_maxsim_hidden_fwd_supported", "lik_maxsim_hidden_fwd_workspace", "lik_maxsim_hidden_fwd",
+    "lik_hidden_winners", "lik_hidden_scatter_rows",
     "lik_plaid_fwd_supported", "lik_plaid_fwd_workspace", "lik_plaid_fwd", "lik_launch_count", "lik_selftest_wait_timeout",
     "lik_topk_merge", "lik_plaid_decompress", "lik_plaid_approx", "lik_plaid_bwd_dq", "lik_row_inv_norm",
     "lik_last_error", "lik_version", "lik_device_supported",

@@ -187,6 +187,39 @@ def hidden_forward(q: SeqSpec, h: SeqSpec, w: torch.Tensor, bias, *, normalize: 
     return scores, argmax
 
 
+@_no_trace
+def hidden_winners(argmax: torch.Tensor, n_q: int, n_d: int, lq: int, ld: int, slots: int):
+    """Launch ``lik_hidden_winners``: the distinct winners of every document as a compact document.  Returns
+    (compact_argmax int32 like argmax, rows int64 [n_d * slots], counts int32 [n_d], bitmap, prefix)."""
+    lib = _lib.load()
+    dev = argmax.device
+    _lib.require_cuda(argmax, op="maxsim_from_hidden backward")
+    words = (ld + 31) // 32
+    am_c = torch.empty_like(argmax)
+    rows = torch.empty(n_d * slots, dtype=torch.int64, device=dev)
+    counts = torch.empty(n_d, dtype=torch.int32, device=dev)
+    bitmap = torch.empty((n_d, words), dtype=torch.int32, device=dev)
+    prefix = torch.empty((n_d, words), dtype=torch.int32, device=dev)
+    with torch.cuda.device(dev):
+        _lib.check(lib.lik_hidden_winners(argmax.data_ptr(), n_q, n_d, lq, ld, slots, am_c.data_ptr(), rows.data_ptr(), counts.data_ptr(),
+                                          bitmap.data_ptr(), prefix.data_ptr(), status_word(dev).data_ptr(), _lib.stream_ptr(dev)),
+                   "lik_hidden_winners")
+    return am_c, rows, counts, bitmap, prefix
+
+
+@_no_trace
+def hidden_scatter_rows(compact_rows: torch.Tensor, bitmap: torch.Tensor, prefix: torch.Tensor, out: torch.Tensor, n_d: int, ld: int, slots: int):
+    """Launch ``lik_hidden_scatter_rows``: ``out`` [n_d * ld, width] = compact rows of the winners, zeros elsewhere."""
+    lib = _lib.load()
+    dev = out.device
+    _lib.require_cuda(compact_rows, out, op="maxsim_from_hidden backward")
+    row_bytes = out.shape[-1] * out.element_size()
+    with torch.cuda.device(dev):
+        _lib.check(lib.lik_hidden_scatter_rows(compact_rows.data_ptr(), row_bytes, n_d, ld, slots, bitmap.data_ptr(), prefix.data_ptr(),
+                                               out.data_ptr(), _lib.stream_ptr(dev)), "lik_hidden_scatter_rows")
+    return out
+
+
 def layout_spec(n_tokens: int, n_seq: int, max_len: int, *, cu=None, lens=None, seq_stride=0) -> Seqs:
     """Document layout without a token matrix (the documents are a compressed index): rows = tokens."""
     return Seqs(data=None, row_stride=0, n_rows=n_tokens, n_seq=n_seq, max_len=max_len, seq_stride=seq_stride,

@@ -35,6 +35,10 @@ struct BwdParams {
   const int* start_q;  // [n_q + 1] run of query i in perm_q
   const int* perm_d;   // [n_pairs] pair indices ordered by document
   const int* start_d;  // [n_d + 1]
+  // grad_q with few query tokens and many documents: the documents of a query are cut into dq_split ranges, one
+  // CTA each, whose fp32 partial rows [dq_split][q rows][dim] are summed in range order by a second kernel
+  int dq_split;
+  float* dq_partial;
 };
 
 // The scores of query i: `count` of them, numbered p0 .. p0 + count - 1 (CROSS, GROUPED: score slots; LIST:
@@ -669,6 +673,27 @@ __device__ __forceinline__ void store_row16(G* out, const float (&acc)[CH][Vec16
 // ---------------------------------------------------------------------------------
 constexpr int DQ16_TOK = 16;  // query tokens per CTA (one per half-warp)
 
+// What a grad_q row still needs once its sum over the documents is complete: the normalise Jacobian or the query's
+// dequantisation factor, then the store.
+template <typename T, typename G, int CH>
+__device__ __forceinline__ void dq16_finish_row(const BwdParams& P, float (&acc)[CH][Vec16<T>::N], long long qrow, bool active, int hl) {
+  constexpr int N = Vec16<T>::N;
+  if (active) {
+    if (P.normalize & LIK_NORM_Q) {
+      normalize_jacobian_row16<T, CH>(acc, (const T*)P.q.data + qrow * P.q.row_stride, P.q.inv_norm[qrow], P.dim, hl);
+    } else {
+      const float qf = P.q.scale_scalar * (P.q.scale ? P.q.scale[qrow] : 1.f);
+      if (qf != 1.f) {
+#pragma unroll
+        for (int c = 0; c < CH; ++c)
+#pragma unroll
+          for (int e = 0; e < N; ++e) acc[c][e] *= qf;
+      }
+    }
+  }
+  store_row16<T, G, CH>((G*)P.grad_q + qrow * P.dim, acc, P.dim, hl);
+}
+
 template <typename T, typename G, int CH>
 __global__ void __launch_bounds__(256) bwd_dq16_kernel(BwdParams P) {
   constexpr int N = Vec16<T>::N;
@@ -701,14 +726,21 @@ __global__ void __launch_bounds__(256) bwd_dq16_kernel(BwdParams P) {
 #pragma unroll
   for (int c = 0; c < CH; ++c) lane_on[c] = elt16<T>(c, hl) < P.dim;
   const bool d_factor = P.d.inv_norm || P.d.scale || P.d.scale_scalar != 1.f;
-  for (int jb = 0; jb < count; jb += DQ_JC) {
+  // this CTA's range of the query's documents (all of them unless the documents are split over blockIdx.z)
+  int jb_lo = 0, jb_hi = count;
+  if (P.dq_split > 1) {
+    const int chunk = ((count + DQ_JC - 1) / DQ_JC + P.dq_split - 1) / P.dq_split * DQ_JC;
+    jb_lo = min(count, (int)blockIdx.z * chunk);
+    jb_hi = min(count, jb_lo + chunk);
+  }
+  for (int jb = jb_lo; jb < jb_hi; jb += DQ_JC) {
     __syncthreads();
 #pragma unroll
     for (int x = tid; x < DQ_JC * DQ16_TOK; x += 256) {
       // entry (jj, r): winner of document jb + jj for query token s0 + r
       const int jj = x >> 4, r = x & 15;
       int2 e = make_int2(-1, 0);
-      if (jb + jj < count && s0 + r < lq) {
+      if (jb + jj < jb_hi && s0 + r < lq) {
         long long slot;
         int j;
         nth_score(P, p0, j0, jb + jj, slot, j);
@@ -752,20 +784,50 @@ __global__ void __launch_bounds__(256) bwd_dq16_kernel(BwdParams P) {
     }
   }
   if (!owns) return;
-  if (active) {
-    if (P.normalize & LIK_NORM_Q) {
-      normalize_jacobian_row16<T, CH>(acc, (const T*)P.q.data + qrow * P.q.row_stride, P.q.inv_norm[qrow], P.dim, hl);
-    } else {
-      const float qf = P.q.scale_scalar * (P.q.scale ? P.q.scale[qrow] : 1.f);
-      if (qf != 1.f) {
+  if (P.dq_split > 1) {  // the partial sum of this range; bwd_dq16_sum_kernel finishes the row
+    store_row16<T, float, CH>(P.dq_partial + ((long long)blockIdx.z * P.q.n_rows + qrow) * P.dim, acc, P.dim, hl);
+    return;
+  }
+  dq16_finish_row<T, G, CH>(P, acc, qrow, active, hl);
+}
+
+// Second half of the split grad_q: the partial rows of the document ranges, summed in range order.
+template <typename T, typename G, int CH>
+__global__ void __launch_bounds__(256) bwd_dq16_sum_kernel(BwdParams P) {
+  constexpr int N = Vec16<T>::N;
+  const int tid = threadIdx.x, hl = tid & 15, hw = tid >> 4;
+  const int i = blockIdx.x;
+  const int s = blockIdx.y * DQ16_TOK + hw;
+  long long qrow0;
+  int qlen;
+  seq_bounds(P.q, i, qrow0, qlen, nullptr);
+  const int q_rows = P.q.cu ? qlen : P.q.max_len;
+  if (s >= q_rows) return;
+  const long long qrow = qrow0 + s;
+  const bool active = s < qlen && s < P.argmax_stride && row_valid(P.q, qrow);
+  float acc[CH][N];
 #pragma unroll
-        for (int c = 0; c < CH; ++c)
+  for (int c = 0; c < CH; ++c)
 #pragma unroll
-          for (int e = 0; e < N; ++e) acc[c][e] *= qf;
+    for (int e = 0; e < N; ++e) acc[c][e] = 0.f;
+  for (int z = 0; z < P.dq_split; ++z) {
+    const float* src = P.dq_partial + ((long long)z * P.q.n_rows + qrow) * P.dim;
+#pragma unroll
+    for (int c = 0; c < CH; ++c) {
+      const int k = elt16<T>(c, hl);
+      if (k < P.dim) {
+#pragma unroll
+        for (int q4 = 0; q4 < N; q4 += 4) {
+          const float4 v = *reinterpret_cast<const float4*>(src + k + q4);
+          acc[c][q4] += v.x;
+          acc[c][q4 + 1] += v.y;
+          acc[c][q4 + 2] += v.z;
+          acc[c][q4 + 3] += v.w;
+        }
       }
     }
   }
-  store_row16<T, G, CH>((G*)P.grad_q + qrow * P.dim, acc, P.dim, hl);
+  dq16_finish_row<T, G, CH>(P, acc, qrow, active, hl);
 }
 
 // ---------------------------------------------------------------------------------
@@ -1307,6 +1369,8 @@ struct BwdPlan {
   bool list_sorted;  // pair list on the deterministic kernels
   int sort_warps;    // warps per CTA of the winner sort: at least 256 entries of a document per warp
   bool row16;  // 16-byte gathers: rows 16-byte aligned, width a multiple of 16 bytes, at most 1024 bytes
+  int dq_split;    // grad_q: document ranges per query (1: one CTA walks all the documents of its query tokens)
+  size_t dqp_off;  // their partial rows
   int ld_pad;
   size_t sort_smem;
 };
@@ -1356,6 +1420,20 @@ BwdPlan plan_bwd(const lik_bwd_args& a) {
     pl.sq_off = take((size_t)(a.q.n_seq + 1) * 4);
     pl.sd_off = take((size_t)(a.d.n_seq + 1) * 4);
     pl.sort_off = take(sort_pairs_scratch(a.n_pairs));
+  }
+  // few query tokens against many documents: one CTA per 16 query tokens would leave most of the GPU idle
+  pl.dq_split = 1;
+  pl.dqp_off = (size_t)-1;
+  if (a.grad_q && pl.row16 && a.pairing == LIK_PAIR_CROSS && a.q.n_seq > 0 && a.q.max_len > 0 && a.dim % 4 == 0) {
+    const long long base = (long long)a.q.n_seq * ceil_div(a.q.max_len, DQ16_TOK);
+    const long long chunks = ceil_div(a.d.n_seq, DQ_JC);
+    long long z = (2ll * sm_count()) / base;
+    if (z > chunks / 2) z = chunks / 2;  // at least two rounds of documents per range
+    if (z > 64) z = 64;
+    if (z >= 2) {
+      pl.dq_split = (int)z;
+      pl.dqp_off = take((size_t)z * a.q.n_rows * a.dim * 4);
+    }
   }
   const bool scatter = list && !pl.list_sorted;
   if (a.grad_q && scatter) pl.gq32_off = take((size_t)a.q.n_rows * a.dim * 4);
@@ -1472,14 +1550,18 @@ int run_bwd(const lik_bwd_args& a, BwdParams& P, const BwdPlan& pl, cudaStream_t
   if (a.grad_q && !list && a.q.n_seq > 0 && a.q.max_len > 0) {
     dim3 grid((unsigned)a.q.n_seq, (unsigned)ceil_div(a.q.max_len, 8));
     if (pl.row16) {
-      const dim3 grid16((unsigned)a.q.n_seq, (unsigned)ceil_div(a.q.max_len, DQ16_TOK));
+      const dim3 grid16((unsigned)a.q.n_seq, (unsigned)ceil_div(a.q.max_len, DQ16_TOK), (unsigned)pl.dq_split);
+      const dim3 grid_sum((unsigned)a.q.n_seq, (unsigned)ceil_div(a.q.max_len, DQ16_TOK));
       const size_t row_bytes = (size_t)a.dim * sizeof(T);
-      if (row_bytes <= 256)
-        bwd_dq16_kernel<T, G, 1><<<grid16, 256, 0, st>>>(P), ::lik::count_launch();
-      else if (row_bytes <= 512)
-        bwd_dq16_kernel<T, G, 2><<<grid16, 256, 0, st>>>(P), ::lik::count_launch();
-      else
-        bwd_dq16_kernel<T, G, 4><<<grid16, 256, 0, st>>>(P), ::lik::count_launch();
+#define LIK_DQ16(CH_)                                                                              \
+  do {                                                                                             \
+    bwd_dq16_kernel<T, G, CH_><<<grid16, 256, 0, st>>>(P), ::lik::count_launch();                  \
+    if (pl.dq_split > 1) bwd_dq16_sum_kernel<T, G, CH_><<<grid_sum, 256, 0, st>>>(P), ::lik::count_launch(); \
+  } while (0)
+      if (row_bytes <= 256) LIK_DQ16(1);
+      else if (row_bytes <= 512) LIK_DQ16(2);
+      else LIK_DQ16(4);
+#undef LIK_DQ16
     } else if (fast) {
       if (a.dim <= 128)
         bwd_dq_fast_kernel<T, G, 1><<<grid, 256, 0, st>>>(P), ::lik::count_launch();
@@ -1630,6 +1712,8 @@ extern "C" int lik_maxsim_bwd(const lik_bwd_args* a, lik_stream_t stream) {
   P.gq32 = P.gd32 = nullptr;
   P.status = a->status;
   P.perm_q = P.start_q = P.perm_d = P.start_d = nullptr;
+  P.dq_split = pl.dq_split;
+  P.dq_partial = pl.dq_split > 1 ? (float*)((char*)a->workspace + pl.dqp_off) : nullptr;
   switch (a->dtype) {
     case LIK_F32:
       return run_bwd_g<float>(*a, P, pl, st);

@@ -420,6 +420,113 @@ head_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Backward helpers: only winning tokens carry gradient, so the backward works on "compact" documents made of the
+// distinct winners of each document, in ascending token order.
+// ---------------------------------------------------------------------------------------------
+// One CTA per document.  A bitmap over the document's tokens collects the winners of every (query, query token);
+// the number of winners below a token is a prefix count per bitmap word plus a popcount inside the word.  Outputs:
+// the winner positions inside the compact document (for the backward kernels), the row of the hidden states behind
+// every compact slot (for the gather), the compact length, and the bitmap with its prefix counts (for the scatter).
+__global__ void __launch_bounds__(256) hidden_winners_kernel(const int* __restrict__ argmax, int n_q, int n_d, int lq, int ld, int slots,
+                                                             int words, int* __restrict__ compact_argmax, long long* __restrict__ rows,
+                                                             int* __restrict__ counts, unsigned* __restrict__ bitmap,
+                                                             int* __restrict__ prefix, int* status) {
+  extern __shared__ unsigned hw_smem[];
+  unsigned* bm = hw_smem;
+  int* pre = reinterpret_cast<int*>(hw_smem + words);
+  __shared__ int warp_sum_s[8];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int j = blockIdx.x;
+  for (int w = tid; w < words; w += 256) bm[w] = 0u;
+  __syncthreads();
+  const int n_ent = n_q * lq;
+  for (int e = tid; e < n_ent; e += 256) {
+    const int i = e / lq, s = e - i * lq;
+    const int t = argmax[((long long)i * n_d + j) * lq + s];
+    if (t >= 0) {
+      if (t < ld) atomicOr(&bm[t >> 5], 1u << (t & 31));
+      else if (status) atomicOr(status, LIK_DEV_INTERNAL);  // a saved winner outside its document: ignored
+    }
+  }
+  __syncthreads();
+  // exclusive prefix of the words' popcounts: every thread owns a run of consecutive words
+  const int per = (words + 255) / 256;
+  const int w0 = min(words, tid * per), w1 = min(words, w0 + per);
+  int mine = 0;
+  for (int w = w0; w < w1; ++w) mine += __popc(bm[w]);
+  int incl = mine;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int v = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += v;
+  }
+  if (lane == 31) warp_sum_s[warp] = incl;
+  __syncthreads();
+  int before = incl - mine, total = 0;
+  for (int w = 0; w < 8; ++w) {
+    if (w < warp) before += warp_sum_s[w];
+    total += warp_sum_s[w];
+  }
+  for (int w = w0; w < w1; ++w) {
+    pre[w] = before;
+    before += __popc(bm[w]);
+  }
+  __syncthreads();
+  if (total > slots) {  // cannot happen for slots >= min(n_q * lq, ld); keep every store in bounds anyway
+    if (tid == 0 && status) atomicOr(status, LIK_DEV_INTERNAL);
+    total = slots;
+  }
+  if (tid == 0) counts[j] = total;
+  for (int w = tid; w < words; w += 256) {
+    const unsigned bits = bm[w];
+    bitmap[(long long)j * words + w] = bits;
+    prefix[(long long)j * words + w] = pre[w];
+    int pos = pre[w];
+    for (unsigned b = bits; b; b &= b - 1) {
+      if (pos < slots) rows[(long long)j * slots + pos] = (long long)j * ld + w * 32 + (__ffs(b) - 1);
+      ++pos;
+    }
+  }
+  for (int p = total + tid; p < slots; p += 256) rows[(long long)j * slots + p] = (long long)j * ld;  // unused slots: any row of the document
+  for (int e = tid; e < n_ent; e += 256) {
+    const int i = e / lq, s = e - i * lq;
+    const long long o = ((long long)i * n_d + j) * lq + s;
+    const int t = argmax[o];
+    int c = -1;
+    if (t >= 0 && t < ld) {
+      c = pre[t >> 5] + __popc(bm[t >> 5] & ((1u << (t & 31)) - 1u));
+      if (c >= slots) c = -1;
+    }
+    compact_argmax[o] = c;
+  }
+}
+
+// grad_h, every row written once: the compact row of a winning token, zeros for all the others.  One warp per
+// bitmap word (32 tokens); rows are copied in 16-byte pieces.
+__global__ void __launch_bounds__(256) hidden_scatter_kernel(const uint4* __restrict__ compact, int row_vecs, int n_d, int ld, int slots,
+                                                             int words, const unsigned* __restrict__ bitmap, const int* __restrict__ prefix,
+                                                             uint4* __restrict__ out) {
+  const int lane = threadIdx.x & 31;
+  const long long n_words = (long long)n_d * words;
+  for (long long gw = (long long)blockIdx.x * 8 + (threadIdx.x >> 5); gw < n_words; gw += (long long)gridDim.x * 8) {
+    const int j = (int)(gw / words), w = (int)(gw - (long long)j * words);
+    const unsigned bits = bitmap[gw];
+    const int base = prefix[gw];
+    const int n_tok = min(32, ld - w * 32);
+    for (int b = 0; b < n_tok; ++b) {
+      uint4* dst = out + ((long long)j * ld + w * 32 + b) * row_vecs;
+      if ((bits >> b) & 1u) {
+        const int pos = base + __popc(bits & ((1u << b) - 1u));
+        const uint4* src = compact + ((long long)j * slots + min(pos, slots - 1)) * row_vecs;
+        for (int v = lane; v < row_vecs; v += 32) dst[v] = src[v];
+      } else {
+        for (int v = lane; v < row_vecs; v += 32) dst[v] = make_uint4(0u, 0u, 0u, 0u);
+      }
+    }
+  }
+}
+
 struct HeadPlan {
   int n_k, n_s2, stages, mt, q_per_tile, grid;
   size_t smem_bytes;
@@ -545,6 +652,44 @@ extern "C" int lik_maxsim_hidden_fwd(const lik_hidden_fwd_args* args, lik_stream
   }
   if (v) head_tc_kernel<true><<<pl.grid, HD_THREADS, pl.smem_bytes, st>>>(q_map, h_map, w_map, P), ::lik::count_launch();
   else head_tc_kernel<false><<<pl.grid, HD_THREADS, pl.smem_bytes, st>>>(q_map, h_map, w_map, P), ::lik::count_launch();
+  LIK_CUDA_OK(cudaGetLastError());
+  return LIK_OK;
+}
+
+extern "C" int lik_hidden_winners(const int32_t* argmax, int32_t n_q, int32_t n_d, int32_t lq, int32_t ld, int32_t slots,
+                                  int32_t* compact_argmax, int64_t* rows, int32_t* counts, uint32_t* bitmap, int32_t* prefix,
+                                  int32_t* status, lik_stream_t stream) {
+  using namespace lik;
+  LIK_REQUIRE(n_q >= 0 && n_d >= 0 && lq > 0 && ld > 0 && slots > 0, "sizes must be positive");
+  LIK_REQUIRE((long long)n_q * lq < (1ll << 31) && (long long)n_d * ld < (1ll << 40), "sizes out of range");
+  if (n_d == 0) return LIK_OK;
+  LIK_REQUIRE(argmax && compact_argmax && rows && counts && bitmap && prefix, "NULL pointer");
+  const int words = (ld + 31) / 32;
+  const size_t smem = (size_t)words * 8;
+  LIK_REQUIRE(smem <= 48 * 1024, "documents longer than 196608 tokens are not supported");
+  hidden_winners_kernel<<<n_d, 256, smem, (cudaStream_t)stream>>>(argmax, n_q, n_d, lq, ld, slots, words, compact_argmax,
+                                                                   (long long*)rows, counts, bitmap, prefix, status),
+      ::lik::count_launch();
+  LIK_CUDA_OK(cudaGetLastError());
+  return LIK_OK;
+}
+
+extern "C" int lik_hidden_scatter_rows(const void* compact_rows, int64_t row_bytes, int32_t n_d, int32_t ld, int32_t slots,
+                                       const uint32_t* bitmap, const int32_t* prefix, void* grad_h, lik_stream_t stream) {
+  using namespace lik;
+  LIK_REQUIRE(n_d >= 0 && ld > 0 && slots > 0 && row_bytes > 0, "sizes must be positive");
+  if (n_d == 0) return LIK_OK;
+  LIK_REQUIRE(compact_rows && bitmap && prefix && grad_h, "NULL pointer");
+  LIK_REQUIRE(row_bytes % 16 == 0 && row_bytes / 16 < (1ll << 31) && ((uintptr_t)compact_rows & 15) == 0 && ((uintptr_t)grad_h & 15) == 0,
+              "rows must be 16-byte aligned and a multiple of 16 bytes long");
+  const int words = (ld + 31) / 32;
+  const long long n_words = (long long)n_d * words;
+  long long grid = ceil_div(n_words, 8);
+  const long long cap = (long long)sm_count() * 8;
+  if (grid > cap) grid = cap;
+  hidden_scatter_kernel<<<(unsigned)grid, 256, 0, (cudaStream_t)stream>>>((const uint4*)compact_rows, (int)(row_bytes / 16), n_d, ld, slots,
+                                                                            words, bitmap, prefix, (uint4*)grad_h),
+      ::lik::count_launch();
   LIK_CUDA_OK(cudaGetLastError());
   return LIK_OK;
 }

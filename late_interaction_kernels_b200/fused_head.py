@@ -74,12 +74,12 @@ class _MaxSimFromHiddenFn(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, grad_scores):
-        # Only winning tokens carry gradient (fused_head.py:332-456 gathers H_d at the winners too): the winners of
-        # every (query token, document) are made unique and sorted, which turns each document into a short "compact"
-        # document of at most Nq * Lq tokens.  Those rows of H_d are gathered and projected again, the deterministic
-        # backward kernels run on the compact documents (with the document-side normalise Jacobian), and the three
-        # GEMMs of the linear layer see the winner rows alone.  Cost and memory follow the winners, not the corpus;
-        # the rest of grad_H is the zero fill.
+        # Only winning tokens carry gradient (fused_head.py:332-456 gathers H_d at the winners too): the distinct winners
+        # of every document, in token order, form a short "compact" document of at most Nq * Lq tokens
+        # (lik_hidden_winners).  Those rows of H_d are gathered and projected again, the deterministic backward kernels
+        # run on the compact documents (with the document-side normalise Jacobian), the three GEMMs of the linear layer
+        # see the winner rows alone, and one pass writes grad_H: a winner's row or zeros (lik_hidden_scatter_rows).
+        # No host synchronisation; cost follows the winners, apart from that one pass over grad_H.
         Q, H_d, W, b, d_mask, argmax = ctx.saved_tensors
         Nq, Lq, d_out = Q.shape
         Nd, Ld, d_model = H_d.shape
@@ -89,37 +89,34 @@ class _MaxSimFromHiddenFn(torch.autograd.Function):
         need_b = need_b and b is not None
         need_d = need_h or need_w or need_b
         g = grad_scores.contiguous().to(torch.float32)
-        sentinel = Nd * Ld  # "no winner": sorts behind every real row
-        doc = torch.arange(Nd, device=dev, dtype=torch.int64).view(1, Nd, 1)
-        has = argmax >= 0
-        rows = torch.where(has, doc * Ld + argmax.to(torch.int64), sentinel)
-        uniq, inv = torch.unique(rows.reshape(-1), return_inverse=True)  # ascending: grouped by document, sentinel last
-        cu = torch.searchsorted(uniq, torch.arange(Nd + 1, device=dev, dtype=torch.int64) * Ld).to(torch.int32)
-        n_rows = int(cu[-1])  # winner rows (the host already waited for the size of `uniq`)
-        # winner -> its position inside the compact document
-        doc_of = torch.div(uniq, Ld, rounding_mode="floor").clamp_(max=Nd - 1)
-        pos = torch.arange(uniq.numel(), device=dev, dtype=torch.int64) - cu[doc_of]
-        am_c = torch.where(has.reshape(-1), pos[inv], -1).to(torch.int32).view(Nq * Nd, Lq)
-        uniq = uniq[:n_rows]
-        gH = torch.zeros_like(H_d) if need_h else None
-        gW = torch.zeros_like(W) if need_w else None
-        gb = torch.zeros_like(b) if need_b else None
-        if n_rows == 0:
-            return (torch.zeros_like(Q) if need_q else None), gH, gW, gb, None, None
-        H_rows = H_d.reshape(Nd * Ld, d_model)[uniq]
+        S = max(1, min(Nq * Lq, Ld))  # slots of a compact document
+        am_c, rows, counts, bitmap, prefix = _ops.hidden_winners(argmax, Nq, Nd, Lq, Ld, S)
+        H_rows = H_d.reshape(Nd * Ld, d_model).index_select(0, rows)  # [Nd * S, d_model]
         P_rows = _project(H_rows, W, b, dt)
         q = _ops.padded_spec(Q.to(dt))
-        dd = _ops.packed_spec(P_rows, cu, max(1, min(Nq * Lq, Ld)))
+        dd = _ops.padded_spec(P_rows.view(Nd, S, d_out), lens=counts)
         norm = _lib.NORM_D if ctx.normalize else _lib.NORM_NONE
-        gq, gp = _ops.backward(q, dd, g, am_c, normalize=norm, deterministic=True, grad_dtype=torch.float32,
+        gq, gp = _ops.backward(q, dd, g, am_c.view(Nq * Nd, Lq), normalize=norm, deterministic=True, grad_dtype=torch.float32,
                                need_q=need_q, need_d=need_d)  # gp: gradient w.r.t. the projected winner rows before normalisation
         gQ = gq.view(Nq, Lq, d_out).to(Q.dtype) if need_q else None
-        if need_h:
-            gH.view(Nd * Ld, d_model).index_copy_(0, uniq, (gp @ W.float()).to(H_d.dtype))  # unique rows: one writer each
-        if need_w:
-            gW = (gp.t() @ H_rows.float()).to(W.dtype)
-        if need_b:
-            gb = gp.sum(0).to(b.dtype)
+        gH = gW = gb = None
+        if need_d:
+            # 16-bit models: the linear layer's gradient GEMMs take 16-bit operands with fp32 accumulation, as its forward does
+            low = dt in (torch.bfloat16, torch.float16)
+            gpl = gp.to(dt) if low else gp
+            if need_h:
+                g_rows = (gpl @ (W.to(dt) if low else W.float())).to(H_d.dtype)
+                gH = torch.empty_like(H_d)
+                if (d_model * gH.element_size()) % 16 == 0:
+                    _ops.hidden_scatter_rows(g_rows, bitmap, prefix, gH.view(Nd * Ld, d_model), Nd, Ld, S)  # one pass, every row written once
+                else:
+                    gH.zero_()
+                    live = (torch.arange(S, device=dev).unsqueeze(0) < counts.unsqueeze(1)).reshape(-1)
+                    gH.view(Nd * Ld, d_model).index_copy_(0, rows[live], g_rows[live])
+            if need_w:
+                gW = (gpl.t() @ (H_rows.to(dt) if low else H_rows.float())).to(W.dtype)
+            if need_b:
+                gb = gp.sum(0).to(b.dtype)
         return gQ, gH, gW, gb, None, None
 
 

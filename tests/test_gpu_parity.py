@@ -252,6 +252,31 @@ def test_backward_given_argmax_and_determinism():
     assert torch.equal(u[0], outs[0][0]), "grad_Q is row-owned in both methods"
 
 
+@pytest.mark.parametrize("dtype,normalize", [(torch.bfloat16, False), (torch.bfloat16, True), (torch.float32, True)])
+def test_backward_few_queries_many_documents(dtype, normalize):
+    """grad_Q of a couple of queries against hundreds of documents: the documents of a query are split over several
+    CTAs whose partial rows are summed in a fixed order (same result as the oracle, same bits every run)."""
+    from late_interaction_kernels_b200 import _lib, _ops
+
+    Nq, Nd, Lq, Ld, d = 2, 333, 20, 24, 64
+    rng = np.random.default_rng(9)
+    Q = rng.standard_normal((Nq, Lq, d)).astype(np.float32)
+    D = rng.standard_normal((Nd, Ld, d)).astype(np.float32)
+    am = rng.integers(-1, Ld, size=(Nq, Nd, Lq)).astype(np.int32)
+    go = rng.standard_normal((Nq, Nd)).astype(np.float32)
+    Qr, Dr = rounded(Q, dtype), rounded(D, dtype)
+    if normalize:
+        wq, wd = O.backward_from_argmax(go, O.l2_normalize(Qr), O.l2_normalize(Dr), am)
+        wq, wd = O.normalize_jacobian(wq, Qr, eps=1e-12), O.normalize_jacobian(wd, Dr, eps=1e-12)
+    else:
+        wq, wd = O.backward_from_argmax(go, Qr, Dr, am)
+    q, dd = _ops.padded_spec(dev(Q, dtype)), _ops.padded_spec(dev(D, dtype))
+    outs = [_ops.backward(q, dd, dev(go), dev(am.reshape(-1, Lq)), normalize=_lib.NORM_BOTH if normalize else _lib.NORM_NONE,
+                          grad_dtype=torch.float32) for _ in range(2)]
+    _grad_check(outs[0][0].view(Nq, Lq, d), outs[0][1].view(Nd, Ld, d), wq, wd, 1e-4 if dtype == torch.float32 else 2e-2)
+    assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
+
+
 def test_backward_kd_varlen_pairs_padded():
     from late_interaction_kernels_b200.score_pairs import score_pairs_packed
 
