@@ -589,6 +589,20 @@ def _time_us(fn, dev, iters=10, warm=3, graph=False):
     return e0.elapsed_time(e1) / iters * 1e3
 
 
+def hidden_inputs(n_q, n_d, ld, dev, d_model=768, d_out=128):
+    """Inputs of maxsim_from_hidden at the reference's ModernBERT-base head shape (benchmarks/kernels/
+    bench_fused_head_train.py:53-66): hidden states [n_d, ld, 768] -> 128, 32-token queries, bf16."""
+    import torch
+    import torch.nn.functional as F
+
+    g = torch.Generator(device=dev).manual_seed(11)
+    H = torch.randn((n_d, ld, d_model), generator=g, device=dev).bfloat16()
+    W = (torch.randn((d_out, d_model), generator=g, device=dev) / d_model ** 0.5).bfloat16()
+    b = (0.1 * torch.randn((d_out,), generator=g, device=dev)).bfloat16()
+    Q = F.normalize(torch.randn((n_q, 32, d_out), generator=g, device=dev), dim=-1).bfloat16()
+    return Q, H, W, b
+
+
 def other_configs(dev):
     """Kernel timings of the other workload shapes (rank 0, one GPU), each with the roofline that bounds it: the KD
     layout in bf16 and e4m3 (HBM: document bytes read once), the packed ColPali-shaped batch forward and forward +
@@ -684,6 +698,28 @@ def other_configs(dev):
                 "roofline": roofline("hbm", T * 36.0, t * 1e-6, kernel="plaid_decompress16_kernel + fwd_tc_kernel (fused top-k) + topk_slots_kernel",
                                      note="compressed bytes (36 B per token) read once; the decoded rows (256 B per token) are written and "
                                           "read back, and with 256 query rows the scoring is tensor work: HBM on compressed bytes is a loose bound")}
+    # document head: 1 query x 1024 documents of 2048 hidden states (768 -> 128), the largest shape of the reference's
+    # fused-head benchmark; forward alone, and the training step against projecting with F.linear first
+    from late_interaction_kernels_b200.fused_head import maxsim_from_hidden
+    hq, hh, hw, hb = hidden_inputs(1, 1024, 2048, dev)
+    t = _time_us(lambda: maxsim_from_hidden(hq, hh, hw, hb), dev)
+    h_bytes = hh.numel() * 2.0
+    out["hidden_head_fwd"] = {"us": t, "shape": "Q[1,32,128] x H[1024,2048,768] -> 128, bf16",
+                              "roofline": roofline("hbm", h_bytes + hw.numel() * 2.0 + hq.numel() * 2.0 + 4.0 * 1024, t * 1e-6, kernel="head_tc_kernel",
+                                                   traffic=scaled_traffic("head_tc_kernel_per_token", 1024 * 2048),
+                                                   note="hidden states read once; the projected tokens stay on chip")}
+    t_unf = _time_us(lambda: lik.maxsim(hq, F.normalize(F.linear(hh, hw, hb), dim=-1)), dev, iters=5)
+    out["hidden_head_fwd"]["unfused_us"] = t_unf
+
+    def head_step(fused):
+        Hg, Wg, Qg = hh.detach().requires_grad_(True), hw.detach().requires_grad_(True), hq.detach().requires_grad_(True)
+        sc_ = maxsim_from_hidden(Qg, Hg, Wg, hb) if fused else lik.maxsim(Qg, F.normalize(F.linear(Hg, Wg, hb), dim=-1))
+        sc_.sum().backward()
+
+    out["hidden_head_step"] = {"us": _time_us(lambda: head_step(True), dev, iters=5), "unfused_us": _time_us(lambda: head_step(False), dev, iters=3),
+                               "note": "forward + backward into Q, H and W; the backward touches the winning rows and writes grad_H once"}
+    del hh
+    torch.cuda.empty_cache()
     # per-row top-k kernel on a score matrix
     sc = torch.randn((1024, 4096), generator=g, device=dev)
     t = _time_us(lambda: _ops.topk_rows(sc, 100), dev, graph=True)
@@ -704,7 +740,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--retrieve-docs", type=int, default=1_000_000,
                     help="corpus size of the sharded top-k retrieve reported under extra.retrieve (0 = skip)")
-    ap.add_argument("--only", default=None, choices=["fwd", "fwd_infer", "bwd", "step", "retrieve", "plaid", "topk_rows", "decompress"],
+    ap.add_argument("--only", default=None, choices=["fwd", "fwd_infer", "bwd", "step", "retrieve", "plaid", "topk_rows", "decompress", "hidden"],
                     help="profiling aid: launch only this part, --steps times, and print its mean time")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
@@ -786,6 +822,10 @@ def main():
             cent, bw = plaid_tables(dev)
             Qc = retrieve_queries(8, dev)
             part = lambda: plaid_mod.retrieve_residual_varlen(Qc, pc, pr, pcu, cent, bw, 2, 10)  # noqa: E731
+        elif args.only == "hidden":  # document head chained into MaxSim: 1 query x 128 documents of 2048 hidden states (0.4 GB)
+            from late_interaction_kernels_b200.fused_head import maxsim_from_hidden
+            hq, hh, hw, hb = hidden_inputs(1, 128, 2048, dev)
+            part = lambda: maxsim_from_hidden(hq, hh, hw, hb)  # noqa: E731
         elif args.only == "decompress":
             pc, pr, pl_ = plaid_corpus(0, 25_000, dev)
             cent, bw = plaid_tables(dev)

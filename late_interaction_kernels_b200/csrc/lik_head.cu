@@ -53,6 +53,7 @@ struct HeadParams {
   int stages;
   int mt;                      // resident query tiles (1 or 2)
   int n_q, lq, q_per_tile;
+  int q_last_rows;             // rows held of the last query tile (a multiple of 8): the rows behind them are never looked at
   int f16;
   int normalize;
   const void* bias;
@@ -138,6 +139,26 @@ __device__ __forceinline__ void hd_convert32(const float (&v)[32], const float* 
   }
 }
 
+// The four K steps of one 128-byte slab as one block: the descriptors of steps 1..3 are the first one's plus 2, 4, 6
+// (16-byte units).  The issuing thread is a serial bottleneck of this kernel (one MMA per 4 KB of hidden states), so
+// the code between two MMAs is kept to the few instructions that build the descriptors.
+__device__ __forceinline__ void tc_mma_slab_f16(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t desc_hi, uint32_t idesc,
+                                                uint32_t accumulate_first) {
+  asm volatile(
+      "{\n\t.reg .pred p0, p1;\n\t.reg .b64 da, db;\n\t.reg .b32 ta, tb;\n\t"
+      "setp.ne.b32 p0, %5, 0;\n\tsetp.eq.b32 p1, %3, %3;\n\t"
+      "mov.b64 da, {%1, %3};\n\tmov.b64 db, {%2, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p0;\n\t"
+      "add.u32 ta, %1, 2;\n\tadd.u32 tb, %2, 2;\n\tmov.b64 da, {ta, %3};\n\tmov.b64 db, {tb, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p1;\n\t"
+      "add.u32 ta, %1, 4;\n\tadd.u32 tb, %2, 4;\n\tmov.b64 da, {ta, %3};\n\tmov.b64 db, {tb, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p1;\n\t"
+      "add.u32 ta, %1, 6;\n\tadd.u32 tb, %2, 6;\n\tmov.b64 da, {ta, %3};\n\tmov.b64 db, {tb, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p1;\n\t}" ::"r"(d_tmem),
+      "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "r"(accumulate_first)
+      : "memory");
+}
+
 template <bool ARGMAX>
 __global__ void __launch_bounds__(HD_THREADS, 1)
 head_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap h_map,
@@ -145,8 +166,10 @@ head_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   const int q_tile_bytes = P.n_s2 * HD_SLAB;
-  unsigned char* q_smem = smem;                                     // [mt][n_s2][128 rows][128 B]
-  unsigned char* p_smem = q_smem + P.mt * q_tile_bytes;             // [n_s2][128 rows][128 B]
+  unsigned char* q_smem = smem;                                     // [mt][n_s2][128 rows (last tile: q_last_rows)][128 B]
+  // (the last query tile holds only the rows that queries occupy: the MMA still reads 128 rows, and what it reads
+  // behind them - the next buffers - only reaches accumulator rows that nobody looks at)
+  unsigned char* p_smem = q_smem + (P.mt - 1) * q_tile_bytes + P.n_s2 * P.q_last_rows * HD_SLAB_ROW;  // [n_s2][128 rows][128 B]
   unsigned char* ring = p_smem + P.n_s2 * HD_SLAB;                  // [stages]{h slab [128][128 B], w slab [d_out][128 B]}
   constexpr int STAGE_BYTES = 2 * HD_SLAB;
   HeadCtl* ctl = reinterpret_cast<HeadCtl*>(ring + (size_t)P.stages * STAGE_BYTES);
@@ -200,10 +223,14 @@ head_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
       uint32_t st = 0, ph = 0, n_load = 0;
       bool ok = true;
       // the query tiles stay for the whole kernel
-      mbar_arrive_expect_tx(smem_u32(&ctl->q_full), (uint32_t)(P.mt * q_tile_bytes));
-      for (int m = 0; m < P.mt; ++m)
+      mbar_arrive_expect_tx(smem_u32(&ctl->q_full), (uint32_t)((P.mt - 1) * q_tile_bytes + P.n_s2 * P.q_last_rows * HD_SLAB_ROW));
+      for (int m = 0; m < P.mt; ++m) {
+        const int rows = m == P.mt - 1 ? P.q_last_rows : TILE_M;
         for (int sl = 0; sl < P.n_s2; ++sl)
-          tma_load_2d(smem_u32(q_smem + m * q_tile_bytes + sl * HD_SLAB), &q_map, sl * 64, m * P.q_per_tile * P.lq, smem_u32(&ctl->q_full));
+          for (int r = 0; r < rows; r += 8)  // boxes of 8 rows (one swizzle atom)
+            tma_load_2d(smem_u32(q_smem + m * q_tile_bytes + (sl * rows + r) * HD_SLAB_ROW), &q_map, sl * 64, m * P.q_per_tile * P.lq + r,
+                        smem_u32(&ctl->q_full));
+      }
       const uint32_t stage_tx = (uint32_t)(HD_SLAB + P.d_out * HD_SLAB_ROW);
       for (int doc = doc_lo; doc < doc_hi && ok; ++doc) {
         const int len = hd_doc_len(P, doc);
@@ -249,20 +276,28 @@ head_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
       const uint32_t q_desc0 = (uint32_t)smem_desc_sw128(smem_u32(q_smem));
       const uint32_t p_desc0 = (uint32_t)smem_desc_sw128(smem_u32(p_smem));
       const uint32_t idesc1 = instr_desc(ab_format, P.d_out);
+      const uint32_t idesc2_0 = instr_desc(ab_format, 0);
       const int k2_steps = P.d_out / 16;
+      const uint32_t full0 = smem_u32(&ctl->ring_full[0]), empty0 = smem_u32(&ctl->ring_empty[0]);
+      const uint32_t last_q_slab = (uint32_t)((P.q_last_rows * HD_SLAB_ROW) >> 4);  // slab pitch of the last (trimmed) query tile
       // scoring MMA of the tile converted last: every resident query tile against the tile's tokens
       auto score_tile = [&](int ncols) -> bool {
         if (n2 == 0 && !hd_wait(&ctl->q_full, 0, ctl, P.status)) return false;
         if (!hd_wait(&ctl->p_full, n2 & 1, ctl, P.status)) return false;
-        const uint32_t idesc2 = instr_desc(ab_format, (ncols + 31) & ~31);
+        const uint32_t idesc2 = idesc2_0 | ((uint32_t)((ncols + 31) >> 5) << 19);  // N / 8 in bits 17..22, N a multiple of 32
         for (int m = 0; m < P.mt; ++m) {
           if (!hd_wait(&ctl->acc2_empty[m], (n2 & 1) ^ 1, ctl, P.status)) return false;
           tc_fence_after();
           const uint32_t d_tmem = tmem_base + 256u + (uint32_t)(m * HD_TOK);
           const uint32_t a0 = q_desc0 + (uint32_t)((m * q_tile_bytes) >> 4);
-          for (int k = 0; k < k2_steps; ++k) {
-            const uint32_t off = (uint32_t)((k & 3) * 2 + (k >> 2) * (HD_SLAB >> 4));
-            tc_mma<false>(d_tmem, a0 + off, p_desc0 + off, desc_hi, idesc2, k ? 1u : 0u);
+          const uint32_t a_slab = m == P.mt - 1 ? last_q_slab : (uint32_t)(HD_SLAB >> 4);
+          if (k2_steps == 8) {
+            tc_mma_slab_f16(d_tmem, a0, p_desc0, desc_hi, idesc2, 0u);
+            tc_mma_slab_f16(d_tmem, a0 + a_slab, p_desc0 + (uint32_t)(HD_SLAB >> 4), desc_hi, idesc2, 1u);
+          } else {
+            for (int k = 0; k < k2_steps; ++k)
+              tc_mma<false>(d_tmem, a0 + (uint32_t)((k & 3) * 2) + (uint32_t)(k >> 2) * a_slab,
+                            p_desc0 + (uint32_t)((k & 3) * 2 + (k >> 2) * (HD_SLAB >> 4)), desc_hi, idesc2, k ? 1u : 0u);
           }
           tc_commit(smem_u32(&ctl->acc2_full[m]));
         }
@@ -279,14 +314,14 @@ head_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
           tc_fence_after();
           const uint32_t d_tmem = tmem_base + a * (uint32_t)HD_TOK;
           for (int ks = 0; ks < P.n_k; ++ks) {
-            ok = hd_wait(&ctl->ring_full[st], ph, ctl, P.status);
-            if (!ok) break;
-            tc_fence_after();
+            // (data landed by TMA and consumed by the MMA: the barrier alone orders the two)
+            if (!mbar_try_wait(full0 + 8u * st, ph)) {
+              ok = hd_wait_slow(full0 + 8u * st, ph, ctl, P.status);
+              if (!ok) break;
+            }
             const uint32_t h_desc = ring_desc0 + st * (uint32_t)(STAGE_BYTES >> 4);
-            const uint32_t w_desc = h_desc + (uint32_t)(HD_SLAB >> 4);
-#pragma unroll
-            for (int k = 0; k < 4; ++k) tc_mma<false>(d_tmem, h_desc + 2 * k, w_desc + 2 * k, desc_hi, idesc1, (ks | k) ? 1u : 0u);
-            tc_commit(smem_u32(&ctl->ring_empty[st]));
+            tc_mma_slab_f16(d_tmem, h_desc, h_desc + (uint32_t)(HD_SLAB >> 4), desc_hi, idesc1, (uint32_t)ks);
+            tc_commit(empty0 + 8u * st);
             if (++st == (uint32_t)P.stages) { st = 0; ph ^= 1; }
           }
           if (!ok) break;
@@ -528,7 +563,7 @@ __global__ void __launch_bounds__(256) hidden_scatter_kernel(const uint4* __rest
 }
 
 struct HeadPlan {
-  int n_k, n_s2, stages, mt, q_per_tile, grid;
+  int n_k, n_s2, stages, mt, q_per_tile, q_last_rows, grid;
   size_t smem_bytes;
   size_t lens_off, total_ws;
 };
@@ -551,7 +586,9 @@ bool head_plan(const lik_hidden_fwd_args& a, HeadPlan& pl) {
   if (a.argmax && a.argmax_stride < a.q.max_len) return false;
   pl.n_k = (a.d_model * 2 + HD_SLAB_ROW - 1) / HD_SLAB_ROW;
   pl.n_s2 = (a.d_out * 2 + HD_SLAB_ROW - 1) / HD_SLAB_ROW;
-  const size_t fixed = (size_t)(pl.mt + 1) * pl.n_s2 * HD_SLAB + sizeof(HeadCtl) + 1024;
+  const int last_queries = a.q.n_seq - (pl.mt - 1) * pl.q_per_tile;
+  pl.q_last_rows = (last_queries * a.q.max_len + 7) & ~7;
+  const size_t fixed = (size_t)pl.mt * pl.n_s2 * HD_SLAB + (size_t)pl.n_s2 * pl.q_last_rows * HD_SLAB_ROW + sizeof(HeadCtl) + 1024;
   const size_t budget = 227 * 1024;
   int st = (int)((budget - fixed) / (2 * HD_SLAB));
   pl.stages = st > HD_MAX_STAGES ? HD_MAX_STAGES : st;
@@ -601,7 +638,7 @@ extern "C" int lik_maxsim_hidden_fwd(const lik_hidden_fwd_args* args, lik_stream
     return LIK_ERR_WORKSPACE;
   }
   CUtensorMap q_map, h_map, w_map;
-  int rc = make_tmap_rows(&q_map, a.q.data, a.dtype, a.d_out, a.q.n_rows, a.q.row_stride, TILE_M);
+  int rc = make_tmap_rows(&q_map, a.q.data, a.dtype, a.d_out, a.q.n_rows, a.q.row_stride, 8);
   if (rc) return rc;
   rc = make_tmap_rows(&h_map, a.h.data, a.dtype, a.d_model, a.h.n_rows, a.h.row_stride, HD_TOK);
   if (rc) return rc;
@@ -631,6 +668,7 @@ extern "C" int lik_maxsim_hidden_fwd(const lik_hidden_fwd_args* args, lik_stream
   P.n_q = a.q.n_seq;
   P.lq = a.q.max_len;
   P.q_per_tile = pl.q_per_tile;
+  P.q_last_rows = pl.q_last_rows;
   P.f16 = a.dtype == LIK_F16;
   P.normalize = a.normalize == LIK_NORM_D;
   P.bias = a.bias;

@@ -2,15 +2,18 @@
 
 ``scores = maxsim(Q, normalize(H_d @ W.T + b), d_mask)`` for corpora stored as hidden states ``[Nd, Ld, d_model]``
 with a small projection to ``d_out``.  The reference folds the projection into its Triton scoring kernel so that
-the projected documents never exist in memory.  Here the projection is a plain GEMM (cuBLAS through
-``torch.nn.functional.linear``) run over *pieces* of the corpus into a bounded scratch buffer, and everything after
-it is this library's kernels: the L2 normalisation is fused into the tensor-core scoring kernel (fp32 inverse norms
-applied in the epilogue).  The backward works on the winning tokens alone: they are gathered from ``H_d``, projected
-again, pushed through the deterministic argmax-driven kernels (with the normalise Jacobian of the document side) as
-short "compact" documents, and the three GEMMs of the linear layer run on those rows.  Peak extra memory of the
-forward is one piece of projected tokens (``_PIECE_TOKENS`` rows of ``d_out``), whatever the corpus size.
+the projected documents never exist in memory; so does this forward, on the tensor cores: ``lik_maxsim_hidden_fwd``
+chains the projection MMA into the scoring MMA through tensor memory and shared memory (16-bit inputs, at most 256
+query tokens in all, ``d_out`` a multiple of 32 up to 128).  Anything else projects pieces of the corpus with a plain
+GEMM (cuBLAS through ``torch.nn.functional.linear``) into a bounded buffer of ``_PIECE_TOKENS`` rows and scores each
+piece with the fused-normalisation kernel.  Both ways round the projected tokens to the input type and apply fp32
+inverse norms to the raw dot products, so they agree far inside the 16-bit tolerance.
 
-A single kernel that chains the projection MMA into the scoring MMA through tensor memory is not built.
+The backward works on the winning tokens alone: ``lik_hidden_winners`` turns the distinct winners of every document
+into a short "compact" document, those rows of ``H_d`` are gathered and projected again, the deterministic
+argmax-driven kernels (with the normalise Jacobian of the document side) produce the gradient of the projected rows,
+the three GEMMs of the linear layer run on those rows, and ``lik_hidden_scatter_rows`` writes ``grad_H`` in one pass
+(a winner's row or zeros).
 """
 
 from __future__ import annotations
