@@ -44,7 +44,7 @@ def dense_case(seed, Nq, Nd, Lq, Ld, d, *, q_len=None, d_len=None, normalized=Fa
 
 
 def config1():
-    """BASELINE config 1: fp32 Q[32,32,128], D[32,180,128], normalize=True,
+    """The small fp32 configuration: fp32 Q[32,32,128], D[32,180,128], normalize=True,
     q lengths U[8,32], d lengths U[32,180]."""
     return dense_case(0, 32, 32, 32, 180, 128, q_len=(8, 32), d_len=(32, 180))
 

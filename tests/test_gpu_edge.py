@@ -1,5 +1,5 @@
 """GPU edge cases and size-independent properties (the reference's test_edge_cases / test_robustness,
-plus checks at BASELINE sizes where the CPU oracle is too slow to be the checker)."""
+plus checks at the headline workload sizes where the CPU oracle is too slow to be the checker)."""
 
 import numpy as np
 import pytest
@@ -105,7 +105,7 @@ def test_int64_offsets_explicit_maxima_and_status_word():
 
 
 def test_full_size_inbatch_properties():
-    """BASELINE config 2 shape: checked through properties instead of the (too slow) oracle."""
+    """The headline in-batch shape: checked through properties instead of the (too slow) oracle."""
     import late_interaction_kernels_b200 as lik
 
     g = torch.Generator(device="cuda").manual_seed(0)
