@@ -720,6 +720,37 @@ def other_configs(dev):
                                "note": "forward + backward into Q, H and W; the backward touches the winning rows and writes grad_H once"}
     del hh
     torch.cuda.empty_cache()
+    # cached-contrastive tile grid (the reference's docs/benchmarks.md:396-426: bs = 256, Lq = 128, mini = 32 -> 64 tiles,
+    # forward + backward): the whole grid in one call against one call per tile
+    from late_interaction_kernels_b200.loss_heads import maxsim_tiles
+    for ld_cc in (2048, 8192):
+        qc = [F.normalize(torch.randn((32, 128, 128), generator=g, device=dev), dim=-1).bfloat16().requires_grad_() for _ in range(8)]
+        dc = [F.normalize(torch.randn((32, ld_cc, 128), generator=g, device=dev), dim=-1).bfloat16().requires_grad_() for _ in range(8)]
+        gg = torch.randn((256, 256), generator=g, device=dev)
+
+        def clear():
+            for x in qc + dc:
+                x.grad = None
+
+        def grid_step():
+            clear()
+            maxsim_tiles(qc, dc).backward(gg)
+
+        def tile_step():
+            clear()
+            for i_ in range(8):
+                for j_ in range(8):
+                    lik.maxsim(qc[i_], dc[j_]).backward(gg[32 * i_:32 * i_ + 32, 32 * j_:32 * j_ + 32])
+
+        fl_cc = 2.0 * 128 * (256 * 128) * (256 * ld_cc)
+        t = _time_us(grid_step, dev, iters=3, warm=2)
+        out[f"cached_contrastive_bs256_ld{ld_cc}"] = {
+            "us": t, "per_tile_calls_us": _time_us(tile_step, dev, iters=2, warm=1), "shape": f"bs 256, Lq 128, Ld {ld_cc}, d 128, 64 tiles of 32 x 32",
+            "roofline": roofline("tensor", fl_cc + 4.0 * 128 * (256 * 128) * 256, t * 1e-6, sustained=ld_cc >= 8192,
+                                 kernel="fwd_tc_kernel + bwd_dq16 + bwd_dd_sort4 + bwd_dd_reduce16 (+ the cat of the chunks and its backward)",
+                                 note="forward + backward of the whole grid in one call (loss_heads.maxsim_tiles)")}
+        del qc, dc
+        torch.cuda.empty_cache()
     # per-row top-k kernel on a score matrix
     sc = torch.randn((1024, 4096), generator=g, device=dev)
     t = _time_us(lambda: _ops.topk_rows(sc, 100), dev, graph=True)

@@ -1,4 +1,7 @@
-"""Positive and explicit-negative MaxSim scores of a training batch in one scoring launch.
+"""Loss-head helpers: several MaxSim calls of a training step folded into one scoring launch.
+
+``maxsim_pos_neg``: positive and explicit-negative scores of a batch.  ``maxsim_tiles``: the whole tile grid of a
+cached-contrastive loss (see its docstring).
 
 The explicit-negative heads of colpali-engine score ``B`` positive pairs and ``B x K`` hard negatives; the reference
 does it with two operators (``maxsim_pairs`` for the positives, the candidate-list ``maxsim`` for the negatives,
@@ -64,4 +67,44 @@ def maxsim_pos_neg(Q, pos_D, neg_D, q_mask=None, pos_mask=None, neg_mask=None, *
     return scores[:, 0], scores[:, 1:]
 
 
-__all__ = ["maxsim_pos_neg"]
+def maxsim_tiles(q_chunks, d_chunks, q_masks=None, d_masks=None, *, normalize: bool = False, backward=None):
+    """All-pairs scores of mini-batched embeddings in one launch -> fp32 ``[sum Bq, sum Bd]``.
+
+    A cached-contrastive loss (PyLate's ``CachedContrastive``, docs/benchmarks.md:396-426 of the reference) embeds a
+    large batch in mini-batches and scores every (query mini-batch, document mini-batch) tile with its own
+    ``colbert_scores`` call: ``(bs / mini) ** 2`` forward launches and as many backward passes, each re-reading its
+    documents.  This takes the lists of mini-batch embeddings - ``q_chunks[i] [Bq_i, Lq_i, d]``, ``d_chunks[j]
+    [Bd_j, Ld_j, d]``, optional boolean masks per chunk - pads the token axes to the longest chunk (added rows are
+    masked out), concatenates (a differentiable ``cat``) and scores the whole grid at once; block ``(i, j)`` of the
+    result is the tile the loss would have computed, and autograd splits the gradients back onto the chunks.
+    """
+    if not q_chunks or not d_chunks:
+        raise ValueError("maxsim_tiles needs at least one query chunk and one document chunk")
+    for name, chunks in (("q_chunks", q_chunks), ("d_chunks", d_chunks)):
+        for c in chunks:
+            if c.dim() != 3 or c.shape[-1] != q_chunks[0].shape[-1] or c.device != q_chunks[0].device:
+                raise ValueError(f"{name}: every chunk must be [B, L, d] with the same d, on one device")
+
+    def gather(chunks, masks):
+        if masks is not None and len(masks) != len(chunks):
+            raise ValueError("one mask (or None) per chunk")
+        L = max(c.shape[1] for c in chunks)
+        dt = chunks[0].dtype
+        for c in chunks[1:]:
+            dt = torch.promote_types(dt, c.dtype)
+        xs, ms = [], []
+        for k, c in enumerate(chunks):
+            x, m = _pad_tokens(c.to(dt), None if masks is None else masks[k], L)
+            xs.append(x)
+            ms.append(m)
+        if all(m is None for m in ms):
+            return torch.cat(xs, 0), None
+        ms = [torch.ones(x.shape[:-1], dtype=torch.bool, device=x.device) if m is None else m.to(torch.bool) for x, m in zip(xs, ms)]
+        return torch.cat(xs, 0), torch.cat(ms, 0)
+
+    Q, qm = gather(list(q_chunks), q_masks)
+    D, dm = gather(list(d_chunks), d_masks)
+    return maxsim(Q, D, q_mask=qm, d_mask=dm, normalize=normalize, backward=backward)
+
+
+__all__ = ["maxsim_pos_neg", "maxsim_tiles"]

@@ -225,3 +225,63 @@ def test_pos_neg_head_equals_the_two_separate_calls(lp, ln, masks):
     want = O.maxsim_pairs(f32(Q), f32(P), d_mask=None if pm is None else pm.cpu().numpy()) if hasattr(O, "maxsim_pairs") else None
     if want is not None:
         assert O.rel_err(f32(pos), want) < 2e-2
+
+
+def test_tile_grid_in_one_launch_equals_the_per_tile_calls():
+    """The (query mini-batch, document mini-batch) grid of a cached-contrastive loss: one call gives the blocks the
+    per-tile calls give, and the same gradients on every chunk."""
+    import late_interaction_kernels_b200 as lik
+    from late_interaction_kernels_b200.loss_heads import maxsim_tiles
+
+    rng = np.random.default_rng(77)
+    d = 128
+    qs = [dev(cases.unit(rng.standard_normal((b, l, d))).astype(np.float32), torch.bfloat16) for b, l in ((3, 40), (2, 33), (4, 40))]
+    ds = [dev(cases.unit(rng.standard_normal((b, l, d))).astype(np.float32), torch.bfloat16) for b, l in ((5, 120), (3, 257))]
+    dms = [dev(cases.prefix_mask(rng.integers(1, 121, size=5), 120)), None]
+    a = [x.clone().requires_grad_(True) for x in qs + ds]
+    b = [x.clone().requires_grad_(True) for x in qs + ds]
+    grid = maxsim_tiles(a[:3], a[3:], d_masks=dms)
+    assert grid.shape == (9, 8)
+    g = torch.randn_like(grid)
+    (grid * g).sum().backward()
+    r0 = 0
+    total = 0.0
+    for i, q in enumerate(b[:3]):
+        c0 = 0
+        for j, dd in enumerate(b[3:]):
+            tile = lik.maxsim(q, dd, d_mask=dms[j])
+            blk = grid[r0:r0 + q.shape[0], c0:c0 + dd.shape[0]]
+            assert torch.equal(tile, blk), (i, j)  # same kernel arithmetic on the same tokens
+            total = total + (tile * g[r0:r0 + q.shape[0], c0:c0 + dd.shape[0]]).sum()
+            c0 += dd.shape[0]
+        r0 += q.shape[0]
+    total.backward()
+    for x, y in zip(a, b):
+        assert O.rel_err(f32(x.grad), f32(y.grad)) < 2e-2  # the per-tile path sums bf16 partial gradients
+
+
+def test_hidden_winners_and_scatter_rows_against_numpy():
+    from late_interaction_kernels_b200 import _ops
+
+    rng = np.random.default_rng(3)
+    Nq, Nd, Lq, Ld, width = 3, 7, 10, 77, 24
+    am = rng.integers(-1, Ld, size=(Nq, Nd, Lq)).astype(np.int32)
+    am[:, 2] = -1  # a document nobody picked
+    am[:, 3] = 5   # one token picked by everybody
+    S = min(Nq * Lq, Ld)
+    am_c, rows, counts, bitmap, prefix = _ops.hidden_winners(dev(am), Nq, Nd, Lq, Ld, S)
+    am_c, rows, counts = am_c.cpu().numpy(), rows.cpu().numpy().reshape(Nd, S), counts.cpu().numpy()
+    for j in range(Nd):
+        uniq = np.unique(am[:, j][am[:, j] >= 0])
+        assert counts[j] == len(uniq)
+        assert (rows[j, :len(uniq)] == j * Ld + uniq).all()
+        assert (rows[j, len(uniq):] == j * Ld).all()
+        want = np.where(am[:, j] >= 0, np.searchsorted(uniq, np.maximum(am[:, j], 0)), -1)
+        assert (am_c[:, j] == want).all()
+    compact = torch.randn(Nd * S, width, device="cuda")
+    out = torch.full((Nd * Ld, width), 7.0, device="cuda")
+    _ops.hidden_scatter_rows(compact, bitmap, prefix, out, Nd, Ld, S)
+    want = torch.zeros_like(out)
+    for j in range(Nd):
+        want[torch.from_numpy(rows[j, :counts[j]]).cuda()] = compact[j * S:j * S + counts[j]]
+    assert torch.equal(out, want)
