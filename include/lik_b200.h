@@ -205,7 +205,7 @@ int lik_maxsim_bwd(const lik_bwd_args* args, lik_stream_t stream);
 /* union per row (used for per-CTA partial lists and for the all-gathered       */
 /* per-GPU lists of the sharded retrieve).                                      */
 /* ------------------------------------------------------------------------- */
-#define LIK_TOPK_MAX 1024
+#define LIK_TOPK_MAX 8192
 int lik_topk_rows(const float* scores, int64_t n_rows, int64_t n_cols, int64_t ld, int32_t k, int32_t largest,
                   int64_t index_offset, int32_t merge, float* out_scores, int64_t* out_index, lik_stream_t stream);
 int lik_topk_merge(const float* cand_scores, const int64_t* cand_index, int32_t n_lists, int64_t n_rows, int32_t k,

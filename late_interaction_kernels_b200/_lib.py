@@ -19,7 +19,7 @@ LIK_F32, LIK_F16, LIK_BF16, LIK_E4M3 = 0, 1, 2, 3
 PAIR_CROSS, PAIR_GROUPED, PAIR_LIST = 0, 1, 2
 NORM_NONE, NORM_Q, NORM_D, NORM_BOTH = 0, 1, 2, 3
 NORM_ROUNDED = 4  # search paths: normalised operands rounded to the input dtype (workspace copies), see lik_b200.h
-TOPK_MAX = 1024
+TOPK_MAX = 8192
 TOPK_CONTINUE, TOPK_PARTIAL = 1, 2
 TOPK_FUSED_MAX = 128  # largest k of the fused scoring + top-k kernel
 STATIC_SCRATCH_BYTES = 16 << 20

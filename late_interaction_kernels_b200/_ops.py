@@ -337,12 +337,43 @@ def backward(q: SeqSpec, d: SeqSpec, grad_scores: torch.Tensor, argmax: torch.Te
     return gq, gd
 
 
+def _topk_rows_sorted(scores, k, largest, index_offset, out):
+    """``k`` beyond the selection kernels' list (``LIK_TOPK_MAX``): library sorts.  The candidates (the running list and
+    the new columns) are ordered by index, then stably by score, so ties go to the lower index as in the kernels."""
+    n_rows, n_cols = scores.shape
+    dev = scores.device
+    key = scores.to(torch.float32) if largest else -scores.to(torch.float32)
+    idx = (torch.arange(n_cols, device=dev, dtype=torch.int64) + index_offset).expand(n_rows, n_cols)
+    if out is not None:
+        live = out[1] >= 0
+        old_key = torch.where(live, out[0] if largest else -out[0], -torch.inf)
+        key = torch.cat([old_key, key], 1)
+        idx = torch.cat([torch.where(live, out[1], torch.iinfo(torch.int64).max), idx], 1)
+    idx, order = torch.sort(idx, dim=1, stable=True)
+    key = torch.gather(key, 1, order)
+    key, order = torch.sort(key, dim=1, descending=True, stable=True)
+    idx = torch.gather(idx, 1, order)
+    n = key.shape[1]
+    top_s = torch.full((n_rows, k), -torch.inf if largest else torch.inf, dtype=torch.float32, device=dev)
+    top_i = torch.full((n_rows, k), -1, dtype=torch.int64, device=dev)
+    m = min(k, n)
+    top_s[:, :m] = key[:, :m] if largest else -key[:, :m]
+    top_i[:, :m] = torch.where(idx[:, :m] == torch.iinfo(torch.int64).max, -1, idx[:, :m])
+    if out is not None:
+        out[0].copy_(top_s)
+        out[1].copy_(top_i)
+        return out
+    return top_s, top_i
+
+
 @_no_trace
 def topk_rows(scores: torch.Tensor, k: int, *, largest=True, index_offset=0, out=None):
     """Per-row top-k of a [n_rows, n_cols] fp32 matrix; ``out=(scores, idx)`` merges into a running list."""
     lib = _lib.load()
     _lib.require_cuda(scores, op="top-k")
     n_rows, n_cols = scores.shape
+    if k > _lib.TOPK_MAX:
+        return _topk_rows_sorted(scores, k, largest, index_offset, out)
     if scores.stride(1) != 1:
         scores = scores.contiguous()
     merge = out is not None

@@ -82,7 +82,8 @@ struct TopkParams {
   long long* out_index;
 };
 
-__global__ void __launch_bounds__(256) topk_kernel(TopkParams P) {
+template <int NT, int MIN_CTAS>
+__global__ void __launch_bounds__(NT, MIN_CTAS) topk_kernel(TopkParams P) {
   extern __shared__ unsigned char raw[];
   long long* top_i = reinterpret_cast<long long*>(raw);
   long long* blk_i = top_i + P.KP;
@@ -311,20 +312,19 @@ int launch_topk_slots(const float* keys, const int* idx, const int2* hdr, long l
 // ---------------------------------------------------------------------------------------------
 // Top-k of score rows by selection instead of sorting (mode 0 of TopkParams).
 //
-// One CTA of SEL_T threads per row.  The row is taken in slabs of SEL_SLAB columns that live in registers
-// (SEL_PER per thread, column = slab + j * SEL_T + thread); the k entries kept so far (the running list, or
-// the list the caller merges into) are SEL_OLD more elements per thread.  The k-th best key of all of them is
+// One CTA per row.  The row is taken in slabs of SEL_SLAB columns that live in registers (SEL_PER per thread,
+// column = slab + j * threads + thread); the k entries kept so far (the running list, or the list the caller
+// merges into) are SEL_OLD more elements per thread.  The k-th best key of all of them is
 // found by a radix select on the order-preserving 32-bit image of the float (four passes of 256 shared-memory
 // counters); entries above it are kept, and of the entries equal to it the ones with the lowest document
 // index (a second select, on the index, only when the equal entries do not all fit).  The kept k are sorted
 // once per slab that changed anything (best first, ties to the lower index) - a slab with nothing above the
 // current k-th best is dismissed after one pass over its values.
 // ---------------------------------------------------------------------------------------------
-constexpr int SEL_T = 256;
-constexpr int SEL_PER = 16;
-constexpr int SEL_SLAB = SEL_T * SEL_PER;
-constexpr int SEL_OLD = LIK_TOPK_MAX / SEL_T;
-constexpr int SEL_NE = SEL_PER + SEL_OLD;
+// Two shapes of the CTA, both with slabs of 4096 columns: 256 threads x (16 slab + 4 kept) elements for k <= 1024
+// (three CTAs per SM), 1024 threads x (4 slab + 8 kept) elements for k <= LIK_TOPK_MAX = 8192.
+constexpr int SEL_SLAB = 4096;
+constexpr int SEL_K_SMALL = 1024;
 
 // Monotone map float -> unsigned (larger float, larger key); 0 is below every float.
 __device__ __forceinline__ unsigned sel_key(float f) {
@@ -340,15 +340,15 @@ struct SelShared {
 // Radix select over the elements every thread holds: key[e] (larger is better) of the elements with on[e], `nbits`
 // wide.  Returns the key of rank `want` (1 = the best) to every thread; *need_eq = how many of the elements equal to
 // it belong to the best `want`, *n_eq = how many elements equal it.  All threads of the block call it.
-template <typename K>
-__device__ K block_select(const K (&key)[SEL_NE], const bool (&on)[SEL_NE], int nbits, int want, SelShared* sh, int* need_eq, int* n_eq) {
+template <typename K, int NE>
+__device__ K block_select(const K (&key)[NE], const bool (&on)[NE], int nbits, int want, SelShared* sh, int* need_eq, int* n_eq) {
   const int tid = threadIdx.x, lane = tid & 31;
   K prefix = 0;
   for (int shift = nbits - 8; shift >= 0; shift -= 8) {
-    sh->hist[tid] = 0;
+    if (tid < 256) sh->hist[tid] = 0;
     __syncthreads();
 #pragma unroll
-    for (int e = 0; e < SEL_NE; ++e) {
+    for (int e = 0; e < NE; ++e) {
       // bits above this digit must match what is fixed already (nothing in the first pass)
       const bool same = shift + 8 >= nbits || (key[e] >> (shift + 8)) == (prefix >> (shift + 8));
       if (on[e] && same) atomicAdd(&sh->hist[(int)((key[e] >> shift) & 255)], 1);
@@ -391,7 +391,10 @@ __device__ K block_select(const K (&key)[SEL_NE], const bool (&on)[SEL_NE], int 
   return prefix;
 }
 
-__global__ void __launch_bounds__(SEL_T, 3) topk_select_kernel(TopkParams P) {
+template <int SEL_T, int SEL_PER, int SEL_OLD, int MIN_CTAS>
+__global__ void __launch_bounds__(SEL_T, MIN_CTAS) topk_select_kernel(TopkParams P) {
+  static_assert(SEL_T * SEL_PER == SEL_SLAB, "a slab is 4096 columns");
+  constexpr int SEL_NE = SEL_PER + SEL_OLD;
   extern __shared__ unsigned char raw[];
   long long* top_i = reinterpret_cast<long long*>(raw);
   float* top_k = reinterpret_cast<float*>(top_i + P.KP);
@@ -468,7 +471,7 @@ __global__ void __launch_bounds__(SEL_T, 3) topk_select_kernel(TopkParams P) {
     unsigned long long Ti = 0;  // ties: the kept ones have ~index >= Ti
     bool all_ties = true;
     if (want > 0 && n_all > P.k) {
-      T = block_select<unsigned>(u, on, 32, want, &sh, &need_eq, &n_eq);
+      T = block_select<unsigned, SEL_NE>(u, on, 32, want, &sh, &need_eq, &n_eq);
       if (need_eq < n_eq) {
         // more entries equal the k-th best than fit: the lowest document indices win
         unsigned long long ik[SEL_NE];
@@ -480,7 +483,7 @@ __global__ void __launch_bounds__(SEL_T, 3) topk_select_kernel(TopkParams P) {
           ik[e] = ~(unsigned long long)id;
         }
         int ne2 = 0, nn2 = 0;
-        Ti = block_select<unsigned long long>(ik, tie, 64, need_eq, &sh, &ne2, &nn2);
+        Ti = block_select<unsigned long long, SEL_NE>(ik, tie, 64, need_eq, &sh, &ne2, &nn2);
         all_ties = false;
       }
     }
@@ -531,12 +534,35 @@ static int launch_topk(TopkParams& P, cudaStream_t st) {
   P.KP = KP;
   if (P.mode == 0) {
     const size_t smem = (size_t)KP * (sizeof(long long) + sizeof(float));
-    topk_select_kernel<<<(unsigned)P.n_rows, SEL_T, smem, st>>>(P), ::lik::count_launch();
+    if (P.k <= SEL_K_SMALL) {
+      topk_select_kernel<256, 16, SEL_K_SMALL / 256, 3><<<(unsigned)P.n_rows, 256, smem, st>>>(P), ::lik::count_launch();
+    } else {
+      static bool raised[64] = {false};  // by device ordinal: the kept list of a large k needs more than 48 KB
+      int dev = 0;
+      LIK_CUDA_OK(cudaGetDevice(&dev));
+      if (dev < 0 || dev >= 64 || !raised[dev]) {
+        LIK_CUDA_OK(cudaFuncSetAttribute(topk_select_kernel<1024, 4, LIK_TOPK_MAX / 1024, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)((size_t)LIK_TOPK_MAX * (sizeof(long long) + sizeof(float)))));
+        if (dev >= 0 && dev < 64) raised[dev] = true;
+      }
+      topk_select_kernel<1024, 4, LIK_TOPK_MAX / 1024, 1><<<(unsigned)P.n_rows, 1024, smem, st>>>(P), ::lik::count_launch();
+    }
     LIK_CUDA_OK(cudaGetLastError());
     return LIK_OK;
   }
   size_t smem = (size_t)KP * 2 * (sizeof(long long) + sizeof(float));
-  topk_kernel<<<(unsigned)P.n_rows, 256, smem, st>>>(P), ::lik::count_launch();
+  if (smem > 48 * 1024) {
+    static bool raised[64] = {false};
+    int dev = 0;
+    LIK_CUDA_OK(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64 || !raised[dev]) {
+      LIK_CUDA_OK(cudaFuncSetAttribute(topk_kernel<1024, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       (int)((size_t)LIK_TOPK_MAX * 2 * (sizeof(long long) + sizeof(float)))));
+      if (dev >= 0 && dev < 64) raised[dev] = true;
+    }
+  }
+  if (KP > 1024) topk_kernel<1024, 1><<<(unsigned)P.n_rows, 1024, smem, st>>>(P), ::lik::count_launch();
+  else topk_kernel<256, 6><<<(unsigned)P.n_rows, 256, smem, st>>>(P), ::lik::count_launch();
   LIK_CUDA_OK(cudaGetLastError());
   return LIK_OK;
 }

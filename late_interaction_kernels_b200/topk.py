@@ -4,8 +4,9 @@ The reference scores a chunk, calls ``torch.topk``, concatenates with the runnin
 ``torch.topk`` again.  Here the scoring kernel itself keeps the candidates (``lik_maxsim_fwd_topk``): one
 launch walks all documents, no ``[Nq, chunk]`` score matrix is written, and a merge kernel returns the
 ``k`` best per query.  Problems that path does not take (fp32 inputs, packed or very long queries,
-``k > 128``) score chunks with ``lik_maxsim_fwd`` and merge them with ``lik_topk_rows``.  Either way ties
-go to the lower document index, so chunked and unchunked calls return identical indices.
+``k > 128``) score chunks with ``lik_maxsim_fwd`` and merge them with ``lik_topk_rows`` (``k`` up to 8192; beyond
+that the chunks' scores are merged with library sorts).  Either way ties go to the lower document index, so chunked
+and unchunked calls return identical indices.
 """
 
 from __future__ import annotations
@@ -34,8 +35,6 @@ def maxsim_topk(Q, D, k, q_mask=None, d_mask=None, *, normalize=False, chunk_siz
     _lib.require_cuda(Q, D, op="maxsim_topk")
     Nd = D.shape[0]
     k = min(k, Nd)
-    if k > _lib.TOPK_MAX:
-        raise ValueError(f"k={k} exceeds the supported maximum {_lib.TOPK_MAX}")
     step = Nd if (chunk_size is None or chunk_size >= Nd) else int(chunk_size)
     out = None
     with torch.no_grad():

@@ -73,3 +73,54 @@ def test_running_list_over_chunks(order):
         out = _ops.topk_rows(sc[:, s0:s0 + chunk].contiguous(), k, index_offset=s0, out=out)
     ws, wi = _want(sc, k)
     assert torch.equal(out[0], ws) and torch.equal(out[1], wi)
+
+
+@pytest.mark.parametrize("rows,cols,k", [(3, 20000, 1025), (2, 30000, 4096), (2, 9000, 8192), (1, 5000, 8192), (2, 20000, 9000)])
+def test_large_k(rows, cols, k):
+    """k above 1024 takes the 1024-thread shape of the selection kernel (up to 8192); beyond that the library-sort path.
+    Same contract: exact agreement with the stable sort, chunked or not, ties included."""
+    from late_interaction_kernels_b200 import _ops
+
+    g = torch.Generator(device="cuda").manual_seed(cols + k)
+    sc = torch.randint(0, 2000, (rows, cols), generator=g, device="cuda").float()  # many ties
+    kk = min(k, cols)
+    ws, wi = _want(sc, kk)
+    s, i = _ops.topk_rows(sc, k)
+    assert torch.equal(s[:, :kk], ws) and torch.equal(i[:, :kk], wi)
+    if k > cols:
+        assert (i[:, cols:] == -1).all()
+    out = None
+    for s0 in range(0, cols, 4096):
+        out = _ops.topk_rows(sc[:, s0:s0 + 4096].contiguous(), k, index_offset=s0, out=out)
+    assert torch.equal(out[0][:, :kk], ws) and torch.equal(out[1][:, :kk], wi)
+    s, i = _ops.topk_rows(sc, k, largest=False)
+    ws, wi = _want(sc, kk, largest=False)
+    assert torch.equal(s[:, :kk], ws) and torch.equal(i[:, :kk], wi)
+
+
+def test_merge_of_lists_with_large_k():
+    from late_interaction_kernels_b200 import _ops
+
+    g = torch.Generator(device="cuda").manual_seed(5)
+    k, n_lists, rows = 3000, 3, 2
+    sc = torch.randint(0, 500, (rows, n_lists * 5000), generator=g, device="cuda").float()
+    parts = [_ops.topk_rows(sc[:, j * 5000:(j + 1) * 5000].contiguous(), k, index_offset=j * 5000) for j in range(n_lists)]
+    cs = torch.stack([p[0] for p in parts])
+    ci = torch.stack([p[1] for p in parts])
+    s, i = _ops.topk_merge(cs, ci, k)
+    ws, wi = _want(sc, k)
+    assert torch.equal(s, ws) and torch.equal(i, wi)
+
+
+def test_maxsim_topk_with_k_above_1024():
+    import late_interaction_kernels_b200 as lik
+
+    g = torch.Generator(device="cuda").manual_seed(3)
+    Q = torch.nn.functional.normalize(torch.randn((2, 8, 64), generator=g, device="cuda"), dim=-1).bfloat16()
+    D = torch.nn.functional.normalize(torch.randn((3000, 12, 64), generator=g, device="cuda"), dim=-1).bfloat16()
+    from late_interaction_kernels_b200.topk import maxsim_topk
+
+    s, i = maxsim_topk(Q, D, 2000, chunk_size=1024)
+    full = lik.maxsim(Q, D)
+    ws, wi = _want(full, 2000)
+    assert torch.equal(s, ws) and torch.equal(i, wi)
