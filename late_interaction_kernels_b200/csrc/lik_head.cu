@@ -19,6 +19,13 @@
 // pipe works on the next projection while the converters run.  A CTA owns a contiguous range of documents, so every
 // score has one writer and the result is bitwise reproducible.
 //
+// What bounds it: DRAM traffic is the hidden states once (w comes back from L2 for every tile), streamed at about
+// 0.8 of the copy bandwidth.  The hidden states wait in the ring for the tensor pipe rather than the other way round:
+// a 128 x 128 x 16 MMA reads 8 KB of operands from shared memory per 64 cycles, all of its bandwidth, while TMA fills
+// the ring and the converters store the operand tile.  Measured and dropped: a ring of its own for w (one more wait
+// and commit per stage on the issuing thread cost more than the deeper hidden-state ring gave), and two token tiles per
+// w slab with single-buffered projection accumulators (the tensor pipe idles while the converters run).
+//
 // Every mbarrier wait is bounded: on expiry the CTA raises LIK_DEV_WAIT_TIMEOUT in the status word, sets a shared
 // abort flag, drains its TMA copies, frees TMEM and returns.
 #include <cuda.h>
