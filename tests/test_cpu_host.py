@@ -39,6 +39,7 @@ def test_struct_sizes_match_the_header_layout():
     assert C.sizeof(_lib.FwdArgs) == 2 * 80 + 96
     assert C.sizeof(_lib.PlaidIndex) == 56
     assert C.sizeof(_lib.TopkSpec) == 40
+    assert C.sizeof(_lib.HiddenFwdArgs) == 2 * 80 + 88
 
 
 def test_argument_validation_without_a_gpu(lib):
@@ -56,6 +57,16 @@ def test_argument_validation_without_a_gpu(lib):
     ix.nbits = 3
     assert lib.lik_plaid_decompress(C.byref(ix), 0, 0, 1, None, 2, None, None) == -1
     assert b"nbits must be 2, 4, or 8" in lib.lik_last_error()
+    # document head: NULL arguments and bad sizes are refused before any CUDA call; without a GPU nothing is supported
+    assert lib.lik_maxsim_hidden_fwd(None, None) == -1
+    h = _lib.HiddenFwdArgs()
+    assert lib.lik_maxsim_hidden_fwd(C.byref(h), None) == -1
+    assert b"must not be NULL" in lib.lik_last_error()
+    assert lib.lik_maxsim_hidden_fwd_supported(C.byref(h)) == 0
+    assert lib.lik_maxsim_hidden_fwd_workspace(C.byref(h)) == 0
+    assert lib.lik_hidden_winners(None, 1, 1, 0, 1, 1, None, None, None, None, None, None, None) == -1
+    assert lib.lik_hidden_winners(None, 1, 0, 4, 8, 4, None, None, None, None, None, None, None) == 0  # no documents: nothing to do
+    assert lib.lik_hidden_scatter_rows(None, 24, 1, 8, 4, None, None, None, None) == -1
 
 
 def test_no_cpu_fallback_anywhere():
