@@ -720,6 +720,21 @@ def other_configs(dev):
                                "note": "forward + backward into Q, H and W; the backward touches the winning rows and writes grad_H once"}
     del hh
     torch.cuda.empty_cache()
+    # rerank shapes of the reference's FP8 table (benchmarks/kernels/bench_fp8.py:32-41): one or four queries against
+    # thousands of short documents, bf16 and e4m3 with per-token scales; bound by the document bytes
+    for label, nq_r, nd_r, ld_r in (("colbert_rerank_8k", 1, 8192, 256), ("batched_rerank_16k", 4, 4096, 256), ("long_docs_2k", 1, 2048, 512)):
+        Qr_ = F.normalize(torch.randn((nq_r, 32, 128), generator=g, device=dev), dim=-1).bfloat16()
+        Dr_ = F.normalize(torch.randn((nd_r, ld_r, 128), generator=g, device=dev), dim=-1).bfloat16()
+        q8_, sq_ = fp8.quantize_fp8_per_token(Qr_)
+        d8_, sd_ = fp8.quantize_fp8_per_token(Dr_)
+        tb = _time_us(lambda: lik.maxsim(Qr_, Dr_), dev, graph=True)
+        t8 = _time_us(lambda: fp8.maxsim_inference_fp8(q8_, d8_, scale_Q=sq_, scale_D=sd_), dev, graph=True)
+        out[f"rerank_{label}"] = {
+            "shape": f"Q[{nq_r},32,128] x D[{nd_r},{ld_r},128]", "bf16_us": tb, "e4m3_us": t8,
+            "roofline": roofline("hbm", Dr_.numel() * 2.0, tb * 1e-6, kernel="fwd_tc_kernel (bf16, few queries)", note="document bytes read once"),
+            "roofline_e4m3": roofline("hbm", d8_.numel() * 1.0 + sd_.numel() * 4.0, t8 * 1e-6, kernel="fwd_tc_kernel (e4m3, per-token scales)",
+                                      note="e4m3 document bytes + fp32 scales read once")}
+        del Dr_, d8_
     # cached-contrastive tile grid (the reference's docs/benchmarks.md:396-426: bs = 256, Lq = 128, mini = 32 -> 64 tiles,
     # forward + backward): the whole grid in one call against one call per tile
     from late_interaction_kernels_b200.loss_heads import maxsim_tiles

@@ -55,6 +55,8 @@ constexpr int EPI_THREADS = 128;     // threads per half of an epilogue group (o
 constexpr int GROUP_WARPS = 8;
 constexpr long long WAIT_LIMIT_CYCLES = 4000000000ll;  // default limit of a wait: about 2 s at 2 GHz
 constexpr int UNIT_RING = 8;                  // slots of the producer -> epilogue unit ring
+constexpr int UNIT_LEN_MASK = 0xFFFFFF;       // unit_info.x: document length in the low 24 bits,
+constexpr int UNIT_SLOT_SHIFT = 24;           // the multiplier slot of its first tile in bits 24..28, LEN_FLAG_MASKED above
 
 // ---------------------------------------------------------------------------------------------
 // Kernel parameters
@@ -106,6 +108,16 @@ struct TcParams {
   int* status;
   const int* tile_q0;  // packed queries: tile m holds queries [tile_q0[m], tile_q0[m+1]); tile_q0[-1] is the tile count
   int d_len_flagged;  // d.lens carries LEN_FLAG_MASKED on documents whose mask is not a plain prefix
+  // Per-column multipliers that are one fp32 per document row (inverse norms, or per-token scales) and whose layout
+  // allows it travel with the tile: the producer copies the tile's run of them into a slot of a small ring in shared
+  // memory (bulk copy on the stage's barrier) instead of the epilogue fetching them from device memory per tile.
+  const float* col_src;  // nullptr: the epilogue stages the multipliers itself
+  // Two rings of sc_per = stages + 1 slots, one per accumulator (tiles that feed both use the first).  Slot n of an
+  // accumulator's ring is refilled for its tile n + sc_per: by then the MMAs of one of the sc_per - 1 tiles between them
+  // have completed (the producer is at most `stages` tiles ahead of the tensor pipe), which needed the accumulator
+  // back from every earlier tile - and an epilogue gives it back only after its last read of the multipliers.
+  int sc_per;
+  int sc_slots;          // 2 * sc_per, or 0
   int d_full_count;   // arrivals that complete a ring stage: 1 (TMA) or the number of decompress warps
   TopkOut topk;       // cand_key == nullptr: scores are written instead
   PlaidSrc plaid;     // PLAID kernels: the compressed documents
@@ -408,7 +420,8 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
   const int d_stage_bytes = P.n_slabs * TILE_N * SLAB_BYTES_ROW;
   unsigned char* q_smem = smem;                              // [2][n_slabs][128 rows][128 B]
   unsigned char* d_smem = smem + 2 * q_tile_bytes;           // [stages][n_slabs][256 rows][128 B]
-  SharedCtl* ctl = reinterpret_cast<SharedCtl*>(d_smem + (size_t)P.stages * d_stage_bytes);
+  float* sc_ring = reinterpret_cast<float*>(d_smem + (size_t)P.stages * d_stage_bytes);  // [sc_slots][TILE_N] (kernels with multipliers)
+  SharedCtl* ctl = reinterpret_cast<SharedCtl*>(d_smem + (size_t)P.stages * d_stage_bytes + (size_t)P.sc_slots * TILE_N * sizeof(float));
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
@@ -462,6 +475,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
       const int pw = warp == 0 ? 0 : warp - (2 + 2 * GROUP_WARPS) + 1;  // decoder warp number 0..2
       int cur_grp = -1;
       uint32_t n_qload = 0, st = 0, ph = 0, n_dload = 0;
+      int sc_cnt[2] = {0, 0};  // next slot in either accumulator's multiplier ring
       long long uc = 0;
       const int x_per_slab = SLAB_BYTES_ROW / P.elt_bytes;
       bool ok = true;
@@ -518,10 +532,14 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
         // which accumulators this unit feeds: both resident tiles, or (one tile) alternating with the unit count
         const uint32_t acc_bits = P.mt == 2 ? (tiles_here == 2 ? (STAGE_ACC0 | STAGE_ACC1) : STAGE_ACC0)
                                             : ((uc & 1) ? STAGE_ACC1 : STAGE_ACC0);
+        const int sc_ring_id = (!SCALED || P.mt == 2 || !(uc & 1)) ? 0 : 1;  // the multiplier ring of the accumulator(s) this unit feeds
         // publish the unit for the epilogue groups, then its stages; an empty document still sends one
         // (empty) stage so that every unit passes through the same hand-shakes
         if (elect) {
-          ctl->unit_info[uc & (UNIT_RING - 1)] = make_int4(dlen | (dmasked ? LEN_FLAG_MASKED : 0), (int)drow0, grp, doc);
+          ctl->unit_info[uc & (UNIT_RING - 1)] = make_int4(
+              (dlen & UNIT_LEN_MASK) | (SCALED ? (sc_ring_id * P.sc_per + sc_cnt[sc_ring_id]) << UNIT_SLOT_SHIFT : 0) |
+                  (dmasked ? LEN_FLAG_MASKED : 0),
+              (int)drow0, grp, doc);
           __threadfence_block();
           ctl->units_posted = (int)uc + 1;
         }
@@ -559,17 +577,26 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
           } else {
             const int boxes = (ncols + BOX_ROWS - 1) / BOX_ROWS;
             if (boxes > 0) {
-              mbar_arrive_expect_tx(full, (uint32_t)(boxes * BOX_ROWS * SLAB_BYTES_ROW * P.n_slabs));
+              // the tile's multipliers ride on the same barrier: whole groups of four floats, never past the array's end
+              uint32_t sc_bytes = 0;
+              if (SCALED && P.col_src) {
+                const long long r = drow0 + c0;
+                sc_bytes = (uint32_t)min((long long)((ncols + 3) & ~3), P.d.n_rows - r) * 4u;
+              }
+              mbar_arrive_expect_tx(full, (uint32_t)(boxes * BOX_ROWS * SLAB_BYTES_ROW * P.n_slabs) + sc_bytes);
               const CUtensorMap* map = &d_maps.m[boxes - 1];
               for (int sl = 0; sl < P.n_slabs; ++sl)
                 tma_load_2d(smem_u32(d_smem + (size_t)st * d_stage_bytes + sl * TILE_N * SLAB_BYTES_ROW), map, sl * x_per_slab,
                             (int)(drow0 + c0), full);
+              if (sc_bytes)
+                bulk_load_1d(smem_u32(sc_ring + (sc_ring_id * P.sc_per + sc_cnt[sc_ring_id]) * TILE_N), P.col_src + drow0 + c0, sc_bytes, full);
             } else {
               mbar_arrive(full);
             }
           }
           ++n_dload;
           if (++st == (uint32_t)P.stages) { st = 0; ph ^= 1; }
+          if (SCALED && ++sc_cnt[sc_ring_id] >= P.sc_per) sc_cnt[sc_ring_id] = 0;
           c0 += TILE_N;
         } while (c0 < dlen);
         ++uc;
@@ -779,6 +806,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
   } while (0)
 
     const bool cross = P.pairing == LIK_PAIR_CROSS;
+    const bool bulk = SCALED && P.col_src != nullptr;  // the multipliers of a tile arrive with it
     const bool every_group_full = P.mt == 1 || (n_tiles & 1) == 0;
     for (;; ++uc) {
       // with one resident tile the two groups take alternate units
@@ -894,7 +922,9 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
       }
       // a tile group with an odd tile out: the second epilogue group has nothing in it
       if (!have_tile) continue;
-      const int dlen = uinfo.x & ~LEN_FLAG_MASKED;
+      const int dlen = uinfo.x & UNIT_LEN_MASK;
+      int sc_slot = SCALED ? (uinfo.x >> UNIT_SLOT_SHIFT) & 31 : 0;  // multiplier slot of the unit's first tile
+      const int sc_base = SCALED && sc_slot >= P.sc_per ? P.sc_per : 0;  // first slot of its ring
       const long long drow0 = uinfo.y;
       const bool holes = (uinfo.x & LEN_FLAG_MASKED) != 0;  // the document's mask is not a plain prefix
       // where this unit's results go: CROSS / GROUPED index by document, LIST by pair (== unit)
@@ -927,7 +957,9 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
     }                                                                                                     \
   } while (0)
         // before the accumulator wait: overlaps the MMAs; the wait's rendezvous also publishes the columns
-        if (SCALED) LIK_STAGE_COLUMNS(c0 > 0);
+        // (not needed when the multipliers came with the tile and the mask has no holes)
+        const bool staged = SCALED && (general || !bulk);
+        if (staged) LIK_STAGE_COLUMNS(c0 > 0);
         if (SCALED || c0 > 0) {
           LIK_GROUP_WAIT_ACC();
           if (!ok) break;
@@ -960,21 +992,30 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
             fold32<ARGMAX>(v, c0 + cc, run_m, run_i);
           }
         } else if (use_cols) {
-          // whole chunks are valid: multiplier only; the partial last chunk also takes the mask (-inf past ncols)
+          // whole chunks are valid: multiplier only; the partial last chunk also takes the mask (-inf past ncols).
+          // Multipliers that came with the tile sit in a ring slot that is refilled once the accumulator has changed
+          // hands often enough: there the accumulator goes back after the last read of them, not before.
+          const float* sc_arr = bulk ? sc_ring + sc_slot * TILE_N : ctl->col_scale[wg];
           for (; cc + 32 <= ncols; cc += 64) {
             float v[32];
             tmem_ld32_issue(lane_addr + (uint32_t)cc, v);
             tmem_ld_wait(v);
-            if (cc + 64 >= ncols) LIK_RELEASE_ACC();
-            scale32(v, &ctl->col_scale[wg][cc]);
+            if (!bulk && cc + 64 >= ncols) LIK_RELEASE_ACC();
+            scale32(v, sc_arr + cc);
+            if (bulk && cc + 64 >= ncols) LIK_RELEASE_ACC();
             fold32<ARGMAX>(v, c0 + cc, run_m, run_i);
           }
           if (cc < ncols) {
             float v[32];
             tmem_ld32_issue(lane_addr + (uint32_t)cc, v);
             tmem_ld_wait(v);
-            LIK_RELEASE_ACC();
-            affine32(v, &ctl->col_scale[wg][cc], &ctl->col_bias[wg][cc]);
+            if (bulk) {
+              scale32_first(v, sc_arr + cc, ncols - cc);
+              LIK_RELEASE_ACC();
+            } else {
+              LIK_RELEASE_ACC();
+              affine32(v, &ctl->col_scale[wg][cc], &ctl->col_bias[wg][cc]);
+            }
             fold32<ARGMAX>(v, c0 + cc, run_m, run_i);
           }
         } else {
@@ -1007,6 +1048,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
         }
 #undef LIK_RELEASE_ACC
         c0 += TILE_N;
+        if (SCALED && ++sc_slot >= sc_base + P.sc_per) sc_slot = sc_base;
       } while (c0 < dlen);
       };
       if (holes) document_tiles(std::true_type{});
@@ -1498,6 +1540,29 @@ int launch_fwd_tc(const lik_fwd_args& a, const float* qn, const float* dn, void*
   P.tile_q0 = nullptr;
   P.list_tab = nullptr;
   P.d_full_count = plaid ? PLAID_WARPS : 1;
+  // Per-column multipliers that are exactly one fp32 array over the document rows (inverse norms or per-token scales,
+  // not both) travel with the tiles when every tile's run of them starts on a 16-byte boundary and whole groups of four
+  // stay inside the array: padded documents whose stride and row count are multiples of four.
+  P.col_src = nullptr;
+  P.sc_per = P.sc_slots = 0;
+  if (!plaid && !a.d.cu && a.d.scale_scalar == 1.0f && ((a.d.scale != nullptr) != (dn != nullptr))) {
+    const float* arr = a.d.scale ? a.d.scale : dn;
+    if (((uintptr_t)arr & 15) == 0 && a.d.seq_stride % 4 == 0 && a.d.n_rows % 4 == 0) {
+      const size_t stage = (size_t)pl.n_slabs * TILE_N * SLAB_BYTES_ROW;
+      const size_t fixed = pl.smem_bytes - (size_t)pl.stages * stage;
+      auto need = [&](int stages) { return fixed + (size_t)stages * stage + (size_t)2 * (stages + 1) * TILE_N * sizeof(float); };
+      int stages = pl.stages;
+      while (stages > 1 && need(stages) > (size_t)227 * 1024) --stages;
+      if (need(stages) <= (size_t)227 * 1024) {
+        pl.stages = stages;
+        pl.smem_bytes = need(stages);
+        P.stages = stages;
+        P.col_src = arr;
+        P.sc_per = stages + 1;
+        P.sc_slots = 2 * P.sc_per;
+      }
+    }
+  }
   if (plaid) {
     P.plaid = *x.plaid;
     P.plaid_f16 = a.dtype == LIK_F16;

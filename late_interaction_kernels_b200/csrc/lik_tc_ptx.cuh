@@ -47,6 +47,12 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
       "l"(map), "r"(x), "r"(y), "r"(bar)
       : "memory");
 }
+// untiled bulk copy global -> shared (16-byte aligned on both sides, a multiple of 16 bytes), completing on an mbarrier
+__device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src),
+               "r"(bytes), "r"(bar)
+               : "memory");
+}
 __device__ __forceinline__ void prefetch_tmap(const CUtensorMap* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
 }
@@ -163,6 +169,17 @@ __device__ __forceinline__ void scale32(float (&v)[32], const float* scale) {
     v[i + 1] *= sc.y;
     v[i + 2] *= sc.z;
     v[i + 3] *= sc.w;
+  }
+}
+// v[i] = v[i] * scale[i] for the first `lim` columns, -inf for the others (whatever scale holds there)
+__device__ __forceinline__ void scale32_first(float (&v)[32], const float* scale, int lim) {
+#pragma unroll
+  for (int i = 0; i < 32; i += 4) {
+    const float4 sc = *reinterpret_cast<const float4*>(scale + i);
+    v[i + 0] = i + 0 < lim ? v[i + 0] * sc.x : -INFINITY;
+    v[i + 1] = i + 1 < lim ? v[i + 1] * sc.y : -INFINITY;
+    v[i + 2] = i + 2 < lim ? v[i + 2] * sc.z : -INFINITY;
+    v[i + 3] = i + 3 < lim ? v[i + 3] * sc.w : -INFINITY;
   }
 }
 // v[i] = v[i] * scale[i] + bias[i]: per-column multiplier and additive mask staged in shared memory
