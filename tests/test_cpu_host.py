@@ -119,6 +119,22 @@ def test_host_validation_messages():
         pack_padded(Q, D[:, None], torch.tensor([3, 3]), torch.tensor([4, 4]))
 
 
+def test_loss_head_helpers_validate_on_the_host():
+    from late_interaction_kernels_b200.loss_heads import maxsim_pos_neg, maxsim_tiles
+
+    q, d = torch.randn(2, 3, 16), torch.randn(2, 4, 16)
+    with pytest.raises(ValueError, match="at least one"):
+        maxsim_tiles([], [d])
+    with pytest.raises(ValueError, match="same d"):
+        maxsim_tiles([q], [torch.randn(2, 4, 8)])
+    with pytest.raises(ValueError, match="one mask"):
+        maxsim_tiles([q, q], [d], q_masks=[None])
+    with pytest.raises(RuntimeError, match="CUDA"):
+        maxsim_tiles([q], [d])  # host tensors: no CPU path
+    with pytest.raises(ValueError, match="expected Q"):
+        maxsim_pos_neg(q, d, d)
+
+
 def test_pack_padded_on_cpu_matches_reference_golden():
     """pack_padded is pure host/torch logic, so it also runs on CPU tensors."""
     import numpy as np
