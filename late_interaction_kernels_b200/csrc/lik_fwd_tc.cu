@@ -55,6 +55,7 @@ constexpr int EPI_THREADS = 128;     // threads per half of an epilogue group (o
 constexpr int GROUP_WARPS = 8;
 constexpr long long WAIT_LIMIT_CYCLES = 4000000000ll;  // default limit of a wait: about 2 s at 2 GHz
 constexpr int UNIT_RING = 8;                  // slots of the producer -> epilogue unit ring
+constexpr int LONG_DOC_TOKENS = 2048;         // documents from this length on take the lazy winner scan
 constexpr int UNIT_LEN_MASK = 0xFFFFFF;       // unit_info.x: document length in the low 24 bits,
 constexpr int UNIT_SLOT_SHIFT = 24;           // the multiplier slot of its first tile in bits 24..28, LEN_FLAG_MASKED above
 
@@ -935,8 +936,9 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
       // The tiles of the document.  The body exists twice in the kernels without per-column multipliers: documents whose
       // mask is a plain prefix (nearly all) take the copy that has no column arrays in it, the others the general one -
       // the common path's time goes with its code size, so the rare one stays out of it.
-      auto document_tiles = [&](auto general_) {
+      auto document_tiles = [&](auto general_, auto lazy_) {
       constexpr bool general = decltype(general_)::value;  // the document's mask has holes
+      constexpr bool lazy = decltype(lazy_)::value;        // long document: winner scan only when some row of the warp needs it
       constexpr bool use_cols = SCALED || general;          // per-column multiplier / additive mask needed
       do {
         const int ncols = max(0, min(TILE_N, dlen - c0));
@@ -989,7 +991,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
             tmem_ld_wait(v);
             if (cc + 64 >= ncols) LIK_RELEASE_ACC();
             affine32(v, &ctl->col_scale[wg][cc], &ctl->col_bias[wg][cc]);  // bias is -inf past ncols and in holes
-            fold32<ARGMAX>(v, c0 + cc, run_m, run_i);
+            fold32<ARGMAX, lazy>(v, c0 + cc, run_m, run_i);
           }
         } else if (use_cols) {
           // whole chunks are valid: multiplier only; the partial last chunk also takes the mask (-inf past ncols).
@@ -1003,7 +1005,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
             if (!bulk && cc + 64 >= ncols) LIK_RELEASE_ACC();
             scale32(v, sc_arr + cc);
             if (bulk && cc + 64 >= ncols) LIK_RELEASE_ACC();
-            fold32<ARGMAX>(v, c0 + cc, run_m, run_i);
+            fold32<ARGMAX, lazy>(v, c0 + cc, run_m, run_i);
           }
           if (cc < ncols) {
             float v[32];
@@ -1016,7 +1018,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
               LIK_RELEASE_ACC();
               affine32(v, &ctl->col_scale[wg][cc], &ctl->col_bias[wg][cc]);
             }
-            fold32<ARGMAX>(v, c0 + cc, run_m, run_i);
+            fold32<ARGMAX, lazy>(v, c0 + cc, run_m, run_i);
           }
         } else {
           for (; cc + 32 <= ncols; cc += 64) {
@@ -1024,7 +1026,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
             tmem_ld32_issue(lane_addr + (uint32_t)cc, v);
             tmem_ld_wait(v);
             if (cc + 64 >= ncols) LIK_RELEASE_ACC();
-            fold32<ARGMAX>(v, c0 + cc, run_m, run_i);
+            fold32<ARGMAX, lazy>(v, c0 + cc, run_m, run_i);
           }
           if (cc < ncols) {
             // partial chunk: pieces of 16, 8, 4, 2 and 1 columns as the bits of its width say, absent
@@ -1051,8 +1053,11 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
         if (SCALED && ++sc_slot >= sc_base + P.sc_per) sc_slot = sc_base;
       } while (c0 < dlen);
       };
-      if (holes) document_tiles(std::true_type{});
-      else document_tiles(std::false_type{});
+      // (a third copy for long documents in the kernels that keep winners: from the second half of such a document on,
+      // most 32-column chunks hold no new maximum for any of a warp's rows, and the scan for its column can be skipped)
+      if (holes) document_tiles(std::true_type{}, std::false_type{});
+      else if (ARGMAX && dlen >= LONG_DOC_TOKENS) document_tiles(std::false_type{}, std::true_type{});
+      else document_tiles(std::false_type{}, std::false_type{});
       if (!ok) break;
       // ---- end of document: half 1 hands over, half 0 merges (lower column wins a tie) ----
       float* xm = ctl->xch_m[wg][n_doc & 1];

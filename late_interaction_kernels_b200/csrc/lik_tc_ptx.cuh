@@ -147,14 +147,19 @@ __device__ __forceinline__ int first_match32(const float (&v)[32], float cmax) {
 // Fold the maximum of one 32-column chunk into the running (max, argmax) of a row.  The column scan
 // only runs when the chunk beats the running maximum (strict: an equal value in a later chunk never
 // displaces an earlier winner) and returns the lowest matching column.
-template <bool ARGMAX>
+// LAZY: the scan is skipped when no row of the warp has a new maximum in this chunk - worth its branch only deep
+// into a long document, where most chunks bring none.
+template <bool ARGMAX, bool LAZY = false>
 __device__ __forceinline__ void fold32(const float (&v)[32], int col0, float& run_m, int& run_i) {
   const float cmax = max32(v);
   if (ARGMAX) {
-    // (unconditional: with 32 rows per warp some row nearly always has a new maximum, and a branch costs more than the scan)
-    const int p = first_match32(v, cmax);
+    // (unconditional by default: with 32 rows per warp some row nearly always has a new maximum in a document of a few
+    // chunks, and a branch costs more than the scan)
     const bool better = cmax > run_m;
-    run_i = better ? col0 + p : run_i;
+    if (!LAZY || __any_sync(0xffffffffu, better)) {
+      const int p = first_match32(v, cmax);
+      run_i = better ? col0 + p : run_i;
+    }
     run_m = better ? cmax : run_m;
   } else {
     run_m = fmaxf(run_m, cmax);

@@ -190,7 +190,8 @@ def test_inbatch_full_shape_grad_d_against_oracle():
 # ----------------------------------------------------------------------------- exact winners in 16-bit types
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("shape", [(3, 5, 7, 19, 16), (4, 6, 32, 300, 128), (2, 3, 33, 65, 96), (8, 8, 32, 64, 128),
-                                   (2, 2, 130, 257, 64), (1, 9, 128, 40, 128)])
+                                   (2, 2, 130, 257, 64), (1, 9, 128, 40, 128),
+                                   (3, 6, 32, 5000, 128), (2, 5, 128, 2300, 64)])  # long documents: the lazy winner scan
 def test_dense_winners_exact_on_integer_data(dtype, shape):
     from late_interaction_kernels_b200.forward import maxsim_forward
 
