@@ -55,7 +55,7 @@ constexpr int EPI_THREADS = 128;     // threads per half of an epilogue group (o
 constexpr int GROUP_WARPS = 8;
 constexpr long long WAIT_LIMIT_CYCLES = 4000000000ll;  // default limit of a wait: about 2 s at 2 GHz
 constexpr int UNIT_RING = 8;                  // slots of the producer -> epilogue unit ring
-constexpr int LONG_DOC_TOKENS = 2048;         // documents from this length on take the lazy winner scan
+constexpr int LONG_DOC_TOKENS = 2048;         // problems whose documents can be this long run the kernel with the lazy winner scan
 constexpr int UNIT_LEN_MASK = 0xFFFFFF;       // unit_info.x: document length in the low 24 bits,
 constexpr int UNIT_SLOT_SHIFT = 24;           // the multiplier slot of its first tile in bits 24..28, LEN_FLAG_MASKED above
 
@@ -411,9 +411,12 @@ __device__ __noinline__ unsigned topk_compact(float* keys, int* idx, int k, int 
   return kth;
 }
 
-template <bool FP8, bool ARGMAX, bool SCALED, bool PLAID>
+// WINNERS: 0 = scores only, 1 = winners saved, 2 = winners saved and every document takes the lazy winner scan (launched
+// for problems whose documents are long, so that the kernels for short documents carry no third copy of the tile loop)
+template <bool FP8, int WINNERS, bool SCALED, bool PLAID>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ DocMaps d_maps, const TcParams P) {
+  constexpr bool ARGMAX = WINNERS != 0;
   extern __shared__ unsigned char smem_raw[];
   // operand tiles need 1024-byte alignment for the 128-byte swizzle
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -1053,11 +1056,10 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
         if (SCALED && ++sc_slot >= sc_base + P.sc_per) sc_slot = sc_base;
       } while (c0 < dlen);
       };
-      // (a third copy for long documents in the kernels that keep winners: from the second half of such a document on,
-      // most 32-column chunks hold no new maximum for any of a warp's rows, and the scan for its column can be skipped)
+      // (long documents, WINNERS == 2: most 32-column chunks past the first few hundred tokens hold no new maximum for any
+      // of a warp's rows, and the scan for its column is skipped there)
       if (holes) document_tiles(std::true_type{}, std::false_type{});
-      else if (ARGMAX && dlen >= LONG_DOC_TOKENS) document_tiles(std::false_type{}, std::true_type{});
-      else document_tiles(std::false_type{}, std::false_type{});
+      else document_tiles(std::false_type{}, std::integral_constant<bool, WINNERS == 2>{});
       if (!ok) break;
       // ---- end of document: half 1 hands over, half 0 merges (lower column wins a tie) ----
       float* xm = ctl->xch_m[wg][n_doc & 1];
@@ -1482,7 +1484,7 @@ int launch_topk_slots(const float* keys, const int* idx, const int2* hdr, long l
 
 // Raise the kernel's dynamic shared memory limit once per device and size instead of on every launch (a host call
 // of a microsecond or two that small problems feel).
-template <bool F, bool A, bool X, bool PL>
+template <bool F, int A, bool X, bool PL>
 static cudaError_t allow_smem(size_t bytes) {
   static size_t allowed[64] = {0};  // by device ordinal
   int dev = 0;
@@ -1621,19 +1623,22 @@ int launch_fwd_tc(const lik_fwd_args& a, const float* qn, const float* dn, void*
     LIK_CUDA_OK((allow_smem<F, A, X, PL>(pl.smem_bytes)));                                                             \
     fwd_tc_kernel<F, A, X, PL><<<grid, block, pl.smem_bytes, st>>>(q_map, d_maps, P), ::lik::count_launch();           \
   } while (0)
+  const bool long_docs = argmax && a.d.max_len >= LONG_DOC_TOKENS;  // the lazy winner scan pays from here on
   if (plaid) {
-    if (argmax) LIK_TC_LAUNCH(false, true, false, true);
-    else LIK_TC_LAUNCH(false, false, false, true);
+    if (argmax) LIK_TC_LAUNCH(false, 1, false, true);
+    else LIK_TC_LAUNCH(false, 0, false, true);
   } else if (fp8) {
-    if (argmax && affine) LIK_TC_LAUNCH(true, true, true, false);
-    else if (argmax) LIK_TC_LAUNCH(true, true, false, false);
-    else if (affine) LIK_TC_LAUNCH(true, false, true, false);
-    else LIK_TC_LAUNCH(true, false, false, false);
+    if (argmax && affine) LIK_TC_LAUNCH(true, 1, true, false);
+    else if (argmax) LIK_TC_LAUNCH(true, 1, false, false);
+    else if (affine) LIK_TC_LAUNCH(true, 0, true, false);
+    else LIK_TC_LAUNCH(true, 0, false, false);
   } else {
-    if (argmax && affine) LIK_TC_LAUNCH(false, true, true, false);
-    else if (argmax) LIK_TC_LAUNCH(false, true, false, false);
-    else if (affine) LIK_TC_LAUNCH(false, false, true, false);
-    else LIK_TC_LAUNCH(false, false, false, false);
+    if (long_docs && affine) LIK_TC_LAUNCH(false, 2, true, false);
+    else if (long_docs) LIK_TC_LAUNCH(false, 2, false, false);
+    else if (argmax && affine) LIK_TC_LAUNCH(false, 1, true, false);
+    else if (argmax) LIK_TC_LAUNCH(false, 1, false, false);
+    else if (affine) LIK_TC_LAUNCH(false, 0, true, false);
+    else LIK_TC_LAUNCH(false, 0, false, false);
   }
 #undef LIK_TC_LAUNCH
   LIK_CUDA_OK(cudaGetLastError());
