@@ -1623,7 +1623,14 @@ int launch_fwd_tc(const lik_fwd_args& a, const float* qn, const float* dn, void*
     LIK_CUDA_OK((allow_smem<F, A, X, PL>(pl.smem_bytes)));                                                             \
     fwd_tc_kernel<F, A, X, PL><<<grid, block, pl.smem_bytes, st>>>(q_map, d_maps, P), ::lik::count_launch();           \
   } while (0)
-  const bool long_docs = argmax && a.d.max_len >= LONG_DOC_TOKENS;  // the lazy winner scan pays from here on
+  // LIK_LONG_DOC_TOKENS overrides the length from which the lazy winner scan is used (a tuning knob)
+  static int long_doc_tokens = 0;
+  if (!long_doc_tokens) {
+    const char* e = getenv("LIK_LONG_DOC_TOKENS");
+    const int v = e ? atoi(e) : 0;
+    long_doc_tokens = v > 0 ? v : LONG_DOC_TOKENS;
+  }
+  const bool long_docs = argmax && a.d.max_len >= long_doc_tokens;
   if (plaid) {
     if (argmax) LIK_TC_LAUNCH(false, 1, false, true);
     else LIK_TC_LAUNCH(false, 0, false, true);
