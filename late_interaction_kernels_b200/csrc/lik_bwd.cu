@@ -854,18 +854,18 @@ struct DdSortOut {
   int* tok_cnt;           // [d.n_rows] list length (zero-initialised by the launcher)
 };
 
-// Offsets of the winner sort.  In: hist[w][t] = winners of token t counted by warp w.  Out: the token's first list entry
-// and count (global), and hist[w][t] = first write position of warp w for token t.  All warps work: each takes whole
-// blocks of 32 tokens (totals, prefix inside the block), warp 0 scans the block totals, then every warp finishes
-// its blocks.  tok_off [ld_pad] and blk [ceil(ld_pad / 32) + 1] are scratch in shared memory.
-__device__ __forceinline__ void dds_offsets(int* hist, int* tok_off, int* blk, int n_warps, int ld_pad, int dlen, long long base,
-                                            long long drow0, const DdSortOut& O, int warp, int lane) {
+// Offsets of the winner sort.  In: hist[w][t] = winners of token t counted by warp w (n_hist of the CTA's n_warps warps
+// count).  Out: the token's first list entry and count (global), and hist[w][t] = first write position of warp w for token
+// t.  All warps work: each takes whole blocks of 32 tokens (totals, prefix inside the block), warp 0 scans the block
+// totals, then every warp finishes its blocks.  tok_off [ld_pad] and blk [ceil(ld_pad / 32) + 1] are scratch in shared memory.
+__device__ __forceinline__ void dds_offsets(int* hist, int* tok_off, int* blk, int n_warps, int n_hist, int ld_pad, int dlen,
+                                            long long base, long long drow0, const DdSortOut& O, int warp, int lane) {
   const int n_blk = (dlen + 31) >> 5;
   for (int b = warp; b < n_blk; b += n_warps) {
     const int t = b * 32 + lane;
     int tot = 0;
     if (t < dlen)
-      for (int w = 0; w < n_warps; ++w) tot += hist[w * ld_pad + t];
+      for (int w = 0; w < n_hist; ++w) tot += hist[w * ld_pad + t];
     int incl = tot;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
@@ -897,7 +897,7 @@ __device__ __forceinline__ void dds_offsets(int* hist, int* tok_off, int* blk, i
     if (t < dlen) {
       const int excl = blk[b] + tok_off[t];
       int pos = excl;
-      for (int w = 0; w < n_warps; ++w) {
+      for (int w = 0; w < n_hist; ++w) {
         const int c = hist[w * ld_pad + t];
         hist[w * ld_pad + t] = pos;
         pos += c;
@@ -909,8 +909,10 @@ __device__ __forceinline__ void dds_offsets(int* hist, int* tok_off, int* blk, i
   __syncthreads();
 }
 
-__global__ void __launch_bounds__(DDS_WARPS * 32) bwd_dd_sort_kernel(BwdParams P, DdSortOut O, int ld_pad) {
-  const int n_warps = blockDim.x >> 5;  // the launcher sizes the CTA to the entries per document
+__global__ void __launch_bounds__(DDS_WARPS * 32) bwd_dd_sort_kernel(BwdParams P, DdSortOut O, int ld_pad, int n_hist) {
+  // n_hist warps take the entries, one histogram each (the launcher sizes that to the entries per document); the CTA may
+  // have more warps than that for the work that goes with the document's length (clearing, offsets)
+  const int n_warps = blockDim.x >> 5;
   extern __shared__ int dds_raw[];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int j = blockIdx.x;
@@ -928,18 +930,18 @@ __global__ void __launch_bounds__(DDS_WARPS * 32) bwd_dd_sort_kernel(BwdParams P
   const int lq = P.argmax_stride;
   const int n_ent = ds.n_qr * lq;
   const long long base = list ? ds.first * lq : (long long)j * n_ent;  // first entry of the document's slice of the list
-  int* hist = dds_raw;                          // [n_warps][ld_pad]
-  int* tok_off = hist + n_warps * ld_pad;     // [ld_pad + 1]
+  int* hist = dds_raw;                          // [n_hist][ld_pad]
+  int* tok_off = hist + n_hist * ld_pad;      // [ld_pad + 1]
   int* blk = tok_off + ld_pad + 1;            // [ceil(ld_pad / 32) + 1]
   float* gcol = reinterpret_cast<float*>(blk + (ld_pad + 31) / 32 + 1);  // [n_qr] (not for pair lists)
 
-  for (int x = tid; x < n_warps * ld_pad; x += blockDim.x) hist[x] = 0;
+  for (int x = tid; x < n_hist * ld_pad; x += blockDim.x) hist[x] = 0;
   if (!list)
     for (int x = tid; x < ds.n_qr; x += blockDim.x) gcol[x] = P.g[doc_slot(P, ds, j, x)];
   __syncthreads();
 
   // entry e = ii * lq + s ; slice of this warp (multiple of 32 so rounds stay aligned)
-  const int per_warp = ((n_ent + n_warps - 1) / n_warps + 31) & ~31;
+  const int per_warp = ((n_ent + n_hist - 1) / n_hist + 31) & ~31;  // (warps beyond n_hist get an empty slice)
   const int e_lo = warp * per_warp, e_hi = min(n_ent, e_lo + per_warp);
 
   // raw saved winner of entry e (no validation): a plain load that can be issued ahead of its use
@@ -976,7 +978,7 @@ __global__ void __launch_bounds__(DDS_WARPS * 32) bwd_dd_sort_kernel(BwdParams P
   }
   __syncthreads();
   // offsets: warp 0 scans the tokens; hist[w][t] becomes the first write position of warp w for token t
-  dds_offsets(hist, tok_off, blk, n_warps, ld_pad, dlen, base, drow0, O, warp, lane);
+  dds_offsets(hist, tok_off, blk, n_warps, n_hist, ld_pad, dlen, base, drow0, O, warp, lane);
   // stable placement
   int t_next = raw_winner(e_lo + lane);
   for (int eb = e_lo; eb < e_hi; eb += 32) {
@@ -1080,8 +1082,10 @@ __global__ void __launch_bounds__(256) bwd_dd_reduce_kernel(BwdParams P, DdSortO
 // load, word, lane): fixed by the data alone, hence reproducible.
 constexpr int DDS_LOADS = 4;  // 16-byte loads in flight per lane
 
-__global__ void __launch_bounds__(DDS_WARPS * 32) bwd_dd_sort4_kernel(BwdParams P, DdSortOut O, int ld_pad) {
-  const int n_warps = blockDim.x >> 5;  // the launcher sizes the CTA to the entries per document
+__global__ void __launch_bounds__(DDS_WARPS * 32) bwd_dd_sort4_kernel(BwdParams P, DdSortOut O, int ld_pad, int n_hist) {
+  // n_hist warps take the entries, one histogram each (the launcher sizes that to the entries per document); the CTA may
+  // have more warps than that for the work that goes with the document's length (clearing, offsets)
+  const int n_warps = blockDim.x >> 5;
   extern __shared__ int dds_raw[];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int j = blockIdx.x;
@@ -1101,14 +1105,14 @@ __global__ void __launch_bounds__(DDS_WARPS * 32) bwd_dd_sort4_kernel(BwdParams 
   const int n_quad = ds.n_qr * qpr;
   const int n_ent = n_quad * 4;
   const long long base = list ? ds.first * lq : (long long)j * n_ent;
-  int* hist = dds_raw;                          // [n_warps][ld_pad]
-  int* tok_off = hist + n_warps * ld_pad;     // [ld_pad + 1]
+  int* hist = dds_raw;                          // [n_hist][ld_pad]
+  int* tok_off = hist + n_hist * ld_pad;      // [ld_pad + 1]
   int* blk = tok_off + ld_pad + 1;            // [ceil(ld_pad / 32) + 1]
   float* gcol = reinterpret_cast<float*>(blk + (ld_pad + 31) / 32 + 1);  // [n_qr] (not for pair lists)
   int* q_first = reinterpret_cast<int*>(gcol + ds.n_qr);  // [n_qr] first row and length of every score's query (not for pair lists)
   int* q_len = q_first + ds.n_qr;
 
-  for (int x = tid; x < n_warps * ld_pad; x += blockDim.x) hist[x] = 0;
+  for (int x = tid; x < n_hist * ld_pad; x += blockDim.x) hist[x] = 0;
   if (!list)
     for (int x = tid; x < ds.n_qr; x += blockDim.x) {
       const long long slot = doc_slot(P, ds, j, x);
@@ -1123,7 +1127,7 @@ __global__ void __launch_bounds__(DDS_WARPS * 32) bwd_dd_sort4_kernel(BwdParams 
 
   // slice of this warp in 16-byte groups (whole warp loads); a round is DDS_LOADS loads per lane
   const int round_quads = 32 * DDS_LOADS;
-  const int per_warp = ((n_quad + n_warps - 1) / n_warps + 31) & ~31;
+  const int per_warp = ((n_quad + n_hist - 1) / n_hist + 31) & ~31;  // (warps beyond n_hist get an empty slice)
   const int m_lo = warp * per_warp, m_hi = min(n_quad, m_lo + per_warp);
   const int4 none = make_int4(-1, -1, -1, -1);
 
@@ -1170,7 +1174,7 @@ __global__ void __launch_bounds__(DDS_WARPS * 32) bwd_dd_sort4_kernel(BwdParams 
   }
   __syncthreads();
   // ---- offsets: warp 0 scans the per-token totals ----
-  dds_offsets(hist, tok_off, blk, n_warps, ld_pad, dlen, base, drow0, O, warp, lane);
+  dds_offsets(hist, tok_off, blk, n_warps, n_hist, ld_pad, dlen, base, drow0, O, warp, lane);
   // ---- pass 2: placement (the winners come from L2 this time) ----
   for (int mb = m_lo; mb < m_hi; mb += round_quads) {
     int4 w[DDS_LOADS];
@@ -1367,7 +1371,8 @@ struct BwdPlan {
   size_t kq_off, kd_off, pq_off, pd_off, sq_off, sd_off, sort_off;  // pair lists grouped by query / by document
   bool fast, sorted;
   bool list_sorted;  // pair list on the deterministic kernels
-  int sort_warps;    // warps per CTA of the winner sort: at least 256 entries of a document per warp
+  int sort_warps;    // warps of the winner sort that take entries (a histogram each): at least 256 entries of a document per warp
+  int sort_threads;  // threads of its CTAs: more warps than that when the documents are long (clearing and offsets go with the length)
   bool row16;  // 16-byte gathers: rows 16-byte aligned, width a multiple of 16 bytes, at most 1024 bytes
   int dq_split;    // grad_q: document ranges per query (1: one CTA walks all the documents of its query tokens)
   size_t dqp_off;  // their partial rows
@@ -1453,6 +1458,11 @@ BwdPlan plan_bwd(const lik_bwd_args& a) {
     };
     while (pl.sort_warps > 1 && smem_for(pl.sort_warps) > 200 * 1024) pl.sort_warps >>= 1;  // long documents: fewer histograms
     pl.sort_smem = smem_for(pl.sort_warps);
+    {
+      long long by_len = ceil_div(pl.ld_pad, 512);
+      if (by_len > DDS_WARPS) by_len = DDS_WARPS;
+      pl.sort_threads = 32 * (int)(by_len > pl.sort_warps ? by_len : pl.sort_warps);
+    }
     if (pl.sort_smem <= 200 * 1024) {
       pl.sorted = true;
       const long long n_ent = n_scores_of(a.pairing, a.q.n_seq, a.d.n_seq, a.n_pairs) * (long long)a.argmax_stride;
@@ -1586,10 +1596,10 @@ int run_bwd(const lik_bwd_args& a, BwdParams& P, const BwdPlan& pl, cudaStream_t
       const bool quads = a.argmax_stride % 4 == 0 && ((uintptr_t)a.argmax % 16) == 0;
       if (quads) {
         LIK_CUDA_OK(cudaFuncSetAttribute(bwd_dd_sort4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.sort_smem));
-        bwd_dd_sort4_kernel<<<(unsigned)a.d.n_seq, pl.sort_warps * 32, pl.sort_smem, st>>>(P, O, pl.ld_pad), ::lik::count_launch();
+        bwd_dd_sort4_kernel<<<(unsigned)a.d.n_seq, pl.sort_threads, pl.sort_smem, st>>>(P, O, pl.ld_pad, pl.sort_warps), ::lik::count_launch();
       } else {
         LIK_CUDA_OK(cudaFuncSetAttribute(bwd_dd_sort_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.sort_smem));
-        bwd_dd_sort_kernel<<<(unsigned)a.d.n_seq, pl.sort_warps * 32, pl.sort_smem, st>>>(P, O, pl.ld_pad), ::lik::count_launch();
+        bwd_dd_sort_kernel<<<(unsigned)a.d.n_seq, pl.sort_threads, pl.sort_smem, st>>>(P, O, pl.ld_pad, pl.sort_warps), ::lik::count_launch();
       }
       LIK_CUDA_OK(cudaGetLastError());
       if (pl.row16) {
