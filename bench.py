@@ -735,6 +735,20 @@ def other_configs(dev):
             "roofline_e4m3": roofline("hbm", d8_.numel() * 1.0 + sd_.numel() * 4.0, t8 * 1e-6, kernel="fwd_tc_kernel (e4m3, per-token scales)",
                                       note="e4m3 document bytes + fp32 scales read once")}
         del Dr_, d8_
+    # long documents (the reference's benchmarks/kernels/bench_longdoc.py shapes, fp16): forward, forward with winners, backward
+    for label, nq_l, nd_l, ld_l in (("train_8k", 8, 16, 8192), ("rerank_8k", 1, 256, 8192), ("huge_doc", 1, 32, 16384)):
+        Ql = F.normalize(torch.randn((nq_l, 32, 128), generator=g, device=dev), dim=-1).half()
+        Dl = F.normalize(torch.randn((nd_l, ld_l, 128), generator=g, device=dev), dim=-1).half()
+        qsl, dsl = _ops.padded_spec(Ql), _ops.padded_spec(Dl)
+        gl = torch.randn((nq_l, nd_l), generator=g, device=dev)
+        _, aml = _ops.forward(qsl, dsl, save_argmax=True)
+        tf = _time_us(lambda: _ops.forward(qsl, dsl), dev, graph=True)
+        out[f"longdoc_{label}"] = {
+            "shape": f"Q[{nq_l},32,128] x D[{nd_l},{ld_l},128] fp16", "fwd_us": tf,
+            "fwd_winners_us": _time_us(lambda: _ops.forward(qsl, dsl, save_argmax=True), dev, graph=True),
+            "bwd_us": _time_us(lambda: _ops.backward(qsl, dsl, gl, aml), dev, graph=True),
+            "roofline": roofline("hbm", Dl.numel() * 2.0, tf * 1e-6, kernel="fwd_tc_kernel (fp16, few queries)", note="document bytes read once")}
+        del Dl
     # cached-contrastive tile grid (the reference's docs/benchmarks.md:396-426: bs = 256, Lq = 128, mini = 32 -> 64 tiles,
     # forward + backward): the whole grid in one call against one call per tile
     from late_interaction_kernels_b200.loss_heads import maxsim_tiles
