@@ -978,15 +978,20 @@ def main():
     e2e_run(2)
     barrier()
     n_e2e = max(4, min(args.steps, 40))  # enough steps for the first copy-in and the last copy-out to be a small share
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    e2e_run(n_e2e)
-    e1.record()
-    barrier()
-    te = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(te, op=dist.ReduceOp.MAX)
-    e2e_val = world * (fwd_flops + bwd_flops) * n_e2e / (float(te.item()) * 1e-3) / 1e12
+    # three repetitions, the fastest counts: the copies cross a host that other tenants of the machine share, and one
+    # repetition in a few runs at a fraction of the usual rate (every repetition is the max over ranks)
+    e2e_ms = []
+    for _ in range(3):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        e2e_run(n_e2e)
+        e1.record()
+        barrier()
+        te = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(te, op=dist.ReduceOp.MAX)
+        e2e_ms.append(float(te.item()))
+    e2e_val = world * (fwd_flops + bwd_flops) * n_e2e / (min(e2e_ms) * 1e-3) / 1e12
     h2d = hQ.numel() * 2 + hD.numel() * 2 + hM.numel() + hG.numel() * 4
     d2h = hS.numel() * 4 + hGQ.numel() * 2 + hGD.numel() * 2
 
@@ -1023,7 +1028,8 @@ def main():
         "dtype": "bf16", "data": "synthetic",
         "config": {"workload": WORKLOAD, "parallelism": f"replicas x{world}", "l2": "flushed between steps (256 MB write)",
                    "fwd_flops_per_step": fwd_flops, "bwd_flops_per_step": bwd_flops},
-        "e2e": {"value": e2e_val, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+        "e2e": {"value": e2e_val, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "steps": n_e2e, "repetitions_ms": e2e_ms, "note": "fastest of three repetitions of `steps` steps"},
         # kernels of this library launched inside the timed region (counted by the library, lik_launch_count)
         "gpu_launches": int(n_launch),
         "roofline": main_roof,
