@@ -747,7 +747,9 @@ def other_configs(dev):
             "shape": f"Q[{nq_l},32,128] x D[{nd_l},{ld_l},128] fp16", "fwd_us": tf,
             "fwd_winners_us": _time_us(lambda: _ops.forward(qsl, dsl, save_argmax=True), dev, graph=True),
             "bwd_us": _time_us(lambda: _ops.backward(qsl, dsl, gl, aml), dev, graph=True),
-            "roofline": roofline("hbm", Dl.numel() * 2.0, tf * 1e-6, kernel="fwd_tc_kernel (fp16, few queries)", note="document bytes read once")}
+            "roofline": roofline("hbm", Dl.numel() * 2.0, tf * 1e-6, kernel="fwd_tc_kernel (fp16, few queries)",
+                                 note=f"document bytes read once; a document is never split across CTAs, so {nd_l} documents keep "
+                                      f"{min(nd_l, 148)} of the 148 SMs busy")}
         del Dl
     # cached-contrastive tile grid (the reference's docs/benchmarks.md:396-426: bs = 256, Lq = 128, mini = 32 -> 64 tiles,
     # forward + backward): the whole grid in one call against one call per tile
