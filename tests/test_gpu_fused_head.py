@@ -121,6 +121,8 @@ def _chained_case(seed, Nq, Nd, Lq, Ld, d_model, d_out, dtype, mask):
     (1, 200, 32, 257, 200, 64, torch.float16, "none", False, True),      # K slab with a zero-filled tail, more documents than SMs
     (3, 17, 40, 128, 256, 128, torch.bfloat16, "prefix", True, False),   # queries that do not fill the tile, no normalisation
     (2, 9, 128, 1024, 768, 128, torch.bfloat16, "none", True, True),     # one query per tile, long documents
+    (2, 50, 16, 70, 64, 32, torch.bfloat16, "prefix", True, True),       # one K slab on either side (d_model 64, d_out 32)
+    (5, 3, 8, 4100, 1024, 128, torch.float16, "holes", False, True),     # few long documents, 16 K slabs, 40 query rows
 ])
 def test_chained_kernel_against_the_oracle_and_the_gemm_path(monkeypatch, Nq, Nd, Lq, Ld, d_model, d_out, dtype, mask, bias, normalize):
     from late_interaction_kernels_b200 import _lib, fused_head
