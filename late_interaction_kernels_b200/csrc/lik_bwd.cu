@@ -1210,12 +1210,9 @@ __global__ void __launch_bounds__(DDS_WARPS * 32) bwd_dd_sort4_kernel(BwdParams 
 
 // grad_d reduce with 16-byte gathers: one half-warp per document token, 16 tokens per CTA.
 template <typename T, typename G, int CH>
-__global__ void __launch_bounds__(256) bwd_dd_reduce16_kernel(BwdParams P, DdSortOut O) {
+__device__ __forceinline__ void dd_reduce16_row(const BwdParams& P, const DdSortOut& O, long long drow, int hl) {
   constexpr int N = Vec16<T>::N;
   constexpr int U = 8 / CH;
-  const int hl = threadIdx.x & 15;
-  const long long drow = (long long)blockIdx.x * 16 + (threadIdx.x >> 4);
-  if (drow >= P.d.n_rows) return;
   float acc[CH][N];
 #pragma unroll
   for (int c = 0; c < CH; ++c)
@@ -1270,6 +1267,34 @@ __global__ void __launch_bounds__(256) bwd_dd_reduce16_kernel(BwdParams P, DdSor
     }
   }
   store_row16<T, G, CH>((G*)P.grad_d + drow * P.dim, acc, P.dim, hl);
+}
+
+template <typename T, typename G, int CH>
+__global__ void __launch_bounds__(256) bwd_dd_reduce16_kernel(BwdParams P, DdSortOut O) {
+  const int hl = threadIdx.x & 15;
+  const long long drow = (long long)blockIdx.x * 16 + (threadIdx.x >> 4);
+  if (drow >= P.d.n_rows) return;
+  dd_reduce16_row<T, G, CH>(P, O, drow, hl);
+}
+
+// The same for very many document tokens (long documents), nearly all of them without a winner: a stream of zero rows.
+// One CTA per 16 tokens costs more to schedule than to run there, so a capped grid walks the tokens, and a token without
+// a winner stores its zero row without looking at anything else.
+template <typename T, typename G, int CH>
+__global__ void __launch_bounds__(256) bwd_dd_reduce16_walk_kernel(BwdParams P, DdSortOut O) {
+  const int hl = threadIdx.x & 15;
+  for (long long drow = (long long)blockIdx.x * 16 + (threadIdx.x >> 4); drow < P.d.n_rows; drow += (long long)gridDim.x * 16) {
+    if (__ldg(O.tok_cnt + drow) == 0) {
+      float zero[CH][Vec16<T>::N];
+#pragma unroll
+      for (int c = 0; c < CH; ++c)
+#pragma unroll
+        for (int e = 0; e < Vec16<T>::N; ++e) zero[c][e] = 0.f;
+      store_row16<T, G, CH>((G*)P.grad_d + drow * P.dim, zero, P.dim, hl);
+    } else {
+      dd_reduce16_row<T, G, CH>(P, O, drow, hl);
+    }
+  }
 }
 
 // ---------------------------------------------------------------------------------
@@ -1603,14 +1628,20 @@ int run_bwd(const lik_bwd_args& a, BwdParams& P, const BwdPlan& pl, cudaStream_t
       }
       LIK_CUDA_OK(cudaGetLastError());
       if (pl.row16) {
-        const unsigned rgrid = (unsigned)ceil_div(a.d.n_rows, 16);
+        // one CTA per 16 tokens, except for very many tokens (long documents): there a capped grid walks them
+        const long long rg = ceil_div(a.d.n_rows, 16);
+        const bool walk = rg > 65536;
+        const unsigned rgrid = (unsigned)(walk ? (long long)sm_count() * 32 : rg);
         const size_t row_bytes = (size_t)a.dim * sizeof(T);
-        if (row_bytes <= 256)
-          bwd_dd_reduce16_kernel<T, G, 1><<<rgrid, 256, 0, st>>>(P, O), ::lik::count_launch();
-        else if (row_bytes <= 512)
-          bwd_dd_reduce16_kernel<T, G, 2><<<rgrid, 256, 0, st>>>(P, O), ::lik::count_launch();
-        else
-          bwd_dd_reduce16_kernel<T, G, 4><<<rgrid, 256, 0, st>>>(P, O), ::lik::count_launch();
+#define LIK_REDUCE16(CH_)                                                                                     \
+  do {                                                                                                        \
+    if (walk) bwd_dd_reduce16_walk_kernel<T, G, CH_><<<rgrid, 256, 0, st>>>(P, O), ::lik::count_launch();     \
+    else bwd_dd_reduce16_kernel<T, G, CH_><<<rgrid, 256, 0, st>>>(P, O), ::lik::count_launch();               \
+  } while (0)
+        if (row_bytes <= 256) LIK_REDUCE16(1);
+        else if (row_bytes <= 512) LIK_REDUCE16(2);
+        else LIK_REDUCE16(4);
+#undef LIK_REDUCE16
       } else {
         const unsigned rgrid = (unsigned)ceil_div(a.d.n_rows, 8);
         if (a.dim <= 128)
