@@ -702,6 +702,12 @@ def other_configs(dev):
     # fused-head benchmark; forward alone, and the training step against projecting with F.linear first
     from late_interaction_kernels_b200.fused_head import maxsim_from_hidden
     hq, hh, hw, hb = hidden_inputs(1, 1024, 2048, dev)
+    # parity before timing: the first documents against a projection in fp32 followed by the scorer
+    got_h = maxsim_from_hidden(hq, hh, hw, hb)[:, :16].float()
+    want_h = lik.maxsim(hq.float(), F.normalize(F.linear(hh[:16].float(), hw.float(), hb.float()), dim=-1))
+    err_h = float((got_h - want_h).abs().max() / want_h.abs().max())
+    if not err_h < 2e-2:
+        raise SystemExit(f"maxsim_from_hidden differs from the fp32 projection + scorer: relative error {err_h:.3e}")
     t = _time_us(lambda: maxsim_from_hidden(hq, hh, hw, hb), dev)
     h_bytes = hh.numel() * 2.0
     out["hidden_head_fwd"] = {"us": t, "shape": "Q[1,32,128] x H[1024,2048,768] -> 128, bf16",
