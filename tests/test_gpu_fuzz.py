@@ -1,0 +1,104 @@
+"""Seeded random shapes through the public API against the CPU oracle: widths, lengths and masks that the hand-picked
+cases do not line up (documents whose stride is or is not a multiple of four, one-token queries, queries longer than a
+tile, masks with holes, fused normalisation), forward with winners and backward.
+
+Integer-valued inputs make the arithmetic exact, so scores and winners are compared with ``==``; real-valued inputs use
+the tolerances of the other parity tests (fp32 1e-5, 16-bit 2e-2 relative) and the kernel's own winners for the
+gradients (an oracle working in fp64 may pick the other side of a near-tie)."""
+
+import numpy as np
+import pytest
+import torch
+
+import cases
+from oracle import maxsim_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+TOL = {torch.float32: 1e-5, torch.bfloat16: 2e-2, torch.float16: 2e-2}
+
+
+def dev(x, dtype=None):
+    if x is None:
+        return None
+    t = torch.from_numpy(np.ascontiguousarray(x)).cuda()
+    return t.to(dtype) if dtype is not None else t
+
+
+def f32(t):
+    return t.detach().float().cpu().numpy()
+
+
+def _mask(rng, n, length, kind):
+    if kind == "none":
+        return None
+    if kind == "prefix":
+        return cases.prefix_mask(rng.integers(1, length + 1, size=n), length)
+    m = rng.random((n, length)) < 0.75
+    m[rng.integers(0, n)] = False  # one sequence without a valid token
+    m[:, 0] |= rng.random(n) < 0.5
+    return m
+
+
+def _shape(rng):
+    return dict(
+        Nq=int(rng.integers(1, 10)), Nd=int(rng.integers(1, 41)),
+        Lq=int(rng.choice([1, 2, 7, 16, 31, 32, 33, 64, 100, 128, 140])),
+        Ld=int(rng.choice([1, 3, 17, 64, 127, 128, 130, 255, 256, 257, 300, 513, 700])),
+        d=int(rng.choice([16, 32, 64, 96, 128])),
+        dtype=[torch.bfloat16, torch.float16, torch.float32][int(rng.integers(0, 3))],
+        qk=str(rng.choice(["none", "prefix", "holes"])), dk=str(rng.choice(["none", "prefix", "holes"])),
+    )
+
+
+@pytest.mark.parametrize("seed", range(40))
+def test_integer_data_scores_and_winners_exact(seed):
+    from late_interaction_kernels_b200.forward import maxsim_forward
+
+    rng = np.random.default_rng(1000 + seed)
+    c = _shape(rng)
+    Q = rng.integers(-2, 3, size=(c["Nq"], c["Lq"], c["d"])).astype(np.float32)
+    D = rng.integers(-2, 3, size=(c["Nd"], c["Ld"], c["d"])).astype(np.float32)
+    qm, dm = _mask(rng, c["Nq"], c["Lq"], c["qk"]), _mask(rng, c["Nd"], c["Ld"], c["dk"])
+    want, want_am = O.maxsim(Q, D, qm, dm, return_argmax=True)
+    s, am = maxsim_forward(dev(Q, c["dtype"]), dev(D, c["dtype"]), dev(qm), dev(dm), save_argmax=True)
+    assert np.array_equal(f32(s), want), c
+    got = am.cpu().numpy().reshape(c["Nq"], c["Nd"], c["Lq"])
+    sel = np.ones(got.shape, bool) if qm is None else np.broadcast_to(qm[:, None, :], got.shape)
+    assert np.array_equal(got[sel], want_am[sel]), c
+    # without winners: the same scores, bit for bit
+    s2, _ = maxsim_forward(dev(Q, c["dtype"]), dev(D, c["dtype"]), dev(qm), dev(dm), save_argmax=False)
+    assert torch.equal(s, s2), c
+
+
+@pytest.mark.parametrize("seed", range(30))
+def test_real_data_forward_and_backward(seed):
+    import late_interaction_kernels_b200 as lik
+
+    rng = np.random.default_rng(2000 + seed)
+    c = _shape(rng)
+    normalize = bool(rng.integers(0, 2))
+    dt = c["dtype"]
+    Q = rng.standard_normal((c["Nq"], c["Lq"], c["d"])).astype(np.float32)
+    D = rng.standard_normal((c["Nd"], c["Ld"], c["d"])).astype(np.float32)
+    if not normalize:
+        Q, D = cases.unit(Q).astype(np.float32), cases.unit(D).astype(np.float32)
+    qm, dm = _mask(rng, c["Nq"], c["Lq"], c["qk"]), _mask(rng, c["Nd"], c["Ld"], c["dk"])
+    tQ, tD = dev(Q, dt).requires_grad_(True), dev(D, dt).requires_grad_(True)
+    Qr, Dr = f32(tQ), f32(tD)  # what the kernels see
+    s = lik.maxsim(tQ, tD, dev(qm), dev(dm), normalize=normalize)
+    want = O.maxsim(Qr, Dr, qm, dm, normalize=normalize)
+    assert O.rel_err(f32(s), want) < TOL[dt], c
+    g = rng.standard_normal(want.shape).astype(np.float32)
+    (s * dev(g)).sum().backward()
+    # gradients for the kernel's own winners
+    from late_interaction_kernels_b200.forward import maxsim_forward
+    _, am = maxsim_forward(tQ.detach(), tD.detach(), dev(qm), dev(dm), save_argmax=True, normalize=normalize)
+    am = am.cpu().numpy().reshape(c["Nq"], c["Nd"], c["Lq"])
+    Qh, Dh = (O.l2_normalize(Qr, 1e-12), O.l2_normalize(Dr, 1e-12)) if normalize else (Qr, Dr)
+    wq, wd = O.backward_from_argmax(g, Qh, Dh, am, qm)
+    if normalize:
+        wq, wd = O.normalize_jacobian(wq, Qr, eps=1e-12), O.normalize_jacobian(wd, Dr, eps=1e-12)
+    tol = 1e-4 if dt == torch.float32 else 2e-2
+    assert O.rel_err(f32(tQ.grad), wq) < tol, c
+    assert O.rel_err(f32(tD.grad), wd) < tol, c
