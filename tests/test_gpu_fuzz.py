@@ -102,3 +102,41 @@ def test_real_data_forward_and_backward(seed):
     tol = 1e-4 if dt == torch.float32 else 2e-2
     assert O.rel_err(f32(tQ.grad), wq) < tol, c
     assert O.rel_err(f32(tD.grad), wd) < tol, c
+
+
+@pytest.mark.parametrize("seed", range(16))
+def test_candidate_lists_packed_and_retrieve_on_integer_data(seed):
+    """The other layouts on exact arithmetic: per-query candidate lists (4-D documents), packed sequences with a pair
+    list, and retrieve (indices exact, ties to the lower document)."""
+    import late_interaction_kernels_b200 as lik
+    from late_interaction_kernels_b200.score_pairs import score_pairs_packed
+
+    rng = np.random.default_rng(3000 + seed)
+    dt = [torch.bfloat16, torch.float16, torch.float32][seed % 3]
+    d = int(rng.choice([32, 64, 128]))
+    # candidate lists
+    Nq, K, Lq, Ld = int(rng.integers(1, 7)), int(rng.integers(1, 9)), int(rng.choice([1, 8, 32, 40])), int(rng.choice([5, 64, 257, 300]))
+    Q = rng.integers(-2, 3, size=(Nq, Lq, d)).astype(np.float32)
+    D = rng.integers(-2, 3, size=(Nq, K, Ld, d)).astype(np.float32)
+    dm = cases.prefix_mask(rng.integers(1, Ld + 1, size=Nq * K), Ld).reshape(Nq, K, Ld)
+    s = lik.maxsim(dev(Q, dt), dev(D, dt), d_mask=dev(dm))
+    assert np.array_equal(f32(s), O.maxsim_kd(Q, D, None, dm))
+    # packed sequences + pair list
+    ql, dl = rng.integers(1, 34, size=5), rng.integers(1, 300, size=7)
+    cu_q, cu_d = np.concatenate([[0], np.cumsum(ql)]).astype(np.int32), np.concatenate([[0], np.cumsum(dl)]).astype(np.int32)
+    Qp = rng.integers(-2, 3, size=(int(ql.sum()), d)).astype(np.float32)
+    Dp = rng.integers(-2, 3, size=(int(dl.sum()), d)).astype(np.float32)
+    sv = lik.maxsim_varlen(dev(Qp, dt), dev(Dp, dt), dev(cu_q), dev(cu_d), int(ql.max()), int(dl.max()))
+    assert np.array_equal(f32(sv), O.maxsim_varlen(Qp, Dp, cu_q, cu_d))
+    pq, pd = rng.integers(0, 5, size=11).astype(np.int32), rng.integers(0, 7, size=11).astype(np.int32)
+    sp = score_pairs_packed(dev(Qp, dt), dev(Dp, dt), dev(cu_q), dev(cu_d), dev(pq), dev(pd), max_seqlen_q=int(ql.max()),
+                            max_seqlen_d=int(dl.max()))
+    assert np.array_equal(f32(sp), O.maxsim_pair_list(Qp, Dp, cu_q, cu_d, pq, pd))
+    # retrieve: integer scores tie often, so the index order is a real check
+    Nd = int(rng.integers(3, 400))
+    Dr = rng.integers(-1, 2, size=(Nd, 24, d)).astype(np.float32)
+    Qr = rng.integers(-1, 2, size=(3, 8, d)).astype(np.float32)
+    k = min(int(rng.integers(1, 60)), Nd)
+    ts, ti = lik.retrieve(dev(Qr, dt), dev(Dr, dt), k, normalize=False)
+    ws, wi = O.retrieve(Qr, Dr, k, normalize=False)
+    assert np.array_equal(f32(ts), ws) and np.array_equal(ti.cpu().numpy(), wi)
