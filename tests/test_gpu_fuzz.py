@@ -140,3 +140,43 @@ def test_candidate_lists_packed_and_retrieve_on_integer_data(seed):
     ts, ti = lik.retrieve(dev(Qr, dt), dev(Dr, dt), k, normalize=False)
     ws, wi = O.retrieve(Qr, Dr, k, normalize=False)
     assert np.array_equal(f32(ts), ws) and np.array_equal(ti.cpu().numpy(), wi)
+
+
+@pytest.mark.parametrize("seed", range(12))
+def test_fp8_and_plaid_random_shapes(seed):
+    """e4m3 inputs with per-token scales (document strides that are and are not multiples of four: the multipliers
+    travel with the tiles or are staged per tile), and PLAID indexes of every bit width, padded and ragged."""
+    from late_interaction_kernels_b200 import fp8, plaid
+
+    rng = np.random.default_rng(4000 + seed)
+    # ---- e4m3
+    Nq, Nd, Lq = int(rng.integers(1, 6)), int(rng.integers(1, 30)), int(rng.choice([4, 32, 50]))
+    Ld = int(rng.choice([7, 64, 130, 256, 300, 301]))
+    d = int(rng.choice([64, 128, 256]))
+    Q = cases.unit(rng.standard_normal((Nq, Lq, d))).astype(np.float32)
+    D = (cases.unit(rng.standard_normal((Nd, Ld, d))) * rng.uniform(0.2, 3.0, size=(Nd, Ld, 1))).astype(np.float32)
+    dm = _mask(rng, Nd, Ld, str(rng.choice(["none", "prefix", "holes"])))
+    q8, sq = fp8.quantize_fp8_per_token(dev(Q))
+    d8, sd = fp8.quantize_fp8_per_token(dev(D))
+    s = fp8.maxsim_inference_fp8(q8, d8, scale_Q=sq, scale_D=sd, d_mask=dev(dm))
+    want = O.maxsim(f32(q8) * f32(sq)[..., None], f32(d8) * f32(sd)[..., None], None, dm)
+    assert O.rel_err(f32(s), want) < 1e-3, (Nq, Nd, Lq, Ld, d)  # bf16 output of the reference kernel is coarser; this one is fp32
+    # ---- PLAID
+    nbits = int(rng.choice([2, 4, 8]))
+    dp = int(rng.choice([32, 64, 96, 128]))
+    Qp, codes, res, lens, cent, bw, _ = cases.plaid_case(seed, Nq=int(rng.integers(1, 5)), Nd=int(rng.integers(1, 40)), Lq=int(rng.choice([3, 32])),
+                                                        Ld=int(rng.choice([9, 70, 300])), d=dp, nbits=nbits, n_centroids=int(rng.choice([16, 300])))
+    for norm in (True, False):
+        sp = plaid.maxsim_residual(dev(Qp), dev(codes), dev(res), dev(lens), dev(cent), dev(bw), nbits, normalize=norm)
+        wp = O.maxsim_residual(Qp, codes, res, lens, cent, bw, nbits, normalize=norm)
+        assert O.rel_err(f32(sp), wp) < 3e-2, (nbits, dp, norm)
+    cu = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+    cf = np.concatenate([codes[j, : lens[j]] for j in range(len(lens))])
+    rf = np.concatenate([res[j, : lens[j]] for j in range(len(lens))])
+    sv = plaid.maxsim_residual_varlen(dev(Qp), dev(cf), dev(rf), dev(cu), dev(cent), dev(bw), nbits)
+    assert O.rel_err(f32(sv), O.maxsim_residual_varlen(Qp, cf, rf, cu, cent, bw, nbits)) < 3e-2
+    k = min(5, len(lens))
+    ts, ti = plaid.retrieve_residual_varlen(dev(Qp), dev(cf), dev(rf), dev(cu), dev(cent), dev(bw), nbits, k)
+    full = f32(sv)
+    # the returned documents are the k best of the dense scores (scores compared: near-ties may swap neighbours)
+    assert O.rel_err(f32(ts), -np.sort(-full, axis=-1)[:, :k]) < 1e-3
